@@ -1,0 +1,172 @@
+/*
+ * intentir_b200 — C ABI of the B200 (sm_100a) execution backend for IntentIR graphs.
+ *
+ * This is the boundary a host binds instead of the reference's CUDA backend:
+ *   - planning replaces  backends/cuda/cpp_codegen/intentir_cuda_codegen.cpp:5855-5873
+ *     (pybind `lower_from_json_str(intent_json, bindings_json) -> json`) and the Python
+ *     dispatcher backends/cuda/codegen/intentir_to_cuda.py:2047-2201;
+ *   - launching replaces the generated torch-extension wrapper of
+ *     frontends/cuda/runtime.py:621-804 (`launch(*tensors, *scalars, grid, block, smem)`),
+ *     with the kernels of backends/cuda/runtime/kernels/*.cuh replaced by the
+ *     pre-compiled sm_100a kernels in this library.
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  Every `const void*` / `void*` tensor argument is a
+ *     DEVICE pointer to a dense row-major array owned by the caller and borrowed for the
+ *     duration of the call.
+ *   - `stream` is a `cudaStream_t` passed as `void*` (NULL = the legacy default stream).
+ *     Calls only enqueue work: the library never synchronises and never allocates device
+ *     memory; scratch memory, where needed, is passed in by the caller (`workspace`).
+ *   - Functions return IB200_OK (0) or a negative status; `ib200_last_error()` returns a
+ *     thread-local, human readable message for the last failure on the calling thread.
+ *   - The device is the caller's current CUDA device.
+ */
+#ifndef INTENTIR_B200_H_
+#define INTENTIR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define IB200_API __attribute__((visibility("default")))
+#else
+#define IB200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------- */
+#define IB200_OK 0
+#define IB200_ERR_INVALID (-1)     /* bad argument (null pointer, negative extent, bad dtype)      */
+#define IB200_ERR_UNSUPPORTED (-2) /* graph / shape / dtype outside what the kernels cover; the    */
+                                   /* counterpart of CudaLoweringError, intentir_to_cuda.py:23-24  */
+#define IB200_ERR_CUDA (-3)        /* a CUDA runtime / driver call failed (CudaRuntimeError,       */
+                                   /* frontends/cuda/runtime.py:23-24)                             */
+#define IB200_ERR_BUFFER (-4)      /* caller-provided output / workspace buffer too small          */
+#define IB200_ERR_DEVICE_WAIT (-5) /* a bounded device-side wait ran out (see ib200_check_status)  */
+
+/* ---- element types (the IntentIR dtype strings of intent_ir/ir/ir_types.py:38-64) ---- */
+#define IB200_F32 0
+#define IB200_BF16 1
+#define IB200_F16 2
+#define IB200_I32 3
+#define IB200_I64 4
+#define IB200_BOOL 5 /* "bool" and "i1": one byte, 0 or 1 */
+#define IB200_U8 6
+#define IB200_I8 7
+#define IB200_I16 8
+#define IB200_F64 9
+
+/* ---- reduction kinds for ib200_reduce ------------------------------------------------- */
+#define IB200_REDUCE_SUM 0 /* reduce_sum, verify/interpreter.py:478-488 (optional scale)        */
+#define IB200_REDUCE_MAX 1 /* reduce_max, :495-500 (NaN propagates, like np.max)                */
+#define IB200_REDUCE_ANY 2 /* reduce_any, :489-494 (element != 0; NaN counts as true)           */
+
+/* ---- activation codes for ib200_gemm_bias_act ---------------------------------------- */
+#define IB200_ACT_NONE 0
+#define IB200_ACT_RELU 1
+
+IB200_API const char* ib200_last_error(void);
+IB200_API int ib200_version(void);
+
+/* ======================================================================================
+ * Planner + executor: IntentIR JSON in, a launchable plan out.
+ * ====================================================================================== */
+
+typedef struct ib200_plan ib200_plan_t;
+
+/* Stateless: lower an IntentIR graph under concrete bindings and write the plan
+ * description as JSON into `out` (NUL terminated).  Replaces
+ * `lower_from_json_str(intent_json, bindings_json)` (intentir_cuda_codegen.cpp:5858).
+ * The JSON mirrors the reference's lowered-kernel record
+ * {kernel_name, cuda_src:"", io_spec{arg_names, tensors{name:{dtype,shape}}, scalars},
+ *  launch{grid,block,shared_mem}, output_names, bindings} (intentir_to_cuda.py:2110-2125)
+ * plus {"steps":[...], "workspace_bytes":N}.  Returns IB200_ERR_BUFFER when `cap` is too
+ * small (the needed size is then reported by ib200_last_error). */
+IB200_API int ib200_plan_json(const char* intent_json, const char* bindings_json, char* out, size_t cap);
+
+/* Build a reusable plan object (same lowering as ib200_plan_json). */
+IB200_API int ib200_plan_create(const char* intent_json, const char* bindings_json, ib200_plan_t** plan);
+IB200_API void ib200_plan_destroy(ib200_plan_t* plan);
+IB200_API int ib200_plan_describe(const ib200_plan_t* plan, char* out, size_t cap);
+/* Number of tensor arguments (io_spec.arg_names order: external inputs, then outputs). */
+IB200_API int ib200_plan_num_args(const ib200_plan_t* plan);
+/* Scratch bytes the caller must provide to ib200_plan_launch (0 for single-kernel plans). */
+IB200_API size_t ib200_plan_workspace_bytes(const ib200_plan_t* plan);
+/* Number of kernel launches one ib200_plan_launch enqueues. */
+IB200_API int ib200_plan_num_launches(const ib200_plan_t* plan);
+
+/* Enqueue the plan.  `args[i]` is the device pointer of io_spec.arg_names[i].  `workspace`
+ * must be 256-byte aligned and at least ib200_plan_workspace_bytes(plan) long (may be NULL
+ * when that is 0).  Replaces `mod.launch(...)` (frontends/cuda/runtime.py:723-746). */
+IB200_API int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/* ======================================================================================
+ * Direct per-op entry points (the same kernels the plans launch).
+ * ====================================================================================== */
+
+/* out[o, i] = reduce over r of x[o, r, i]  — x viewed as [outer, reduce, inner], dense.
+ * SUM: out = scale * sum (scale 1.0 for plain sums); MAX propagates NaN; ANY writes one
+ * byte per output (x_dtype may be a float type or IB200_BOOL; out_dtype must be IB200_BOOL).
+ * Replaces the generated reduce_sum / reduce_max / any_dim kernels
+ * (intentir_to_cuda.py:1553-1776) and kernels/reduce.cuh. */
+IB200_API int ib200_reduce(const void* x, void* out, int x_dtype, int out_dtype, int kind, int64_t outer,
+                 int64_t reduce, int64_t inner, float scale, void* stream);
+
+/* The BASELINE any_kernel_dim case: out[m] = any_n(x[m, n] != 0), f32 in, one byte out. */
+IB200_API int ib200_reduce_any_f32(const float* x, uint8_t* out, int64_t rows, int64_t cols, void* stream);
+
+/* Row softmax over the last axis with max subtraction (verify/interpreter.py:501-506).
+ * `row_max` / `row_sum` (f32[rows]) are optional extra outputs (NULL to skip): the row
+ * maximum and the sum of exp(x - max), as the decomposed graph of
+ * pipeline/cuda/core.py:453-493 exposes them.  Replaces kernels/softmax.cuh (no 1024
+ * column limit). dtype: IB200_F32, IB200_BF16 or IB200_F16 (same for x and y). */
+IB200_API int ib200_softmax(const void* x, void* y, float* row_max, float* row_sum, int dtype, int64_t rows,
+                  int64_t cols, void* stream);
+
+/* Normalisation over contiguous rows of `cols` elements with centred (two-pass) variance:
+ *   mean = sum(x)/cols; var = sum((x-mean)^2)/cols; rstd = 1/sqrt(var+eps);
+ *   y[r, j] = (x[r, j]-mean)*rstd * w[widx] + b[widx],  widx = ((r*cols + j) / affine_inner) % affine_period
+ * layernorm: affine_inner = 1, affine_period = cols.  groupnorm over X[N,C,HW] with G groups:
+ * rows = N*G, cols = (C/G)*HW, affine_inner = HW, affine_period = C.  w / b may be NULL
+ * (identity affine).  mean / rstd (f32[rows]) may be NULL.  x, y share `dtype`; w, b share
+ * `affine_dtype`.  Replaces kernels/layernorm.cuh (which uses E[x^2]-mean^2); groupnorm has
+ * no counterpart in the reference CUDA backend (oracle: pipeline/tilelang/core.py:187-232). */
+IB200_API int ib200_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                    int dtype, int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner,
+                    int64_t affine_period, float eps, void* stream);
+
+IB200_API int ib200_layernorm(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                    int dtype, int64_t rows, int64_t cols, float eps, void* stream);
+
+IB200_API int ib200_groupnorm(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                    int dtype, int64_t n, int64_t c, int64_t hw, int64_t groups, float eps,
+                    void* stream);
+
+/* C[M,N] = act(A[M,K] · B + bias[N]); fp32 accumulation.  B is [K,N] row-major, or [N,K]
+ * when transpose_b != 0.  bias may be NULL.  in_dtype (A and B) and out_dtype (C) are
+ * IB200_BF16 or IB200_F32; bias has out_dtype.  bf16 inputs whose K and N are multiples of 8 run on
+ * the tcgen05 / TMEM tensor-core path; everything else runs on a tiled fp32 FMA kernel.
+ * `status` is a caller-provided device int32 (zero it once); the tensor-core kernel sets it
+ * non-zero if one of its bounded waits runs out (read it with ib200_check_status).  May be
+ * NULL for the FMA path only.  Replaces kernels/wmma_matmul.cuh and matmul_fallback.cuh. */
+IB200_API int ib200_gemm_bias_act(const void* a, const void* b, const void* bias, void* c, int in_dtype,
+                        int out_dtype, int64_t m, int64_t n, int64_t k, int transpose_b, int act,
+                        int32_t* status, void* stream);
+
+/* Copy the device status word to the host (this call DOES synchronise `stream`) and map a
+ * non-zero word to IB200_ERR_DEVICE_WAIT. */
+IB200_API int ib200_check_status(const int32_t* status, void* stream);
+
+/* out[i, j] = x[j, i] for a dense [rows, cols] matrix of 2- or 4-byte elements.
+ * Replaces the generated transpose2d kernel (intentir_to_cuda.py:1487-1550). */
+IB200_API int ib200_transpose2d(const void* x, void* out, int elem_bytes, int64_t rows, int64_t cols,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INTENTIR_B200_H_ */

@@ -1,0 +1,86 @@
+// The extern "C" surface declared in include/intentir_b200.h: argument checks, the
+// thread-local error message, and forwarding to the per-file launchers.
+#include <string>
+
+#include "common.cuh"
+
+namespace ib200 {
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+int cuda_fail(cudaError_t err, const char* what) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorName(err) + " (" + cudaGetErrorString(err) + ")";
+  return IB200_ERR_CUDA;
+}
+
+}  // namespace ib200
+
+using namespace ib200;
+
+extern "C" {
+
+const char* ib200_last_error(void) { return g_last_error.c_str(); }
+int ib200_version(void) { return 100; }
+
+int ib200_reduce(const void* x, void* out, int x_dtype, int out_dtype, int kind, int64_t outer, int64_t reduce, int64_t inner,
+                 float scale, void* stream) {
+  return launch_reduce(x, out, x_dtype, out_dtype, kind, outer, reduce, inner, scale, static_cast<cudaStream_t>(stream));
+}
+
+int ib200_reduce_any_f32(const float* x, uint8_t* out, int64_t rows, int64_t cols, void* stream) {
+  return launch_reduce(x, out, IB200_F32, IB200_BOOL, IB200_REDUCE_ANY, rows, cols, 1, 1.0f, static_cast<cudaStream_t>(stream));
+}
+
+int ib200_softmax(const void* x, void* y, float* row_max, float* row_sum, int dtype, int64_t rows, int64_t cols, void* stream) {
+  return launch_softmax(x, y, row_max, row_sum, dtype, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+int ib200_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int affine_dtype,
+                    int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps, void* stream) {
+  return launch_norm_rows(x, w, b, y, mean, rstd, dtype, affine_dtype, rows, cols, affine_inner, affine_period, eps,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int ib200_layernorm(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int64_t rows,
+                    int64_t cols, float eps, void* stream) {
+  return launch_norm_rows(x, w, b, y, mean, rstd, dtype, dtype, rows, cols, 1, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
+int ib200_groupnorm(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int64_t n,
+                    int64_t c, int64_t hw, int64_t groups, float eps, void* stream) {
+  if (groups <= 0 || c < 0 || n < 0 || hw < 0) return fail(IB200_ERR_INVALID, "groupnorm: bad extents");
+  if (c % groups != 0) return fail(IB200_ERR_INVALID, "groupnorm: C must be a multiple of the group count");
+  return launch_norm_rows(x, w, b, y, mean, rstd, dtype, dtype, n * groups, (c / groups) * hw, hw > 0 ? hw : 1, c > 0 ? c : 1,
+                          eps, static_cast<cudaStream_t>(stream));
+}
+
+int ib200_gemm_bias_act(const void* a, const void* b, const void* bias, void* c, int in_dtype, int out_dtype, int64_t m,
+                        int64_t n, int64_t k, int transpose_b, int act, int32_t* status, void* stream) {
+  return launch_gemm(a, b, bias, c, in_dtype, out_dtype, m, n, k, transpose_b, act, status, static_cast<cudaStream_t>(stream));
+}
+
+int ib200_check_status(const int32_t* status, void* stream) {
+  if (!status) return fail(IB200_ERR_INVALID, "check_status: null pointer");
+  int32_t host = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  IB200_CUDA_OK(cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, s));
+  IB200_CUDA_OK(cudaStreamSynchronize(s));
+  if (host != 0) {
+    static const char* where[] = {"", "producer waiting for a free ring stage", "MMA issuer waiting for a drained accumulator",
+                                  "MMA issuer waiting for a TMA stage", "epilogue waiting for a finished accumulator"};
+    return fail(IB200_ERR_DEVICE_WAIT, std::string("gemm: bounded device wait expired (") +
+                                           (host > 0 && host < 5 ? where[host] : "unknown site") + ")");
+  }
+  return IB200_OK;
+}
+
+int ib200_transpose2d(const void* x, void* out, int elem_bytes, int64_t rows, int64_t cols, void* stream) {
+  return launch_transpose2d(x, out, elem_bytes, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,302 @@
+// Fused elementwise / broadcast chains: one pass over the output, executing the micro-op
+// program of ew_program.h.  Replaces the per-graph generated source of the reference
+// (backends/cuda/codegen/intentir_to_cuda.py:229-534, one thread per element with int64
+// div/mod and scalar loads) with one pre-compiled kernel:
+//
+//   * each thread owns 8 output elements: two 128-bit vectors when the innermost extent is
+//     a multiple of 4 and the operands are aligned (VEC), else 8 strided scalars;
+//   * output coordinates come from 32-bit multiply-shift division by the collapsed extents,
+//     once per vector, and give each operand's offset through its (possibly zero) strides —
+//     numpy broadcasting and broadcast_in_dim are just zero strides, iota is a ramp;
+//   * contiguous f32 / bf16 / f16 operands are staged global -> shared with cp.async (all
+//     operands in flight at once, no register round trip); the slot file lives in shared
+//     memory, one conflict-free column per thread, so no barrier is ever needed;
+//   * the chain itself runs on an accumulator held in registers.
+//
+// HBM-bound: bytes moved = each distinct operand once + each output once.
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "ew_program.h"
+
+namespace ib200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kPerThread = 8;
+constexpr int kTile = kThreads * kPerThread;
+
+struct EwDivs {
+  FastDiv d[kEwMaxRank];
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+}
+
+__device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t off) {
+  switch (dtype) {
+    case IB200_F32: return static_cast<const float*>(p)[off];
+    case IB200_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[off]);
+    case IB200_F16: return __half2float(static_cast<const __half*>(p)[off]);
+    case IB200_BOOL: case IB200_U8: return static_cast<const uint8_t*>(p)[off] ? 1.0f : 0.0f;
+    case IB200_I32: return (float)static_cast<const int32_t*>(p)[off];
+    case IB200_I64: return (float)static_cast<const long long*>(p)[off];
+    case IB200_I8: return (float)static_cast<const int8_t*>(p)[off];
+    case IB200_I16: return (float)static_cast<const int16_t*>(p)[off];
+    default: return 0.0f;
+  }
+}
+
+__device__ __forceinline__ void store_scalar(void* p, int dtype, int64_t off, float v) {
+  switch (dtype) {
+    case IB200_F32: static_cast<float*>(p)[off] = v; break;
+    case IB200_BF16: static_cast<__nv_bfloat16*>(p)[off] = __float2bfloat16_rn(v); break;
+    case IB200_F16: static_cast<__half*>(p)[off] = __float2half_rn(v); break;
+    case IB200_BOOL: case IB200_U8: static_cast<uint8_t*>(p)[off] = v != 0.0f ? 1 : 0; break;
+    case IB200_I32: static_cast<int32_t*>(p)[off] = __float2int_rz(v); break;
+    case IB200_I64: static_cast<long long*>(p)[off] = __float2ll_rz(v); break;
+    case IB200_I8: static_cast<int8_t*>(p)[off] = (int8_t)__float2int_rz(v); break;
+    case IB200_I16: static_cast<int16_t*>(p)[off] = (int16_t)__float2int_rz(v); break;
+    default: break;
+  }
+}
+
+__device__ __forceinline__ void store_vec4(void* p, int dtype, int64_t off, const float (&v)[4]) {
+  switch (dtype) {
+    case IB200_F32: store4<float>(static_cast<float*>(p) + off, v); break;
+    case IB200_BF16: store4<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p) + off, v); break;
+    case IB200_F16: store4<__half>(static_cast<__half*>(p) + off, v); break;
+    case IB200_BOOL: case IB200_U8: store4<uint8_t>(static_cast<uint8_t*>(p) + off, v); break;
+    case IB200_I32: store4<int32_t>(static_cast<int32_t*>(p) + off, v); break;
+    default:
+#pragma unroll
+      for (int k = 0; k < 4; ++k) store_scalar(p, dtype, off + k, v[k]);
+  }
+}
+
+// one micro-op over the thread's 8 values; the opcode is uniform across the grid, so the
+// switch is a single uniform branch per instruction, not per element
+__device__ __forceinline__ void apply(uint8_t op, const float (&a)[kPerThread], const float (&b)[kPerThread],
+                                      float (&acc)[kPerThread]) {
+#define EW_CASE(OP, EXPR)                      \
+  case OP:                                     \
+    _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) { \
+      const float x = a[j], y = b[j];          \
+      (void)y;                                 \
+      acc[j] = (EXPR);                         \
+    }                                          \
+    break;
+  switch (op) {
+    EW_CASE(EW_MOV, x)
+    EW_CASE(EW_ADD, x + y)
+    EW_CASE(EW_SUB, x - y)
+    EW_CASE(EW_MUL, x * y)
+    EW_CASE(EW_DIV, x / y)
+    EW_CASE(EW_MAX, max_nan(x, y))
+    EW_CASE(EW_MIN, min_nan(x, y))
+    EW_CASE(EW_RELU, max_nan(x, 0.0f))
+    EW_CASE(EW_EXP, expf(x))
+    EW_CASE(EW_RSQRT, 1.0f / sqrtf(x))
+    EW_CASE(EW_ABS, fabsf(x))
+    EW_CASE(EW_FLOOR, floorf(x))
+    EW_CASE(EW_NE, x != y ? 1.0f : 0.0f)
+    EW_CASE(EW_LT, x < y ? 1.0f : 0.0f)
+    EW_CASE(EW_LE, x <= y ? 1.0f : 0.0f)
+    EW_CASE(EW_GT, x > y ? 1.0f : 0.0f)
+    EW_CASE(EW_GE, x >= y ? 1.0f : 0.0f)
+    EW_CASE(EW_AND, (x != 0.0f && y != 0.0f) ? 1.0f : 0.0f)
+    EW_CASE(EW_OR, (x != 0.0f || y != 0.0f) ? 1.0f : 0.0f)
+    EW_CASE(EW_NOT, x != 0.0f ? 0.0f : 1.0f)
+    EW_CASE(EW_TO_BOOL, x != 0.0f ? 1.0f : 0.0f)
+    EW_CASE(EW_TO_INT, truncf(x))
+    EW_CASE(EW_ROUND_BF16, __bfloat162float(__float2bfloat16_rn(x)))
+    EW_CASE(EW_ROUND_F16, __half2float(__float2half_rn(x)))
+    default: break;
+  }
+#undef EW_CASE
+}
+
+// Slot file: slot s, value j (0..7), thread t.  VEC: values 4u..4u+3 form one float4 at
+// ((s*2+u)*kThreads + t)*16 bytes; scalar: value j at ((s*8+j)*kThreads + t)*4 bytes.
+template <bool VEC> __device__ __forceinline__ float* slot_ptr(float* file, int s, int j, int t) {
+  return VEC ? file + ((size_t)(s * 2 + (j >> 2)) * kThreads + t) * 4 + (j & 3) : file + ((size_t)(s * 8 + j) * kThreads + t);
+}
+
+template <bool VEC> __device__ __forceinline__ void fetch(float (&dst)[kPerThread], uint8_t code, const float (&acc)[kPerThread],
+                                                          float imm, float* file, int t) {
+  if (code == EW_ACC) {
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) dst[j] = acc[j];
+  } else if (code == EW_IMM) {
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) dst[j] = imm;
+  } else if (VEC) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const float4 q = *reinterpret_cast<const float4*>(slot_ptr<true>(file, code, 4 * u, t));
+      dst[4 * u] = q.x; dst[4 * u + 1] = q.y; dst[4 * u + 2] = q.z; dst[4 * u + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) dst[j] = *slot_ptr<false>(file, code, j, t);
+  }
+}
+
+template <bool VEC> __device__ __forceinline__ void put(const float (&src)[kPerThread], int s, float* file, int t) {
+  if (VEC) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      *reinterpret_cast<float4*>(slot_ptr<true>(file, s, 4 * u, t)) = make_float4(src[4 * u], src[4 * u + 1], src[4 * u + 2], src[4 * u + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) *slot_ptr<false>(file, s, j, t) = src[j];
+  }
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) ew_kernel(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs) {
+  extern __shared__ __align__(16) float file[];
+  const int t = threadIdx.x;
+  constexpr int W = VEC ? 4 : 1;          // elements per unit (sharing all but the innermost coordinate)
+  constexpr int U = kPerThread / W;       // units per thread
+  const int64_t ntiles = (prog.total + kTile - 1) / kTile;
+
+  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t base = tile * kTile;
+    // ---- stage the operands --------------------------------------------------------------
+    bool needs_convert = false;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = base + (int64_t)(u * kThreads + t) * W;  // first element of the unit
+      if (e >= prog.total) continue;
+      uint32_t coord[kEwMaxRank];
+      uint32_t rem = (uint32_t)e;
+      for (int d = prog.rank - 1; d > 0; --d) {
+        uint32_t q;
+        divs.d[d].divmod(rem, q, coord[d]);
+        rem = q;
+      }
+      coord[0] = rem;
+      for (int k = 0; k < prog.n_inputs; ++k) {
+        const EwInput& in = prog.in[k];
+        int64_t off = 0;
+        for (int d = 0; d < prog.rank; ++d) off += (int64_t)coord[d] * in.stride[d];
+        float* dst = slot_ptr<VEC>(file, k, u * W, t);
+        if (in.kind == EW_IN_IOTA) {
+          const int64_t step = in.stride[prog.rank - 1];
+#pragma unroll
+          for (int j = 0; j < W; ++j) dst[j] = (float)(off + j * step);
+          continue;
+        }
+        if (VEC) {
+          const int64_t step = in.stride[prog.rank - 1];
+          if (in.vec_ok) {
+            if (in.dtype == IB200_F32) cp_async16(dst, static_cast<const float*>(in.ptr) + off);
+            else if (in.dtype == IB200_BF16 || in.dtype == IB200_F16) {
+              cp_async8(dst, static_cast<const uint16_t*>(in.ptr) + off);
+              needs_convert = true;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dst[j] = load_scalar(in.ptr, in.dtype, off + j);
+            }
+          } else if (step == 0) {
+            const float v = load_scalar(in.ptr, in.dtype, off);
+            *reinterpret_cast<float4*>(dst) = make_float4(v, v, v, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = load_scalar(in.ptr, in.dtype, off + j * step);
+          }
+        } else {
+          if (in.dtype == IB200_F32) cp_async4(dst, static_cast<const float*>(in.ptr) + off);
+          else *dst = load_scalar(in.ptr, in.dtype, off);
+        }
+      }
+    }
+    cp_async_wait_all();
+    if (VEC && needs_convert) {  // widen the 8-byte bf16/f16 vectors in place
+      for (int k = 0; k < prog.n_inputs; ++k) {
+        const EwInput& in = prog.in[k];
+        if (!(in.vec_ok && in.kind == EW_IN_TENSOR && (in.dtype == IB200_BF16 || in.dtype == IB200_F16))) continue;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float* dst = slot_ptr<VEC>(file, k, u * W, t);
+          float v[4];
+          if (in.dtype == IB200_BF16) load4<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(dst), v);
+          else load4<__half>(reinterpret_cast<const __half*>(dst), v);
+          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+      }
+    }
+
+    // ---- run the chain ---------------------------------------------------------------------
+    float acc[kPerThread];
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) acc[j] = 0.0f;
+    for (int ip = 0; ip < prog.n_instr; ++ip) {
+      const EwInstr ins = prog.instr[ip];
+      float a[kPerThread], b[kPerThread];
+      fetch<VEC>(a, ins.a, acc, ins.imm, file, t);
+      fetch<VEC>(b, ins.b, acc, ins.imm, file, t);
+      if (ins.op == EW_WHERE) {
+        float c[kPerThread];
+        fetch<VEC>(c, ins.c, acc, ins.imm, file, t);
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j) acc[j] = a[j] != 0.0f ? b[j] : c[j];
+      } else {
+        apply(ins.op, a, b, acc);
+      }
+      if (ins.dst != EW_NODST) put<VEC>(acc, ins.dst, file, t);
+    }
+
+    // ---- write the results -----------------------------------------------------------------
+    for (int o = 0; o < prog.n_outputs; ++o) {
+      const EwOutput& out = prog.out[o];
+      float v[kPerThread];
+      fetch<VEC>(v, out.src, acc, 0.0f, file, t);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t e = base + (int64_t)(u * kThreads + t) * W;
+        if (e >= prog.total) continue;
+        if (VEC) {
+          const float q[4] = {v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]};
+          store_vec4(out.ptr, out.dtype, e, q);
+        } else {
+          store_scalar(out.ptr, out.dtype, e, v[u]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
+  if (prog.total == 0) return IB200_OK;
+  if (prog.total < 0 || prog.total >= ((int64_t)1 << 31)) return fail(IB200_ERR_UNSUPPORTED, "elementwise: more than 2^31-1 output elements");
+  if (prog.rank < 1 || prog.rank > kEwMaxRank || prog.n_inputs > kEwMaxInputs || prog.n_outputs < 1 ||
+      prog.n_outputs > kEwMaxOutputs || prog.n_instr > kEwMaxInstr || prog.n_slots > kEwMaxSlots || prog.n_slots < prog.n_inputs)
+    return fail(IB200_ERR_INVALID, "elementwise: malformed program");
+  EwDivs divs;
+  for (int d = 0; d < prog.rank; ++d) divs.d[d] = FastDiv(prog.dim[d]);
+  const size_t smem = (size_t)(prog.n_slots > 0 ? prog.n_slots : 1) * kTile * sizeof(float);
+  const int64_t tiles = (prog.total + kTile - 1) / kTile;
+  const int per_sm = (int)(220 * 1024 / smem) < 8 ? (int)(220 * 1024 / smem) : 8;
+  const int64_t cap = (int64_t)kSmCount * (per_sm > 0 ? per_sm : 1) * 4;
+  const int grid = (int)(tiles < cap ? tiles : cap);
+  auto kern = prog.vec ? ew_kernel<true> : ew_kernel<false>;
+  if (smem > 48 * 1024) IB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, kThreads, smem, s>>>(prog, divs);
+  return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "elementwise launch");
+}
+
+}  // namespace ib200

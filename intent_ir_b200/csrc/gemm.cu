@@ -1,0 +1,438 @@
+// C[M,N] = act(A[M,K] · B + bias), fp32 accumulation.
+//
+// Tensor-core path (bf16 operands; K and N multiples of 8): a persistent, warp-specialised
+// sm_100a kernel, one CTA per SM, 128x256 output tiles, K in blocks of 64:
+//   warp 0   : TMA producer — cp.async.bulk.tensor (128-byte swizzle) into a 4-stage
+//              shared-memory ring, completion on mbarriers;
+//   warp 1   : allocates tensor memory and issues tcgen05.mma (cta_group::1, kind::f16,
+//              M=128 N=256 K=16) from one elected thread; tcgen05.commit releases ring
+//              stages back to the producer and publishes finished accumulators;
+//   warps 2-5: epilogue — tcgen05.ld of the fp32 accumulator (one row per thread), + bias,
+//              activation, conversion, 16-byte stores.
+// Two 256-column accumulators fill the 512 TMEM columns, so the epilogue of tile i overlaps
+// the main loop of tile i+1.  A is K-major; B is read as stored: [K,N] row-major is the
+// MN-major operand form (the descriptor's major bit), [N,K] (transpose_b) is K-major — no
+// transposition pass either way.  Every mbarrier wait is bounded: on expiry the thread
+// records where it gave up in *status and the kernel drains and exits, so a wrong
+// descriptor can produce a wrong answer or an error code, never a hung GPU.
+//
+// Replaces the reference's opt-in TF32 wmma/mma.sync kernel (kernels/wmma_matmul.cuh) and
+// its FMA default (kernels/matmul_fallback.cuh); the bias+activation epilogue that the
+// reference leaves as separate ops (pipeline/tilelang/core.py:895-901) is fused.
+//
+// FMA path: every other shape / dtype (fp32 operands, ragged K or N): 64x64 tiles, 4x4 per
+// thread, operands staged through shared memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace ib200 {
+namespace {
+
+// ============================== tcgen05 path ==========================================
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;          // 16 KiB
+constexpr int B_STAGE_BYTES = BK * BN * 2;          // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait, then give up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after recording `code`) when the limit expires or when
+// another thread has already flagged a failure.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = now_ns();
+  uint32_t spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 0x3ff) == 0) {
+      if (*abort_flag) return false;
+      if (now_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// 64-bit shared-memory matrix descriptor (tcgen05): start address, leading / stride byte
+// offsets (all >> 4), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct GemmParams {
+  int M, N, K;
+  int b_kmajor;  // 1: B is [N,K] (transpose_b)
+  int act;
+  const void* bias;
+  void* c;
+  int32_t* status;
+};
+
+template <typename TOut>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int ntiles = tiles_m * tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // allocate all 512 TMEM columns (one CTA per SM owns the whole tensor memory)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1))) break;
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(sa, &map_a, &full[s], kb * BK, m0);
+          if (p.b_kmajor) {
+            tma_load_2d(sb, &map_b, &full[s], kb * BK, n0);  // one 64(K) x 256(N rows) box
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)  // four 64(N) x 64(K rows) boxes
+              tma_load_2d(sb + j * (BK * 128), &map_b, &full[s], n0 + j * 64, kb * BK);
+          }
+        }
+      }
+      // drain: every stage that was armed must land before the CTA may exit
+      for (int i = 0; i < STAGES; ++i) {
+        if (it == 0) break;
+        const uint32_t last = it - 1;  // the newest armed iteration
+        const int s = i;
+        // the newest iteration that used stage s
+        if (last < (uint32_t)s) continue;
+        const uint32_t j = last - ((last - s) % STAGES);
+        (void)mbar_wait(&full[s], (j / STAGES) & 1, abort_flag, nullptr, 0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.b_kmajor ? 0u : 1u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      uint32_t it = 0, t_local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t_local) {
+        const int buf = t_local & 1;
+        const uint32_t acc_ph = (t_local >> 1) & 1;
+        if (!(ok = mbar_wait(&acc_empty[buf], acc_ph ^ 1, abort_flag, p.status, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // A: K-major, 128-byte swizzled rows; one UMMA_K step = 32 bytes inside the row
+            const uint64_t adesc = umma_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            // B: K-major ([N,K]) like A, or MN-major ([K,N]): 64-column chunks BK*128 bytes
+            // apart (leading offset), 8-row K groups 1024 bytes apart (stride offset); one
+            // UMMA_K step = 16 K rows = 2048 bytes
+            const uint64_t bdesc = p.b_kmajor ? umma_desc(sb + k * (UMMA_K * 2), 16, 1024)
+                                              : umma_desc(sb + k * (UMMA_K * 128), BK * 128, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ----------------------------
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's
+    uint32_t t_local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t_local) {
+      const int buf = t_local & 1;
+      const uint32_t acc_ph = (t_local >> 1) & 1;
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      ok = mbar_wait(&acc_full[buf], acc_ph, abort_flag, p.status, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      TOut* crow = static_cast<TOut*>(p.c) + (size_t)row * p.N;
+      const TOut* bias = static_cast<const TOut*>(p.bias);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c * 32, r);
+        const int col0 = n0 + c * 32;
+        if (row < p.M) {
+#pragma unroll
+          for (int g = 0; g < 32; g += 8) {
+            const int col = col0 + g;
+            if (col >= p.N) break;  // N % 8 == 0: a group of 8 columns is all in or all out
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[j] = __uint_as_float(r[g + j]);
+              if (bias) v[j] += to_f32<TOut>(bias[col + j]);
+              if (p.act == IB200_ACT_RELU) v[j] = max_nan(v[j], 0.0f);
+            }
+            if (sizeof(TOut) == 2) {
+              uint4 q;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+              q.x = *reinterpret_cast<uint32_t*>(&h0); q.y = *reinterpret_cast<uint32_t*>(&h1);
+              q.z = *reinterpret_cast<uint32_t*>(&h2); q.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(crow + col) = q;
+            } else {
+              *reinterpret_cast<float4*>(crow + col) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(crow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encoder(EncodeTiledFn* out) {
+  static EncodeTiledFn cached = nullptr;
+  if (!cached) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    IB200_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || !fn) return fail(IB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cached = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = cached;
+  return IB200_OK;
+}
+
+// bf16 row-major [rows, cols] tensor, box [box_rows, box_cols], 128-byte swizzle
+int make_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows, int box_cols) {
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(IB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+  return IB200_OK;
+}
+
+int run_tcgen05(const void* a, const void* b, const void* bias, void* c, int out_dtype, int64_t m, int64_t n, int64_t k,
+                int transpose_b, int act, int32_t* status, cudaStream_t s) {
+  EncodeTiledFn enc;
+  if (int rc = get_encoder(&enc)) return rc;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_map(enc, &map_a, a, m, k, BM, BK)) return rc;
+  if (transpose_b) {
+    if (int rc = make_map(enc, &map_b, b, n, k, BN, BK)) return rc;  // [N,K]: box 256 rows x 64 K
+  } else {
+    if (int rc = make_map(enc, &map_b, b, k, n, BK, 64)) return rc;  // [K,N]: box 64 K rows x 64 N
+  }
+  GemmParams p{(int)m, (int)n, (int)k, transpose_b ? 1 : 0, act, bias, c, status};
+  const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
+  auto kern = out_dtype == IB200_BF16 ? gemm_tcgen05_kernel<__nv_bfloat16> : gemm_tcgen05_kernel<float>;
+  IB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(map_a, map_b, p);
+  return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "gemm tcgen05 launch");
+}
+
+// ============================== FMA path ==============================================
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256) gemm_fma_kernel(const TIn* __restrict__ A, const TIn* __restrict__ B,
+                                                       const TOut* __restrict__ bias, TOut* __restrict__ C, int M, int N, int K,
+                                                       int b_kmajor, int act) {
+  constexpr int T = 64, KB = 16;
+  __shared__ float sa[KB][T + 1], sb[KB][T + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * T, n0 = blockIdx.x * T;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += KB) {
+    for (int i = threadIdx.x; i < T * KB; i += 256) {
+      {  // A tile: T rows x KB cols, read along K
+        const int r = i / KB, kk = i % KB;
+        const int gm = m0 + r, gk = k0 + kk;
+        sa[kk][r] = (gm < M && gk < K) ? to_f32<TIn>(A[(size_t)gm * K + gk]) : 0.0f;
+      }
+      if (b_kmajor) {  // B stored [N,K]
+        const int c = i / KB, kk = i % KB;
+        const int gn = n0 + c, gk = k0 + kk;
+        sb[kk][c] = (gn < N && gk < K) ? to_f32<TIn>(B[(size_t)gn * K + gk]) : 0.0f;
+      } else {  // B stored [K,N], read along N
+        const int kk = i / T, c = i % T;
+        const int gn = n0 + c, gk = k0 + kk;
+        sb[kk][c] = (gn < N && gk < K) ? to_f32<TIn>(B[(size_t)gk * N + gn]) : 0.0f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < KB; ++kk) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { av[i] = sa[kk][ty * 4 + i]; bv[i] = sb[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= N) continue;
+      float v = acc[i][j];
+      if (bias) v += to_f32<TOut>(bias[gn]);
+      if (act == IB200_ACT_RELU) v = max_nan(v, 0.0f);
+      C[(size_t)gm * N + gn] = from_f32<TOut>(v);
+    }
+  }
+}
+
+template <typename TIn, typename TOut>
+int run_fma(const void* a, const void* b, const void* bias, void* c, int64_t m, int64_t n, int64_t k, int transpose_b, int act,
+            cudaStream_t s) {
+  dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64));
+  if (grid.y > 65535) return fail(IB200_ERR_UNSUPPORTED, "gemm (FMA path): M above 64*65535");
+  gemm_fma_kernel<TIn, TOut><<<grid, 256, 0, s>>>(static_cast<const TIn*>(a), static_cast<const TIn*>(b),
+                                                   static_cast<const TOut*>(bias), static_cast<TOut*>(c), (int)m, (int)n, (int)k,
+                                                   transpose_b ? 1 : 0, act);
+  return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "gemm fma launch");
+}
+
+}  // namespace
+
+int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_dtype, int out_dtype, int64_t m, int64_t n,
+                int64_t k, int transpose_b, int act, int32_t* status, cudaStream_t s) {
+  if (m < 0 || n < 0 || k < 0) return fail(IB200_ERR_INVALID, "gemm: negative extent");
+  if (m == 0 || n == 0) return IB200_OK;
+  if (!a || !b || !c) {
+    if (k > 0 || !c) return fail(IB200_ERR_INVALID, "gemm: null pointer");
+  }
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail(IB200_ERR_UNSUPPORTED, "gemm: extent above 2^31-1");
+  if (act != IB200_ACT_NONE && act != IB200_ACT_RELU) return fail(IB200_ERR_INVALID, "gemm: unknown activation");
+  const bool tc = in_dtype == IB200_BF16 && (out_dtype == IB200_BF16 || out_dtype == IB200_F32) && k >= 8 && k % 8 == 0 &&
+                  n % 8 == 0 && aligned16(a) && aligned16(b) && aligned16(c) && (!bias || aligned16(bias));
+  if (tc) {
+    if (!status) return fail(IB200_ERR_INVALID, "gemm: the tensor-core path needs a device status word");
+    return run_tcgen05(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
+  }
+  if (in_dtype == IB200_F32 && out_dtype == IB200_F32) return run_fma<float, float>(a, b, bias, c, m, n, k, transpose_b, act, s);
+  if (in_dtype == IB200_BF16 && out_dtype == IB200_BF16) return run_fma<__nv_bfloat16, __nv_bfloat16>(a, b, bias, c, m, n, k, transpose_b, act, s);
+  if (in_dtype == IB200_BF16 && out_dtype == IB200_F32) return run_fma<__nv_bfloat16, float>(a, b, bias, c, m, n, k, transpose_b, act, s);
+  if (in_dtype == IB200_F32 && out_dtype == IB200_BF16) return run_fma<float, __nv_bfloat16>(a, b, bias, c, m, n, k, transpose_b, act, s);
+  return fail(IB200_ERR_UNSUPPORTED, "gemm: operand dtypes must be f32 or bf16");
+}
+
+}  // namespace ib200

@@ -1,0 +1,356 @@
+// Row normalisation (layernorm, groupnorm) with centred two-pass statistics:
+//   mean = sum(x)/L, var = sum((x-mean)^2)/L, rstd = 1/sqrt(var + eps),
+//   y = (x-mean)*rstd * w[widx] + b[widx],
+// the arithmetic of the reference's primitive-op chains (pipeline/tilelang/core.py:1334-1374
+// for layernorm, :187-232 for groupnorm) as verify/interpreter.py executes them.  The
+// reference's own CUDA layernorm (kernels/layernorm.cuh) uses E[x^2]-mean^2; the centred
+// form is kept here because the metamorphic shift relations punish the one-pass form.
+//
+// A "row" is L contiguous elements.  For layernorm L = N and widx = column; for groupnorm
+// over X[N,C,HW] a row is one (sample, group) = (C/G)*HW contiguous elements and
+// widx = channel = (linear index / HW) % C.  Both are the mapping
+//   widx = (linear / affine_inner) % affine_period.
+//
+// HBM-bound: the row is read once with 128-bit loads and stays in registers for both
+// statistics passes and the normalisation; x is never re-read from memory.
+//   L <= 1024   : one warp per row;
+//   L <= 16384  : one CTA per row (256..1024 threads);
+//   L <= 131072 : one thread-block cluster of 2..8 CTAs per row, partial sums exchanged
+//                 through distributed shared memory;
+//   larger      : one CTA per row streaming the row three times (passes 2 and 3 hit L2).
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "rowio.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace ib200 {
+namespace {
+
+enum Affine { AFF_NONE = 0, AFF_COL = 1, AFF_GENERIC = 2 };
+
+struct AffineMap {  // widx = (linear / inner) % period, evaluated without 64-bit division per element
+  FastDiv inner, period;
+};
+
+template <int NV> __device__ __forceinline__ float local_sum(const float (&v)[NV][4]) {
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
+  return s;
+}
+
+// v <- v - mean on valid columns (0 on padding); returns the local sum of squares.
+template <int NV, bool VEC>
+__device__ __forceinline__ float centre_and_square(float (&v)[NV][4], float mean, int cols, int tid, int nthreads) {
+  float q = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = 4 * (i * nthreads + tid);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const bool valid = VEC ? (c < cols) : (c + k < cols);
+      v[i][k] = valid ? v[i][k] - mean : 0.0f;
+      q += v[i][k] * v[i][k];
+    }
+  }
+  return q;
+}
+
+// v <- v*rstd*w + b.  `col0` is the column of this thread's first element of the row segment,
+// `lin_q` / `lin_r` are quotient and remainder of the row's first linear index by affine_inner.
+template <typename TW, int NV, bool VEC, int AFF>
+__device__ __forceinline__ void normalise(float (&v)[NV][4], float rstd, const TW* __restrict__ w, const TW* __restrict__ b,
+                                          int cols, int col_offset, int tid, int nthreads, const AffineMap& map,
+                                          uint32_t lin_q, uint32_t lin_r) {
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = 4 * (i * nthreads + tid);
+    if (VEC && c >= cols) continue;
+    float wv[4] = {1.f, 1.f, 1.f, 1.f}, bv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (AFF == AFF_COL) {
+      if (VEC) {
+        if (w) load4<TW>(w + col_offset + c, wv);
+        if (b) load4<TW>(b + col_offset + c, bv);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (c + k < cols) {
+            if (w) wv[k] = to_f32<TW>(w[col_offset + c + k]);
+            if (b) bv[k] = to_f32<TW>(b[col_offset + c + k]);
+          }
+      }
+    } else if (AFF == AFF_GENERIC) {
+      if (VEC && (map.inner.d & 3u) == 0) {  // the 4 elements share one channel
+        const uint32_t ch = map.period.d == 1 ? 0u : (lin_q + map.inner.div(lin_r + col_offset + c));
+        uint32_t qq, idx;
+        map.period.divmod(ch, qq, idx);
+        const float ws = w ? to_f32<TW>(w[idx]) : 1.f, bs = b ? to_f32<TW>(b[idx]) : 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { wv[k] = ws; bv[k] = bs; }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (c + k < cols) {
+            uint32_t qq, idx;
+            map.period.divmod(lin_q + map.inner.div(lin_r + col_offset + c + k), qq, idx);
+            if (w) wv[k] = to_f32<TW>(w[idx]);
+            if (b) bv[k] = to_f32<TW>(b[idx]);
+          }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[i][k] = v[i][k] * rstd * wv[k] + bv[k];
+  }
+}
+
+// quotient (mod period) and remainder of a row's first linear index by affine_inner
+__device__ __forceinline__ void row_origin(int64_t row, int64_t cols, const AffineMap& map, uint32_t& q, uint32_t& r) {
+  const uint64_t lin = (uint64_t)row * (uint64_t)cols;
+  const uint64_t qq = lin / map.inner.d;
+  r = (uint32_t)(lin - qq * map.inner.d);
+  q = (uint32_t)(qq % map.period.d);
+}
+
+template <typename T, typename TW, int NV, bool VEC, int AFF>
+__global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
+                                                 T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                 int64_t rows, int cols, float eps, AffineMap map) {
+  const int lane = threadIdx.x & 31;
+  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += stride) {
+    float v[NV][4];
+    load_row<T, NV, VEC>(x + r * cols, cols, lane, 32, 0.0f, v);
+    const float mean = warp_reduce<SumOp>(local_sum<NV>(v)) / (float)cols;
+    const float var = warp_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, lane, 32)) / (float)cols;
+    const float rstd = 1.0f / sqrtf(var + eps);
+    uint32_t lq = 0, lr = 0;
+    if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
+    normalise<TW, NV, VEC, AFF>(v, rstd, w, b, cols, 0, lane, 32, map, lq, lr);
+    store_row<T, NV, VEC>(y + r * cols, cols, lane, 32, v);
+    if (lane == 0) {
+      if (mean_out) mean_out[r] = mean;
+      if (rstd_out) rstd_out[r] = rstd;
+    }
+  }
+}
+
+template <typename T, typename TW, int THREADS, int NV, bool VEC, int AFF>
+__global__ void __launch_bounds__(THREADS) norm_block(const T* __restrict__ x, const TW* __restrict__ w,
+                                                      const TW* __restrict__ b, T* __restrict__ y,
+                                                      float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                      int64_t rows, int cols, float eps, AffineMap map) {
+  __shared__ float slots[2][32];
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float v[NV][4];
+    load_row<T, NV, VEC>(x + r * cols, cols, threadIdx.x, THREADS, 0.0f, v);
+    const float mean = block_reduce<SumOp>(local_sum<NV>(v), slots[0]) / (float)cols;
+    const float var = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, threadIdx.x, THREADS), slots[1]) / (float)cols;
+    const float rstd = 1.0f / sqrtf(var + eps);
+    uint32_t lq = 0, lr = 0;
+    if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
+    normalise<TW, NV, VEC, AFF>(v, rstd, w, b, cols, 0, threadIdx.x, THREADS, map, lq, lr);
+    store_row<T, NV, VEC>(y + r * cols, cols, threadIdx.x, THREADS, v);
+    if (threadIdx.x == 0) {
+      if (mean_out) mean_out[r] = mean;
+      if (rstd_out) rstd_out[r] = rstd;
+    }
+  }
+}
+
+// One cluster of `csize` CTAs per row: CTA k keeps columns [k*seg, (k+1)*seg) in registers;
+// the two statistics are combined by reading every CTA's partial through distributed
+// shared memory.  One cluster handles one row (grid = rows * csize CTAs).
+template <typename T, typename TW, int THREADS, int NV, bool VEC, int AFF>
+__global__ void __launch_bounds__(THREADS) norm_cluster(const T* __restrict__ x, const TW* __restrict__ w,
+                                                        const TW* __restrict__ b, T* __restrict__ y,
+                                                        float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                        int64_t rows, int cols, int seg, float eps, AffineMap map) {
+  __shared__ float slots[2][32];
+  __shared__ float partial[2];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+  const int64_t r = blockIdx.x / csize;  // grid is exactly rows * csize, so r < rows
+  const int col0 = rank * seg;
+  const int mine = min(seg, cols - col0) > 0 ? min(seg, cols - col0) : 0;
+  float v[NV][4];
+  load_row<T, NV, VEC>(x + r * cols + col0, mine, threadIdx.x, THREADS, 0.0f, v);
+
+  float s = block_reduce<SumOp>(local_sum<NV>(v), slots[0]);
+  if (threadIdx.x == 0) partial[0] = s;
+  cluster.sync();
+  float total = 0.0f;
+  for (int k = 0; k < csize; ++k) total += *cluster.map_shared_rank(&partial[0], k);
+  const float mean = total / (float)cols;
+
+  float q = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, mine, threadIdx.x, THREADS), slots[1]);
+  if (threadIdx.x == 0) partial[1] = q;
+  cluster.sync();
+  total = 0.0f;
+  for (int k = 0; k < csize; ++k) total += *cluster.map_shared_rank(&partial[1], k);
+  const float rstd = 1.0f / sqrtf(total / (float)cols + eps);
+
+  uint32_t lq = 0, lr = 0;
+  if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
+  normalise<TW, NV, VEC, AFF>(v, rstd, w, b, mine, col0, threadIdx.x, THREADS, map, lq, lr);
+  store_row<T, NV, VEC>(y + r * cols + col0, mine, threadIdx.x, THREADS, v);
+  if (rank == 0 && threadIdx.x == 0) {
+    if (mean_out) mean_out[r] = mean;
+    if (rstd_out) rstd_out[r] = rstd;
+  }
+  cluster.sync();  // no CTA may exit while a peer can still read its `partial`
+}
+
+template <typename T, typename TW, int AFF>
+__global__ void __launch_bounds__(1024) norm_stream(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
+                                                    T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                    int64_t rows, int64_t cols, float eps, int64_t inner, int64_t period) {
+  __shared__ float slots[2][32];
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* xr = x + r * cols;
+    T* yr = y + r * cols;
+    float s = 0.0f;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += to_f32<T>(xr[c]);
+    const float mean = block_reduce<SumOp>(s, slots[0]) / (float)cols;
+    float q = 0.0f;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float d = to_f32<T>(xr[c]) - mean;
+      q += d * d;
+    }
+    const float rstd = 1.0f / sqrtf(block_reduce<SumOp>(q, slots[1]) / (float)cols + eps);
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      float wv = 1.0f, bv = 0.0f;
+      if (AFF != AFF_NONE) {
+        const int64_t idx = AFF == AFF_COL ? c : ((r * cols + c) / inner) % period;
+        if (w) wv = to_f32<TW>(w[idx]);
+        if (b) bv = to_f32<TW>(b[idx]);
+      }
+      yr[c] = from_f32<T>((to_f32<T>(xr[c]) - mean) * rstd * wv + bv);
+    }
+    if (threadIdx.x == 0) {
+      if (mean_out) mean_out[r] = mean;
+      if (rstd_out) rstd_out[r] = rstd;
+    }
+  }
+}
+
+struct Args {
+  const void *x, *w, *b;
+  void* y;
+  float *mean, *rstd;
+  int64_t rows, cols, inner, period;
+  float eps;
+  cudaStream_t s;
+};
+
+template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a) {
+  const T* x = static_cast<const T*>(a.x);
+  T* y = static_cast<T*>(a.y);
+  const TW *w = static_cast<const TW*>(a.w), *b = static_cast<const TW*>(a.b);
+  AffineMap map;
+  if (AFF == AFF_GENERIC) {
+    map.inner = FastDiv((uint32_t)a.inner);
+    map.period = FastDiv((uint32_t)a.period);
+  }
+  const int c = (int)a.cols;
+#define IB200_WARP(NV)                                                                                            \
+  {                                                                                                               \
+    const int64_t blocks = (a.rows + 3) / 4;                                                                      \
+    const int grid = (int)(blocks < (int64_t)kSmCount * 32 ? blocks : (int64_t)kSmCount * 32);                    \
+    norm_warp<T, TW, NV, VEC, AFF><<<grid, 128, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map);     \
+  }
+#define IB200_BLOCK(TH, NV)                                                                                       \
+  {                                                                                                               \
+    const int64_t cap = (int64_t)kSmCount * (2048 / TH) * 2;                                                      \
+    const int grid = (int)(a.rows < cap ? a.rows : cap);                                                          \
+    norm_block<T, TW, TH, NV, VEC, AFF><<<grid, TH, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
+  }
+  if (a.cols <= 128) IB200_WARP(1)
+  else if (a.cols <= 256) IB200_WARP(2)
+  else if (a.cols <= 512) IB200_WARP(4)
+  else if (a.cols <= 1024) IB200_WARP(8)
+  else if (a.cols <= 2048) IB200_BLOCK(256, 2)
+  else if (a.cols <= 4096) IB200_BLOCK(256, 4)
+  else if (a.cols <= 8192) IB200_BLOCK(512, 4)
+  else if (a.cols <= 16384) IB200_BLOCK(1024, 4)
+  else if (a.cols <= 131072 && a.rows * 8 < (int64_t)INT32_MAX) {
+    // cluster of 2, 4 or 8 CTAs x 1024 threads x 16 elements
+    int csize = a.cols <= 32768 ? 2 : (a.cols <= 65536 ? 4 : 8);
+    int seg = (int)((a.cols + csize - 1) / csize);
+    seg = (seg + 3) & ~3;  // keep every segment start aligned to a 4-element vector
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(a.rows * csize));
+    cfg.blockDim = dim3(1024);
+    cfg.stream = a.s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, norm_cluster<T, TW, 1024, 4, VEC, AFF>, x, w, b, y, a.mean, a.rstd, a.rows,
+                                       c, seg, a.eps, map);
+    if (e != cudaSuccess) return cuda_fail(e, "norm cluster launch");
+  } else {
+    if (AFF == AFF_GENERIC && (a.rows * a.cols) / a.inner >= (int64_t)1 << 62) return fail(IB200_ERR_UNSUPPORTED, "norm: extent too large");
+    const int grid = (int)(a.rows < (int64_t)kSmCount * 2 ? a.rows : (int64_t)kSmCount * 2);
+    norm_stream<T, TW, AFF><<<grid, 1024, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, a.cols, a.eps, a.inner, a.period);
+  }
+#undef IB200_WARP
+#undef IB200_BLOCK
+  return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "norm launch");
+}
+
+template <typename T, typename TW> int pick_mode(const Args& a) {
+  bool vec = aligned16(a.x) && aligned16(a.y) && a.cols % 4 == 0;
+  int aff = AFF_GENERIC;
+  if (!a.w && !a.b) aff = AFF_NONE;
+  else if (a.inner == 1 && a.period == a.cols) aff = AFF_COL;
+  if (aff == AFF_COL && vec) vec = (!a.w || aligned16(a.w)) && (!a.b || aligned16(a.b));
+  // the register-resident generic mapping divides 32-bit offsets: the per-row offset
+  // (remainder + column) must stay below 2^31
+  if (aff == AFF_GENERIC && (a.inner >= ((int64_t)1 << 30) || a.period >= ((int64_t)1 << 30) || a.cols >= ((int64_t)1 << 30)))
+    return fail(IB200_ERR_UNSUPPORTED, "norm: affine_inner / affine_period / cols must be below 2^30");
+#define IB200_GO(V, A) return dispatch<T, TW, V, A>(a)
+  if (vec) {
+    if (aff == AFF_NONE) IB200_GO(true, AFF_NONE);
+    if (aff == AFF_COL) IB200_GO(true, AFF_COL);
+    IB200_GO(true, AFF_GENERIC);
+  }
+  if (aff == AFF_NONE) IB200_GO(false, AFF_NONE);
+  if (aff == AFF_COL) IB200_GO(false, AFF_COL);
+  IB200_GO(false, AFF_GENERIC);
+#undef IB200_GO
+}
+
+}  // namespace
+
+int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype,
+                     int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps,
+                     cudaStream_t s) {
+  if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "norm: negative extent");
+  if (rows == 0 || cols == 0) return IB200_OK;
+  if (!x || !y) return fail(IB200_ERR_INVALID, "norm: null pointer");
+  if ((w || b) && (affine_inner < 1 || affine_period < 1)) return fail(IB200_ERR_INVALID, "norm: affine_inner and affine_period must be >= 1");
+  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s};
+  const int adt = (w || b) ? affine_dtype : dtype;
+  switch (dtype) {
+    case IB200_F32:
+      if (adt == IB200_F32) return pick_mode<float, float>(a);
+      break;
+    case IB200_BF16:
+      if (adt == IB200_BF16) return pick_mode<__nv_bfloat16, __nv_bfloat16>(a);
+      if (adt == IB200_F32) return pick_mode<__nv_bfloat16, float>(a);
+      break;
+    case IB200_F16:
+      if (adt == IB200_F16) return pick_mode<__half, __half>(a);
+      if (adt == IB200_F32) return pick_mode<__half, float>(a);
+      break;
+    default: break;
+  }
+  return fail(IB200_ERR_UNSUPPORTED, "norm: x/y must be f32, bf16 or f16; w/b the same type or f32");
+}
+
+}  // namespace ib200

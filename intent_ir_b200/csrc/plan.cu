@@ -1,0 +1,1757 @@
+// IntentIR planner and plan executor (host C++).
+//
+// ib200_plan_create(intent_json, bindings_json) lowers one IntentIR graph under concrete
+// shape bindings to a short list of launches of the pre-compiled kernels in this library.
+// It replaces the reference's source-emitting C++ codegen
+// (backends/cuda/cpp_codegen/intentir_cuda_codegen.cpp:5777-5852) and its Python twin
+// (backends/cuda/codegen/intentir_to_cuda.py:2131-2201): same role — pattern dispatch over
+// the op list — but the result is a plan over fixed kernels, not CUDA source.
+//
+// Three phases:
+//   A. build: every op becomes a node with a concrete shape, following the interpreter's
+//      semantics (verify/interpreter.py:211-545): numpy broadcasting, the declared-symbol
+//      alignment of rank-1 operands (:752-841), broadcast_in_dim (:594-608), reduce axis
+//      resolution (:676-694), one-input binary ops whose second operand is an attribute
+//      (:215-226), matmul epilogue trees (:567-591).
+//   B. match: whole-graph patterns that map to one fused kernel — row softmax (single op
+//      or the reduce_max/sub/exp/reduce_sum/div chain, with optional row_max / row_sum
+//      outputs), layernorm / groupnorm (the centred-variance chain in any of its surface
+//      forms, with optional mean / rstd outputs), matmul + bias + relu, and any(x != 0).
+//      Matching is structural over the dataflow, looking through reshape /
+//      broadcast_in_dim / identity views, and every broadcast is verified through strides.
+//   C. general lowering for everything else: maximal elementwise/broadcast subgraphs
+//      become single micro-op kernels (ew_program.h); reductions, softmax, matmul and
+//      transposes become their kernels; intermediates live in a caller-provided workspace.
+#include <algorithm>
+#include <deque>
+#include <functional>
+#include <map>
+#include <memory>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "ew_program.h"
+#include "json.hpp"
+
+namespace ib200 {
+namespace {
+
+struct Unsupported : std::runtime_error { using std::runtime_error::runtime_error; };
+struct Invalid : std::runtime_error { using std::runtime_error::runtime_error; };
+
+using Shape = std::vector<int64_t>;
+
+int64_t numel(const Shape& s) { int64_t n = 1; for (auto d : s) n *= d; return n; }
+Shape contiguous_strides(const Shape& s) {
+  Shape st(s.size());
+  int64_t acc = 1;
+  for (int i = (int)s.size() - 1; i >= 0; --i) { st[i] = acc; acc *= s[i]; }
+  return st;
+}
+std::string shape_str(const Shape& s) {
+  std::string o = "[";
+  for (size_t i = 0; i < s.size(); ++i) o += (i ? "," : "") + std::to_string(s[i]);
+  return o + "]";
+}
+
+enum DClass { DC_FLOAT = 0, DC_BOOL = 1, DC_INT = 2 };
+
+int dtype_code(const std::string& s) {
+  static const std::map<std::string, int> m = {{"f32", IB200_F32}, {"bf16", IB200_BF16}, {"f16", IB200_F16}, {"i32", IB200_I32},
+                                               {"i64", IB200_I64}, {"bool", IB200_BOOL}, {"i1", IB200_BOOL}, {"u8", IB200_U8},
+                                               {"i8", IB200_I8}, {"i16", IB200_I16}, {"f64", IB200_F64}};
+  auto it = m.find(s);
+  if (it == m.end()) throw Invalid("unknown dtype '" + s + "'");
+  return it->second;
+}
+const char* dtype_name(int c) {
+  static const char* n[] = {"f32", "bf16", "f16", "i32", "i64", "bool", "u8", "i8", "i16", "f64"};
+  return c >= 0 && c < 10 ? n[c] : "?";
+}
+int class_of_dtype(int c) {
+  if (c == IB200_BOOL) return DC_BOOL;
+  if (c == IB200_F32 || c == IB200_BF16 || c == IB200_F16 || c == IB200_F64) return DC_FLOAT;
+  return DC_INT;
+}
+int storage_of_class(int dc) { return dc == DC_BOOL ? IB200_BOOL : dc == DC_INT ? IB200_I32 : IB200_F32; }
+
+// ---- strided views -------------------------------------------------------------------------
+struct View {
+  int buffer = -1;
+  Shape shape, strides;
+  int64_t offset = 0;
+  bool contiguous() const {
+    int64_t acc = 1;
+    for (int i = (int)shape.size() - 1; i >= 0; --i) {
+      if (shape[i] != 1 && strides[i] != acc) return false;
+      acc *= shape[i];
+    }
+    return offset == 0;
+  }
+};
+
+// new strides for viewing (shape, strides) as `to` without copying; false if impossible.
+// Dims are grouped into chunks that are contiguous among themselves (broadcast chunks have
+// stride 0 throughout); each chunk must be covered by a run of target dims.
+bool reshape_view(const Shape& shape, const Shape& strides, const Shape& to, Shape& out) {
+  out.assign(to.size(), 0);
+  if (numel(shape) != numel(to)) return false;
+  if (numel(to) == 0) { out = contiguous_strides(to); return true; }
+  if (shape.empty()) return true;  // a scalar viewed as [1,1,...]
+  int view_d = (int)to.size() - 1;
+  int64_t chunk_base = strides.back(), tensor_numel = 1, view_numel = 1;
+  for (int d = (int)shape.size() - 1; d >= 0; --d) {
+    tensor_numel *= shape[d];
+    if (d == 0 || (shape[d - 1] != 1 && strides[d - 1] != tensor_numel * chunk_base)) {
+      while (view_d >= 0 && (view_numel < tensor_numel || to[view_d] == 1)) {
+        out[view_d] = view_numel * chunk_base;
+        view_numel *= to[view_d];
+        --view_d;
+      }
+      if (view_numel != tensor_numel) return false;
+      if (d > 0) { chunk_base = strides[d - 1]; tensor_numel = 1; view_numel = 1; }
+    }
+  }
+  return view_d == -1;
+}
+
+// ---- graph nodes -----------------------------------------------------------------------------
+struct Node {
+  std::string name, op;
+  std::vector<int> in;
+  Shape shape;
+  int dclass = DC_FLOAT;
+  int decl_dtype = -1;
+  double cval = 0.0;
+  std::vector<int> axes;  // reduce axes | transpose perm | broadcast dims
+  bool keepdims = false;
+  double scale = 1.0;
+  int axis = 0;
+  bool ta = false, tb = false;
+  int cast_to = -1;
+  // lowering state
+  enum Repr { NONE, STRIDED, CONSTANT, IOTA, EXPR } repr = NONE;
+  View view;
+};
+
+const std::set<std::string> kBinary = {"add", "sub", "mul", "div", "max", "min"};
+const std::set<std::string> kUnary = {"relu", "exp", "rsqrt", "abs", "floor"};
+const std::set<std::string> kCompare = {"ne", "lt", "le", "gt", "ge"};
+const std::set<std::string> kLogic2 = {"and", "or"};
+const std::set<std::string> kViews = {"reshape", "broadcast_in_dim", "identity", "layout_cast", "transpose"};
+
+bool is_elementwise(const std::string& op) {
+  return kBinary.count(op) || kUnary.count(op) || kCompare.count(op) || kLogic2.count(op) || op == "not" || op == "where" || op == "cast";
+}
+
+struct Buffer {
+  bool is_arg = false;
+  int arg_index = -1;
+  size_t ws_offset = 0, bytes = 0;
+  int dtype = IB200_F32;
+  std::string name;
+};
+
+struct Step {
+  enum Kind { REDUCE, SOFTMAX, NORM, GEMM, ELEMENTWISE, TRANSPOSE } kind;
+  std::string label;
+  int in[3] = {-1, -1, -1};
+  int out[3] = {-1, -1, -1};
+  int64_t d[4] = {0, 0, 0, 0};  // kernel extents
+  int64_t aff_inner = 1, aff_period = 1;
+  int reduce_kind = 0;
+  float scale = 1.0f, eps = 0.0f;
+  int dtype = IB200_F32, dtype2 = IB200_F32;
+  int transpose_b = 0, act = 0;
+  EwProgram ew;
+  std::vector<int> ew_in_buf, ew_out_buf;
+  std::vector<int64_t> ew_in_off;  // element offsets into the input buffers
+};
+
+}  // namespace
+}  // namespace ib200
+
+struct ib200_plan {
+  std::string kernel_name;
+  std::vector<ib200::Buffer> buffers;
+  std::vector<ib200::Step> steps;
+  std::vector<std::string> arg_names;
+  std::vector<std::string> output_names;
+  size_t workspace_bytes = 0;
+  size_t status_offset = 0;
+  bool uses_status = false;
+  ib200::Json description;
+};
+
+namespace ib200 {
+namespace {
+
+class Planner {
+ public:
+  Planner(const Json& intent, const Json& bindings) : intent_(intent) {
+    if (!intent.is_obj()) throw Invalid("intent must be a JSON object");
+    if (bindings.is_obj())
+      for (auto& kv : bindings.obj)
+        if (kv.second.is_num()) bind_[kv.first] = kv.second.num;
+  }
+
+  std::unique_ptr<ib200_plan> run() {
+    plan_.reset(new ib200_plan);
+    const Json* nm = intent_.find("name");
+    plan_->kernel_name = nm && nm->is_str() ? nm->s : "intent_fn";
+    build();
+    if (!match_fused()) lower_general();
+    finish();
+    return std::move(plan_);
+  }
+
+ private:
+  const Json& intent_;
+  std::map<std::string, double> bind_;
+  std::map<std::string, Json> decl_;       // declared tensors
+  std::vector<std::string> decl_order_;
+  std::deque<Node> nodes_;  // a deque: references stay valid while lowering appends nodes
+  std::map<std::string, int> by_name_;
+  std::vector<std::string> outputs_;
+  std::vector<int> inputs_;                // node ids of external inputs, first-use order
+  std::unique_ptr<ib200_plan> plan_;
+
+  // =============================== phase A: build ==========================================
+  int64_t dim_value(const Json& d, const std::string& where) const {
+    if (d.is_num()) return d.as_int();
+    if (d.is_str()) {
+      auto it = bind_.find(d.s);
+      if (it != bind_.end()) return (int64_t)it->second;
+      char* end = nullptr;
+      long long v = std::strtoll(d.s.c_str(), &end, 10);
+      if (end && *end == 0 && !d.s.empty()) return v;
+      throw Invalid("unbound symbolic dim '" + d.s + "' in " + where);
+    }
+    throw Invalid("bad dim in " + where);
+  }
+  Shape shape_of(const Json& arr, const std::string& where) const {
+    Shape s;
+    if (!arr.is_arr()) throw Invalid(where + " must be a list");
+    for (auto& d : arr.arr) s.push_back(dim_value(d, where));
+    return s;
+  }
+
+  int add(Node n) {
+    nodes_.push_back(std::move(n));
+    int id = (int)nodes_.size() - 1;
+    if (!nodes_[id].name.empty()) by_name_[nodes_[id].name] = id;
+    return id;
+  }
+  int add_const(double v) {
+    Node n;
+    n.op = "const";
+    n.cval = v;
+    return add(n);
+  }
+
+  int lookup(const std::string& name) {
+    auto it = by_name_.find(name);
+    if (it != by_name_.end()) return it->second;
+    auto d = decl_.find(name);
+    if (d == decl_.end()) throw Invalid("undefined value referenced: " + name);
+    Node n;
+    n.name = name;
+    n.op = "input";
+    const Json* dt = d->second.find("dtype");
+    n.decl_dtype = dtype_code(dt && dt->is_str() ? dt->s : "f32");
+    n.dclass = class_of_dtype(n.decl_dtype);
+    const Json* sh = d->second.find("shape");
+    n.shape = sh ? shape_of(*sh, "tensors." + name + ".shape") : Shape{};
+    int id = add(n);
+    inputs_.push_back(id);
+    return id;
+  }
+
+  // declared shape tokens, as the interpreter's match_axis sees them
+  bool decl_tokens(const std::string& name, std::vector<const Json*>& toks) const {
+    auto d = decl_.find(name);
+    if (d == decl_.end()) return false;
+    const Json* sh = d->second.find("shape");
+    if (!sh || !sh->is_arr()) return false;
+    for (auto& t : sh->arr) toks.push_back(&t);
+    return true;
+  }
+  bool token_value(const Json& t, int64_t& v) const {
+    if (t.is_num()) { v = t.as_int(); return true; }
+    if (t.is_str()) {
+      auto it = bind_.find(t.s);
+      if (it != bind_.end()) { v = (int64_t)it->second; return true; }
+    }
+    return false;
+  }
+  // interpreter.py:803-821
+  int match_axis(const std::string& vec, const std::string& ten, int ten_rank) const {
+    std::vector<const Json*> v, t;
+    if (vec.empty() || ten.empty() || !decl_tokens(vec, v) || !decl_tokens(ten, t)) return -1;
+    if (v.size() != 1 || (int)t.size() != ten_rank) return -1;
+    if (v[0]->is_str()) {
+      int hit = -1, n = 0;
+      for (int i = 0; i < ten_rank; ++i)
+        if (t[i]->is_str() && t[i]->s == v[0]->s) { hit = i; ++n; }
+      if (n == 1) return hit;
+    }
+    int64_t want;
+    if (!token_value(*v[0], want)) return -1;
+    int hit = -1, n = 0;
+    for (int i = 0; i < ten_rank; ++i) {
+      int64_t x;
+      if (token_value(*t[i], x) && x == want) { hit = i; ++n; }
+    }
+    return n == 1 ? hit : -1;
+  }
+  // interpreter.py:832-841: lift a rank-1 operand onto the axis its declared symbol names
+  void align(const std::string& an, int& a, const std::string& bn, int& b) {
+    auto lift = [&](int vec, const std::string& vn, int ten, const std::string& tn) {
+      const int rank = (int)nodes_[ten].shape.size();
+      int ax = match_axis(vn, tn, rank);
+      if (ax < 0 || nodes_[vec].shape[0] != nodes_[ten].shape[ax]) return vec;
+      Node n;
+      n.op = "reshape";
+      n.in = {vec};
+      n.shape.assign(rank, 1);
+      n.shape[ax] = nodes_[vec].shape[0];
+      n.dclass = nodes_[vec].dclass;
+      return add(n);
+    };
+    if (nodes_[a].shape.size() == 1 && nodes_[b].shape.size() >= 2) a = lift(a, an, b, bn);
+    if (nodes_[b].shape.size() == 1 && nodes_[a].shape.size() >= 2) b = lift(b, bn, a, an);
+  }
+  static Shape broadcast(const Shape& a, const Shape& b, const std::string& what) {
+    Shape o(std::max(a.size(), b.size()), 1);
+    for (size_t i = 0; i < o.size(); ++i) {
+      int64_t x = i < o.size() - a.size() ? 1 : a[i - (o.size() - a.size())];
+      int64_t y = i < o.size() - b.size() ? 1 : b[i - (o.size() - b.size())];
+      if (x != y && x != 1 && y != 1) throw Invalid(what + ": operands could not be broadcast together: " + shape_str(a) + " vs " + shape_str(b));
+      o[i] = x == 1 ? y : x;
+    }
+    return o;
+  }
+
+  // attribute operand: a value name, a bound symbol, or a number (interpreter.py:633-643)
+  int scalar_operand(const Json& v, const std::string& where) {
+    if (v.is_num()) return add_const(v.num);
+    if (v.type == Json::Bool) return add_const(v.b ? 1.0 : 0.0);
+    if (v.is_str()) {
+      if (by_name_.count(v.s)) return by_name_[v.s];
+      auto it = bind_.find(v.s);
+      if (it != bind_.end()) return add_const(it->second);
+      char* end = nullptr;
+      double d = std::strtod(v.s.c_str(), &end);
+      if (end && *end == 0 && !v.s.empty()) return add_const(d);
+      throw Unsupported(where + ": unresolved scalar value '" + v.s + "' (expression strings must be resolved by the host)");
+    }
+    throw Invalid(where + ": bad scalar attribute");
+  }
+  double number_attr(const Json& v, const std::string& where) const {
+    if (v.is_num()) return v.num;
+    if (v.is_str()) {
+      auto it = bind_.find(v.s);
+      if (it != bind_.end()) return it->second;
+      if (v.s == "eps") return 1e-5;
+      char* end = nullptr;
+      double d = std::strtod(v.s.c_str(), &end);
+      if (end && *end == 0 && !v.s.empty()) return d;
+      throw Unsupported(where + ": '" + v.s + "' is an expression; the host must resolve it to a number");
+    }
+    throw Invalid(where + ": expected a number");
+  }
+
+  int build_epilogue(const Json& node, int acc) {
+    if (node.is_str()) return node.s == "$x" ? acc : lookup(node.s);
+    const Json* opj = node.find("op");
+    const Json* ins = node.find("inputs");
+    if (!opj || !opj->is_str() || !ins || !ins->is_arr()) throw Invalid("malformed matmul epilogue");
+    std::vector<int> args;
+    for (auto& i : ins->arr) args.push_back(build_epilogue(i, acc));
+    return make_elementwise(opj->s, args, std::vector<std::string>(args.size()), "", nullptr);
+  }
+
+  int make_elementwise(const std::string& op, std::vector<int> args, const std::vector<std::string>& names, const std::string& out_name,
+                       const Json* attrs) {
+    Node n;
+    n.name = out_name;
+    n.op = op;
+    if (kBinary.count(op) || kCompare.count(op) || kLogic2.count(op)) {
+      if (args.size() != 2) throw Invalid(op + " requires 2 inputs (or 1+attrs)");
+      align(names[0], args[0], names[1], args[1]);
+      n.shape = broadcast(nodes_[args[0]].shape, nodes_[args[1]].shape, op);
+      if (kBinary.count(op)) {
+        const int ca = nodes_[args[0]].dclass, cb = nodes_[args[1]].dclass;
+        const bool a_const = nodes_[args[0]].op == "const", b_const = nodes_[args[1]].op == "const";
+        n.dclass = (ca == DC_FLOAT || cb == DC_FLOAT || op == "div") ? DC_FLOAT : DC_INT;
+        if (a_const && !b_const && cb == DC_INT && std::floor(nodes_[args[0]].cval) == nodes_[args[0]].cval && op != "div") n.dclass = DC_INT;
+        if (b_const && !a_const && ca == DC_INT && std::floor(nodes_[args[1]].cval) == nodes_[args[1]].cval && op != "div") n.dclass = DC_INT;
+      } else {
+        n.dclass = DC_BOOL;
+      }
+    } else if (kUnary.count(op) || op == "not" || op == "cast" || op == "identity") {
+      if (args.size() != 1) throw Invalid(op + " requires 1 input");
+      n.shape = nodes_[args[0]].shape;
+      n.dclass = op == "not" ? DC_BOOL : (op == "exp" || op == "rsqrt") ? DC_FLOAT : nodes_[args[0]].dclass;
+      if (op == "cast") {
+        const Json* to = attrs ? attrs->find("to") : nullptr;
+        if (!to || !to->is_str()) throw Invalid("cast requires attrs.to");
+        n.cast_to = dtype_code(to->s);
+        n.dclass = class_of_dtype(n.cast_to);
+      }
+    } else if (op == "where") {
+      if (args.size() != 3) throw Invalid("where requires 3 inputs (cond, x, y)");
+      align(names[0], args[0], names[1], args[1]);
+      align(names[0], args[0], names[2], args[2]);
+      align(names[1], args[1], names[2], args[2]);
+      n.shape = broadcast(broadcast(nodes_[args[0]].shape, nodes_[args[1]].shape, op), nodes_[args[2]].shape, op);
+      n.dclass = (nodes_[args[1]].dclass == DC_FLOAT || nodes_[args[2]].dclass == DC_FLOAT) ? DC_FLOAT
+                 : (nodes_[args[1]].dclass == DC_INT || nodes_[args[2]].dclass == DC_INT) ? DC_INT : DC_BOOL;
+    } else {
+      throw Unsupported("elementwise op '" + op + "' is not covered");
+    }
+    n.in = args;
+    return add(n);
+  }
+
+  std::vector<int> reduce_axes(const Json* raw, int rank) const {
+    std::vector<int> axes;
+    if (!raw || raw->is_null()) {
+      for (int i = 0; i < rank; ++i) axes.push_back(i);
+      return axes;
+    }
+    std::vector<const Json*> items;
+    if (raw->is_arr()) for (auto& j : raw->arr) items.push_back(&j);
+    else items.push_back(raw);
+    for (auto* j : items) {
+      if (j->is_num()) axes.push_back((int)j->as_int());
+      else if (j->is_str() && !j->s.empty() && std::all_of(j->s.begin(), j->s.end(), ::isdigit)) axes.push_back(std::atoi(j->s.c_str()));
+    }
+    if (axes.empty()) for (int i = 1; i < rank; ++i) axes.push_back(i);
+    for (auto& a : axes) {
+      if (a < 0) a += rank;
+      if (a < 0 || a >= rank) throw Invalid("reduce axis out of range");
+    }
+    std::sort(axes.begin(), axes.end());
+    axes.erase(std::unique(axes.begin(), axes.end()), axes.end());
+    return axes;
+  }
+
+  void build() {
+    const Json* tensors = intent_.find("tensors");
+    if (tensors && tensors->is_obj())
+      for (auto& kv : tensors->obj) { decl_[kv.first] = kv.second; decl_order_.push_back(kv.first); }
+    const Json* ops = intent_.find("ops");
+    if (!ops || !ops->is_arr() || ops->arr.empty()) throw Invalid("ops must not be empty");
+    for (size_t idx = 0; idx < ops->arr.size(); ++idx) {
+      const Json& o = ops->arr[idx];
+      const Json* opj = o.find("op");
+      const Json* outj = o.find("output");
+      if (!opj || !opj->is_str() || !outj || !outj->is_str()) throw Invalid("op[" + std::to_string(idx) + "] needs op and output strings");
+      const std::string op = opj->s, out = outj->s, where = "op[" + std::to_string(idx) + "] " + op;
+      static const Json empty_obj = Json::object();
+      const Json* attrs = o.find("attrs");
+      if (!attrs || !attrs->is_obj()) attrs = &empty_obj;
+      std::vector<std::string> in_names;
+      if (const Json* ins = o.find("inputs"))
+        if (ins->is_arr()) for (auto& i : ins->arr) if (i.is_str()) in_names.push_back(i.s);
+      std::vector<int> in;
+      for (auto& nme : in_names) in.push_back(lookup(nme));
+      int id = -1;
+
+      if (is_elementwise(op)) {
+        static const std::map<std::string, std::string> scalar_attr = {{"div", "divisor"}, {"add", "addend"}, {"sub", "subtract"},
+                                                                       {"mul", "mul_factor"}, {"max", "other"}, {"min", "other"}};
+        std::vector<std::string> names = in_names;
+        if (kBinary.count(op) && in.size() == 1) {
+          const Json* extra = attrs->find(scalar_attr.at(op));
+          if (extra) { in.push_back(scalar_operand(*extra, where)); names.push_back(""); }
+        }
+        id = make_elementwise(op, in, names, out, attrs);
+      } else if (op == "identity" || op == "layout_cast") {
+        if (in.size() != 1) throw Invalid(where + " requires 1 input");
+        Node n; n.name = out; n.op = op; n.in = in; n.shape = nodes_[in[0]].shape; n.dclass = nodes_[in[0]].dclass;
+        id = add(n);
+      } else if (op == "const") {
+        const Json* v = attrs->find("value");
+        if (!v) throw Invalid(where + " requires attrs.value");
+        if (v->is_str() && by_name_.count(v->s)) {  // alias of an existing value (interpreter.py:527-528)
+          Node n; n.name = out; n.op = "identity"; n.in = {by_name_[v->s]}; n.shape = nodes_[n.in[0]].shape; n.dclass = nodes_[n.in[0]].dclass;
+          id = add(n);
+        } else {
+          Node n; n.name = out; n.op = "const";
+          n.cval = v->type == Json::Bool ? (v->b ? 1.0 : 0.0) : number_attr(*v, where);
+          const Json* dt = attrs->find("dtype");
+          if (dt && dt->is_str()) {
+            n.dclass = class_of_dtype(dtype_code(dt->s));
+            const int code = dtype_code(dt->s);
+            // np.array(value, dtype) rounds the literal to the const's dtype (bf16 is carried as f16)
+            if (code == IB200_F32) n.cval = (double)(float)n.cval;
+            else if (code == IB200_F16 || code == IB200_BF16) n.cval = (double)__half2float(__float2half_rn((float)n.cval));
+            else if (n.dclass == DC_INT) n.cval = std::trunc(n.cval);
+            else if (n.dclass == DC_BOOL) n.cval = n.cval != 0.0;
+          } else {
+            n.dclass = (v->type == Json::Bool) ? DC_BOOL : (v->is_num() && v->integral) ? DC_INT : DC_FLOAT;
+          }
+          id = add(n);
+        }
+      } else if (op == "iota") {
+        Node n; n.name = out; n.op = "iota";
+        const Json* sh = attrs->find("shape");
+        if (!sh) throw Invalid(where + " requires attrs.shape");
+        n.shape = shape_of(*sh, where);
+        const Json* ax = attrs->find("axis");
+        n.axis = ax && ax->is_num() ? (int)ax->as_int() : 0;
+        if (n.axis < 0 || n.axis >= (int)n.shape.size()) throw Invalid(where + ": iota axis out of range");
+        const Json* dt = attrs->find("dtype");
+        n.dclass = class_of_dtype(dtype_code(dt && dt->is_str() ? dt->s : "i32"));
+        id = add(n);
+      } else if (op == "reshape") {
+        if (in.size() != 1) throw Invalid(where + " requires 1 input");
+        Node n; n.name = out; n.op = op; n.in = in; n.dclass = nodes_[in[0]].dclass;
+        const Json* sh = attrs->find("shape");
+        if (!sh) throw Invalid(where + " requires attrs.shape");
+        n.shape = shape_of(*sh, where);
+        int64_t known = 1; int infer = -1;
+        for (size_t i = 0; i < n.shape.size(); ++i) { if (n.shape[i] == -1) infer = (int)i; else known *= n.shape[i]; }
+        if (infer >= 0) n.shape[infer] = known ? numel(nodes_[in[0]].shape) / known : 0;
+        if (numel(n.shape) != numel(nodes_[in[0]].shape))
+          throw Invalid(where + ": cannot reshape " + shape_str(nodes_[in[0]].shape) + " into " + shape_str(n.shape));
+        id = add(n);
+      } else if (op == "broadcast_in_dim") {
+        if (in.size() != 1) throw Invalid(where + " requires 1 input");
+        Node n; n.name = out; n.op = op; n.in = in; n.dclass = nodes_[in[0]].dclass;
+        const Json* sh = attrs->find("out_shape");
+        const Json* bd = attrs->find("broadcast_dims");
+        if (!sh || !bd || !bd->is_arr()) throw Invalid(where + " requires out_shape and broadcast_dims");
+        n.shape = shape_of(*sh, where);
+        for (auto& j : bd->arr) n.axes.push_back((int)j.as_int());
+        for (int a : n.axes) if (a < 0 || a >= (int)n.shape.size()) throw Invalid(where + ": broadcast_dims out of range");
+        id = add(n);
+      } else if (op == "transpose") {
+        if (in.size() != 1) throw Invalid(where + " requires 1 input");
+        Node n; n.name = out; n.op = op; n.in = in; n.dclass = nodes_[in[0]].dclass;
+        const Json* pj = attrs->find("perm");
+        if (!pj || !pj->is_arr() || pj->arr.size() != nodes_[in[0]].shape.size()) throw Invalid(where + " requires attrs.perm of the input's rank");
+        for (auto& j : pj->arr) {
+          int a = (int)j.as_int();
+          if (a < 0) a += (int)pj->arr.size();
+          if (a < 0 || a >= (int)pj->arr.size()) throw Invalid(where + ": perm out of range");
+          n.axes.push_back(a);
+          n.shape.push_back(nodes_[in[0]].shape[a]);
+        }
+        id = add(n);
+      } else if (op == "reduce_sum" || op == "reduce_max" || op == "reduce_any") {
+        if (in.size() != 1) throw Invalid(where + " requires 1 input");
+        Node n; n.name = out; n.op = op; n.in = in;
+        const Json* raw = attrs->find("axes");
+        if (!raw) raw = attrs->find("dims");
+        if (!raw) raw = attrs->find("axis");
+        const Shape& xs = nodes_[in[0]].shape;
+        n.axes = reduce_axes(raw, (int)xs.size());
+        const Json* kd = attrs->find("keepdims");
+        n.keepdims = kd && ((kd->type == Json::Bool && kd->b) || (kd->is_num() && kd->num != 0));
+        for (int i = 0; i < (int)xs.size(); ++i) {
+          const bool red = std::binary_search(n.axes.begin(), n.axes.end(), i);
+          if (!red) n.shape.push_back(xs[i]);
+          else if (n.keepdims) n.shape.push_back(1);
+        }
+        const Json* rt = attrs->find("reduction_type");
+        if (op == "reduce_sum" && rt && rt->is_str() && rt->s == "any") n.op = "reduce_any";
+        n.dclass = n.op == "reduce_any" ? DC_BOOL : nodes_[in[0]].dclass;
+        if (op == "reduce_sum") {
+          const Json* sc = attrs->find("scale");
+          if (sc && !sc->is_null()) {
+            double f;
+            if (sc->is_str() && sc->s == "num_elements" && !bind_.count("num_elements") && bind_.count("group_size") && bind_.count("HW"))
+              f = bind_.at("group_size") * bind_.at("HW");
+            else f = number_attr(*sc, where + ".scale");
+            if (n.op == "reduce_any") {  // np.any(...) * factor is a float
+              int rid = add(n);
+              n = Node();
+              n.op = "mul"; n.in = {rid, add_const(f)}; n.shape = nodes_[rid].shape; n.dclass = DC_FLOAT; n.name = out;
+              nodes_[rid].name.clear();
+            } else {
+              n.scale = f;
+              n.dclass = DC_FLOAT;
+            }
+          }
+        }
+        id = add(n);
+      } else if (op == "softmax") {
+        if (in.size() != 1) throw Invalid(where + " requires 1 input");
+        Node n; n.name = out; n.op = op; n.in = in; n.shape = nodes_[in[0]].shape; n.dclass = DC_FLOAT;
+        const Json* ax = attrs->find("axis");
+        n.axis = ax && ax->is_num() ? (int)ax->as_int() : -1;
+        if (n.axis < 0) n.axis += (int)n.shape.size();
+        if (n.axis < 0 || n.axis >= (int)n.shape.size()) throw Invalid(where + ": axis out of range");
+        id = add(n);
+      } else if (op == "matmul") {
+        if (in.size() != 2) throw Invalid(where + " requires 2 inputs (A, B)");
+        Node n; n.op = op; n.in = in; n.dclass = DC_FLOAT;
+        auto flag = [&](const char* k) { const Json* j = attrs->find(k); return j && ((j->type == Json::Bool && j->b) || (j->is_num() && j->num != 0)); };
+        n.ta = flag("transpose_a");
+        n.tb = flag("transpose_b");
+        Shape a = nodes_[in[0]].shape, b = nodes_[in[1]].shape;
+        if (a.size() != 2 || b.size() != 2) throw Unsupported(where + ": only rank-2 operands are covered (got " + shape_str(a) + " x " + shape_str(b) + ")");
+        if (n.ta) std::swap(a[0], a[1]);
+        if (n.tb) std::swap(b[0], b[1]);
+        if (a[1] != b[0]) throw Invalid(where + ": inner extents differ: " + shape_str(a) + " x " + shape_str(b));
+        n.shape = {a[0], b[1]};
+        const Json* ep = attrs->find("epilogue");
+        if (ep && !ep->is_null() && !(ep->is_str() && ep->s.empty()) && !(ep->is_obj() && ep->obj.empty())) {
+          const int mm = add(n);
+          const int e = build_epilogue(*ep, mm);
+          if (nodes_[e].name.empty()) { nodes_[e].name = out; by_name_[out] = e; id = e; }
+          else {  // the epilogue is just another named value: alias it
+            Node al; al.op = "identity"; al.in = {e}; al.shape = nodes_[e].shape; al.dclass = nodes_[e].dclass; al.name = out;
+            id = add(al);
+          }
+        } else {
+          n.name = out;
+          id = add(n);
+        }
+      } else {
+        throw Unsupported("op '" + op + "' is not covered by the B200 kernels (name=" + plan_->kernel_name + ")");
+      }
+      // declared dtype of the produced tensor, if any
+      auto d = decl_.find(out);
+      if (d != decl_.end()) {
+        const Json* dt = d->second.find("dtype");
+        if (dt && dt->is_str()) nodes_[by_name_[out]].decl_dtype = dtype_code(dt->s);
+      }
+    }
+    const Json* outs = intent_.find("outputs");
+    if (outs && outs->is_arr()) for (auto& j : outs->arr) if (j.is_str()) outputs_.push_back(j.s);
+    if (outputs_.empty()) outputs_.push_back(ops->arr.back().find("output")->s);
+    for (auto& o : outputs_) {
+      if (!by_name_.count(o)) throw Invalid("output '" + o + "' is never produced");
+      if (!decl_.count(o)) throw Invalid("outputs entry not found in tensors: " + o);
+    }
+    // argument list: external inputs in first-use order, then outputs
+    for (int id : inputs_) {
+      Buffer b; b.is_arg = true; b.arg_index = (int)plan_->arg_names.size(); b.dtype = nodes_[id].decl_dtype; b.name = nodes_[id].name;
+      b.bytes = (size_t)numel(nodes_[id].shape) * dtype_size(b.dtype);
+      plan_->buffers.push_back(b);
+      plan_->arg_names.push_back(nodes_[id].name);
+      nodes_[id].repr = Node::STRIDED;
+      nodes_[id].view.buffer = (int)plan_->buffers.size() - 1;
+      nodes_[id].view.shape = nodes_[id].shape;
+      nodes_[id].view.strides = contiguous_strides(nodes_[id].shape);
+    }
+    for (auto& o : outputs_) {
+      const int id = by_name_[o];
+      Buffer b; b.is_arg = true; b.arg_index = (int)plan_->arg_names.size(); b.name = o;
+      b.dtype = nodes_[id].decl_dtype >= 0 ? nodes_[id].decl_dtype : storage_of_class(nodes_[id].dclass);
+      b.bytes = (size_t)numel(nodes_[id].shape) * dtype_size(b.dtype);
+      plan_->buffers.push_back(b);
+      out_buffer_[o] = (int)plan_->buffers.size() - 1;
+      plan_->arg_names.push_back(o);
+      plan_->output_names.push_back(o);
+    }
+  }
+  std::map<std::string, int> out_buffer_;
+
+  // =============================== helpers shared by B and C ================================
+  int skip_views(int id) const {
+    while (kViews.count(nodes_[id].op) && nodes_[id].op != "transpose") id = nodes_[id].in[0];
+    return id;
+  }
+  int skip_reshapes(int id) const {
+    while (nodes_[id].op == "reshape" || nodes_[id].op == "identity" || nodes_[id].op == "layout_cast") id = nodes_[id].in[0];
+    return id;
+  }
+  bool const_value(int id, double& v) const {
+    id = skip_views(id);
+    if (nodes_[id].op != "const") return false;
+    v = nodes_[id].cval;
+    return true;
+  }
+  bool is_input(int id) const { return nodes_[id].op == "input"; }
+
+  // strides of `id` (which must bottom out at an external input through view ops only)
+  // expressed over id's own shape; false if it is not a pure view of an input
+  bool input_view(int id, View& v) const {
+    const Node& n = nodes_[id];
+    if (n.op == "input") { v = n.view; return true; }
+    if (!kViews.count(n.op)) return false;
+    View src;
+    if (!input_view(n.in[0], src)) return false;
+    return apply_view(n, src, v);
+  }
+  bool apply_view(const Node& n, const View& src, View& v) const {
+    v.buffer = src.buffer;
+    v.offset = src.offset;
+    v.shape = n.shape;
+    if (n.op == "identity" || n.op == "layout_cast") { v.strides = src.strides; return true; }
+    if (n.op == "reshape") return reshape_view(src.shape, src.strides, n.shape, v.strides);
+    if (n.op == "transpose") {
+      v.strides.resize(n.shape.size());
+      for (size_t i = 0; i < n.axes.size(); ++i) v.strides[i] = src.strides[n.axes[i]];
+      return true;
+    }
+    if (n.op == "broadcast_in_dim") {
+      Shape staged(n.shape.size(), 1), st;
+      for (size_t i = 0; i < n.axes.size(); ++i)
+        if (i < src.shape.size()) staged[n.axes[i]] = src.shape[i];
+      if (!reshape_view(src.shape, src.strides, staged, st)) return false;
+      v.strides.resize(n.shape.size());
+      for (size_t d = 0; d < n.shape.size(); ++d) {
+        if (staged[d] == n.shape[d]) v.strides[d] = staged[d] == 1 ? 0 : st[d];
+        else if (staged[d] == 1) v.strides[d] = 0;
+        else throw Invalid("broadcast_in_dim: cannot broadcast " + shape_str(staged) + " to " + shape_str(n.shape));
+      }
+      return true;
+    }
+    return false;
+  }
+  // strides of a view `v` right-aligned and broadcast onto `target`
+  static bool broadcast_strides(const View& v, const Shape& target, Shape& out) {
+    out.assign(target.size(), 0);
+    if (v.shape.size() > target.size()) return false;
+    const size_t lead = target.size() - v.shape.size();
+    for (size_t i = 0; i < v.shape.size(); ++i) {
+      if (v.shape[i] == target[lead + i]) out[lead + i] = v.shape[i] == 1 ? 0 : v.strides[i];
+      else if (v.shape[i] == 1) out[lead + i] = 0;
+      else return false;
+    }
+    return true;
+  }
+
+  int new_workspace_buffer(int dtype, int64_t elements, const std::string& name) {
+    Buffer b;
+    b.dtype = dtype;
+    b.bytes = (size_t)elements * dtype_size(dtype);
+    b.ws_offset = plan_->workspace_bytes;
+    b.name = name;
+    plan_->workspace_bytes += (b.bytes + 255) & ~(size_t)255;
+    plan_->buffers.push_back(b);
+    return (int)plan_->buffers.size() - 1;
+  }
+  // where a non-elementwise op writes its result: straight into the output argument when the
+  // value is a declared graph output, else into the workspace
+  int result_buffer(int id, int dtype_if_temp) {
+    const Node& n = nodes_[id];
+    auto it = out_buffer_.find(n.name);
+    if (!n.name.empty() && it != out_buffer_.end() && !out_written_.count(n.name)) {
+      out_written_.insert(n.name);
+      return it->second;
+    }
+    return new_workspace_buffer(dtype_if_temp, numel(n.shape), n.name);
+  }
+  std::set<std::string> out_written_;
+  void set_strided(int id, int buffer) {
+    Node& n = nodes_[id];
+    n.repr = Node::STRIDED;
+    n.view = View();
+    n.view.buffer = buffer;
+    n.view.shape = n.shape;
+    n.view.strides = contiguous_strides(n.shape);
+  }
+
+  // =============================== phase B: fused patterns ==================================
+  static bool close(double a, double b) { return std::fabs(a - b) <= 1e-6 * std::max(1.0, std::fabs(b)); }
+
+  // `id` == mean over `axes`-trailing elements of Z: div(sum, L) | mul(sum, 1/L) | sum{scale 1/L}
+  bool match_mean(int id, int& z, int& red, int64_t& L) const {
+    id = skip_views(id);
+    const Node& n = nodes_[id];
+    auto sum_of = [&](int s, double factor) {
+      s = skip_views(s);
+      const Node& r = nodes_[s];
+      if (r.op != "reduce_sum") return false;
+      const Shape& xs = nodes_[r.in[0]].shape;
+      int64_t l = 1;
+      for (int a : r.axes) l *= xs[a];
+      // trailing, adjacent axes only
+      for (size_t i = 0; i < r.axes.size(); ++i)
+        if (r.axes[i] != (int)xs.size() - (int)r.axes.size() + (int)i) return false;
+      if (l <= 0 || !close(r.scale * factor * (double)l, 1.0)) return false;
+      z = r.in[0]; red = s; L = l;
+      return true;
+    };
+    double c;
+    if (n.op == "reduce_sum") return sum_of(id, 1.0);
+    if (n.op == "div" && const_value(n.in[1], c) && c != 0) return sum_of(n.in[0], 1.0 / c);
+    if (n.op == "mul") {
+      if (const_value(n.in[1], c)) return sum_of(n.in[0], c);
+      if (const_value(n.in[0], c)) return sum_of(n.in[1], c);
+    }
+    return false;
+  }
+
+  // is `id` (used as an operand against a full tensor of shape `full`, rows x L) a per-row
+  // scalar, i.e. does its right-aligned broadcast have contiguous row strides and stride 0
+  // along the reduced trailing elements?
+  bool per_row_operand(int id, int base, const Shape& full, int64_t L) const {
+    // walk the view chain from id down to base, composing views over base's own shape
+    std::vector<int> chain;
+    int cur = id;
+    while (cur != base) {
+      if (!kViews.count(nodes_[cur].op) || nodes_[cur].op == "transpose") return false;
+      chain.push_back(cur);
+      cur = nodes_[cur].in[0];
+    }
+    View v;
+    v.shape = nodes_[base].shape;
+    v.strides = contiguous_strides(v.shape);
+    for (auto it = chain.rbegin(); it != chain.rend(); ++it) {
+      View nv;
+      if (!apply_view(nodes_[*it], v, nv)) return false;
+      v = nv;
+    }
+    Shape st;
+    if (!broadcast_strides(v, full, st)) return false;
+    // linearise: element (row r, col j) must read base element r
+    int64_t inner = 1;
+    int d = (int)full.size() - 1;
+    for (; d >= 0 && inner < L; --d) {
+      if (full[d] != 1 && st[d] != 0) return false;
+      inner *= full[d];
+    }
+    if (inner != L) return false;
+    int64_t acc = 1;
+    for (; d >= 0; --d) {
+      if (full[d] != 1 && st[d] != acc) return false;
+      acc *= full[d];
+    }
+    return acc == numel(nodes_[base].shape);
+  }
+
+  // affine operand W used against a full tensor: widx = (linear / inner) % period
+  bool affine_operand(int id, const Shape& full, int& input_id, int64_t& inner, int64_t& period) const {
+    View v;
+    if (!input_view(id, v)) return false;
+    input_id = -1;
+    for (int i : inputs_) if (nodes_[i].view.buffer == v.buffer) input_id = i;
+    if (input_id < 0 || v.offset != 0) return false;
+    Shape st;
+    if (!broadcast_strides(v, full, st)) return false;
+    period = numel(nodes_[input_id].shape);
+    inner = 1;
+    int d = (int)full.size() - 1;
+    for (; d >= 0 && (full[d] == 1 || st[d] == 0); --d) inner *= full[d];
+    int64_t acc = 1;
+    for (; d >= 0 && acc < period; --d) {
+      if (full[d] != 1 && st[d] != acc) return false;
+      acc *= full[d];
+    }
+    if (acc != period) return false;
+    for (; d >= 0; --d)
+      if (full[d] != 1 && st[d] != 0) return false;
+    return true;
+  }
+
+  bool all_outputs_in(const std::map<std::string, int>& covered) const {
+    for (auto& o : outputs_) if (!covered.count(o)) return false;
+    return true;
+  }
+  int float_dtype_of_input(int id) const {
+    const int dt = nodes_[id].decl_dtype;
+    return (dt == IB200_F32 || dt == IB200_BF16 || dt == IB200_F16) ? dt : -1;
+  }
+
+  bool match_fused() { return match_softmax() || match_norm() || match_gemm() || match_any(); }
+
+  bool match_any() {
+    if (outputs_.size() != 1) return false;
+    const int out = by_name_[outputs_[0]];
+    const Node& r = nodes_[out];
+    if (r.op != "reduce_any") return false;
+    int x = skip_reshapes(r.in[0]);
+    const Node& c = nodes_[x];
+    if (c.op == "ne") {
+      double z;
+      if (const_value(c.in[1], z) && z == 0.0) x = skip_reshapes(c.in[0]);
+      else if (const_value(c.in[0], z) && z == 0.0) x = skip_reshapes(c.in[1]);
+      else return false;
+      if (nodes_[x].shape != nodes_[r.in[0]].shape && numel(nodes_[x].shape) != numel(nodes_[r.in[0]].shape)) return false;
+    }
+    if (!is_input(x) || numel(nodes_[x].shape) != numel(nodes_[r.in[0]].shape)) return false;
+    const int xd = nodes_[x].decl_dtype;
+    if (!(xd == IB200_F32 || xd == IB200_BF16 || xd == IB200_F16 || xd == IB200_BOOL)) return false;
+    const Shape& xs = nodes_[r.in[0]].shape;
+    if (r.axes.empty()) return false;
+    for (size_t i = 1; i < r.axes.size(); ++i) if (r.axes[i] != r.axes[i - 1] + 1) return false;
+    Step s;
+    s.kind = Step::REDUCE;
+    s.label = "reduce_any";
+    s.reduce_kind = IB200_REDUCE_ANY;
+    s.d[0] = s.d[1] = s.d[2] = 1;
+    for (int i = 0; i < (int)xs.size(); ++i) (i < r.axes.front() ? s.d[0] : i > r.axes.back() ? s.d[2] : s.d[1]) *= xs[i];
+    s.in[0] = nodes_[x].view.buffer;
+    s.out[0] = out_buffer_[outputs_[0]];
+    s.dtype = xd;
+    s.dtype2 = plan_->buffers[s.out[0]].dtype;
+    if (s.dtype2 != IB200_BOOL) return false;
+    plan_->steps.push_back(s);
+    return true;
+  }
+
+  bool match_softmax() {
+    // locate the main output: softmax(X) or div(E, S)
+    for (auto& oname : outputs_) {
+      const int out = skip_reshapes(by_name_[oname]);
+      const Node& y = nodes_[out];
+      int x = -1, rmax = -1, rsum = -1;
+      if (y.op == "softmax") {
+        x = skip_reshapes(y.in[0]);
+        if (y.axis != (int)y.shape.size() - 1) continue;
+      } else if (y.op == "div") {
+        const int e = skip_views(y.in[0]);
+        const Node& en = nodes_[e];
+        if (en.op != "exp") continue;
+        const int sub = skip_views(en.in[0]);
+        if (nodes_[sub].op != "sub") continue;
+        x = skip_reshapes(nodes_[sub].in[0]);
+        rmax = skip_views(nodes_[sub].in[1]);
+        rsum = skip_views(y.in[1]);
+        const Node &mx = nodes_[rmax], &sm = nodes_[rsum];
+        if (mx.op != "reduce_max" || sm.op != "reduce_sum" || sm.scale != 1.0) continue;
+        if (skip_reshapes(mx.in[0]) != x || skip_views(sm.in[0]) != e) continue;
+        const int rank = (int)nodes_[mx.in[0]].shape.size();
+        if (mx.axes != std::vector<int>{rank - 1} || sm.axes != std::vector<int>{(int)nodes_[sm.in[0]].shape.size() - 1}) continue;
+        const int64_t L = nodes_[mx.in[0]].shape.back();
+        if (nodes_[e].shape.empty() || nodes_[e].shape.back() != L || y.shape != nodes_[e].shape) continue;
+        if (!per_row_operand(nodes_[sub].in[1], rmax, nodes_[sub].shape, L)) continue;
+        if (!per_row_operand(y.in[1], rsum, y.shape, L)) continue;
+      } else {
+        continue;
+      }
+      if (x < 0 || !is_input(x) || float_dtype_of_input(x) < 0) continue;
+      if (numel(nodes_[x].shape) != numel(y.shape) || y.shape.empty()) continue;
+      std::map<std::string, int> covered;
+      covered[oname] = 0;
+      Step s;
+      s.kind = Step::SOFTMAX;
+      s.label = "softmax";
+      s.d[1] = y.shape.back();
+      s.d[0] = s.d[1] ? numel(y.shape) / s.d[1] : 0;
+      s.in[0] = nodes_[x].view.buffer;
+      s.out[0] = out_buffer_[oname];
+      s.dtype = nodes_[x].decl_dtype;
+      if (plan_->buffers[s.out[0]].dtype != s.dtype) continue;
+      for (auto& other : outputs_) {
+        if (other == oname) continue;
+        const int o = skip_reshapes(by_name_[other]);
+        const int buf = out_buffer_[other];
+        if (plan_->buffers[buf].dtype != IB200_F32) continue;
+        if (rmax >= 0 && o == rmax) { s.out[1] = buf; covered[other] = 1; }
+        else if (rsum >= 0 && o == rsum) { s.out[2] = buf; covered[other] = 2; }
+      }
+      if (!all_outputs_in(covered)) continue;
+      plan_->steps.push_back(s);
+      return true;
+    }
+    return false;
+  }
+
+  bool match_norm() {
+    for (auto& oname : outputs_) {
+      int y = skip_reshapes(by_name_[oname]);
+      int w = -1, b = -1;
+      // Y = XH*W + B | XH*W | XH + B | XH
+      auto is_xhat = [&](int id, int& d, int& rs) {
+        id = skip_reshapes(id);
+        const Node& n = nodes_[id];
+        if (n.op != "mul") return false;
+        for (int k = 0; k < 2; ++k) {
+          const int cand_d = skip_reshapes(n.in[k]), cand_rs = skip_views(n.in[1 - k]);
+          if (nodes_[cand_d].op == "sub" && nodes_[cand_rs].op == "rsqrt") { d = cand_d; rs = cand_rs; xh_rs_operand_ = n.in[1 - k]; xh_node_ = id; return true; }
+        }
+        return false;
+      };
+      int d = -1, rs = -1, xh = -1;
+      Shape w_full;
+      {
+        const Node& n = nodes_[y];
+        int scaled = y;
+        if (n.op == "add") {
+          for (int k = 0; k < 2; ++k) {
+            View tmp;
+            if (input_view(n.in[k], tmp) && !input_view(n.in[1 - k], tmp)) { b = n.in[k]; scaled = skip_reshapes(n.in[1 - k]); break; }
+          }
+          if (b < 0) continue;
+        }
+        const Node& m = nodes_[scaled];
+        if (is_xhat(scaled, d, rs)) xh = scaled;
+        else if (m.op == "mul") {
+          for (int k = 0; k < 2; ++k) {
+            View tmp;
+            if (input_view(m.in[k], tmp) && is_xhat(m.in[1 - k], d, rs)) { w = m.in[k]; w_full = m.shape; xh = skip_reshapes(m.in[1 - k]); break; }
+          }
+        }
+        if (xh < 0) continue;
+      }
+      // D = X - mean(X)
+      const Node& dn = nodes_[d];
+      const int x = skip_reshapes(dn.in[0]);
+      if (!is_input(x) || float_dtype_of_input(x) < 0) continue;
+      int z1, red1, z2, red2;
+      int64_t L1, L2;
+      if (!match_mean(dn.in[1], z1, red1, L1) || skip_reshapes(z1) != x) continue;
+      const int mu = skip_views(dn.in[1]);
+      // RS = rsqrt(mean(D*D) + eps)
+      const Node& rn = nodes_[rs];
+      const int ve = skip_views(rn.in[0]);
+      if (nodes_[ve].op != "add") continue;
+      double eps = 0;
+      int var = -1;
+      if (const_value(nodes_[ve].in[1], eps)) var = nodes_[ve].in[0];
+      else if (const_value(nodes_[ve].in[0], eps)) var = nodes_[ve].in[1];
+      else continue;
+      if (!match_mean(var, z2, red2, L2) || L2 != L1) continue;
+      const int sq = skip_reshapes(z2);
+      if (nodes_[sq].op != "mul" || skip_reshapes(nodes_[sq].in[0]) != d || skip_reshapes(nodes_[sq].in[1]) != d) continue;
+      const int64_t L = L1, total = numel(nodes_[x].shape);
+      if (L <= 0 || total % L != 0 || numel(dn.shape) != total || numel(nodes_[y].shape) != total) continue;
+      // the mean and rstd operands must broadcast per row
+      if (!per_row_operand(dn.in[1], mu, dn.shape, L)) continue;
+      if (!per_row_operand(xh_rs_operand_, rs, nodes_[xh_node_].shape, L)) continue;
+      // row-major views only between X, D, XH and Y (no transposes): guaranteed by skip_reshapes
+      int w_in = -1, b_in = -1;
+      int64_t inner = 1, period = 1, inner2 = 1, period2 = 1;
+      if (w >= 0 && !affine_operand(w, w_full, w_in, inner, period)) continue;
+      if (b >= 0 && !affine_operand(b, nodes_[y].shape, b_in, inner2, period2)) continue;
+      if (w >= 0 && b >= 0 && (inner != inner2 || period != period2)) continue;
+      if (w < 0 && b >= 0) { inner = inner2; period = period2; }
+      const int wd = w_in >= 0 ? nodes_[w_in].decl_dtype : b_in >= 0 ? nodes_[b_in].decl_dtype : nodes_[x].decl_dtype;
+      if (w_in >= 0 && b_in >= 0 && nodes_[w_in].decl_dtype != nodes_[b_in].decl_dtype) continue;
+      if (!(wd == nodes_[x].decl_dtype || wd == IB200_F32)) continue;
+
+      std::map<std::string, int> covered;
+      covered[oname] = 0;
+      Step s;
+      s.kind = Step::NORM;
+      s.label = (inner == 1 && period == L) || (w < 0 && b < 0) ? "layernorm" : "groupnorm";
+      s.d[0] = total / L;
+      s.d[1] = L;
+      s.aff_inner = inner;
+      s.aff_period = period;
+      s.eps = (float)eps;
+      s.in[0] = nodes_[x].view.buffer;
+      s.in[1] = w_in >= 0 ? nodes_[w_in].view.buffer : -1;
+      s.in[2] = b_in >= 0 ? nodes_[b_in].view.buffer : -1;
+      s.out[0] = out_buffer_[oname];
+      s.dtype = nodes_[x].decl_dtype;
+      s.dtype2 = wd;
+      if (plan_->buffers[s.out[0]].dtype != s.dtype) continue;
+      for (auto& other : outputs_) {
+        if (other == oname) continue;
+        const int o = skip_reshapes(by_name_[other]);
+        const int buf = out_buffer_[other];
+        if (plan_->buffers[buf].dtype != IB200_F32 || numel(nodes_[by_name_[other]].shape) != s.d[0]) continue;
+        if (o == mu) { s.out[1] = buf; covered[other] = 1; }
+        else if (o == rs) { s.out[2] = buf; covered[other] = 2; }
+      }
+      if (!all_outputs_in(covered)) continue;
+      plan_->steps.push_back(s);
+      return true;
+    }
+    return false;
+  }
+  int xh_rs_operand_ = -1, xh_node_ = -1;
+  bool match_gemm() {
+    if (outputs_.size() != 1) return false;
+    int cur = skip_reshapes(by_name_[outputs_[0]]);
+    int act = IB200_ACT_NONE, bias = -1;
+    if (nodes_[cur].op == "relu") { act = IB200_ACT_RELU; cur = skip_reshapes(nodes_[cur].in[0]); }
+    int mm = -1;
+    if (nodes_[cur].op == "add") {
+      for (int k = 0; k < 2; ++k) {
+        const int c = skip_reshapes(nodes_[cur].in[k]);
+        View tmp;
+        if (nodes_[c].op == "matmul" && input_view(nodes_[cur].in[1 - k], tmp)) { mm = c; bias = nodes_[cur].in[1 - k]; }
+      }
+      if (mm < 0) return false;
+    } else if (nodes_[cur].op == "matmul") {
+      mm = cur;
+    } else {
+      return false;
+    }
+    const Node& m = nodes_[mm];
+    if (m.ta) return false;  // A^T needs a transposition pass: left to the general path
+    const int a = m.in[0], b = m.in[1];
+    if (!is_input(a) || !is_input(b)) return false;
+    const int in_dt = nodes_[a].decl_dtype;
+    if (in_dt != nodes_[b].decl_dtype || !(in_dt == IB200_F32 || in_dt == IB200_BF16)) return false;
+    const int out_buf = out_buffer_[outputs_[0]];
+    const int out_dt = plan_->buffers[out_buf].dtype;
+    if (!(out_dt == IB200_F32 || out_dt == IB200_BF16)) return false;
+    if (numel(nodes_[by_name_[outputs_[0]]].shape) != numel(m.shape)) return false;
+    int bias_in = -1;
+    if (bias >= 0) {
+      int64_t inner, period;
+      if (!affine_operand(bias, m.shape, bias_in, inner, period)) return false;
+      if (inner != 1 || period != m.shape[1]) return false;
+      if (nodes_[bias_in].decl_dtype != out_dt) return false;
+    }
+    Step s;
+    s.kind = Step::GEMM;
+    s.label = std::string("gemm") + (bias >= 0 ? "+bias" : "") + (act ? "+relu" : "");
+    s.d[0] = m.shape[0];
+    s.d[1] = m.shape[1];
+    s.d[2] = m.tb ? nodes_[b].shape[1] : nodes_[b].shape[0];
+    s.in[0] = nodes_[a].view.buffer;
+    s.in[1] = nodes_[b].view.buffer;
+    s.in[2] = bias_in >= 0 ? nodes_[bias_in].view.buffer : -1;
+    s.out[0] = out_buf;
+    s.dtype = in_dt;
+    s.dtype2 = out_dt;
+    s.transpose_b = m.tb;
+    s.act = act;
+    plan_->uses_status = true;
+    plan_->steps.push_back(s);
+    return true;
+  }
+
+  // =============================== phase C: general lowering ================================
+  // number of consumers of each node (ops + graph outputs)
+  void lower_general() {
+    for (size_t id = 0; id < nodes_.size(); ++id) lower_node((int)id);
+    // graph outputs: whatever is not yet in its argument buffer is written by elementwise kernels
+    std::vector<int> pending;
+    for (auto& o : outputs_) {
+      const int id = by_name_[o];
+      const Node& n = nodes_[id];
+      if (n.repr == Node::STRIDED && n.view.buffer == out_buffer_[o] && n.view.contiguous()) continue;
+      pending.push_back(id);
+    }
+    // group by shape so that sibling outputs share one pass over their operands
+    while (!pending.empty()) {
+      std::vector<int> group = {pending[0]};
+      for (size_t i = 1; i < pending.size() && group.size() < (size_t)kEwMaxOutputs; ++i)
+        if (nodes_[pending[i]].shape == nodes_[pending[0]].shape) group.push_back(pending[i]);
+      std::vector<int> bufs;
+      for (int id : group) bufs.push_back(out_buffer_[nodes_[id].name]);
+      if (!emit_elementwise(group, bufs, /*may_fail=*/group.size() > 1)) {
+        group.resize(1);
+        bufs.resize(1);
+        emit_elementwise(group, bufs, false);
+      }
+      for (int id : group) pending.erase(std::find(pending.begin(), pending.end(), id));
+    }
+  }
+
+  void lower_node(int id) {
+    Node& n = nodes_[id];
+    if (n.repr != Node::NONE) return;
+    const std::string& op = n.op;
+    if (op == "const") { n.repr = Node::CONSTANT; return; }
+    if (op == "iota") { n.repr = Node::IOTA; return; }
+    if (is_elementwise(op)) { n.repr = Node::EXPR; return; }
+    if (kViews.count(op)) {
+      Node& src = nodes_[n.in[0]];
+      if (src.repr == Node::CONSTANT) { n.repr = Node::CONSTANT; n.cval = src.cval; return; }
+      if (src.repr == Node::EXPR && (op == "identity" || op == "layout_cast")) { n.repr = Node::EXPR; n.op = "identity"; return; }
+      if (src.repr != Node::STRIDED) materialise(n.in[0]);
+      View v;
+      if (!apply_view(n, nodes_[n.in[0]].view, v)) {  // e.g. reshape of a transposed / broadcast view
+        materialise_contiguous(n.in[0]);
+        if (!apply_view(n, nodes_[n.in[0]].view, v)) throw Unsupported(op + ": cannot express as a view");
+      }
+      n.repr = Node::STRIDED;
+      n.view = v;
+      return;
+    }
+    if (op == "reduce_sum" || op == "reduce_max" || op == "reduce_any") {
+      const Shape xs = nodes_[n.in[0]].shape;
+      if (n.axes.empty()) {  // nothing to reduce (rank-0 input): the value itself
+        n.repr = Node::EXPR; n.op = op == "reduce_any" ? "cast" : "identity"; n.cast_to = IB200_BOOL;
+        return;
+      }
+      for (size_t i = 1; i < n.axes.size(); ++i)
+        if (n.axes[i] != n.axes[i - 1] + 1) {
+          // non-adjacent axes are fine when everything between them has extent 1
+          for (int a = n.axes[i - 1] + 1; a < n.axes[i]; ++a)
+            if (xs[a] != 1) throw Unsupported(op + " over non-adjacent axes of " + shape_str(xs) + " is not covered");
+        }
+      materialise_contiguous(n.in[0]);
+      const Node& x = nodes_[n.in[0]];
+      const int xdt = plan_->buffers[x.view.buffer].dtype;
+      if (op != "reduce_any" && class_of_dtype(xdt) != DC_FLOAT) throw Unsupported(op + " over a non-float tensor is not covered");
+      Step s;
+      s.kind = Step::REDUCE;
+      s.label = op;
+      s.reduce_kind = op == "reduce_sum" ? IB200_REDUCE_SUM : op == "reduce_max" ? IB200_REDUCE_MAX : IB200_REDUCE_ANY;
+      s.d[0] = s.d[1] = s.d[2] = 1;
+      for (int i = 0; i < (int)xs.size(); ++i) (i < n.axes.front() ? s.d[0] : i > n.axes.back() ? s.d[2] : s.d[1]) *= xs[i];
+      s.scale = (float)n.scale;
+      s.in[0] = x.view.buffer;
+      s.dtype = xdt;
+      const int tmp_dt = op == "reduce_any" ? IB200_BOOL : IB200_F32;
+      s.out[0] = result_buffer(id, tmp_dt);
+      s.dtype2 = plan_->buffers[s.out[0]].dtype;
+      if (op == "reduce_any" ? s.dtype2 != IB200_BOOL : class_of_dtype(s.dtype2) != DC_FLOAT || s.dtype2 == IB200_F64) {
+        // the declared output type needs a conversion pass: reduce into the workspace instead
+        out_written_.erase(n.name);
+        s.out[0] = new_workspace_buffer(tmp_dt, numel(n.shape), n.name);
+        s.dtype2 = tmp_dt;
+      }
+      plan_->steps.push_back(s);
+      set_strided(id, s.out[0]);
+      return;
+    }
+    if (op == "softmax") {
+      if (n.axis != (int)n.shape.size() - 1) {
+        bool trailing_units = true;
+        for (int a = n.axis + 1; a < (int)n.shape.size(); ++a) trailing_units &= n.shape[a] == 1;
+        if (!trailing_units) throw Unsupported("softmax over a non-trailing axis is not covered");
+      }
+      materialise_contiguous(n.in[0]);
+      const Node& x = nodes_[n.in[0]];
+      const int xdt = plan_->buffers[x.view.buffer].dtype;
+      if (!(xdt == IB200_F32 || xdt == IB200_BF16 || xdt == IB200_F16)) throw Unsupported("softmax over a non-float tensor is not covered");
+      Step s;
+      s.kind = Step::SOFTMAX;
+      s.label = "softmax";
+      s.d[1] = n.shape[n.axis];
+      s.d[0] = s.d[1] ? numel(n.shape) / s.d[1] : 0;
+      s.in[0] = x.view.buffer;
+      s.dtype = xdt;
+      s.out[0] = result_buffer(id, xdt);
+      if (plan_->buffers[s.out[0]].dtype != xdt) {
+        out_written_.erase(n.name);
+        s.out[0] = new_workspace_buffer(xdt, numel(n.shape), n.name);
+      }
+      plan_->steps.push_back(s);
+      set_strided(id, s.out[0]);
+      return;
+    }
+    if (op == "matmul") {
+      int a = n.in[0], b = n.in[1];
+      if (n.ta) a = transposed_copy(a);
+      materialise_contiguous(a);
+      materialise_contiguous(b);
+      int adt = plan_->buffers[nodes_[a].view.buffer].dtype, bdt = plan_->buffers[nodes_[b].view.buffer].dtype;
+      if (adt != bdt || !(adt == IB200_F32 || adt == IB200_BF16)) {
+        a = converted_copy(a, IB200_F32);
+        b = converted_copy(b, IB200_F32);
+        adt = IB200_F32;
+      }
+      Step s;
+      s.kind = Step::GEMM;
+      s.label = "gemm";
+      s.d[0] = n.shape[0];
+      s.d[1] = n.shape[1];
+      s.d[2] = n.tb ? nodes_[b].shape[1] : nodes_[b].shape[0];
+      s.in[0] = nodes_[a].view.buffer;
+      s.in[1] = nodes_[b].view.buffer;
+      s.dtype = adt;
+      s.transpose_b = n.tb;
+      s.out[0] = result_buffer(id, IB200_F32);
+      s.dtype2 = plan_->buffers[s.out[0]].dtype;
+      if (!(s.dtype2 == IB200_F32 || s.dtype2 == IB200_BF16)) {
+        out_written_.erase(n.name);
+        s.out[0] = new_workspace_buffer(IB200_F32, numel(n.shape), n.name);
+        s.dtype2 = IB200_F32;
+      }
+      plan_->uses_status = true;
+      plan_->steps.push_back(s);
+      set_strided(id, s.out[0]);
+      return;
+    }
+    if (op == "input") return;
+    throw Unsupported("op '" + op + "' is not covered by the B200 kernels");
+  }
+
+  // make `id` a STRIDED value (any strides)
+  void materialise(int id) {
+    Node& n = nodes_[id];
+    if (n.repr == Node::STRIDED) return;
+    // a value that is also a graph output is computed straight into its argument buffer
+    const int buf = result_buffer(id, storage_of_class(n.dclass));
+    emit_elementwise({id}, {buf}, false);
+  }
+  // make `id` a STRIDED value that is dense row-major at offset 0
+  void materialise_contiguous(int id) {
+    materialise(id);
+    Node& n = nodes_[id];
+    if (n.view.contiguous()) return;
+    const int dt = plan_->buffers[n.view.buffer].dtype;
+    const int buf = new_workspace_buffer(dt, numel(n.shape), n.name + ".dense");
+    if (n.shape.size() == 2 && n.view.offset == 0 && n.view.strides[1] == n.shape[0] && n.view.strides[0] == 1) {
+      Step s;  // a plain 2-D transpose of a dense matrix
+      s.kind = Step::TRANSPOSE;
+      s.label = "transpose2d";
+      s.in[0] = n.view.buffer;
+      s.out[0] = buf;
+      s.d[0] = n.shape[1];
+      s.d[1] = n.shape[0];
+      s.dtype = dt;
+      plan_->steps.push_back(s);
+      set_strided(id, buf);
+    } else {
+      emit_elementwise({id}, {buf}, false);
+    }
+  }
+  int transposed_copy(int id) {
+    Node t;
+    t.op = "transpose";
+    t.in = {id};
+    t.axes = {1, 0};
+    t.shape = {nodes_[id].shape[1], nodes_[id].shape[0]};
+    t.dclass = nodes_[id].dclass;
+    const int tid = add(t);
+    lower_node(tid);
+    return tid;
+  }
+  int converted_copy(int id, int dtype) {
+    materialise(id);
+    if (plan_->buffers[nodes_[id].view.buffer].dtype == dtype && nodes_[id].view.contiguous()) return id;
+    Node c;
+    c.op = "identity";
+    c.in = {id};
+    c.shape = nodes_[id].shape;
+    c.dclass = class_of_dtype(dtype);
+    const int cid = add(c);
+    nodes_[cid].repr = Node::EXPR;
+    const int buf = new_workspace_buffer(dtype, numel(c.shape), "");
+    emit_elementwise({cid}, {buf}, false);
+    return cid;
+  }
+
+  // ---- micro-op code generation ----------------------------------------------------------
+  struct Gen {
+    EwProgram prog{};
+    std::vector<int> in_buf;
+    std::vector<int64_t> in_off;
+    std::map<int, int> leaf_slot;   // node id -> input slot
+    std::map<int, int> value_slot;  // computed node id -> slot
+    std::map<int, int> uses;        // remaining in-kernel uses of computed nodes
+    std::vector<int> free_slots;
+    int acc_holds = -1;
+    bool failed = false;
+  };
+
+  static uint8_t ew_opcode(const Node& n) {
+    static const std::map<std::string, uint8_t> m = {
+        {"add", EW_ADD}, {"sub", EW_SUB}, {"mul", EW_MUL}, {"div", EW_DIV}, {"max", EW_MAX}, {"min", EW_MIN}, {"relu", EW_RELU},
+        {"exp", EW_EXP}, {"rsqrt", EW_RSQRT}, {"abs", EW_ABS}, {"floor", EW_FLOOR}, {"ne", EW_NE}, {"lt", EW_LT}, {"le", EW_LE},
+        {"gt", EW_GT}, {"ge", EW_GE}, {"and", EW_AND}, {"or", EW_OR}, {"not", EW_NOT}, {"where", EW_WHERE}, {"identity", EW_MOV}};
+    if (n.op == "cast") {
+      switch (n.cast_to) {
+        case IB200_BOOL: return EW_TO_BOOL;
+        case IB200_BF16: case IB200_F16: return EW_ROUND_F16;  // the oracle carries bf16 as float16
+        case IB200_F32: case IB200_F64: return EW_MOV;
+        default: return EW_TO_INT;
+      }
+    }
+    return m.at(n.op);
+  }
+
+  // count in-kernel uses of EXPR nodes reachable from `id`
+  void count_uses(int id, Gen& g, std::set<int>& seen) {
+    if (nodes_[id].repr != Node::EXPR) return;
+    g.uses[id]++;
+    if (!seen.insert(id).second) return;
+    for (int c : nodes_[id].in) count_uses(c, g, seen);
+  }
+
+  int alloc_slot(Gen& g) {
+    if (!g.free_slots.empty()) { int s = g.free_slots.back(); g.free_slots.pop_back(); return s; }
+    if (g.prog.n_slots >= kEwMaxSlots) { g.failed = true; return 0; }
+    return g.prog.n_slots++;
+  }
+
+  // operand code for node `id` as seen from a kernel over `root_shape`; emits code if needed
+  uint8_t operand(int id, Gen& g, const Shape& root_shape, float& imm, bool& has_imm, bool force_slot) {
+    Node& n = nodes_[id];
+    if (n.repr == Node::CONSTANT) {
+      if (has_imm && imm != (float)n.cval) {  // one immediate per instruction: stage this one through ACC/slot
+        return stage_constant((float)n.cval, g, force_slot);
+      }
+      imm = (float)n.cval;
+      has_imm = true;
+      return EW_IMM;
+    }
+    if (n.repr == Node::STRIDED || n.repr == Node::IOTA) {
+      auto it = g.leaf_slot.find(id);
+      if (it != g.leaf_slot.end()) return (uint8_t)it->second;
+      return (uint8_t)add_leaf(id, g, root_shape);
+    }
+    if (n.repr != Node::EXPR) throw Unsupported("internal: operand '" + n.name + "' has no representation");
+    auto vs = g.value_slot.find(id);
+    if (vs != g.value_slot.end()) return (uint8_t)vs->second;
+    if (g.acc_holds == id && !force_slot) return EW_ACC;
+    emit_node(id, g, root_shape, force_slot);
+    auto vs2 = g.value_slot.find(id);
+    if (vs2 != g.value_slot.end()) return (uint8_t)vs2->second;
+    return EW_ACC;
+  }
+
+  uint8_t stage_constant(float v, Gen& g, bool force_slot) {
+    if (g.prog.n_instr >= kEwMaxInstr) { g.failed = true; return EW_ACC; }
+    EwInstr& ins = g.prog.instr[g.prog.n_instr++];
+    ins = EwInstr{};
+    ins.op = EW_MOV; ins.a = EW_IMM; ins.b = EW_IMM; ins.c = EW_IMM; ins.imm = v; ins.dst = EW_NODST;
+    g.acc_holds = -1;
+    if (force_slot) { ins.dst = (uint8_t)alloc_slot(g); return ins.dst; }
+    return EW_ACC;
+  }
+
+  int add_leaf(int id, Gen& g, const Shape& root_shape) {
+    const Node& n = nodes_[id];
+    if (g.prog.n_inputs >= kEwMaxInputs) { g.failed = true; return 0; }
+    // inputs occupy the first slots: they must all be registered before temporaries, which
+    // emit_elementwise guarantees by collecting leaves first
+    EwInput& in = g.prog.in[g.prog.n_inputs];
+    in = EwInput{};
+    View v;
+    if (n.repr == Node::IOTA) {
+      in.kind = EW_IN_IOTA;
+      v.shape = n.shape;
+      v.strides.assign(n.shape.size(), 0);
+      v.strides[n.axis] = 1;
+      in.dtype = IB200_I32;
+      g.in_buf.push_back(-1);
+      g.in_off.push_back(0);
+    } else {
+      in.kind = EW_IN_TENSOR;
+      v = n.view;
+      in.dtype = plan_->buffers[v.buffer].dtype;
+      g.in_buf.push_back(v.buffer);
+      g.in_off.push_back(v.offset);
+    }
+    Shape st;
+    if (!broadcast_strides(v, root_shape, st)) throw Invalid("cannot broadcast " + shape_str(v.shape) + " onto " + shape_str(root_shape));
+    leaf_strides_.push_back(st);
+    const int slot = g.prog.n_inputs++;
+    g.leaf_slot[id] = slot;
+    return slot;
+  }
+  std::vector<Shape> leaf_strides_;
+
+  void emit_node(int id, Gen& g, const Shape& root_shape, bool force_slot) {
+    Node& n = nodes_[id];
+    // decide evaluation order: operands that still need instructions go first; all but the
+    // last of them must be parked in slots because the next computation clobbers ACC
+    std::vector<int> pending;
+    for (int c : n.in)
+      if (nodes_[c].repr == Node::EXPR && !g.value_slot.count(c) && g.acc_holds != c) pending.push_back(c);
+    std::sort(pending.begin(), pending.end());
+    pending.erase(std::unique(pending.begin(), pending.end()), pending.end());
+    for (size_t i = 0; i < pending.size(); ++i) {
+      const bool park = i + 1 < pending.size();
+      emit_node(pending[i], g, root_shape, park);
+      if (g.failed) return;
+    }
+    if (g.prog.n_instr >= kEwMaxInstr) { g.failed = true; return; }
+    EwInstr ins{};
+    ins.op = ew_opcode(n);
+    ins.dst = EW_NODST;
+    float imm = 0.0f;
+    bool has_imm = false;
+    uint8_t codes[3] = {EW_ACC, EW_ACC, EW_ACC};
+    // a constant that cannot ride as the immediate is staged through a slot *before* the
+    // other operands are resolved, so that ACC still holds what they expect
+    int n_const = 0;
+    for (size_t k = 0; k < n.in.size() && k < 3; ++k) n_const += nodes_[n.in[k]].repr == Node::CONSTANT;
+    std::map<size_t, uint8_t> staged;
+    if (n_const > 1) {
+      bool first = true;
+      for (size_t k = 0; k < n.in.size() && k < 3; ++k) {
+        if (nodes_[n.in[k]].repr != Node::CONSTANT) continue;
+        if (first) { first = false; continue; }
+        if ((float)nodes_[n.in[k]].cval == (float)nodes_[n.in[0]].cval && nodes_[n.in[0]].repr == Node::CONSTANT) continue;
+        // park whatever ACC holds if one of our operands lives there
+        for (int c : n.in)
+          if (g.acc_holds == c && !g.value_slot.count(c)) park_acc(c, g);
+        staged[k] = stage_constant((float)nodes_[n.in[k]].cval, g, true);
+        if (g.failed) return;
+      }
+    }
+    for (size_t k = 0; k < n.in.size() && k < 3; ++k) {
+      if (staged.count(k)) { codes[k] = staged[k]; continue; }
+      codes[k] = operand(n.in[k], g, root_shape, imm, has_imm, false);
+      if (g.failed) return;
+    }
+    ins.a = codes[0];
+    ins.b = n.in.size() > 1 ? codes[1] : codes[0];
+    ins.c = n.in.size() > 2 ? codes[2] : codes[0];
+    ins.imm = imm;
+    // release operand slots whose last use this was
+    for (int c : n.in) {
+      if (nodes_[c].repr != Node::EXPR) continue;
+      if (--g.uses[c] == 0) {
+        auto it = g.value_slot.find(c);
+        if (it != g.value_slot.end()) { g.free_slots.push_back(it->second); g.value_slot.erase(it); }
+      }
+    }
+    for (auto& kv : staged) g.free_slots.push_back(kv.second);
+    if (force_slot || g.uses[id] > 1) {
+      ins.dst = (uint8_t)alloc_slot(g);
+      g.value_slot[id] = ins.dst;
+    }
+    if (g.prog.n_instr >= kEwMaxInstr) { g.failed = true; return; }
+    g.prog.instr[g.prog.n_instr++] = ins;
+    g.acc_holds = id;
+  }
+
+  void park_acc(int id, Gen& g) {
+    if (g.prog.n_instr >= kEwMaxInstr) { g.failed = true; return; }
+    EwInstr& ins = g.prog.instr[g.prog.n_instr++];
+    ins = EwInstr{};
+    ins.op = EW_MOV; ins.a = ins.b = ins.c = EW_ACC; ins.dst = (uint8_t)alloc_slot(g);
+    g.value_slot[id] = ins.dst;
+  }
+
+  void collect_leaves(int id, Gen& g, const Shape& root_shape, std::set<int>& seen) {
+    if (!seen.insert(id).second) return;
+    Node& n = nodes_[id];
+    if (n.repr == Node::NONE) lower_node(id);
+    if (n.repr == Node::STRIDED || n.repr == Node::IOTA) {
+      if (!g.leaf_slot.count(id)) add_leaf(id, g, root_shape);
+      return;
+    }
+    if (n.repr == Node::EXPR)
+      for (int c : n.in) collect_leaves(c, g, root_shape, seen);
+  }
+
+  // One kernel computing `roots` (same shape) into `bufs`.  Returns false (emitting nothing)
+  // when may_fail and the program does not fit; otherwise splits by materialising operands.
+  bool emit_elementwise(const std::vector<int>& roots, const std::vector<int>& bufs, bool may_fail) {
+    const Shape root_shape = nodes_[roots[0]].shape;
+    Gen g;
+    leaf_strides_.clear();
+    std::set<int> seen;
+    for (int r : roots) collect_leaves(r, g, root_shape, seen);
+    g.prog.n_slots = g.prog.n_inputs;
+    std::set<int> seen2;
+    for (int r : roots) { count_uses(r, g, seen2); }
+    // every root but the last must be kept in a slot until the stores
+    for (size_t i = 0; i < roots.size() && !g.failed; ++i) {
+      Node& n = nodes_[roots[i]];
+      EwOutput& o = g.prog.out[g.prog.n_outputs++];
+      o = EwOutput{};
+      o.dtype = plan_->buffers[bufs[i]].dtype;
+      const bool last = i + 1 == roots.size();
+      if (n.repr == Node::EXPR) {
+        float imm; bool has_imm = false;
+        o.src = operand(roots[i], g, root_shape, imm, has_imm, !last);
+        if (o.src == EW_ACC && !last) g.failed = true;
+      } else if (n.repr == Node::CONSTANT) {
+        o.src = stage_constant((float)n.cval, g, !last);
+      } else {
+        o.src = (uint8_t)g.leaf_slot.at(roots[i]);
+      }
+    }
+    if (g.failed) {
+      if (may_fail) return false;
+      if (roots.size() != 1) throw Unsupported("internal: multi-output kernel must be allowed to fail");
+      // too big for one kernel: materialise the root's EXPR operands first, then retry
+      bool progressed = false;
+      for (int c : nodes_[roots[0]].in)
+        if (nodes_[c].repr == Node::EXPR) { materialise(c); progressed = true; }
+      if (!progressed) throw Unsupported("elementwise chain does not fit the micro-op program limits");
+      return emit_elementwise(roots, bufs, false);
+    }
+    // collapse the output dims: drop unit dims, then merge adjacent dims wherever every
+    // operand's strides allow it (the outputs are dense, so they always do)
+    Shape dims = root_shape;
+    std::vector<Shape> strides = leaf_strides_;
+    for (int d = (int)dims.size() - 1; d >= 0; --d)
+      if (dims[d] == 1) { dims.erase(dims.begin() + d); for (auto& st : strides) st.erase(st.begin() + d); }
+    if (dims.empty()) { dims = {1}; for (auto& st : strides) st = {0}; }
+    for (int d = (int)dims.size() - 2; d >= 0; --d) {
+      bool ok = true;
+      for (auto& st : strides) ok &= st[d] == st[d + 1] * dims[d + 1];
+      if (!ok) continue;
+      dims[d] *= dims[d + 1];
+      dims.erase(dims.begin() + d + 1);
+      for (auto& st : strides) { st[d] = st[d + 1]; st.erase(st.begin() + d + 1); }
+    }
+    if ((int)dims.size() > kEwMaxRank) throw Unsupported("elementwise kernel over more than 5 non-mergeable dims");
+    EwProgram& p = g.prog;
+    p.rank = (int)dims.size();
+    p.total = numel(dims);
+    for (int d = 0; d < p.rank; ++d) p.dim[d] = (uint32_t)dims[d];
+    for (int k = 0; k < p.n_inputs; ++k)
+      for (int d = 0; d < p.rank; ++d) p.in[k].stride[d] = strides[k][d];
+    Step s;
+    s.kind = Step::ELEMENTWISE;
+    s.label = "elementwise(" + std::to_string(p.n_instr) + " ops, " + std::to_string(p.n_inputs) + " in, " + std::to_string(p.n_outputs) + " out)";
+    s.ew = p;
+    s.ew_in_buf = g.in_buf;
+    s.ew_in_off = g.in_off;
+    s.ew_out_buf = bufs;
+    plan_->steps.push_back(s);
+    for (size_t i = 0; i < roots.size(); ++i) {
+      set_strided(roots[i], bufs[i]);
+      if (out_buffer_.count(nodes_[roots[i]].name) && out_buffer_[nodes_[roots[i]].name] == bufs[i]) out_written_.insert(nodes_[roots[i]].name);
+    }
+    return true;
+  }
+
+  // =============================== description ==============================================
+  void finish() {
+    if (plan_->uses_status) {
+      plan_->status_offset = plan_->workspace_bytes;
+      plan_->workspace_bytes += 256;
+    }
+    Json d = Json::object();
+    d.set("kernel_name", Json::string(plan_->kernel_name));
+    d.set("cuda_src", Json::string(""));
+    Json io = Json::object(), names = Json::array(), tensors = Json::object();
+    for (auto& a : plan_->arg_names) names.push(Json::string(a));
+    for (size_t i = 0; i < plan_->arg_names.size(); ++i) {
+      const Buffer& b = plan_->buffers[i];
+      Json t = Json::object(), sh = Json::array();
+      t.set("dtype", Json::string(dtype_name(b.dtype)));
+      for (auto v : nodes_[by_name_[b.name]].shape) sh.push(Json::number((double)v));
+      t.set("shape", sh);
+      tensors.set(b.name, t);
+    }
+    io.set("arg_names", names);
+    io.set("tensors", tensors);
+    io.set("scalars", Json::object());
+    d.set("io_spec", io);
+    Json launch = Json::object(), g3 = Json::array(), b3 = Json::array();
+    for (int i = 0; i < 3; ++i) { g3.push(Json::number(i == 0 ? (double)plan_->steps.size() : 1)); b3.push(Json::number(1)); }
+    launch.set("grid", g3);  // informational: grids are chosen by the kernels' launchers
+    launch.set("block", b3);
+    launch.set("shared_mem", Json::number(0));
+    d.set("launch", launch);
+    Json outs = Json::array();
+    for (auto& o : plan_->output_names) outs.push(Json::string(o));
+    d.set("output_names", outs);
+    Json binds = Json::object();
+    for (auto& kv : bind_) binds.set(kv.first, Json::number(kv.second));
+    d.set("bindings", binds);
+    Json steps = Json::array();
+    for (auto& s : plan_->steps) {
+      Json j = Json::object();
+      j.set("kernel", Json::string(s.label));
+      Json ext = Json::array();
+      for (int i = 0; i < 4; ++i) ext.push(Json::number((double)s.d[i]));
+      if (s.kind == Step::ELEMENTWISE) { ext = Json::array(); for (int i = 0; i < s.ew.rank; ++i) ext.push(Json::number((double)s.ew.dim[i])); }
+      j.set("extents", ext);
+      steps.push(j);
+    }
+    d.set("steps", steps);
+    d.set("workspace_bytes", Json::number((double)plan_->workspace_bytes));
+    plan_->description = d;
+  }
+};
+
+void* buffer_ptr(const ib200_plan& p, int id, void* const* args, void* ws) {
+  if (id < 0) return nullptr;
+  const Buffer& b = p.buffers[id];
+  return b.is_arg ? args[b.arg_index] : static_cast<char*>(ws) + b.ws_offset;
+}
+
+int write_out(const std::string& s, char* out, size_t cap) {
+  if (!out || cap < s.size() + 1) return fail(IB200_ERR_BUFFER, "output buffer too small: " + std::to_string(s.size() + 1) + " bytes needed");
+  std::memcpy(out, s.c_str(), s.size() + 1);
+  return IB200_OK;
+}
+
+int create(const char* intent_json, const char* bindings_json, std::unique_ptr<ib200_plan>& out) {
+  try {
+    Json intent = Json::parse(intent_json);
+    Json bindings = bindings_json && *bindings_json ? Json::parse(bindings_json) : Json::object();
+    Planner pl(intent, bindings);
+    out = pl.run();
+    return IB200_OK;
+  } catch (const Unsupported& e) {
+    return fail(IB200_ERR_UNSUPPORTED, e.what());
+  } catch (const std::exception& e) {
+    return fail(IB200_ERR_INVALID, e.what());
+  }
+}
+
+}  // namespace
+}  // namespace ib200
+
+using namespace ib200;
+
+extern "C" {
+
+int ib200_plan_create(const char* intent_json, const char* bindings_json, ib200_plan_t** plan) {
+  if (!plan || !intent_json) return fail(IB200_ERR_INVALID, "plan_create: null argument");
+  std::unique_ptr<ib200_plan> p;
+  if (int rc = create(intent_json, bindings_json, p)) return rc;
+  *plan = p.release();
+  return IB200_OK;
+}
+
+void ib200_plan_destroy(ib200_plan_t* plan) { delete plan; }
+
+int ib200_plan_describe(const ib200_plan_t* plan, char* out, size_t cap) {
+  if (!plan) return fail(IB200_ERR_INVALID, "plan_describe: null plan");
+  return write_out(plan->description.dump(), out, cap);
+}
+
+int ib200_plan_json(const char* intent_json, const char* bindings_json, char* out, size_t cap) {
+  if (!intent_json) return fail(IB200_ERR_INVALID, "plan_json: null intent");
+  std::unique_ptr<ib200_plan> p;
+  if (int rc = create(intent_json, bindings_json, p)) return rc;
+  return write_out(p->description.dump(), out, cap);
+}
+
+int ib200_plan_num_args(const ib200_plan_t* plan) { return plan ? (int)plan->arg_names.size() : 0; }
+size_t ib200_plan_workspace_bytes(const ib200_plan_t* plan) { return plan ? plan->workspace_bytes : 0; }
+int ib200_plan_num_launches(const ib200_plan_t* plan) { return plan ? (int)plan->steps.size() : 0; }
+
+int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!plan) return fail(IB200_ERR_INVALID, "plan_launch: null plan");
+  if (n_args != (int)plan->arg_names.size()) return fail(IB200_ERR_INVALID, "plan_launch: expected " + std::to_string(plan->arg_names.size()) + " arguments");
+  if (plan->workspace_bytes > 0 && (!workspace || workspace_bytes < plan->workspace_bytes))
+    return fail(IB200_ERR_BUFFER, "plan_launch: workspace of " + std::to_string(plan->workspace_bytes) + " bytes needed");
+  if (plan->workspace_bytes > 0 && (reinterpret_cast<uintptr_t>(workspace) & 255u)) return fail(IB200_ERR_INVALID, "plan_launch: workspace must be 256-byte aligned");
+  for (size_t i = 0; i < plan->arg_names.size(); ++i)
+    if (!args[i] && plan->buffers[i].bytes > 0) return fail(IB200_ERR_INVALID, "plan_launch: argument '" + plan->arg_names[i] + "' is null");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int32_t* status = plan->uses_status ? reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + plan->status_offset) : nullptr;
+  for (const Step& st : plan->steps) {
+    int rc = IB200_OK;
+    auto P = [&](int id) { return buffer_ptr(*plan, id, args, workspace); };
+    switch (st.kind) {
+      case Step::REDUCE:
+        rc = launch_reduce(P(st.in[0]), P(st.out[0]), st.dtype, st.dtype2, st.reduce_kind, st.d[0], st.d[1], st.d[2], st.scale, s);
+        break;
+      case Step::SOFTMAX:
+        rc = launch_softmax(P(st.in[0]), P(st.out[0]), static_cast<float*>(P(st.out[1])), static_cast<float*>(P(st.out[2])), st.dtype,
+                            st.d[0], st.d[1], s);
+        break;
+      case Step::NORM:
+        rc = launch_norm_rows(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), static_cast<float*>(P(st.out[1])),
+                              static_cast<float*>(P(st.out[2])), st.dtype, st.dtype2, st.d[0], st.d[1], st.aff_inner, st.aff_period,
+                              st.eps, s);
+        break;
+      case Step::GEMM:
+        rc = launch_gemm(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), st.dtype, st.dtype2, st.d[0], st.d[1], st.d[2],
+                         st.transpose_b, st.act, status, s);
+        break;
+      case Step::TRANSPOSE:
+        rc = launch_transpose2d(P(st.in[0]), P(st.out[0]), dtype_size(st.dtype), st.d[0], st.d[1], s);
+        break;
+      case Step::ELEMENTWISE: {
+        EwProgram prog = st.ew;
+        bool vec = prog.dim[prog.rank - 1] % 4 == 0;
+        for (int k = 0; k < prog.n_inputs; ++k) {
+          EwInput& in = prog.in[k];
+          if (in.kind == EW_IN_TENSOR) {
+            in.ptr = static_cast<const char*>(P(st.ew_in_buf[k])) + st.ew_in_off[k] * dtype_size(in.dtype);
+            bool ok = in.stride[prog.rank - 1] == 1 && aligned16(in.ptr);
+            for (int d = 0; d + 1 < prog.rank; ++d) ok &= in.stride[d] % 4 == 0;
+            in.vec_ok = ok;
+          }
+        }
+        for (int o = 0; o < prog.n_outputs; ++o) {
+          prog.out[o].ptr = P(st.ew_out_buf[o]);
+          vec &= aligned16(prog.out[o].ptr);
+        }
+        prog.vec = vec;
+        rc = launch_elementwise(prog, s);
+        break;
+      }
+    }
+    if (rc != IB200_OK) return rc;
+  }
+  return IB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,269 @@
+"""Parity of the direct C-ABI kernels (through intent_ir_b200.ops, i.e. ctypes) against the
+CPU oracle on the same seeded inputs: bit-exact for boolean results, within the oracle's
+inferred tolerances (verify/tolerances.py figures, written out below) for floating point."""
+
+import numpy as np
+import pytest
+
+from intent_ir_b200.ir import IntentFunction
+from oracle import execute_intent, infer_tolerances
+from oracle.diff import compare_outputs
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _graph(op, attrs, in_shape, out_shape, out_dtype="f32", in_dtype="f32"):
+    return IntentFunction.from_json_dict({
+        "name": f"one_{op}",
+        "tensors": {"x": {"dtype": in_dtype, "shape": list(in_shape), "layout": "row_major"},
+                    "y": {"dtype": out_dtype, "shape": list(out_shape), "layout": "row_major"}},
+        "ops": [{"op": op, "inputs": ["x"], "output": "y", "attrs": attrs}], "outputs": ["y"]})
+
+
+def _agree(got: np.ndarray, want: np.ndarray, atol: float, rtol: float):
+    """The oracle's own comparison (diff_runner.py:357-418).  That comparison rejects any NaN
+    (it tests the non-finite values with ``np.array_equal``, for which NaN != NaN), so NaN
+    positions are first checked to coincide exactly and then neutralised on both sides;
+    infinities still have to match in place and sign."""
+    got, want = np.asarray(got), np.asarray(want)
+    if got.dtype.kind == "f" or want.dtype.kind == "f":
+        gn, wn = np.isnan(got), np.isnan(want)
+        assert np.array_equal(gn, wn), "NaN pattern differs"
+        if gn.any():
+            got, want = np.where(gn, 0, got), np.where(wn, 0, want)
+    d = compare_outputs({"y": want}, {"y": got}, ["y"], {"atol": atol, "rtol": rtol})
+    assert d.ok, (d.summary, d.max_abs_err, d.first_bad_index)
+
+
+def _dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+# ---------------------------------------------------------------- reductions ----------------
+
+def test_reduce_any_baseline_case_bit_exact():
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(0)
+    mask = rng.random((16, 256)) < 0.05
+    x = np.where(mask, rng.standard_normal((16, 256), dtype=np.float32), np.float32(0))
+    x[3] = 0  # an all-zero row
+    want = execute_intent(_graph("reduce_any", {"dims": [1]}, ["M", "N"], ["M"], "bool"), {"x": x})["y"]
+    got = ops.reduce(_dev(x), "any", [1]).cpu().numpy()
+    assert got.dtype == np.bool_ and np.array_equal(got, want)
+
+
+def test_reduce_any_non_finite_and_signed_zero_rows(golden_edges):
+    from intent_ir_b200 import ops
+    x = golden_edges["x"]
+    got = ops.reduce(_dev(x), "any", [1]).cpu().numpy()
+    assert np.array_equal(got, golden_edges["reduce_any"])
+    got = ops.reduce(_dev(x), "max", [1]).cpu().numpy()
+    assert np.array_equal(got, golden_edges["reduce_max"], equal_nan=True)
+
+
+@pytest.mark.parametrize("shape,dims", [
+    ((1, 1), [1]), ((7, 3), [1]), ((5, 17), [1]), ((33, 256), [1]), ((9, 1000), [1]), ((4, 4096), [1]),
+    ((3, 5000), [1]), ((2, 70001), [1]), ((64, 33), [0]), ((6, 40, 9), [1]), ((3, 5, 7, 11), [2, 3]),
+    ((4, 6, 8), [0, 1]), ((5, 6), [0, 1]), ((2049, 2), [0]),
+])
+@pytest.mark.parametrize("kind", ["sum", "max", "any"])
+def test_reduce_matches_oracle(shape, dims, kind):
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(hash((shape, tuple(dims), kind)) % 2**32)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    if kind == "any":
+        x = np.where(rng.random(shape) < 0.002, x, np.float32(0))
+    sym = [f"D{i}" for i in range(len(shape))]
+    out_sym = [s for i, s in enumerate(sym) if i not in dims]
+    want = execute_intent(_graph(f"reduce_{kind}", {"dims": dims}, sym, out_sym, "bool" if kind == "any" else "f32"), {"x": x})["y"]
+    got = ops.reduce(_dev(x), kind, dims).cpu().numpy()
+    assert got.shape == np.asarray(want).shape
+    if kind == "any":
+        assert np.array_equal(got, want)
+    else:
+        _agree(got, want, 1e-3, 1e-3)  # reduce_sum / reduce_max: (1e-3, 1e-3)
+
+
+def test_reduce_sum_scale_and_keepdims():
+    from intent_ir_b200 import ops
+    x = np.random.default_rng(1).standard_normal((12, 50), dtype=np.float32)
+    got = ops.reduce(_dev(x), "sum", [1], keepdims=True, scale=1.0 / 50).cpu().numpy()
+    assert got.shape == (12, 1)
+    _agree(got, x.sum(axis=1, keepdims=True) * (1.0 / 50), 1e-3, 1e-3)
+
+
+def test_reduce_empty_and_errors():
+    from intent_ir_b200 import ops
+    from intent_ir_b200.errors import B200LoweringError, B200RuntimeError
+    assert ops.reduce(torch.empty((0, 8), device="cuda"), "sum", [1]).shape == (0,)
+    got = ops.reduce(torch.empty((4, 0), device="cuda"), "sum", [1]).cpu().numpy()
+    assert np.array_equal(got, np.zeros(4, np.float32))
+    with pytest.raises(B200LoweringError):
+        ops.reduce(torch.zeros((2, 3, 4), device="cuda"), "sum", [0, 2])
+    with pytest.raises(B200RuntimeError):
+        ops.reduce(torch.zeros((2, 3)), "sum", [1])  # host tensor
+
+
+# ---------------------------------------------------------------- softmax -------------------
+
+@pytest.mark.parametrize("shape", [(1, 1), (3, 2), (7, 37), (16, 128), (5, 129), (64, 1000), (9, 1024), (33, 2048),
+                                   (17, 4096), (3, 4100), (4, 8192), (2, 16384), (3, 20000), (2, 3, 50)])
+def test_softmax_matches_oracle(shape):
+    from intent_ir_b200 import ops
+    x = 3 * np.random.default_rng(shape[-1]).standard_normal(shape, dtype=np.float32)
+    sym = [f"D{i}" for i in range(len(shape))]
+    g = _graph("softmax", {"axis": -1}, sym, sym)
+    want = execute_intent(g, {"x": x})["y"]
+    got = ops.softmax(_dev(x)).cpu().numpy()
+    tol = infer_tolerances(g).to_dict()
+    assert tol == {"atol": 1e-4, "rtol": 1e-4}
+    _agree(got, want, **tol)
+    assert np.allclose(got.sum(axis=-1), 1.0, atol=1e-5)
+
+
+def test_softmax_non_finite_rows(golden_edges):
+    from intent_ir_b200 import ops
+    got = ops.softmax(_dev(golden_edges["x"])).cpu().numpy()
+    _agree(got, golden_edges["softmax"], 1e-4, 1e-4)  # compare_outputs demands identical NaN patterns
+
+
+def test_softmax_aux_outputs_and_bf16():
+    from intent_ir_b200 import ops
+    x = 2 * np.random.default_rng(3).standard_normal((11, 300), dtype=np.float32)
+    xd = _dev(x)
+    mx = torch.empty(11, device="cuda")
+    sm = torch.empty(11, device="cuda")
+    ops.softmax(xd, row_max=mx, row_sum=sm)
+    assert np.array_equal(mx.cpu().numpy(), x.max(axis=1))
+    _agree(sm.cpu().numpy(), np.exp(x - x.max(axis=1, keepdims=True)).sum(axis=1), 1e-3, 1e-3)
+    xb = xd.to(torch.bfloat16)
+    got = ops.softmax(xb).float().cpu().numpy()
+    xr = xb.float().cpu().numpy()
+    e = np.exp(xr - xr.max(axis=1, keepdims=True))
+    _agree(got, e / e.sum(axis=1, keepdims=True), 1e-3, 1e-3)  # bf16 visible: floor (1e-3, 1e-3)
+
+
+# ---------------------------------------------------------------- normalisation -------------
+
+def _ln_ref(x, w, b, eps=1e-5):
+    mean = x.mean(axis=-1, keepdims=True, dtype=np.float64)
+    var = ((x - mean) ** 2).mean(axis=-1, keepdims=True)
+    rstd = 1.0 / np.sqrt(var + eps)
+    y = (x - mean) * rstd
+    if w is not None:
+        y = y * w
+    if b is not None:
+        y = y + b
+    return y, mean[..., 0], rstd[..., 0]
+
+
+@pytest.mark.parametrize("shape", [(1, 2), (5, 3), (16, 128), (7, 129), (40, 1000), (9, 1024), (6, 2050), (33, 4096),
+                                   (3, 8192), (2, 16384), (3, 32768), (2, 40004), (2, 131072), (1, 140000)])
+def test_layernorm_matches_oracle_arithmetic(shape):
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(shape[1])
+    x = rng.standard_normal(shape, dtype=np.float32) + np.float32(0.5)
+    w = rng.uniform(0.5, 1.5, shape[1]).astype(np.float32)
+    b = (0.1 * rng.standard_normal(shape[1])).astype(np.float32)
+    y, mean, rstd = ops.layernorm(_dev(x), _dev(w), _dev(b), 1e-5)
+    wy, wm, wr = _ln_ref(x, w, b)
+    _agree(y.cpu().numpy(), wy, 1e-3, 1e-3)  # reduce_sum + rsqrt chain: capped at (1e-3, 1e-3)
+    _agree(mean.cpu().numpy(), wm, 1e-3, 1e-3)
+    _agree(rstd.cpu().numpy(), wr, 1e-3, 1e-3)
+
+
+def test_layernorm_shift_relation_and_non_finite():
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((8, 512), dtype=np.float32)
+    w = rng.standard_normal(512, dtype=np.float32)
+    b = rng.standard_normal(512, dtype=np.float32)
+    y0, m0, r0 = ops.layernorm(_dev(x), _dev(w), _dev(b))
+    y1, m1, r1 = ops.layernorm(_dev(x + np.float32(100.0)), _dev(w), _dev(b))  # a one-pass variance fails this
+    _agree(y1.cpu().numpy(), y0.cpu().numpy(), 1e-3, 1e-3)
+    _agree(m1.cpu().numpy(), m0.cpu().numpy() + 100.0, 1e-3, 1e-3)
+    _agree(r1.cpu().numpy(), r0.cpu().numpy(), 1e-3, 1e-3)
+    x[0, 0] = np.nan
+    x[1, 0], x[1, 1] = np.inf, -np.inf
+    y, m, r = ops.layernorm(_dev(x), _dev(w), _dev(b))
+    with np.errstate(all="ignore"):
+        wy, wm, wr = _ln_ref(x, w, b)
+    _agree(y.cpu().numpy(), wy, 1e-3, 1e-3)
+    _agree(m.cpu().numpy(), wm, 1e-3, 1e-3)
+
+
+@pytest.mark.parametrize("n,c,hw,g", [(1, 2, 2, 2), (2, 8, 16, 4), (3, 6, 5, 3), (2, 32, 49, 8), (2, 64, 256, 8),
+                                      (2, 16, 4096, 2), (1, 8, 4097, 2), (1, 4, 70000, 1)])
+def test_groupnorm_matches_oracle_arithmetic(n, c, hw, g):
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(n * 1000 + c + hw)
+    x = rng.standard_normal((n, c, hw), dtype=np.float32)
+    w = rng.standard_normal(c, dtype=np.float32)
+    b = rng.standard_normal(c, dtype=np.float32)
+    y, mean, rstd = ops.groupnorm(_dev(x), _dev(w), _dev(b), g, 1e-5)
+    x4 = x.reshape(n, g, c // g, hw).astype(np.float64)
+    m = x4.mean(axis=(2, 3), keepdims=True)
+    v = ((x4 - m) ** 2).mean(axis=(2, 3), keepdims=True)
+    r = 1.0 / np.sqrt(v + 1e-5)
+    wy = ((x4 - m) * r).reshape(n, c, hw) * w[None, :, None] + b[None, :, None]
+    _agree(y.cpu().numpy(), wy, 1e-3, 1e-3)
+    _agree(mean.cpu().numpy(), m.reshape(n, g), 1e-3, 1e-3)
+    _agree(rstd.cpu().numpy(), r.reshape(n, g), 1e-3, 1e-3)
+
+
+# ---------------------------------------------------------------- matmul --------------------
+
+def _bf16_round(a):
+    return torch.from_numpy(a).to(torch.bfloat16).float().numpy()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 128), (256, 512, 256), (300, 264, 72), (1, 8, 8),
+                                   (130, 520, 1000), (512, 1024, 4096)])
+@pytest.mark.parametrize("transpose_b", [False, True])
+def test_gemm_tensor_core_path(m, n, k, transpose_b):
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(m + n + k)
+    a = _bf16_round((0.5 * rng.standard_normal((m, k))).astype(np.float32))
+    b = _bf16_round((0.5 * rng.standard_normal((k, n))).astype(np.float32))
+    bias = _bf16_round((0.1 * rng.standard_normal(n)).astype(np.float32))
+    want = np.maximum(a.astype(np.float64) @ b.astype(np.float64) + bias, 0)
+    bd = _dev(np.ascontiguousarray(b.T) if transpose_b else b, torch.bfloat16)
+    got = ops.gemm_bias_act(_dev(a, torch.bfloat16), bd, _dev(bias, torch.bfloat16), "relu", transpose_b)
+    ops.check_device_status()
+    _agree(got.float().cpu().numpy(), want, 2e-2, 2e-2)  # matmul: (2e-2, 2e-2)
+    got32 = ops.gemm_bias_act(_dev(a, torch.bfloat16), bd, None, "none", transpose_b, out_dtype=torch.float32)
+    ops.check_device_status()
+    _agree(got32.cpu().numpy(), a.astype(np.float64) @ b.astype(np.float64), 1e-3, 1e-3)
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 48, 16), (1, 1, 1), (65, 67, 33), (7, 200, 129)])
+def test_gemm_fma_path_f32(m, n, k):
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    got = ops.gemm_bias_act(_dev(a), _dev(b), _dev(bias), "relu")
+    _agree(got.cpu().numpy(), np.maximum(a @ b + bias, 0), 1e-4, 1e-4)
+    got = ops.gemm_bias_act(_dev(a), _dev(np.ascontiguousarray(b.T)), None, "none", transpose_b=True)
+    _agree(got.cpu().numpy(), a @ b, 1e-4, 1e-4)
+
+
+def test_gemm_known_answer_all_ones():
+    from intent_ir_b200 import ops
+    # the reference's tests/test_diff_runner.py: all-ones GEMM + bias + ReLU = K + 1
+    for dt, k in ((torch.float32, 3), (torch.bfloat16, 64)):
+        a = torch.ones((128, k), dtype=dt, device="cuda")
+        b = torch.ones((k, 256), dtype=dt, device="cuda")
+        bias = torch.ones(256, dtype=dt, device="cuda")
+        got = ops.gemm_bias_act(a, b, bias, "relu")
+        ops.check_device_status()
+        assert torch.all(got.float() == k + 1.0)
+
+
+def test_transpose2d():
+    from intent_ir_b200 import ops
+    x = np.random.default_rng(0).standard_normal((70, 33), dtype=np.float32)
+    assert np.array_equal(ops.transpose2d(_dev(x)).cpu().numpy(), x.T)
