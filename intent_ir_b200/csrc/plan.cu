@@ -1117,6 +1117,20 @@ class Planner {
       const int id = by_name_[o];
       const Node& n = nodes_[id];
       if (n.repr == Node::STRIDED && n.view.buffer == out_buffer_[o] && n.view.contiguous()) continue;
+      if (n.repr == Node::STRIDED && n.shape.size() == 2 && n.view.offset == 0 && n.view.strides[0] == 1 &&
+          n.view.strides[1] == n.shape[0] && n.shape[0] > 1 && n.shape[1] > 1 &&
+          plan_->buffers[n.view.buffer].dtype == plan_->buffers[out_buffer_[o]].dtype) {
+        Step s;  // the output is the transpose of a dense matrix: tiled transpose, no gather
+        s.kind = Step::TRANSPOSE;
+        s.label = "transpose2d";
+        s.in[0] = n.view.buffer;
+        s.out[0] = out_buffer_[o];
+        s.d[0] = n.shape[1];
+        s.d[1] = n.shape[0];
+        s.dtype = plan_->buffers[n.view.buffer].dtype;
+        plan_->steps.push_back(s);
+        continue;
+      }
       pending.push_back(id);
     }
     // group by shape so that sibling outputs share one pass over their operands
@@ -1632,6 +1646,7 @@ class Planner {
     }
     d.set("steps", steps);
     d.set("workspace_bytes", Json::number((double)plan_->workspace_bytes));
+    d.set("status_offset", Json::number(plan_->uses_status ? (double)plan_->status_offset : -1.0));
     plan_->description = d;
   }
 };

@@ -1,0 +1,184 @@
+"""Running a lowered plan.
+
+``run_b200_kernel`` mirrors the reference runner
+``run_cuda_kernel(*, kernel_name, cuda_src, io_spec, launch, bindings, inputs_np, output_names,
+extra_cuda_cflags=None) -> Dict[str, np.ndarray]`` (backends/cuda/runtime.py:22-45, body
+frontends/cuda/runtime.py:926-1031): numpy arrays in, host->device copies, one launch of the
+lowered kernel on torch's current stream, synchronise, device->host copies, and the returned
+dict holds the inputs AND the outputs.  Scalar (rank-0) inputs missing from ``inputs_np`` are
+materialised from ``bindings`` as the reference does (:984-992).
+
+``launch_lowered`` is the device-resident variant used for timing: torch CUDA tensors in and
+out, no copies, no synchronisation.
+
+There is no fallback: without a CUDA device, or without the compiled library, these raise.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any, Dict, Iterable, Mapping, Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from .errors import B200LoweringError, B200RuntimeError
+from .lowering import B200LoweredKernel, lookup_plan
+from .ops import TORCH_OF_DTYPE
+
+__all__ = ["run_b200_kernel", "run_lowered", "launch_lowered", "check_plan_status"]
+
+_WORKSPACES: Dict[Any, torch.Tensor] = {}
+
+
+def _require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise B200RuntimeError("torch.cuda is not available; the B200 backend has no CPU path")
+
+
+def _shape_of(spec: Mapping[str, Any], bindings: Mapping[str, Any]):
+    return tuple(int(bindings[str(d)]) if isinstance(d, str) else int(d) for d in spec.get("shape", []))
+
+
+def _workspace(lowered: B200LoweredKernel, device) -> Optional[torch.Tensor]:
+    if lowered.workspace_bytes == 0:
+        return None
+    key = (lowered.io_spec["plan_id"], str(device))
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        # zero-filled once: the tensor-core GEMM's status word lives in it and is only ever
+        # written when a bounded wait expires
+        ws = torch.zeros(lowered.workspace_bytes + 256, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+        if len(_WORKSPACES) > 256:
+            _WORKSPACES.pop(next(iter(_WORKSPACES)))
+    return ws
+
+
+def _aligned_ptr(ws: Optional[torch.Tensor]) -> Optional[int]:
+    if ws is None:
+        return None
+    return (ws.data_ptr() + 255) & ~255
+
+
+def launch_lowered(lowered: B200LoweredKernel, tensors: Mapping[str, torch.Tensor],
+                   outputs: Optional[Mapping[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
+    """Enqueue the plan on the current stream.  ``tensors`` maps input names to contiguous
+    CUDA tensors of the declared dtype and shape; output tensors are allocated unless given.
+    Returns the outputs.  Does not synchronise."""
+    _require_cuda()
+    specs = lowered.io_spec["tensors"]
+    out_set = set(lowered.output_names)
+    args, outs = [], {}
+    device = None
+    for name in lowered.io_spec["arg_names"]:
+        spec = specs[name]
+        dtype = TORCH_OF_DTYPE[spec["dtype"]]
+        shape = tuple(int(d) for d in spec["shape"])
+        if name in out_set:
+            t = outputs.get(name) if outputs else None
+            if t is None:
+                if device is None:
+                    device = torch.device("cuda", torch.cuda.current_device())
+                t = torch.empty(shape, dtype=dtype, device=device)
+            outs[name] = t
+        else:
+            if name not in tensors:
+                raise B200RuntimeError(f"missing input {name} for B200 plan; have keys={sorted(tensors)}")
+            t = tensors[name]
+            device = t.device
+        if not t.is_cuda:
+            raise B200RuntimeError(f"{name} must be a CUDA tensor")
+        if not t.is_contiguous():
+            raise B200RuntimeError(f"{name} must be contiguous")
+        if t.dtype != dtype:
+            raise B200RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+        if tuple(t.shape) != shape:
+            raise B200RuntimeError(f"{name} must have shape {shape}, got {tuple(t.shape)}")
+        args.append(t)
+    arr = (C.c_void_p * len(args))(*[t.data_ptr() or None for t in args])
+    ws = _workspace(lowered, device)
+    rc = _lib.load().ib200_plan_launch(lowered.plan.ptr, arr, len(args), _aligned_ptr(ws), lowered.workspace_bytes,
+                                       torch.cuda.current_stream().cuda_stream)
+    if rc != _lib.OK:
+        raise B200RuntimeError(f"B200 plan launch failed: {_lib.last_error()} (status {rc})")
+    return outs
+
+
+def check_plan_status(lowered: B200LoweredKernel) -> None:
+    """After a synchronise: raise if a bounded device-side wait expired during the plan."""
+    if lowered.status_offset < 0:
+        return
+    for key, ws in list(_WORKSPACES.items()):
+        if key[0] != lowered.io_spec["plan_id"]:
+            continue
+        base = _aligned_ptr(ws) - ws.data_ptr() + lowered.status_offset
+        word = ws[base: base + 4].view(torch.int32)
+        code = int(word.item())
+        if code != 0:
+            word.zero_()
+            raise B200RuntimeError(f"B200 kernel gave up on a bounded device-side wait (site {code})")
+
+
+def _to_device(name: str, arr: np.ndarray, dtype: torch.dtype, device) -> torch.Tensor:
+    a = np.asarray(arr, order="C")  # (ascontiguousarray would turn a 0-d array into shape (1,))
+    if a.dtype == np.float64 and dtype != torch.float64:
+        a = a.astype(np.float32)
+    t = torch.from_numpy(a).to(device=device)
+    if t.dtype != dtype:
+        t = t.to(dtype=dtype)
+    return t.contiguous()
+
+
+def run_lowered(lowered: B200LoweredKernel, inputs_np: Mapping[str, np.ndarray], device: str = "cuda") -> Dict[str, np.ndarray]:
+    _require_cuda()
+    specs = lowered.io_spec["tensors"]
+    out_set = set(lowered.output_names)
+    dev_in: Dict[str, torch.Tensor] = {}
+    try:
+        for name in lowered.io_spec["arg_names"]:
+            if name in out_set:
+                continue
+            spec = specs[name]
+            dtype = TORCH_OF_DTYPE[spec["dtype"]]
+            shape = tuple(int(d) for d in spec["shape"])
+            if name in inputs_np:
+                arr = np.asarray(inputs_np[name])
+                if tuple(arr.shape) != shape:
+                    if arr.size == int(np.prod(shape, dtype=np.int64)) and arr.size <= 1:
+                        arr = arr.reshape(shape)
+                    else:
+                        raise B200RuntimeError(f"input {name} has shape {tuple(arr.shape)}, the plan was lowered for {shape}")
+                dev_in[name] = _to_device(name, arr, dtype, device)
+            elif shape == () and name in lowered.bindings:
+                val = lowered.bindings[name]
+                dev_in[name] = torch.tensor(float(val) if dtype.is_floating_point else int(val), device=device, dtype=dtype)
+            else:
+                raise B200RuntimeError(f"missing input {name} for B200 plan; have keys={sorted(inputs_np.keys())}")
+        outs = launch_lowered(lowered, dev_in)
+        torch.cuda.synchronize()
+    except RuntimeError as e:
+        if isinstance(e, (B200RuntimeError, B200LoweringError)):
+            raise
+        if "out of memory" in str(e).lower():
+            raise B200RuntimeError(f"CUDA OOM during input/output allocation: {e}") from e
+        raise B200RuntimeError(f"B200 plan launch failed: {type(e).__name__}: {e}") from e
+    check_plan_status(lowered)
+    result: Dict[str, np.ndarray] = {k: np.asarray(v) for k, v in inputs_np.items()}
+    for name, t in outs.items():
+        if t.dtype in (torch.bfloat16, torch.float16):
+            t = t.float()  # numpy has no bfloat16; values are exactly representable in float32
+        result[name] = t.detach().cpu().numpy()
+    return result
+
+
+def run_b200_kernel(*, kernel_name: str = "", cuda_src: str = "", io_spec: Mapping[str, Any], launch: Any = None,
+                    bindings: Optional[Mapping[str, Any]] = None, inputs_np: Mapping[str, np.ndarray],
+                    output_names: Optional[Iterable[str]] = None, extra_cuda_cflags: Optional[Iterable[str]] = None,
+                    device: str = "cuda") -> Dict[str, np.ndarray]:
+    """Keyword-compatible with the reference's ``run_cuda_kernel``.  ``io_spec`` must be the
+    one returned by :func:`lower_intent_to_b200_kernel` (it names the plan); ``cuda_src``,
+    ``launch`` and ``extra_cuda_cflags`` are accepted and unused (nothing is compiled)."""
+    lowered = lookup_plan(io_spec)
+    return run_lowered(lowered, inputs_np, device=device)

@@ -241,3 +241,79 @@ def main(ref_root: str) -> None:
 
 if __name__ == "__main__":
     main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("INTENTIR_REF", ""))
+
+
+def validation_cases():
+    """Graphs that the reference's IntentFunction.from_json_dict must accept or reject."""
+    T = lambda shape, dtype="f32", **kw: dict({"dtype": dtype, "shape": shape, "layout": "row_major"}, **kw)  # noqa: E731
+    base = {"name": "g", "tensors": {"x": T(["M", "N"]), "y": T(["M", "N"])},
+            "ops": [{"op": "relu", "inputs": ["x"], "output": "y"}], "outputs": ["y"]}
+
+    def variant(**patch):
+        import copy
+        g = copy.deepcopy(base)
+        for k, v in patch.items():
+            g[k] = v
+        return g
+
+    op = lambda **kw: [dict({"op": "relu", "inputs": ["x"], "output": "y"}, **kw)]  # noqa: E731
+    return {
+        "ok_minimal": base,
+        "ok_outputs_default": {k: v for k, v in base.items() if k != "outputs"},
+        "ok_layout_dense": variant(tensors={"x": T(["M", "N"], layout="dense"), "y": T(["M", "N"])}),
+        "ok_reduce_dims_alias": variant(tensors={"x": T(["M", "N"]), "y": T(["M"])}, ops=op(op="reduce_sum", attrs={"reduce_dims": [1]})),
+        "ok_reduce_axis_int": variant(tensors={"x": T(["M", "N"]), "y": T(["M"])}, ops=op(op="reduce_max", attrs={"axis": 1})),
+        "ok_div_scalar_attr": variant(ops=op(op="div", attrs={"divisor": "N"})),
+        "bad_unknown_op": variant(ops=op(op="frobnicate")),
+        "bad_undefined_input": variant(ops=op(inputs=["nope"])),
+        "bad_duplicate_output": variant(ops=op() + op()),
+        "bad_empty_ops": variant(ops=[]),
+        "bad_output_undeclared": variant(outputs=["zzz"]),
+        "bad_dtype": variant(tensors={"x": T(["M"], "f8"), "y": T(["M"])}),
+        "bad_layout": variant(tensors={"x": T(["M"], layout="zigzag"), "y": T(["M"])}),
+        "bad_shape_type": variant(tensors={"x": T([1.5]), "y": T(["M"])}),
+        "bad_reduce_no_dims": variant(ops=op(op="reduce_sum", attrs={})),
+        "bad_reduce_dims_type": variant(ops=op(op="reduce_sum", attrs={"dims": ["N"]})),
+        "bad_softmax_no_axis": variant(ops=op(op="softmax", attrs={})),
+        "bad_softmax_axis_type": variant(ops=op(op="softmax", attrs={"axis": "1"})),
+        "bad_matmul_arity": variant(ops=op(op="matmul")),
+        "bad_matmul_accum": variant(ops=op(op="matmul", inputs=["x", "x"], attrs={"accum_dtype": "f8"})),
+        "bad_matmul_epilogue_op": variant(ops=op(op="matmul", inputs=["x", "x"], attrs={"epilogue": {"op": "erf", "inputs": ["$x"]}})),
+        "bad_const_inputs": variant(ops=op(op="const", attrs={"value": 1})),
+        "bad_const_no_value": variant(ops=op(op="const", inputs=[], attrs={})),
+        "bad_cast_no_to": variant(ops=op(op="cast", attrs={"dtype": "f16"})),
+        "bad_identity_attrs": variant(ops=op(op="identity", attrs={"slice": [0, 1]})),
+        "bad_add_arity": variant(ops=op(op="add")),
+        "bad_where_arity": variant(ops=op(op="where", inputs=["x", "x"])),
+        "bad_broadcast_no_shape": variant(ops=op(op="broadcast_in_dim", attrs={"broadcast_dims": [0]})),
+        "bad_broadcast_dims_type": variant(ops=op(op="broadcast_in_dim", attrs={"out_shape": ["M", "N"], "broadcast_dims": ["a"]})),
+        "bad_transpose_perm": variant(ops=op(op="transpose", attrs={"perm": []})),
+        "bad_reshape_shape": variant(ops=op(op="reshape", attrs={})),
+        "bad_iota_axis": variant(ops=op(op="iota", inputs=[], attrs={"shape": ["M"], "dimension": 0})),
+        "bad_layout_cast_to": variant(ops=op(op="layout_cast", attrs={})),
+        "bad_parallel_axes": variant(parallel_axes=["Q"]),
+        "bad_axis_role": variant(axis_roles={"M": "diagonal"}),
+        "bad_schedule_mismatch": variant(parallel_axes=["M"], schedule={"tile_m": 16, "parallel_axes": ["N"]}),
+        "bad_tensors_type": variant(tensors=[]),
+        "bad_op_attrs_type": variant(ops=op(attrs=[1])),
+    }
+
+
+def write_validation(ref_root: str) -> None:
+    sys.path.insert(0, ref_root)
+    from intent_ir.ir import IntentFunction, IntentIRValidationError
+
+    out = {}
+    for key, js in validation_cases().items():
+        try:
+            IntentFunction.from_json_dict(js)
+            out[key] = {"json": js, "ok": True, "message": None}
+        except IntentIRValidationError as e:
+            out[key] = {"json": js, "ok": False, "message": str(e).splitlines()[0]}
+    with open(os.path.join(HERE, "validation.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+    print(f"wrote {len(out)} validation cases ({sum(1 for v in out.values() if not v['ok'])} rejected)")
+
+
+if __name__ == "__main__":
+    write_validation(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("INTENTIR_REF", ""))

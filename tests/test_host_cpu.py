@@ -1,0 +1,170 @@
+"""Host-side logic that needs no GPU: the C-ABI library loads and exports every declared
+symbol, graph validation agrees with the reference, the planner lowers the reference's own
+graphs to the expected kernels, bindings / expression handling, the registry idiom, and the
+loud failure of the execution path when there is no CUDA device."""
+
+import ctypes
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+
+from intent_ir_b200 import _lib, registry
+from intent_ir_b200.bindings import derive_bindings, eval_expression, normalise_bindings, resolve_expressions
+from intent_ir_b200.errors import B200LoweringError, B200RuntimeError
+from intent_ir_b200.ir import IntentFunction, IntentIRValidationError
+from intent_ir_b200.lowering import lower_intent_to_b200_kernel, plan_json
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "intentir_b200.h")).read()
+    declared = set(re.findall(r"IB200_API[^;(]*?\b(ib200_\w+)\s*\(", header))
+    assert declared and declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert _lib.load().ib200_version() >= 100
+
+
+def test_validation_agrees_with_reference():
+    with open(os.path.join(ROOT, "tests", "golden", "validation.json")) as f:
+        cases = json.load(f)
+    for key, c in cases.items():
+        try:
+            IntentFunction.from_json_dict(c["json"])
+            got = (True, None)
+        except IntentIRValidationError as e:
+            got = (False, str(e).splitlines()[0])
+        assert got == (c["ok"], c["message"]), key
+
+
+EXPECTED_KERNELS = {
+    "any_kernel_dim": ["reduce_any"], "any_const_ne": ["reduce_any"],
+    "softmax_inner": ["softmax"], "softmax_inner__cuda_pipeline_form": ["softmax"], "softmax_like_rowvec": ["softmax"],
+    "layer_norm_persistent": ["layernorm"], "layer_norm_persistent__cuda_pipeline_form": ["layernorm"],
+    "group_norm_kernel": ["groupnorm"], "matmul_bias_relu2d": ["gemm+bias+relu"], "matmul_relu2d": ["gemm+relu"],
+    "row_sum": ["reduce_sum"], "row_max": ["reduce_max"], "transpose2d": ["transpose2d"],
+}
+
+
+@pytest.mark.parametrize("key", sorted(EXPECTED_KERNELS))
+def test_planner_picks_the_fused_kernel(key, golden_graphs):
+    g = golden_graphs[key]
+    d = plan_json(g["intent"], g["shapes"])
+    assert [s["kernel"] for s in d["steps"]] == EXPECTED_KERNELS[key]
+    assert d["cuda_src"] == "" and d["kernel_name"] == g["intent"]["name"]
+    assert d["output_names"] == g["outputs"]
+    # io_spec lists external inputs (first use) then outputs, with concrete shapes
+    assert d["io_spec"]["arg_names"][-len(g["outputs"]):] == g["outputs"]
+    assert sorted(d["io_spec"]["arg_names"][: -len(g["outputs"])]) == sorted(g["inputs"])
+
+
+def test_planner_fuses_elementwise_chains_into_one_pass(golden_graphs):
+    for key, n_in in (("add_bias2d", 2), ("where2d", 2), ("clamp2d", 3), ("scalar_attr_forms", 1), ("rowmask_where2d", 2)):
+        g = golden_graphs[key]
+        d = plan_json(g["intent"], g["shapes"])
+        assert len(d["steps"]) == 1 and d["steps"][0]["kernel"].startswith("elementwise("), (key, d["steps"])
+        assert f"{n_in} in, 1 out" in d["steps"][0]["kernel"]
+        assert d["workspace_bytes"] == 0
+
+
+def test_planner_general_path_and_workspace(golden_graphs):
+    g = golden_graphs["mlp2d"]
+    d = plan_json(g["intent"], g["shapes"])
+    kinds = [s["kernel"].split("(")[0] for s in d["steps"]]
+    assert kinds == ["gemm", "elementwise", "gemm", "elementwise"]
+    assert d["workspace_bytes"] > 0 and d["status_offset"] >= 0
+
+
+def test_planner_rejects_what_it_does_not_cover(golden_graphs):
+    with pytest.raises(B200LoweringError, match="gather"):
+        plan_json(golden_graphs["gather2d"]["intent"], golden_graphs["gather2d"]["shapes"])
+    g = golden_graphs["softmax_inner"]
+    with pytest.raises(B200LoweringError, match="unbound symbolic dim"):
+        plan_json(g["intent"], {"M": 4})
+    with pytest.raises(B200LoweringError, match="invalid IntentIR graph"):
+        plan_json({"name": "x", "tensors": {}, "ops": []}, {})
+
+
+def test_lowered_record_mirrors_the_reference_fields(golden_graphs):
+    g = golden_graphs["softmax_inner"]
+    low = lower_intent_to_b200_kernel(IntentFunction.from_json_dict(g["intent"]),
+                                      shape_bindings={"M": 8, "N": 100, "SOFTMAX_THREADS": 128, "ALLOW_TF32": True, "junk": "x"})
+    assert low.kernel_name == "softmax_inner" and low.cuda_src == ""
+    assert set(low.io_spec) >= {"arg_names", "tensors", "scalars"}
+    assert low.io_spec["tensors"]["input_ptr"] == {"dtype": "f32", "shape": [8, 100]}
+    assert low.output_names == ["output_ptr"]
+    assert low.bindings["M"] == 8 and low.bindings["ALLOW_TF32"] == 1 and "junk" not in low.bindings
+    assert len(low.launch.grid) == 3 and len(low.launch.block) == 3
+    again = lower_intent_to_b200_kernel(IntentFunction.from_json_dict(g["intent"]), shape_bindings={"M": 8, "N": 100,
+                                        "SOFTMAX_THREADS": 128, "ALLOW_TF32": True})
+    assert again is low  # plans are cached per (graph, bindings)
+
+
+def test_reference_style_intent_object_is_accepted(golden_graphs):
+    class Foreign:  # stands in for the reference's IntentFunction: anything with to_json_dict()
+        def __init__(self, js):
+            self._js = js
+
+        def to_json_dict(self):
+            return self._js
+
+    g = golden_graphs["row_sum"]
+    low = lower_intent_to_b200_kernel(Foreign(g["intent"]), shape_bindings=g["shapes"])
+    assert [s["kernel"] for s in low.steps] == ["reduce_sum"]
+
+
+def test_bindings_rules():
+    assert normalise_bindings({"M": 4, "f": 2.0, "g": 2.5, "t": True, "s": "7", "bad": "x", "n": None}) == \
+        {"M": 4, "f": 2, "g": 2.5, "t": 1, "s": 7}
+    d = derive_bindings({"N": 16, "C": 64, "HW": 16, "num_groups": 4})
+    assert d["group_size"] == 16 and d["num_elements"] == 256 and d["G"] == 1
+    d = derive_bindings({"batch": 3, "HEAD_DIM": 64, "group": 2})
+    assert d["Z"] == 3 and d["HEAD_DIM_DIV2"] == 32 and d["num_groups"] == 2
+    assert eval_expression("1.0/(HEAD_DIM**0.5)", {"HEAD_DIM": 64}) == 0.125
+    with pytest.raises(ValueError):
+        eval_expression("__import__('os').system('true')", {})
+    js = {"tensors": {"x": {}}, "ops": [{"op": "const", "inputs": [], "output": "c", "attrs": {"value": "1.0/N"}},
+                                         {"op": "reduce_sum", "inputs": ["x"], "output": "s", "attrs": {"dims": [1], "scale": "1.0/N"}},
+                                         {"op": "const", "inputs": [], "output": "e", "attrs": {"value": "eps"}}]}
+    out = resolve_expressions(js, {"N": 4})
+    assert out["ops"][0]["attrs"]["value"] == 0.25 and out["ops"][1]["attrs"]["scale"] == 0.25
+    assert out["ops"][2]["attrs"]["value"] == "eps" and js["ops"][0]["attrs"]["value"] == "1.0/N"
+
+
+def test_registry_idiom():
+    backend = registry.get("b200")
+    assert backend.name == "b200" and registry.get("b200") is backend
+    with pytest.raises(KeyError, match="backend not registered: triton"):
+        registry.get("triton")
+
+    class Other:
+        name = "other"
+
+    registry.register(Other)
+    assert registry.get("other") is Other
+
+
+def test_no_cpu_fallback(golden_graphs):
+    torch = pytest.importorskip("torch")
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    g = golden_graphs["add2d"]
+    low = lower_intent_to_b200_kernel(g["intent"], shape_bindings=g["shapes"])  # planning is host-only
+    from intent_ir_b200.runtime import run_b200_kernel
+
+    with pytest.raises(B200RuntimeError, match="no CPU path"):
+        run_b200_kernel(io_spec=low.io_spec, inputs_np={"A": np.zeros((16, 16), np.float32), "B": np.zeros((16, 16), np.float32)})
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "intent_ir_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", text, re.M), f

@@ -1,0 +1,276 @@
+"""End-to-end parity through the drop-in boundary: IntentIR JSON -> lower_intent_to_b200_kernel
+-> run_b200_kernel (ctypes -> C ABI -> sm_100a kernels) against
+
+  * the reference interpreter's own outputs (tests/golden, generated from the reference), and
+  * the CPU oracle's run_diff over generated edge-size cases,
+
+bit-exact for boolean / integer results and within the oracle's inferred tolerances
+(verify/tolerances.py) for floating point.  The tests read like the reference's
+tests/backends/cuda/test_cuda_backend_smoke.py."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+
+from intent_ir_b200.ir import IntentFunction
+from oracle import TestCase, execute_intent, generate_cases, infer_tolerances, run_diff
+from oracle.diff import compare_outputs, derive_bindings
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+with open(os.path.join(GOLDEN, "intents.json")) as _f:
+    _GRAPHS = json.load(_f)
+UNCOVERED = {"gather2d": "gather", "_attn_fwd": "rank-2"}  # raise B200LoweringError (see test below)
+KEYS = sorted(k for k in _GRAPHS if k not in UNCOVERED)
+
+
+def _lower_and_run(intent, bindings, inputs):
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+    from intent_ir_b200.runtime import run_b200_kernel
+
+    lowered = lower_intent_to_b200_kernel(intent, shape_bindings=bindings)
+    return run_b200_kernel(kernel_name=lowered.kernel_name, cuda_src=lowered.cuda_src, io_spec=lowered.io_spec,
+                           launch=lowered.launch, bindings=lowered.bindings, inputs_np=inputs,
+                           output_names=lowered.output_names), lowered
+
+
+def _agree(got, want, tol, name=""):
+    got, want = np.asarray(got), np.asarray(want)
+    assert got.shape == want.shape, (name, got.shape, want.shape)
+    if want.dtype == np.bool_ or want.dtype.kind in "iu":
+        assert np.array_equal(got.astype(want.dtype), want), f"{name}: exact mismatch"
+        return
+    gn, wn = np.isnan(got), np.isnan(want)
+    assert np.array_equal(gn, wn), f"{name}: NaN pattern differs"
+    if gn.any():
+        got, want = np.where(gn, 0, got), np.where(wn, 0, want)
+    d = compare_outputs({"y": want}, {"y": got}, ["y"], tol)
+    assert d.ok, (name, d.summary, d.max_abs_err, d.first_bad_index)
+
+
+@pytest.mark.parametrize("key", KEYS)
+def test_golden_graph_matches_reference_interpreter(key, golden_graphs, golden_vectors, golden_verdicts):
+    g = golden_graphs[key]
+    intent = IntentFunction.from_json_dict(g["intent"])
+    inputs = {n: golden_vectors[f"{key}/in/{n}"] for n in g["inputs"]}
+    out, lowered = _lower_and_run(intent, g["shapes"], inputs)
+    tol = golden_verdicts[key]["tol_decl"]
+    for name in g["outputs"]:
+        _agree(out[name], golden_vectors[f"{key}/out/{name}"], tol, f"{key}/{name}")
+    for name in inputs:  # the runner returns inputs as well (frontends/cuda/runtime.py:1028)
+        assert name in out
+
+
+@pytest.mark.parametrize("key", ["any_kernel_dim", "softmax_inner", "softmax_inner__cuda_pipeline_form", "layer_norm_persistent",
+                                 "layer_norm_persistent__cuda_pipeline_form", "group_norm_kernel", "matmul_bias_relu2d",
+                                 "add_bias2d", "where2d", "row_sum", "row_max", "clamp2d", "rms_norm2d", "mlp2d",
+                                 "masked_softmax2d", "layer_norm_residual2d", "transpose2d", "grouped_row_sum2d"])
+def test_run_diff_over_generated_edge_cases(key, golden_graphs):
+    """verify.diff_runner.run_diff with the B200 backend as run_ref_fn, over the deterministic
+    edge-size grid of verify.gen_cases ({1,2,3} U {t-1,t,t+1,2t+1} per axis)."""
+    from intent_ir_b200.backend import make_run_ref_fn
+
+    g = golden_graphs[key]
+    intent = IntentFunction.from_json_dict(g["intent"])
+    base = dict(g["shapes"])
+    cases = []
+    for c in generate_cases(intent, limit=24, seed=7):
+        shapes = {**base, **c.shapes}
+        if key == "group_norm_kernel":
+            shapes["C"] = shapes["num_groups"] * shapes["group_size"]  # the generator varies both freely
+        if key == "grouped_row_sum2d":
+            shapes["N"] = shapes["group_size"] * max(1, shapes["N"] // shapes["group_size"])
+        cases.append(TestCase(shapes=shapes, dtypes={}, seed=c.seed + len(cases)))
+    cases.append(TestCase(shapes=base, dtypes={}, seed=1))
+    run = make_run_ref_fn(intent)
+    diffs, cex = run_diff(intent, run, cases, tolerances=infer_tolerances(intent).to_dict())
+    bad = [(c.case.shapes, c.diff.summary, c.diff.max_abs_err) for c in cex]
+    assert not bad, bad[:3]
+    assert len(diffs) == len(cases) and all(d.ok for d in diffs)
+
+
+def test_mismatching_runner_is_caught():
+    """The reference's tests/test_diff_runner.py:55-70 with the backend in the loop: corrupt
+    one output element after the GPU run and the diff must produce a counterexample."""
+    from intent_ir_b200.backend import make_run_ref_fn
+
+    intent = IntentFunction.from_json_dict(_GRAPHS["matmul_bias_relu2d"]["intent"])
+    run = make_run_ref_fn(intent)
+
+    def corrupted(case):
+        io = run(case)
+        io["C"] = io["C"].copy()
+        io["C"][0, 0] += 5.0
+        return io
+
+    diffs, cex = run_diff(intent, corrupted, [TestCase(shapes={"M": 4, "N": 8, "K": 8}, dtypes={}, seed=0)])
+    assert not diffs[0].ok and cex
+
+
+# ---- the reference's backend smoke tests, against this backend -----------------------------
+
+def _smoke(js, bindings, inputs):
+    out, _ = _lower_and_run(IntentFunction.from_json_dict(js), bindings, inputs)
+    return out
+
+
+def _t(shape, dtype="f32"):
+    return {"dtype": dtype, "shape": shape, "layout": "row_major"}
+
+
+def test_smoke_matmul_matches_numpy():
+    js = {"name": "mm_smoke", "tensors": {"A": _t(["M", "K"]), "B": _t(["K", "N"]), "C": _t(["M", "N"])},
+          "ops": [{"op": "matmul", "inputs": ["A", "B"], "output": "C", "attrs": {}}], "outputs": ["C"],
+          "parallel_axes": ["M", "N"], "schedule": {"tile_m": 8, "tile_n": 16, "tile_k": 16, "parallel_axes": ["M", "N"]}}
+    M, N, K = 32, 48, 16
+    rng = np.random.default_rng(0)
+    A, B = rng.standard_normal((M, K), dtype=np.float32), rng.standard_normal((K, N), dtype=np.float32)
+    got = _smoke(js, {"M": M, "N": N, "K": K}, {"A": A, "B": B})["C"]
+    np.testing.assert_allclose(got, A @ B, rtol=1e-4, atol=1e-4)
+
+
+def test_smoke_fused_elementwise_broadcast_relu():
+    js = {"name": "ew_smoke", "tensors": {"A": _t(["M", "N"]), "B": _t(["N"]), "T": _t(["M", "N"]), "Out": _t(["M", "N"])},
+          "ops": [{"op": "add", "inputs": ["A", "B"], "output": "T", "attrs": {}},
+                  {"op": "relu", "inputs": ["T"], "output": "Out", "attrs": {}}], "outputs": ["Out"]}
+    rng = np.random.default_rng(0)
+    A, B = rng.standard_normal((8, 16), dtype=np.float32), rng.standard_normal(16, dtype=np.float32)
+    got = _smoke(js, {"M": 8, "N": 16}, {"A": A, "B": B})["Out"]
+    np.testing.assert_allclose(got, np.maximum(A + B[None, :], 0), rtol=1e-5, atol=1e-5)
+
+
+def test_smoke_transpose_row_sum_row_max_any():
+    rng = np.random.default_rng(0)
+    A = rng.standard_normal((16, 8), dtype=np.float32)
+    js = {"name": "tr", "tensors": {"A": _t(["M", "N"]), "B": _t(["N", "M"])},
+          "ops": [{"op": "transpose", "inputs": ["A"], "output": "B", "attrs": {"perm": [1, 0]}}], "outputs": ["B"]}
+    assert np.array_equal(_smoke(js, {"M": 16, "N": 8}, {"A": A})["B"], A.T)
+    for op, ref in (("reduce_sum", A.sum(axis=1)), ("reduce_max", A.max(axis=1))):
+        js = {"name": op, "tensors": {"A": _t(["M", "N"]), "S": _t(["M"])},
+              "ops": [{"op": op, "inputs": ["A"], "output": "S", "attrs": {"dims": [1]}}], "outputs": ["S"]}
+        np.testing.assert_allclose(_smoke(js, {"M": 16, "N": 8}, {"A": A})["S"], ref, rtol=1e-6, atol=1e-6)
+    Z = rng.integers(0, 2, size=(8, 8)).astype(np.float32) * (rng.random((8, 8)) < 0.2)
+    js = {"name": "any", "tensors": {"A": _t(["M", "N"]), "z": _t([]), "T": _t(["M", "N"], "i1"), "Out": _t(["M"], "i1")},
+          "ops": [{"op": "const", "inputs": [], "output": "z", "attrs": {"value": 0.0}},
+                  {"op": "ne", "inputs": ["A", "z"], "output": "T", "attrs": {}},
+                  {"op": "reduce_any", "inputs": ["T"], "output": "Out", "attrs": {"dims": [1]}}], "outputs": ["Out"]}
+    got = _smoke(js, {"M": 8, "N": 8}, {"A": Z.astype(np.float32)})["Out"]
+    assert got.dtype == np.bool_ and np.array_equal(got, np.any(Z != 0, axis=1))
+
+
+# ---- BASELINE configurations ------------------------------------------------------------------
+
+def test_config_reduce_any_16x256(golden_graphs):
+    intent = IntentFunction.from_json_dict(golden_graphs["any_kernel_dim"]["intent"])
+    rng = np.random.default_rng(0)
+    x = np.where(rng.random((16, 256)) < 0.05, rng.standard_normal((16, 256), dtype=np.float32), np.float32(0))
+    out, lowered = _lower_and_run(intent, {"M": 16, "N": 256}, {"inp": x})
+    assert lowered.n_launches == 1
+    assert np.array_equal(out["out"], execute_intent(intent, {"inp": x})["out"])
+
+
+def test_config_softmax_4096x4096(golden_graphs):
+    intent = IntentFunction.from_json_dict(golden_graphs["softmax_inner"]["intent"])
+    x = 3 * np.random.default_rng(1).standard_normal((4096, 4096), dtype=np.float32)
+    out, lowered = _lower_and_run(intent, {"M": 4096, "N": 4096}, {"input_ptr": x})
+    assert [s["kernel"] for s in lowered.steps] == ["softmax"]
+    want = execute_intent(intent, {"input_ptr": x})["output_ptr"]
+    _agree(out["output_ptr"], want, {"atol": 1e-4, "rtol": 1e-4}, "softmax")  # 1-op softmax: (1e-4, 1e-4)
+
+
+def test_config_layernorm_8192x4096(golden_graphs):
+    intent = IntentFunction.from_json_dict(golden_graphs["layer_norm_persistent"]["intent"])
+    rng = np.random.default_rng(2)
+    M, N = 8192, 4096
+    x = rng.standard_normal((M, N), dtype=np.float32)
+    w = rng.uniform(0.5, 1.5, N).astype(np.float32)
+    b = (0.1 * rng.standard_normal(N)).astype(np.float32)
+    out, lowered = _lower_and_run(intent, {"M": M, "N": N}, {"in_ptr": x, "weight_ptr": w, "bias_ptr": b})
+    assert [s["kernel"] for s in lowered.steps] == ["layernorm"]
+    # the oracle on a slice of the rows (rows are independent) ...
+    rows = slice(0, 512)
+    want = execute_intent(intent, {"in_ptr": x[rows], "weight_ptr": w, "bias_ptr": b}, {"M": 512, "N": N})
+    tol = {"atol": 1e-3, "rtol": 1e-3}
+    _agree(out["out_ptr"][rows], want["out_ptr"], tol, "y")
+    _agree(out["out_mean_ptr"][rows], want["out_mean_ptr"], tol, "mean")
+    _agree(out["out_rstd_ptr"][rows], want["out_rstd_ptr"], tol, "rstd")
+    # ... and size-independent properties on all of them: (y - b)/w has zero mean and unit variance
+    z = (out["out_ptr"].astype(np.float64) - b) / w
+    assert np.abs(z.mean(axis=1)).max() < 1e-4
+    assert np.abs(z.var(axis=1) - 1.0).max() < 1e-3
+    assert np.allclose(out["out_mean_ptr"], x.mean(axis=1, dtype=np.float64), atol=1e-5)
+
+
+def test_config_groupnorm_32x256x4096(golden_graphs):
+    intent = IntentFunction.from_json_dict(golden_graphs["group_norm_kernel"]["intent"])
+    rng = np.random.default_rng(4)
+    shapes = {"N": 32, "C": 256, "HW": 4096, "num_groups": 32}
+    x = rng.standard_normal((32, 256, 4096), dtype=np.float32)
+    w = rng.standard_normal(256, dtype=np.float32)
+    b = rng.standard_normal(256, dtype=np.float32)
+    out, lowered = _lower_and_run(intent, shapes, {"X": x, "W": w, "B": b})
+    assert [s["kernel"] for s in lowered.steps] == ["groupnorm"]
+    sub = {"N": 2, "C": 256, "HW": 4096, "num_groups": 32}
+    want = execute_intent(intent, {"X": x[:2], "W": w, "B": b}, derive_bindings(sub))
+    tol = {"atol": 1e-3, "rtol": 1e-3}
+    _agree(out["Y"][:2], want["Y"], tol, "Y")
+    _agree(out["Mean"][:2], want["Mean"], tol, "Mean")
+    _agree(out["Rstd"][:2], want["Rstd"], tol, "Rstd")
+    x4 = x.reshape(32, 32, 8 * 4096)
+    assert np.allclose(out["Mean"], x4.mean(axis=2, dtype=np.float64), atol=1e-5)
+    assert np.allclose(out["Rstd"], 1.0 / np.sqrt(x4.var(axis=2, dtype=np.float64) + 1e-5), rtol=1e-4)
+
+
+def test_config_matmul_bias_relu_bf16_4096(golden_graphs):
+    from intent_ir_b200.backend import round_to_bf16
+
+    js = json.loads(json.dumps(golden_graphs["matmul_bias_relu2d"]["intent"]))
+    for name in ("A", "B", "bias", "C"):
+        js["tensors"][name]["dtype"] = "bf16"
+    js["ops"][0]["attrs"] = {"accum_dtype": "f32"}
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(3)
+    n = 4096
+    A = round_to_bf16(0.02 * rng.standard_normal((n, n), dtype=np.float32))
+    B = round_to_bf16(0.02 * rng.standard_normal((n, n), dtype=np.float32))
+    bias = round_to_bf16(0.1 * rng.standard_normal(n, dtype=np.float32))
+    out, lowered = _lower_and_run(intent, {"M": n, "N": n, "K": n}, {"A": A, "B": B, "bias": bias})
+    assert [s["kernel"] for s in lowered.steps] == ["gemm+bias+relu"]
+    want = execute_intent(intent, {"A": A, "B": B, "bias": bias})["C"]  # float32-carried bf16 values
+    tol = infer_tolerances(intent).to_dict()
+    assert tol == {"atol": 2e-2, "rtol": 2e-2}
+    _agree(out["C"], want, tol, "C")
+    # tighter than the verifier asks: bf16 rounding of an fp32-accumulated result
+    assert np.abs(out["C"] - want).max() <= 2.0 ** -8 * np.abs(want).max() + 1e-6
+
+
+# ---- error behaviour ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("key", sorted(UNCOVERED))
+def test_uncovered_graphs_fail_loudly(key, golden_graphs):
+    from intent_ir_b200.errors import B200LoweringError
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+
+    g = golden_graphs[key]
+    with pytest.raises(B200LoweringError) as e:
+        lower_intent_to_b200_kernel(IntentFunction.from_json_dict(g["intent"]), shape_bindings=g["shapes"])
+    assert UNCOVERED[key] in str(e.value)
+
+
+def test_missing_input_and_wrong_shape_raise(golden_graphs):
+    from intent_ir_b200.errors import B200RuntimeError
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+    from intent_ir_b200.runtime import run_b200_kernel
+
+    g = golden_graphs["add2d"]
+    lowered = lower_intent_to_b200_kernel(IntentFunction.from_json_dict(g["intent"]), shape_bindings={"M": 4, "N": 4})
+    kw = dict(kernel_name=lowered.kernel_name, cuda_src="", io_spec=lowered.io_spec, launch=lowered.launch,
+              bindings=lowered.bindings, output_names=lowered.output_names)
+    with pytest.raises(B200RuntimeError, match="missing input"):
+        run_b200_kernel(inputs_np={"A": np.zeros((4, 4), np.float32)}, **kw)
+    with pytest.raises(B200RuntimeError, match="shape"):
+        run_b200_kernel(inputs_np={"A": np.zeros((4, 5), np.float32), "B": np.zeros((4, 4), np.float32)}, **kw)
