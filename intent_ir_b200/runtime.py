@@ -27,7 +27,7 @@ from .errors import B200LoweringError, B200RuntimeError
 from .lowering import B200LoweredKernel, lookup_plan
 from .ops import TORCH_OF_DTYPE
 
-__all__ = ["run_b200_kernel", "run_lowered", "launch_lowered", "check_plan_status"]
+__all__ = ["run_b200_kernel", "run_lowered", "run_lowered_pinned", "launch_lowered", "check_plan_status"]
 
 _WORKSPACES: Dict[Any, torch.Tensor] = {}
 
@@ -171,6 +171,23 @@ def run_lowered(lowered: B200LoweredKernel, inputs_np: Mapping[str, np.ndarray],
             t = t.float()  # numpy has no bfloat16; values are exactly representable in float32
         result[name] = t.detach().cpu().numpy()
     return result
+
+
+def run_lowered_pinned(lowered: B200LoweredKernel, host_inputs: Mapping[str, torch.Tensor],
+                       host_outputs: Mapping[str, torch.Tensor], device: str = "cuda") -> Dict[str, torch.Tensor]:
+    """Host buffers in, host buffers out, without numpy conversions: ``host_inputs`` are
+    (ideally pinned) CPU tensors of the declared dtypes, ``host_outputs`` are CPU tensors that
+    receive the results.  One call = host->device copies, the plan, device->host copies and a
+    stream synchronise; this is the end-to-end path the benchmark times."""
+    _require_cuda()
+    out_set = set(lowered.output_names)
+    dev_in = {n: host_inputs[n].to(device, non_blocking=True) for n in lowered.io_spec["arg_names"] if n not in out_set}
+    outs = launch_lowered(lowered, dev_in)
+    for name, t in outs.items():
+        host_outputs[name].copy_(t, non_blocking=True)
+    torch.cuda.current_stream().synchronize()
+    check_plan_status(lowered)
+    return dict(host_outputs)
 
 
 def run_b200_kernel(*, kernel_name: str = "", cuda_src: str = "", io_spec: Mapping[str, Any], launch: Any = None,

@@ -1,0 +1,366 @@
+"""The seeded verification sweep: many (graph, shapes, seed) cases, each lowered, run on the
+GPU and diffed against the CPU interpreter, sharded over the GPUs of one box.
+
+This is the reference's "Task5 cases + diff" stage (``generate_cases`` ->
+``run_diff(intent, run_ref_fn, cases)``, pipeline/triton/core.py:2552-2602,
+verify/diff_runner.py:37-275) turned into a batch job:
+
+* cases are independent, so case ``i`` goes to rank ``i % world`` — one process per GPU, no
+  device-side communication at all; each rank appends one JSON record per case to its own
+  JSONL shard (restart skips the ids already recorded) and rank 0 merges the shards with a
+  host-side gather;
+* a failing case never stops the sweep: exceptions from lowering, from the GPU run or from
+  the checker become failed records, the way ``pipeline/run.py:60-79`` isolates per-kernel
+  errors;
+* large row-independent cases can be split on their leading axis into sub-cases so that both
+  the GPU work and the CPU checking of one big case spread over ranks.
+
+The checker is injected: ``run_sweep(..., diff_fn=run_diff, tolerances_fn=infer_tolerances,
+case_type=TestCase)`` takes the reference's own ``verify`` functions (or anything with the
+same signatures).  ``reference_checker()`` imports them from a reference checkout named by
+``$INTENTIR_REF``; this module never falls back to a checker of its own.
+"""
+
+from __future__ import annotations
+
+import importlib
+import json
+import os
+import sys
+import time
+from dataclasses import asdict, dataclass, field
+from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from .backend import round_to_bf16
+
+__all__ = ["SweepCase", "generate_sweep_cases", "split_rows", "run_sweep", "merge_records", "reference_checker", "KINDS"]
+
+EDGE_SIZES = (1, 2, 3, 7, 8, 15, 16, 17, 31, 32, 33)
+KINDS = ("reduce_any", "reduce_sum", "reduce_max", "softmax", "layernorm", "groupnorm", "matmul_bias_relu", "chain")
+
+
+@dataclass
+class SweepCase:
+    case_id: int
+    kind: str
+    dtype: str
+    shapes: Dict[str, int]
+    seed: int
+    intent: Dict[str, Any] = field(repr=False, default_factory=dict)
+    elements: int = 0  # size of the largest tensor, for load balancing and memory caps
+
+
+# ---- graph templates (IntentIR JSON, the wire format of intent_ir/ir/ir_types.py:273-291) ---------
+
+def _t(shape, dtype="f32"):
+    return {"dtype": dtype, "shape": list(shape), "layout": "row_major"}
+
+
+def g_reduce(kind: str, dtype: str) -> Dict[str, Any]:
+    out_dt = "bool" if kind == "reduce_any" else "f32"
+    return {"name": f"sweep_{kind}", "tensors": {"inp": _t(["M", "N"], dtype), "out": _t(["M"], out_dt)},
+            "ops": [{"op": kind, "inputs": ["inp"], "output": "out", "attrs": {"dims": [1], "keepdims": False}}],
+            "outputs": ["out"]}
+
+
+def g_softmax(dtype: str) -> Dict[str, Any]:
+    return {"name": "sweep_softmax", "tensors": {"inp": _t(["M", "N"], dtype), "out": _t(["M", "N"], dtype)},
+            "ops": [{"op": "softmax", "inputs": ["inp"], "output": "out", "attrs": {"axis": -1}}], "outputs": ["out"]}
+
+
+def g_layernorm() -> Dict[str, Any]:
+    ops = [
+        {"op": "reduce_sum", "inputs": ["x"], "output": "s", "attrs": {"dims": [1], "keepdims": True}},
+        {"op": "div", "inputs": ["s"], "output": "mu", "attrs": {"divisor": "N"}},
+        {"op": "sub", "inputs": ["x", "mu"], "output": "d"},
+        {"op": "mul", "inputs": ["d", "d"], "output": "sq"},
+        {"op": "reduce_sum", "inputs": ["sq"], "output": "vs", "attrs": {"dims": [1], "keepdims": True}},
+        {"op": "div", "inputs": ["vs"], "output": "var", "attrs": {"divisor": "N"}},
+        {"op": "const", "inputs": [], "output": "eps", "attrs": {"value": 1e-5, "dtype": "f32"}},
+        {"op": "add", "inputs": ["var", "eps"], "output": "ve"},
+        {"op": "rsqrt", "inputs": ["ve"], "output": "rs"},
+        {"op": "mul", "inputs": ["d", "rs"], "output": "xh"},
+        {"op": "broadcast_in_dim", "inputs": ["w"], "output": "wb", "attrs": {"out_shape": ["M", "N"], "broadcast_dims": [1]}},
+        {"op": "broadcast_in_dim", "inputs": ["b"], "output": "bb", "attrs": {"out_shape": ["M", "N"], "broadcast_dims": [1]}},
+        {"op": "mul", "inputs": ["xh", "wb"], "output": "sc"},
+        {"op": "add", "inputs": ["sc", "bb"], "output": "y"},
+        {"op": "reshape", "inputs": ["mu"], "output": "mean", "attrs": {"shape": ["M"]}},
+        {"op": "reshape", "inputs": ["rs"], "output": "rstd", "attrs": {"shape": ["M"]}},
+    ]
+    return {"name": "sweep_layernorm",
+            "tensors": {"x": _t(["M", "N"]), "w": _t(["N"]), "b": _t(["N"]), "y": _t(["M", "N"]), "mean": _t(["M"]), "rstd": _t(["M"])},
+            "ops": ops, "outputs": ["y", "mean", "rstd"]}
+
+
+def g_groupnorm() -> Dict[str, Any]:
+    g4 = ["N", "num_groups", 1, 1]
+    ops = [
+        {"op": "reshape", "inputs": ["X"], "output": "X4", "attrs": {"shape": ["N", "num_groups", "group_size", "HW"]}},
+        {"op": "reduce_sum", "inputs": ["X4"], "output": "s", "attrs": {"dims": [2, 3], "keepdims": True}},
+        {"op": "div", "inputs": ["s"], "output": "mu", "attrs": {"divisor": "num_elements"}},
+        {"op": "sub", "inputs": ["X4", "mu"], "output": "d"},
+        {"op": "mul", "inputs": ["d", "d"], "output": "sq"},
+        {"op": "reduce_sum", "inputs": ["sq"], "output": "vs", "attrs": {"dims": [2, 3], "keepdims": True}},
+        {"op": "div", "inputs": ["vs"], "output": "var", "attrs": {"divisor": "num_elements"}},
+        {"op": "const", "inputs": [], "output": "eps", "attrs": {"value": 1e-5, "dtype": "f32"}},
+        {"op": "add", "inputs": ["var", "eps"], "output": "ve"},
+        {"op": "rsqrt", "inputs": ["ve"], "output": "rs"},
+        {"op": "mul", "inputs": ["d", "rs"], "output": "xh4"},
+        {"op": "reshape", "inputs": ["xh4"], "output": "xh", "attrs": {"shape": ["N", "C", "HW"]}},
+        {"op": "broadcast_in_dim", "inputs": ["W"], "output": "W3", "attrs": {"out_shape": ["N", "C", "HW"], "broadcast_dims": [1]}},
+        {"op": "broadcast_in_dim", "inputs": ["B"], "output": "B3", "attrs": {"out_shape": ["N", "C", "HW"], "broadcast_dims": [1]}},
+        {"op": "mul", "inputs": ["xh", "W3"], "output": "sc"},
+        {"op": "add", "inputs": ["sc", "B3"], "output": "Y"},
+        {"op": "reshape", "inputs": ["mu"], "output": "Mean", "attrs": {"shape": ["N", "num_groups"]}},
+        {"op": "reshape", "inputs": ["rs"], "output": "Rstd", "attrs": {"shape": ["N", "num_groups"]}},
+    ]
+    tensors = {"X": _t(["N", "C", "HW"]), "W": _t(["C"]), "B": _t(["C"]), "Y": _t(["N", "C", "HW"]),
+               "Mean": _t(["N", "num_groups"]), "Rstd": _t(["N", "num_groups"]), "mu": _t(g4), "rs": _t(g4)}
+    return {"name": "sweep_groupnorm", "tensors": tensors, "ops": ops, "outputs": ["Y", "Mean", "Rstd"]}
+
+
+def g_matmul(dtype: str) -> Dict[str, Any]:
+    return {"name": "sweep_matmul_bias_relu",
+            "tensors": {"A": _t(["M", "K"], dtype), "B": _t(["K", "N"], dtype), "bias": _t(["N"], dtype), "C": _t(["M", "N"], dtype)},
+            "ops": [{"op": "matmul", "inputs": ["A", "B"], "output": "mm", "attrs": {"accum_dtype": "f32"}},
+                    {"op": "broadcast_in_dim", "inputs": ["bias"], "output": "b2", "attrs": {"out_shape": ["M", "N"], "broadcast_dims": [1]}},
+                    {"op": "add", "inputs": ["mm", "b2"], "output": "mb"},
+                    {"op": "relu", "inputs": ["mb"], "output": "C"}],
+            "outputs": ["C"]}
+
+
+def g_chain(rng: np.random.Generator, dtype: str) -> Dict[str, Any]:
+    """2..6 add/mul ops over x[M,N] with [N], [M,1] and scalar operands; output f32."""
+    n_ops = int(rng.integers(2, 7))
+    tensors = {"x": _t(["M", "N"], dtype), "col": _t(["N"], dtype), "row": _t(["M", 1], dtype), "y": _t(["M", "N"])}
+    ops, cur = [], "x"
+    for i in range(n_ops):
+        op = "add" if rng.random() < 0.5 else "mul"
+        out = "y" if i == n_ops - 1 else f"t{i}"
+        which = int(rng.integers(0, 3))
+        if which == 0:
+            ops.append({"op": op, "inputs": [cur, "col"], "output": out})
+        elif which == 1:
+            ops.append({"op": op, "inputs": [cur, "row"], "output": out})
+        else:
+            key = "addend" if op == "add" else "mul_factor"
+            ops.append({"op": op, "inputs": [cur], "output": out, "attrs": {key: float(np.round(rng.uniform(-1.5, 1.5), 3))}})
+        cur = out
+    if not any("col" in o["inputs"] for o in ops):  # keep every declared input in use
+        ops[0] = {"op": ops[0]["op"], "inputs": ["x", "col"], "output": ops[0]["output"]}
+    if not any("row" in o["inputs"] for o in ops):
+        ops[-1] = {"op": ops[-1]["op"], "inputs": [ops[-1]["inputs"][0], "row"], "output": "y"}
+    return {"name": "sweep_chain", "tensors": tensors, "ops": ops, "outputs": ["y"]}
+
+
+# ---- case generation ------------------------------------------------------------------------------------
+
+def _dim(rng: np.random.Generator, hi: int = 4096) -> int:
+    if rng.random() < 0.25:
+        t = int(rng.choice((16, 32, 64, 128, 256, 1024)))
+        return int(min(hi, rng.choice(EDGE_SIZES + (t - 1, t, t + 1, 2 * t + 1))))
+    return int(rng.integers(1, hi + 1))
+
+
+def _fit(dims: List[int], cap: int) -> List[int]:
+    """Halve the extents in turn (first one first) until their product is at most ``cap``."""
+    dims = [max(1, int(d)) for d in dims]
+    i = 0
+    while int(np.prod(dims, dtype=np.int64)) > cap and any(d > 1 for d in dims):
+        if dims[i % len(dims)] > 1:
+            dims[i % len(dims)] //= 2
+        i += 1
+    return dims
+
+
+def generate_sweep_cases(n_cases: int, base_seed: int = 1000, max_elements: int = 1 << 24,
+                         canonical_groupnorm_every: int = 0, kinds: Sequence[str] = KINDS) -> List[SweepCase]:
+    """Deterministic: case ``i`` is a function of ``base_seed + i`` only.  Every free extent is
+    uniform in [1, 4096] mixed with the edge sizes of verify/gen_cases.py ({1,2,3}, t-1, t, t+1,
+    2t+1); dtypes are f32 or bf16; ``max_elements`` caps the largest tensor of a case."""
+    out: List[SweepCase] = []
+    for i in range(n_cases):
+        seed = base_seed + i
+        rng = np.random.default_rng(seed)
+        kind = kinds[int(rng.integers(0, len(kinds)))]
+        dtype = "bf16" if rng.random() < 0.3 else "f32"
+        if kind in ("reduce_any", "reduce_sum", "reduce_max", "softmax", "chain"):
+            m, n = _fit([_dim(rng), _dim(rng)], max_elements)
+            shapes = {"M": m, "N": n}
+            intent = g_softmax(dtype) if kind == "softmax" else g_chain(rng, dtype) if kind == "chain" else g_reduce(kind, dtype)
+            elements = m * n
+        elif kind == "layernorm":
+            dtype = "f32"
+            m, n = _fit([_dim(rng), _dim(rng)], max_elements)
+            shapes, intent, elements = {"M": m, "N": n}, g_layernorm(), m * n
+        elif kind == "groupnorm":
+            dtype = "f32"
+            if canonical_groupnorm_every and i % canonical_groupnorm_every == 0:
+                shapes = {"N": 32, "C": 256, "HW": 4096, "num_groups": 32}
+            else:
+                groups, gs = int(rng.integers(1, 33)), int(rng.integers(1, 17))
+                hw, nb, gs, groups = _fit([_dim(rng), int(rng.integers(1, 9)), gs, groups], max_elements)
+                shapes = {"N": nb, "C": groups * gs, "HW": hw, "num_groups": groups}
+            intent = g_groupnorm()
+            elements = shapes["N"] * shapes["C"] * shapes["HW"]
+        else:  # matmul_bias_relu
+            m, n, k = _dim(rng, 2048), _dim(rng, 2048), _dim(rng, 2048)
+            if dtype == "bf16":  # the tensor-core path wants 16-byte rows; other shapes also run (FMA path)
+                if rng.random() < 0.7:
+                    n, k = max(8, n // 8 * 8), max(8, k // 8 * 8)
+            shapes, intent, elements = {"M": m, "N": n, "K": k}, g_matmul(dtype), max(m * k, k * n, m * n)
+        out.append(SweepCase(case_id=i, kind=kind, dtype=dtype, shapes=shapes, seed=seed, intent=intent, elements=elements))
+    return out
+
+
+_ROW_AXIS = {"reduce_any": "M", "reduce_sum": "M", "reduce_max": "M", "softmax": "M", "layernorm": "M", "chain": "M",
+             "matmul_bias_relu": "M", "groupnorm": "N"}
+
+
+def split_rows(case: SweepCase, parts: int, id_stride: int = 1 << 20) -> List[SweepCase]:
+    """Split a case on its leading independent axis into up to ``parts`` sub-cases (rows of
+    every kind here are independent; matmul replicates B).  Sub-case ``j`` gets the id
+    ``case_id + (j+1)*id_stride`` and its own seed."""
+    axis = _ROW_AXIS[case.kind]
+    rows = case.shapes[axis]
+    parts = max(1, min(parts, rows))
+    if parts == 1:
+        return [case]
+    base, extra = divmod(rows, parts)
+    subs = []
+    for j in range(parts):
+        r = base + (1 if j < extra else 0)
+        shapes = dict(case.shapes)
+        shapes[axis] = r
+        subs.append(SweepCase(case_id=case.case_id + (j + 1) * id_stride, kind=case.kind, dtype=case.dtype, shapes=shapes,
+                              seed=case.seed * 131 + j, intent=case.intent, elements=case.elements * r // max(rows, 1)))
+    return subs
+
+
+def case_inputs(case: SweepCase) -> Dict[str, np.ndarray]:
+    """Seeded inputs with the value distributions of the benchmark configurations; bf16 tensors
+    are float32 arrays holding bf16-representable values."""
+    rng = np.random.default_rng(case.seed)
+    s = case.shapes
+    q = round_to_bf16 if case.dtype == "bf16" else (lambda a: a)
+    k = case.kind
+    if k in ("reduce_any",):
+        m, n = s["M"], s["N"]
+        return {"inp": q(np.where(rng.random((m, n)) < 0.05, rng.standard_normal((m, n), dtype=np.float32), np.float32(0)))}
+    if k in ("reduce_sum", "reduce_max"):
+        return {"inp": q(rng.standard_normal((s["M"], s["N"]), dtype=np.float32))}
+    if k == "softmax":
+        return {"inp": q(3 * rng.standard_normal((s["M"], s["N"]), dtype=np.float32))}
+    if k == "chain":
+        return {"x": q(rng.standard_normal((s["M"], s["N"]), dtype=np.float32)), "col": q(rng.standard_normal(s["N"], dtype=np.float32)),
+                "row": q(rng.standard_normal((s["M"], 1), dtype=np.float32))}
+    if k == "layernorm":
+        return {"x": rng.standard_normal((s["M"], s["N"]), dtype=np.float32), "w": rng.uniform(0.5, 1.5, s["N"]).astype(np.float32),
+                "b": (0.1 * rng.standard_normal(s["N"])).astype(np.float32)}
+    if k == "groupnorm":
+        return {"X": rng.standard_normal((s["N"], s["C"], s["HW"]), dtype=np.float32), "W": rng.standard_normal(s["C"], dtype=np.float32),
+                "B": rng.standard_normal(s["C"], dtype=np.float32)}
+    if k == "matmul_bias_relu":
+        sc = np.float32(1.0 / np.sqrt(max(s["K"], 1)))
+        return {"A": q(rng.standard_normal((s["M"], s["K"]), dtype=np.float32)), "B": q(sc * rng.standard_normal((s["K"], s["N"]), dtype=np.float32)),
+                "bias": q(0.1 * rng.standard_normal(s["N"], dtype=np.float32))}
+    raise ValueError(f"unknown sweep kind {k}")
+
+
+# ---- the driver -------------------------------------------------------------------------------------------
+
+def reference_checker() -> Tuple[Callable, Callable, type]:
+    """(run_diff, infer_tolerances, TestCase) imported from the reference checkout at
+    ``$INTENTIR_REF``.  Raises if it is not there: the sweep has no checker of its own."""
+    root = os.environ.get("INTENTIR_REF")
+    if not root or not os.path.isdir(root):
+        raise RuntimeError("set INTENTIR_REF to a checkout of the reference (its verify/ package is the checker), "
+                           "or pass diff_fn / tolerances_fn / case_type explicitly")
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    dr = importlib.import_module("verify.diff_runner")
+    tol = importlib.import_module("verify.tolerances")
+    gc = importlib.import_module("verify.gen_cases")
+    return dr.run_diff, tol.infer_tolerances, gc.TestCase
+
+
+def _done_ids(path: str) -> set:
+    done = set()
+    if os.path.exists(path):
+        with open(path) as f:
+            for line in f:
+                try:
+                    done.add(int(json.loads(line)["case_id"]))
+                except Exception:
+                    pass
+    return done
+
+
+def run_sweep(cases: Iterable[SweepCase], *, diff_fn: Callable, tolerances_fn: Callable, case_type: type,
+              rank: int = 0, world: int = 1, out_dir: Optional[str] = None, make_runner: Optional[Callable] = None,
+              intent_from_json: Optional[Callable] = None) -> List[Dict[str, Any]]:
+    """Run this rank's share of ``cases`` (case i -> rank i % world, by position) and return
+    its records.  ``make_runner(intent, input_gen)`` defaults to the B200 backend's
+    ``make_run_ref_fn``; ``intent_from_json`` to this package's ``IntentFunction``."""
+    if make_runner is None:
+        from .backend import make_run_ref_fn as make_runner
+    if intent_from_json is None:
+        from .ir import IntentFunction
+
+        intent_from_json = IntentFunction.from_json_dict
+    shard = None
+    done: set = set()
+    if out_dir:
+        os.makedirs(out_dir, exist_ok=True)
+        shard = os.path.join(out_dir, f"sweep.rank{rank}.jsonl")
+        done = _done_ids(shard)
+    records: List[Dict[str, Any]] = []
+    fh = open(shard, "a") if shard else None
+    try:
+        for pos, case in enumerate(cases):
+            if pos % world != rank or case.case_id in done:
+                continue
+            t0 = time.perf_counter()
+            rec: Dict[str, Any] = {"case_id": case.case_id, "kind": case.kind, "dtype": case.dtype, "shapes": case.shapes, "rank": rank}
+            try:
+                intent = intent_from_json(case.intent)
+                timing: Dict[str, float] = {}
+                backend_fn = make_runner(intent, lambda c, _case=case: case_inputs(_case))
+
+                def timed(c, _fn=backend_fn, _t=timing):
+                    t = time.perf_counter()
+                    try:
+                        return _fn(c)
+                    finally:
+                        _t["gpu"] = time.perf_counter() - t
+
+                tol = tolerances_fn(intent).to_dict()
+                diffs, _ = diff_fn(intent, timed, [case_type(shapes=dict(case.shapes), dtypes={}, seed=case.seed)], tolerances=tol)
+                d = diffs[0]
+                rec.update(ok=bool(d.ok), summary=d.summary, max_abs=float(d.max_abs_err) if np.isfinite(d.max_abs_err) else None,
+                           max_rel=float(d.max_rel_err) if np.isfinite(d.max_rel_err) else None, t_gpu=timing.get("gpu"))
+            except Exception as e:  # lowering, GPU or checker failure: a failed record, not a dead sweep
+                rec.update(ok=False, summary=f"{type(e).__name__}: {e}"[:300], max_abs=None, max_rel=None, t_gpu=None)
+            rec["t_total"] = time.perf_counter() - t0
+            records.append(rec)
+            if fh:
+                fh.write(json.dumps(rec) + "\n")
+                fh.flush()
+    finally:
+        if fh:
+            fh.close()
+    return records
+
+
+def merge_records(per_rank: Sequence[Sequence[Dict[str, Any]]]) -> Dict[str, Any]:
+    """Host-side gather: one summary from every rank's records."""
+    rows = sorted((r for part in per_rank for r in part), key=lambda r: r["case_id"])
+    by_kind: Dict[str, Dict[str, int]] = {}
+    for r in rows:
+        k = by_kind.setdefault(r["kind"], {"cases": 0, "ok": 0})
+        k["cases"] += 1
+        k["ok"] += int(bool(r["ok"]))
+    return {"cases": len(rows), "ok": sum(int(bool(r["ok"])) for r in rows), "by_kind": by_kind,
+            "failed": [{"case_id": r["case_id"], "kind": r["kind"], "shapes": r["shapes"], "summary": r["summary"]} for r in rows if not r["ok"]][:20]}

@@ -1,0 +1,117 @@
+"""The sweep driver without a GPU: deterministic case generation, row splitting, and the
+world_size-2 path (gloo ranks on CPU) with a numpy stand-in for the GPU runner — the same
+fake the reference's own tests use for run_ref_fn (tests/test_diff_runner.py:58-64)."""
+
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+from intent_ir_b200.ir import IntentFunction
+from intent_ir_b200.sweep import KINDS, case_inputs, generate_sweep_cases, merge_records, run_sweep, split_rows
+from oracle import TestCase, execute_intent, infer_tolerances, run_diff
+from oracle.diff import derive_bindings
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def numpy_runner(intent, input_gen):
+    """Stands in for the GPU: outputs come from the interpreter itself."""
+    def run(case):
+        ins = input_gen(case)
+        with np.errstate(all="ignore"):
+            outs = execute_intent(intent, ins, derive_bindings(case.shapes))
+        return {**ins, **outs}
+    return run
+
+
+CHECKER = dict(diff_fn=run_diff, tolerances_fn=infer_tolerances, case_type=TestCase)
+
+
+def test_cases_are_deterministic_and_in_range():
+    a = generate_sweep_cases(200, base_seed=1000, max_elements=1 << 20)
+    b = generate_sweep_cases(200, base_seed=1000, max_elements=1 << 20)
+    assert [(c.kind, c.dtype, c.shapes, c.seed) for c in a] == [(c.kind, c.dtype, c.shapes, c.seed) for c in b]
+    assert {c.kind for c in a} == set(KINDS) and {c.dtype for c in a} == {"f32", "bf16"}
+    for c in a:
+        assert c.elements <= 1 << 20 or c.kind == "matmul_bias_relu"
+        assert all(1 <= v <= 4096 for k, v in c.shapes.items())
+        IntentFunction.from_json_dict(c.intent)  # every template is a valid graph
+    # case i depends on base_seed + i only
+    assert generate_sweep_cases(5, base_seed=1003, max_elements=1 << 20)[0].shapes == a[3].shapes
+
+
+def test_split_rows_preserves_total_rows():
+    c = generate_sweep_cases(50, base_seed=7, max_elements=1 << 16)
+    big = max((x for x in c if x.kind == "softmax"), key=lambda x: x.shapes["M"])
+    subs = split_rows(big, 4)
+    assert sum(s.shapes["M"] for s in subs) == big.shapes["M"] and len({s.case_id for s in subs}) == len(subs)
+    assert split_rows(big, 1) == [big]
+
+
+def test_single_rank_sweep_with_resume(tmp_path):
+    cases = generate_sweep_cases(24, base_seed=1000, max_elements=1 << 12)
+    recs = run_sweep(cases, out_dir=str(tmp_path), make_runner=numpy_runner, **CHECKER)
+    assert len(recs) == 24 and all(r["ok"] for r in recs), [r["summary"] for r in recs if not r["ok"]]
+    again = run_sweep(cases, out_dir=str(tmp_path), make_runner=numpy_runner, **CHECKER)
+    assert again == []  # every id already recorded in the shard file
+    s = merge_records([recs])
+    assert s["cases"] == s["ok"] == 24 and not s["failed"]
+
+
+def test_failures_are_isolated():
+    cases = generate_sweep_cases(6, base_seed=1000, max_elements=1 << 10)
+
+    def flaky(intent, input_gen):
+        inner = numpy_runner(intent, input_gen)
+
+        def run(case):
+            if case.seed % 2:
+                raise RuntimeError("worker lost its device")
+            io = inner(case)
+            return io
+
+        return run
+
+    recs = run_sweep(cases, make_runner=flaky, **CHECKER)
+    assert len(recs) == 6
+    assert [r["ok"] for r in recs] == [c.seed % 2 == 0 for c in cases]
+    assert all("ref runner error" in r["summary"] for r in recs if not r["ok"])
+
+
+_WORKER = r"""
+import json, os, sys
+sys.path.insert(0, {root!r})
+import torch.distributed as dist
+from tests.test_sweep_cpu import CHECKER, numpy_runner
+from intent_ir_b200.sweep import generate_sweep_cases, merge_records, run_sweep
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+cases = generate_sweep_cases(20, base_seed=1000, max_elements=1 << 10)
+recs = run_sweep(cases, rank=rank, world=world, out_dir={out!r}, make_runner=numpy_runner, **CHECKER)
+gathered = [None] * world if rank == 0 else None
+dist.gather_object(recs, gathered, dst=0)
+if rank == 0:
+    s = merge_records(gathered)
+    s["per_rank"] = [len(g) for g in gathered]
+    json.dump(s, open(os.path.join({out!r}, "summary.json"), "w"))
+dist.destroy_process_group()
+"""
+
+
+def test_two_rank_sweep_over_gloo(tmp_path):
+    pytest.importorskip("torch")
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER.format(root=ROOT, out=str(tmp_path)))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29631", str(script)], env=env, capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    s = json.load(open(tmp_path / "summary.json"))
+    assert s["cases"] == s["ok"] == 20 and s["per_rank"] == [10, 10]
+    shards = sorted(p.name for p in tmp_path.iterdir() if p.name.startswith("sweep.rank"))
+    assert shards == ["sweep.rank0.jsonl", "sweep.rank1.jsonl"]
