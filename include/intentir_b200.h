@@ -104,6 +104,19 @@ IB200_API int ib200_plan_num_launches(const ib200_plan_t* plan);
 IB200_API int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, void* workspace,
                       size_t workspace_bytes, void* stream);
 
+/* Same as ib200_plan_launch, for callers that cannot supply a workspace because they are not
+ * allowed to allocate device memory (their memory belongs to another runtime's pool, or
+ * their hot loop must never reach cudaMalloc).  The scratch is a fixed array of
+ * ib200_noalloc_workspace_limit() bytes (32 MiB) built into the library image and resident
+ * on every GPU that loads the library; plans needing more return IB200_ERR_BUFFER and launch
+ * nothing.  The array is shared by all calls in the process: calls whose kernels could
+ * overlap on the GPU race on it, so keep them ordered.  The first call on a device resolves
+ * the array's address and should be made outside any stream capture.  Never allocates.
+ * This entry point has no counterpart in the reference: its runner always allocates through
+ * torch (frontends/cuda/runtime.py:961-1008). */
+IB200_API int ib200_plan_launch_noalloc(const ib200_plan_t* plan, void* const* args, int n_args, void* stream);
+IB200_API size_t ib200_noalloc_workspace_limit(void);
+
 /* ======================================================================================
  * Direct per-op entry points (the same kernels the plans launch).
  * ====================================================================================== */

@@ -1680,6 +1680,10 @@ int create(const char* intent_json, const char* bindings_json, std::unique_ptr<i
 }  // namespace
 }  // namespace ib200
 
+namespace ib200 {
+long plan_status_offset(const ib200_plan* plan) { return plan && plan->uses_status ? (long)plan->status_offset : -1; }
+}  // namespace ib200
+
 using namespace ib200;
 
 extern "C" {
