@@ -163,6 +163,149 @@ template <bool VEC> __device__ __forceinline__ void put(const float (&src)[kPerT
   }
 }
 
+// The instruction loop.  Operands that are the previous result are used in place (no copy of
+// the accumulator); the opcode and operand codes are uniform, so every branch here is uniform.
+template <bool VEC>
+__device__ __forceinline__ void run_chain(const EwProgram& prog, float (&acc)[kPerThread], float* file, int t) {
+#pragma unroll
+  for (int j = 0; j < kPerThread; ++j) acc[j] = 0.0f;
+  for (int ip = 0; ip < prog.n_instr; ++ip) {
+    const EwInstr ins = prog.instr[ip];
+    if (ins.op == EW_WHERE) {
+      float a[kPerThread], b[kPerThread], c[kPerThread];
+      fetch<VEC>(a, ins.a, acc, ins.imm, file, t);
+      fetch<VEC>(b, ins.b, acc, ins.imm, file, t);
+      fetch<VEC>(c, ins.c, acc, ins.imm, file, t);
+#pragma unroll
+      for (int j = 0; j < kPerThread; ++j) acc[j] = a[j] != 0.0f ? b[j] : c[j];
+    } else if (ins.a == EW_ACC && ins.b == EW_ACC) {
+      apply(ins.op, acc, acc, acc);
+    } else if (ins.a == EW_ACC) {
+      float b[kPerThread];
+      fetch<VEC>(b, ins.b, acc, ins.imm, file, t);
+      apply(ins.op, acc, b, acc);
+    } else if (ins.b == EW_ACC) {
+      float a[kPerThread];
+      fetch<VEC>(a, ins.a, acc, ins.imm, file, t);
+      apply(ins.op, a, acc, acc);
+    } else {
+      float a[kPerThread], b[kPerThread];
+      fetch<VEC>(a, ins.a, acc, ins.imm, file, t);
+      fetch<VEC>(b, ins.b, acc, ins.imm, file, t);
+      apply(ins.op, a, b, acc);
+    }
+    if (ins.dst != EW_NODST) put<VEC>(acc, ins.dst, file, t);
+  }
+}
+
+template <bool VEC>
+__device__ __forceinline__ void write_outputs(const EwProgram& prog, const float (&acc)[kPerThread], float* file, int t, int64_t base) {
+  constexpr int W = VEC ? 4 : 1, U = kPerThread / W;
+  for (int o = 0; o < prog.n_outputs; ++o) {
+    const EwOutput& out = prog.out[o];
+    float v[kPerThread];
+    fetch<VEC>(v, out.src, acc, 0.0f, file, t);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = base + (int64_t)(u * kThreads + t) * W;
+      if (e >= prog.total) continue;
+      if (VEC) {
+        const float q[4] = {v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]};
+        store_vec4(out.ptr, out.dtype, e, q);
+      } else {
+        store_scalar(out.ptr, out.dtype, e, v[u]);
+      }
+    }
+  }
+}
+
+// Specialised staging for the common shapes: at most MAXIN operands, collapsed rank RANK,
+// every operand offset below 2^31.  Operand descriptors (pointer, 32-bit strides, staging
+// mode) are read once per CTA into registers; the per-tile work is RANK-1 multiply-shift
+// divisions per vector and one 32-bit multiply-add per operand and dimension.
+template <int MAXIN, int RANK, bool VEC>
+__global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs) {
+  extern __shared__ __align__(16) float file[];
+  const int t = threadIdx.x;
+  constexpr int W = VEC ? 4 : 1, U = kPerThread / W;
+  const char* ptr[MAXIN];
+  uint32_t stride[MAXIN][RANK];
+  int mode[MAXIN], dtype[MAXIN];
+  bool convert = false;
+#pragma unroll
+  for (int k = 0; k < MAXIN; ++k) {
+    const bool live = k < prog.n_inputs;
+    ptr[k] = live ? static_cast<const char*>(prog.in[k].ptr) : nullptr;
+    mode[k] = live ? prog.in[k].mode : EW_STAGE_NONE;
+    dtype[k] = live ? prog.in[k].dtype : IB200_F32;
+#pragma unroll
+    for (int d = 0; d < RANK; ++d) stride[k][d] = live ? (uint32_t)prog.in[k].stride[d] : 0u;
+    convert |= mode[k] == EW_STAGE_ASYNC_HALF4;
+  }
+  const int64_t ntiles = (prog.total + kTile - 1) / kTile;
+  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t base = tile * kTile;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = base + (int64_t)(u * kThreads + t) * W;
+      if (e >= prog.total) continue;
+      uint32_t coord[RANK];
+      uint32_t rem = (uint32_t)e;
+#pragma unroll
+      for (int d = RANK - 1; d > 0; --d) {
+        uint32_t q;
+        divs.d[d].divmod(rem, q, coord[d]);
+        rem = q;
+      }
+      coord[0] = rem;
+#pragma unroll
+      for (int k = 0; k < MAXIN; ++k) {
+        if (mode[k] == EW_STAGE_NONE) continue;
+        uint32_t off = 0;
+#pragma unroll
+        for (int d = 0; d < RANK; ++d) off += coord[d] * stride[k][d];
+        float* dst = slot_ptr<VEC>(file, k, u * W, t);
+        switch (mode[k]) {
+          case EW_STAGE_ASYNC_F32X4: cp_async16(dst, reinterpret_cast<const float*>(ptr[k]) + off); break;
+          case EW_STAGE_ASYNC_HALF4: cp_async8(dst, reinterpret_cast<const uint16_t*>(ptr[k]) + off); break;
+          case EW_STAGE_ASYNC_F32: cp_async4(dst, reinterpret_cast<const float*>(ptr[k]) + off); break;
+          case EW_STAGE_BROADCAST: {
+            const float v = load_scalar(ptr[k], dtype[k], off);
+#pragma unroll
+            for (int j = 0; j < W; ++j) dst[j] = v;
+            break;
+          }
+          case EW_STAGE_IOTA:
+#pragma unroll
+            for (int j = 0; j < W; ++j) dst[j] = (float)(off + j * stride[k][RANK - 1]);
+            break;
+          default:  // EW_STAGE_GATHER
+#pragma unroll
+            for (int j = 0; j < W; ++j) dst[j] = load_scalar(ptr[k], dtype[k], (int64_t)off + (int64_t)j * stride[k][RANK - 1]);
+        }
+      }
+    }
+    cp_async_wait_all();
+    if (VEC && convert) {
+#pragma unroll
+      for (int k = 0; k < MAXIN; ++k) {
+        if (mode[k] != EW_STAGE_ASYNC_HALF4) continue;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float* dst = slot_ptr<VEC>(file, k, u * W, t);
+          float v[4];
+          if (dtype[k] == IB200_BF16) load4<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(dst), v);
+          else load4<__half>(reinterpret_cast<const __half*>(dst), v);
+          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+      }
+    }
+    float acc[kPerThread];
+    run_chain<VEC>(prog, acc, file, t);
+    write_outputs<VEC>(prog, acc, file, t, base);
+  }
+}
+
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads) ew_kernel(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs) {
   extern __shared__ __align__(16) float file[];
@@ -240,41 +383,9 @@ __global__ void __launch_bounds__(kThreads) ew_kernel(const __grid_constant__ Ew
 
     // ---- run the chain ---------------------------------------------------------------------
     float acc[kPerThread];
-#pragma unroll
-    for (int j = 0; j < kPerThread; ++j) acc[j] = 0.0f;
-    for (int ip = 0; ip < prog.n_instr; ++ip) {
-      const EwInstr ins = prog.instr[ip];
-      float a[kPerThread], b[kPerThread];
-      fetch<VEC>(a, ins.a, acc, ins.imm, file, t);
-      fetch<VEC>(b, ins.b, acc, ins.imm, file, t);
-      if (ins.op == EW_WHERE) {
-        float c[kPerThread];
-        fetch<VEC>(c, ins.c, acc, ins.imm, file, t);
-#pragma unroll
-        for (int j = 0; j < kPerThread; ++j) acc[j] = a[j] != 0.0f ? b[j] : c[j];
-      } else {
-        apply(ins.op, a, b, acc);
-      }
-      if (ins.dst != EW_NODST) put<VEC>(acc, ins.dst, file, t);
-    }
+    run_chain<VEC>(prog, acc, file, t);
 
-    // ---- write the results -----------------------------------------------------------------
-    for (int o = 0; o < prog.n_outputs; ++o) {
-      const EwOutput& out = prog.out[o];
-      float v[kPerThread];
-      fetch<VEC>(v, out.src, acc, 0.0f, file, t);
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int64_t e = base + (int64_t)(u * kThreads + t) * W;
-        if (e >= prog.total) continue;
-        if (VEC) {
-          const float q[4] = {v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]};
-          store_vec4(out.ptr, out.dtype, e, q);
-        } else {
-          store_scalar(out.ptr, out.dtype, e, v[u]);
-        }
-      }
-    }
+    write_outputs<VEC>(prog, acc, file, t, base);
   }
 }
 
@@ -293,9 +404,38 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
   const int per_sm = (int)(220 * 1024 / smem) < 8 ? (int)(220 * 1024 / smem) : 8;
   const int64_t cap = (int64_t)kSmCount * (per_sm > 0 ? per_sm : 1) * 4;
   const int grid = (int)(tiles < cap ? tiles : cap);
-  auto kern = prog.vec ? ew_kernel<true> : ew_kernel<false>;
+  // staging mode per operand, and whether the specialised kernel applies
+  EwProgram p = prog;
+  bool fast = p.n_inputs <= 4 && p.rank <= 3;
+  for (int k = 0; k < p.n_inputs; ++k) {
+    EwInput& in = p.in[k];
+    const int64_t inner = in.stride[p.rank - 1];
+    int64_t reach = 0;
+    for (int d = 0; d < p.rank; ++d) {
+      if (in.stride[d] < 0) fast = false;
+      reach += (int64_t)(p.dim[d] - 1) * in.stride[d];
+    }
+    if (reach >= ((int64_t)1 << 31) - 8) fast = false;
+    if (in.kind == EW_IN_IOTA) in.mode = EW_STAGE_IOTA;
+    else if (p.vec) {
+      if (in.vec_ok && in.dtype == IB200_F32) in.mode = EW_STAGE_ASYNC_F32X4;
+      else if (in.vec_ok && (in.dtype == IB200_BF16 || in.dtype == IB200_F16)) in.mode = EW_STAGE_ASYNC_HALF4;
+      else if (inner == 0) in.mode = EW_STAGE_BROADCAST;
+      else in.mode = EW_STAGE_GATHER;
+    } else {
+      in.mode = in.dtype == IB200_F32 ? EW_STAGE_ASYNC_F32 : EW_STAGE_GATHER;
+    }
+  }
+  void (*kern)(const EwProgram, const EwDivs) = p.vec ? ew_kernel<true> : ew_kernel<false>;
+  if (fast) {
+    const int mi = p.n_inputs <= 2 ? 2 : 4;
+#define IB200_EW(MI, R)                                                                       \
+  if (mi == MI && p.rank == R) kern = p.vec ? ew_kernel_fast<MI, R, true> : ew_kernel_fast<MI, R, false>;
+    IB200_EW(2, 1) IB200_EW(2, 2) IB200_EW(2, 3) IB200_EW(4, 1) IB200_EW(4, 2) IB200_EW(4, 3)
+#undef IB200_EW
+  }
   if (smem > 48 * 1024) IB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, kThreads, smem, s>>>(prog, divs);
+  kern<<<grid, kThreads, smem, s>>>(p, divs);
   return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "elementwise launch");
 }
 

@@ -47,13 +47,23 @@ enum EwInputKind : int32_t {
   EW_IN_IOTA = 1,    // value = offset  (strides form a one-hot ramp along the iota axis)
 };
 
+enum EwStageMode : int32_t {  // how an operand reaches the slot file
+  EW_STAGE_NONE = 0,
+  EW_STAGE_ASYNC_F32X4,  // cp.async 16 bytes (4 contiguous f32)
+  EW_STAGE_ASYNC_HALF4,  // cp.async 8 bytes (4 contiguous bf16 / f16), widened in place afterwards
+  EW_STAGE_ASYNC_F32,    // cp.async 4 bytes (scalar mode)
+  EW_STAGE_BROADCAST,    // one scalar load, replicated (inner stride 0)
+  EW_STAGE_GATHER,       // scalar loads with the inner stride
+  EW_STAGE_IOTA,         // value = offset
+};
+
 struct EwInput {
   const void* ptr;
   int32_t dtype;
   int32_t kind;
   int64_t stride[kEwMaxRank];  // element strides over the collapsed output dims; 0 = broadcast
   int32_t vec_ok;              // inner stride 1, base 16-byte aligned, outer strides % 4 == 0
-  int32_t pad;
+  int32_t mode;                // EwStageMode, filled by launch_elementwise
 };
 
 struct EwOutput {

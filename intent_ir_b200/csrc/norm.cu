@@ -15,8 +15,8 @@
 // statistics passes and the normalisation; x is never re-read from memory.
 //   L <= 1024   : one warp per row;
 //   L <= 16384  : one CTA per row (256..1024 threads);
-//   L <= 131072 : one thread-block cluster of 2..8 CTAs per row, partial sums exchanged
-//                 through distributed shared memory;
+//   L <= 131072 : one thread-block cluster of 2..8 CTAs (256..1024 threads) per row, partial
+//                 sums exchanged through distributed shared memory;
 //   larger      : one CTA per row streaming the row three times (passes 2 and 3 hit L2).
 #include <cooperative_groups.h>
 
@@ -159,17 +159,27 @@ __global__ void __launch_bounds__(THREADS) norm_block(const T* __restrict__ x, c
   }
 }
 
-// One cluster of `csize` CTAs per row: CTA k keeps columns [k*seg, (k+1)*seg) in registers;
-// the two statistics are combined by reading every CTA's partial through distributed
-// shared memory.  One cluster handles one row (grid = rows * csize CTAs).
+// One cluster of `csize` CTAs per row: CTA k keeps columns [k*seg, (k+1)*seg) in registers and
+// computes the statistics of its own segment exactly (sum -> segment mean -> centred sum of
+// squares, two block reductions).  The segments are then merged with the pairwise update
+//   mean = sum_k n_k*mean_k / L,   M2 = sum_k M2_k + sum_k n_k*(mean_k - mean)^2,
+// which is algebraically the centred two-pass variance of the whole row.  Each CTA pushes its
+// (mean_k, M2_k, n_k) into every peer's shared memory, so there is a single cluster barrier
+// per row and afterwards every CTA reads only its own shared memory (no CTA can be exited
+// while a peer still needs it).  The barrier arrive issued at kernel entry and waited on before
+// the first remote store guarantees that every CTA of the cluster has started.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 template <typename T, typename TW, int THREADS, int NV, bool VEC, int AFF>
 __global__ void __launch_bounds__(THREADS) norm_cluster(const T* __restrict__ x, const TW* __restrict__ w,
                                                         const TW* __restrict__ b, T* __restrict__ y,
                                                         float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                         int64_t rows, int cols, int seg, float eps, AffineMap map) {
   __shared__ float slots[2][32];
-  __shared__ float partial[2];
+  __shared__ float part[8][3];  // per peer: segment mean, centred sum of squares, element count
   cg::cluster_group cluster = cg::this_cluster();
+  cluster_arrive();
   const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
   const int64_t r = blockIdx.x / csize;  // grid is exactly rows * csize, so r < rows
   const int col0 = rank * seg;
@@ -177,19 +187,34 @@ __global__ void __launch_bounds__(THREADS) norm_cluster(const T* __restrict__ x,
   float v[NV][4];
   load_row<T, NV, VEC>(x + r * cols + col0, mine, threadIdx.x, THREADS, 0.0f, v);
 
-  float s = block_reduce<SumOp>(local_sum<NV>(v), slots[0]);
-  if (threadIdx.x == 0) partial[0] = s;
-  cluster.sync();
-  float total = 0.0f;
-  for (int k = 0; k < csize; ++k) total += *cluster.map_shared_rank(&partial[0], k);
-  const float mean = total / (float)cols;
+  const float s = block_reduce<SumOp>(local_sum<NV>(v), slots[0]);
+  const float mean_k = mine > 0 ? s / (float)mine : 0.0f;
+  const float q = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean_k, mine, threadIdx.x, THREADS), slots[1]);
 
-  float q = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, mine, threadIdx.x, THREADS), slots[1]);
-  if (threadIdx.x == 0) partial[1] = q;
-  cluster.sync();
-  total = 0.0f;
-  for (int k = 0; k < csize; ++k) total += *cluster.map_shared_rank(&partial[1], k);
-  const float rstd = 1.0f / sqrtf(total / (float)cols + eps);
+  cluster_wait();  // every CTA of the cluster is running: remote shared memory may be written
+  if (threadIdx.x < csize) {
+    float* dst = cluster.map_shared_rank(&part[rank][0], threadIdx.x);
+    dst[0] = mean_k;
+    dst[1] = q;
+    dst[2] = (float)mine;
+  }
+  cluster_arrive();
+  cluster_wait();
+
+  float mean = 0.0f;
+  for (int k = 0; k < csize; ++k) mean += part[k][2] * part[k][0];
+  mean /= (float)cols;
+  float m2 = 0.0f;
+  for (int k = 0; k < csize; ++k) {
+    const float d = part[k][0] - mean;
+    m2 += part[k][1] + part[k][2] * d * d;
+  }
+  const float rstd = 1.0f / sqrtf(m2 / (float)cols + eps);
+  const float shift = mean_k - mean;  // registers hold x - mean_k
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[i][k] += shift;
 
   uint32_t lq = 0, lr = 0;
   if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
@@ -199,7 +224,6 @@ __global__ void __launch_bounds__(THREADS) norm_cluster(const T* __restrict__ x,
     if (mean_out) mean_out[r] = mean;
     if (rstd_out) rstd_out[r] = rstd;
   }
-  cluster.sync();  // no CTA may exit while a peer can still read its `partial`
 }
 
 template <typename T, typename TW, int AFF>
@@ -275,13 +299,18 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   else if (a.cols <= 8192) IB200_BLOCK(512, 4)
   else if (a.cols <= 16384) IB200_BLOCK(1024, 4)
   else if (a.cols <= 131072 && a.rows * 8 < (int64_t)INT32_MAX) {
-    // cluster of 2, 4 or 8 CTAs x 1024 threads x 16 elements
-    int csize = a.cols <= 32768 ? 2 : (a.cols <= 65536 ? 4 : 8);
+    // a cluster of up to 8 CTAs per row, 16 elements per thread: the smallest CTA (256, 512 or
+    // 1024 threads) whose 8-CTA cluster still covers the row keeps several CTAs per SM, so
+    // the loads of one cluster overlap the reductions and stores of others
+    const int threads = a.cols <= 32768 ? 256 : (a.cols <= 65536 ? 512 : 1024);
+    const int64_t per_cta = (int64_t)threads * 16;
+    int csize = 1;
+    while ((int64_t)csize * per_cta < a.cols) csize *= 2;
     int seg = (int)((a.cols + csize - 1) / csize);
     seg = (seg + 3) & ~3;  // keep every segment start aligned to a 4-element vector
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(a.rows * csize));
-    cfg.blockDim = dim3(1024);
+    cfg.blockDim = dim3(threads);
     cfg.stream = a.s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -290,8 +319,13 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, norm_cluster<T, TW, 1024, 4, VEC, AFF>, x, w, b, y, a.mean, a.rstd, a.rows,
-                                       c, seg, a.eps, map);
+    cudaError_t e;
+    if (threads == 256)
+      e = cudaLaunchKernelEx(&cfg, norm_cluster<T, TW, 256, 4, VEC, AFF>, x, w, b, y, a.mean, a.rstd, a.rows, c, seg, a.eps, map);
+    else if (threads == 512)
+      e = cudaLaunchKernelEx(&cfg, norm_cluster<T, TW, 512, 4, VEC, AFF>, x, w, b, y, a.mean, a.rstd, a.rows, c, seg, a.eps, map);
+    else
+      e = cudaLaunchKernelEx(&cfg, norm_cluster<T, TW, 1024, 4, VEC, AFF>, x, w, b, y, a.mean, a.rstd, a.rows, c, seg, a.eps, map);
     if (e != cudaSuccess) return cuda_fail(e, "norm cluster launch");
   } else {
     if (AFF == AFF_GENERIC && (a.rows * a.cols) / a.inner >= (int64_t)1 << 62) return fail(IB200_ERR_UNSUPPORTED, "norm: extent too large");

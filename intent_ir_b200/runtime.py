@@ -27,7 +27,7 @@ from .errors import B200LoweringError, B200RuntimeError
 from .lowering import B200LoweredKernel, lookup_plan
 from .ops import TORCH_OF_DTYPE
 
-__all__ = ["run_b200_kernel", "run_lowered", "run_lowered_pinned", "launch_lowered", "check_plan_status"]
+__all__ = ["run_b200_kernel", "run_lowered", "run_lowered_pinned", "launch_lowered", "bind_lowered", "check_plan_status"]
 
 _WORKSPACES: Dict[Any, torch.Tensor] = {}
 
@@ -104,6 +104,30 @@ def launch_lowered(lowered: B200LoweredKernel, tensors: Mapping[str, torch.Tenso
     if rc != _lib.OK:
         raise B200RuntimeError(f"B200 plan launch failed: {_lib.last_error()} (status {rc})")
     return outs
+
+
+def bind_lowered(lowered: B200LoweredKernel, tensors: Mapping[str, torch.Tensor],
+                 outputs: Optional[Mapping[str, torch.Tensor]] = None):
+    """Validate once, launch many times: returns ``(launch, outputs)`` where ``launch()``
+    enqueues the plan on the current stream with the tensors bound here (one C call, no
+    per-launch checks or allocations).  For latency-bound plans such as a [16,256]
+    reduce_any, where argument checking would cost more than the kernel.  The bound tensors
+    must stay alive and keep their storage while ``launch`` is in use."""
+    outs = launch_lowered(lowered, tensors, outputs)  # full validation, allocates missing outputs
+    out_set = set(lowered.output_names)
+    order = [outs[n] if n in out_set else tensors[n] for n in lowered.io_spec["arg_names"]]
+    arr = (C.c_void_p * len(order))(*[t.data_ptr() or None for t in order])
+    ws = _workspace(lowered, order[0].device if order else None)
+    ws_ptr, ws_bytes, plan_ptr, n = _aligned_ptr(ws), lowered.workspace_bytes, lowered.plan.ptr, len(order)
+    fn = _lib.load().ib200_plan_launch
+    keep = (order, ws, lowered)
+
+    def launch(_keep=keep):
+        rc = fn(plan_ptr, arr, n, ws_ptr, ws_bytes, torch.cuda.current_stream().cuda_stream)
+        if rc != _lib.OK:
+            raise B200RuntimeError(f"B200 plan launch failed: {_lib.last_error()} (status {rc})")
+
+    return launch, outs
 
 
 def check_plan_status(lowered: B200LoweredKernel) -> None:
