@@ -171,7 +171,8 @@ IB200_API int ib200_gemm_bias_act(const void* a, const void* b, const void* bias
                         int32_t* status, void* stream);
 
 /* Copy the device status word to the host (this call DOES synchronise `stream`) and map a
- * non-zero word to IB200_ERR_DEVICE_WAIT. */
+ * non-zero word to IB200_ERR_DEVICE_WAIT.  With status == NULL it checks the library's own word,
+ * which the direct normalisation entry points use for their bounded waits on staged rows. */
 IB200_API int ib200_check_status(const int32_t* status, void* stream);
 
 /* out[i, j] = x[j, i] for a dense [rows, cols] matrix of 2- or 4-byte elements.

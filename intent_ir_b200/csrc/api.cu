@@ -65,16 +65,18 @@ int ib200_gemm_bias_act(const void* a, const void* b, const void* bias, void* c,
 }
 
 int ib200_check_status(const int32_t* status, void* stream) {
-  if (!status) return fail(IB200_ERR_INVALID, "check_status: null pointer");
+  if (!status) status = norm_default_status();  // the word used by the direct normalisation entry points
+  if (!status) return fail(IB200_ERR_CUDA, "check_status: no status word on this device");
   int32_t host = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   IB200_CUDA_OK(cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, s));
   IB200_CUDA_OK(cudaStreamSynchronize(s));
   if (host != 0) {
     static const char* where[] = {"", "producer waiting for a free ring stage", "MMA issuer waiting for a drained accumulator",
-                                  "MMA issuer waiting for a TMA stage", "epilogue waiting for a finished accumulator"};
-    return fail(IB200_ERR_DEVICE_WAIT, std::string("gemm: bounded device wait expired (") +
-                                           (host > 0 && host < 5 ? where[host] : "unknown site") + ")");
+                                  "MMA issuer waiting for a TMA stage", "epilogue waiting for a finished accumulator",
+                                  "normalisation waiting for a staged row segment"};
+    return fail(IB200_ERR_DEVICE_WAIT, std::string("bounded device wait expired (") +
+                                           (host > 0 && host < 6 ? where[host] : "unknown site") + ")");
   }
   return IB200_OK;
 }

@@ -44,12 +44,20 @@ int launch_softmax(const void* x, void* y, float* row_max, float* row_sum, int d
                    int64_t cols, cudaStream_t s);
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
                      int dtype, int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner,
-                     int64_t affine_period, float eps, cudaStream_t s);
+                     int64_t affine_period, float eps, cudaStream_t s, int32_t* status = nullptr);
+int32_t* norm_default_status();
 int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_dtype, int out_dtype,
                 int64_t m, int64_t n, int64_t k, int transpose_b, int act, int32_t* status,
                 cudaStream_t s);
 int launch_transpose2d(const void* x, void* out, int elem_bytes, int64_t rows, int64_t cols,
                        cudaStream_t s);
+struct GatherArgs {
+  const void* idx[4];  // one index tensor per data axis, each of n elements
+  int64_t dim[4], stride[4];
+  int64_t n;
+  int n_idx, idx_is_64;
+};
+int launch_gather(const void* data, const GatherArgs& a, void* out, int elem_bytes, double other, cudaStream_t s);
 
 #ifdef __CUDACC__
 // ---- element conversion ---------------------------------------------------------------------

@@ -86,11 +86,11 @@ __device__ __forceinline__ void store_vec4(void* p, int dtype, int64_t off, cons
 
 // one micro-op over the thread's 8 values; the opcode is uniform across the grid, so the
 // switch is a single uniform branch per instruction, not per element
-__device__ __forceinline__ void apply(uint8_t op, const float (&a)[kPerThread], const float (&b)[kPerThread],
-                                      float (&acc)[kPerThread]) {
+template <int N>
+__device__ __forceinline__ void apply(uint8_t op, const float (&a)[N], const float (&b)[N], float (&acc)[N]) {
 #define EW_CASE(OP, EXPR)                      \
   case OP:                                     \
-    _Pragma("unroll") for (int j = 0; j < kPerThread; ++j) { \
+    _Pragma("unroll") for (int j = 0; j < N; ++j) { \
       const float x = a[j], y = b[j];          \
       (void)y;                                 \
       acc[j] = (EXPR);                         \
@@ -126,85 +126,85 @@ __device__ __forceinline__ void apply(uint8_t op, const float (&a)[kPerThread], 
 #undef EW_CASE
 }
 
-// Slot file: slot s, value j (0..7), thread t.  VEC: values 4u..4u+3 form one float4 at
-// ((s*2+u)*kThreads + t)*16 bytes; scalar: value j at ((s*8+j)*kThreads + t)*4 bytes.
-template <bool VEC> __device__ __forceinline__ float* slot_ptr(float* file, int s, int j, int t) {
-  return VEC ? file + ((size_t)(s * 2 + (j >> 2)) * kThreads + t) * 4 + (j & 3) : file + ((size_t)(s * 8 + j) * kThreads + t);
+// Slot file: slot s, value j (0..N-1), thread t.  VEC: values 4u..4u+3 form one float4 at
+// ((s*N/4+u)*kThreads + t)*16 bytes; scalar: value j at ((s*N+j)*kThreads + t)*4 bytes.
+template <bool VEC, int N> __device__ __forceinline__ float* slot_ptr(float* file, int s, int j, int t) {
+  return VEC ? file + ((size_t)(s * (N / 4) + (j >> 2)) * kThreads + t) * 4 + (j & 3) : file + ((size_t)(s * N + j) * kThreads + t);
 }
 
-template <bool VEC> __device__ __forceinline__ void fetch(float (&dst)[kPerThread], uint8_t code, const float (&acc)[kPerThread],
-                                                          float imm, float* file, int t) {
+template <bool VEC, int N>
+__device__ __forceinline__ void fetch(float (&dst)[N], uint8_t code, const float (&acc)[N], float imm, float* file, int t) {
   if (code == EW_ACC) {
 #pragma unroll
-    for (int j = 0; j < kPerThread; ++j) dst[j] = acc[j];
+    for (int j = 0; j < N; ++j) dst[j] = acc[j];
   } else if (code == EW_IMM) {
 #pragma unroll
-    for (int j = 0; j < kPerThread; ++j) dst[j] = imm;
+    for (int j = 0; j < N; ++j) dst[j] = imm;
   } else if (VEC) {
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const float4 q = *reinterpret_cast<const float4*>(slot_ptr<true>(file, code, 4 * u, t));
+    for (int u = 0; u < N / 4; ++u) {
+      const float4 q = *reinterpret_cast<const float4*>(slot_ptr<true, N>(file, code, 4 * u, t));
       dst[4 * u] = q.x; dst[4 * u + 1] = q.y; dst[4 * u + 2] = q.z; dst[4 * u + 3] = q.w;
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < kPerThread; ++j) dst[j] = *slot_ptr<false>(file, code, j, t);
+    for (int j = 0; j < N; ++j) dst[j] = *slot_ptr<false, N>(file, code, j, t);
   }
 }
 
-template <bool VEC> __device__ __forceinline__ void put(const float (&src)[kPerThread], int s, float* file, int t) {
+template <bool VEC, int N> __device__ __forceinline__ void put(const float (&src)[N], int s, float* file, int t) {
   if (VEC) {
 #pragma unroll
-    for (int u = 0; u < 2; ++u)
-      *reinterpret_cast<float4*>(slot_ptr<true>(file, s, 4 * u, t)) = make_float4(src[4 * u], src[4 * u + 1], src[4 * u + 2], src[4 * u + 3]);
+    for (int u = 0; u < N / 4; ++u)
+      *reinterpret_cast<float4*>(slot_ptr<true, N>(file, s, 4 * u, t)) = make_float4(src[4 * u], src[4 * u + 1], src[4 * u + 2], src[4 * u + 3]);
   } else {
 #pragma unroll
-    for (int j = 0; j < kPerThread; ++j) *slot_ptr<false>(file, s, j, t) = src[j];
+    for (int j = 0; j < N; ++j) *slot_ptr<false, N>(file, s, j, t) = src[j];
   }
 }
 
 // The instruction loop.  Operands that are the previous result are used in place (no copy of
 // the accumulator); the opcode and operand codes are uniform, so every branch here is uniform.
-template <bool VEC>
-__device__ __forceinline__ void run_chain(const EwProgram& prog, float (&acc)[kPerThread], float* file, int t) {
+template <bool VEC, int N>
+__device__ __forceinline__ void run_chain(const EwProgram& prog, float (&acc)[N], float* file, int t) {
 #pragma unroll
-  for (int j = 0; j < kPerThread; ++j) acc[j] = 0.0f;
+  for (int j = 0; j < N; ++j) acc[j] = 0.0f;
   for (int ip = 0; ip < prog.n_instr; ++ip) {
     const EwInstr ins = prog.instr[ip];
     if (ins.op == EW_WHERE) {
-      float a[kPerThread], b[kPerThread], c[kPerThread];
-      fetch<VEC>(a, ins.a, acc, ins.imm, file, t);
-      fetch<VEC>(b, ins.b, acc, ins.imm, file, t);
-      fetch<VEC>(c, ins.c, acc, ins.imm, file, t);
+      float a[N], b[N], c[N];
+      fetch<VEC, N>(a, ins.a, acc, ins.imm, file, t);
+      fetch<VEC, N>(b, ins.b, acc, ins.imm, file, t);
+      fetch<VEC, N>(c, ins.c, acc, ins.imm, file, t);
 #pragma unroll
-      for (int j = 0; j < kPerThread; ++j) acc[j] = a[j] != 0.0f ? b[j] : c[j];
+      for (int j = 0; j < N; ++j) acc[j] = a[j] != 0.0f ? b[j] : c[j];
     } else if (ins.a == EW_ACC && ins.b == EW_ACC) {
-      apply(ins.op, acc, acc, acc);
+      apply<N>(ins.op, acc, acc, acc);
     } else if (ins.a == EW_ACC) {
-      float b[kPerThread];
-      fetch<VEC>(b, ins.b, acc, ins.imm, file, t);
-      apply(ins.op, acc, b, acc);
+      float b[N];
+      fetch<VEC, N>(b, ins.b, acc, ins.imm, file, t);
+      apply<N>(ins.op, acc, b, acc);
     } else if (ins.b == EW_ACC) {
-      float a[kPerThread];
-      fetch<VEC>(a, ins.a, acc, ins.imm, file, t);
-      apply(ins.op, a, acc, acc);
+      float a[N];
+      fetch<VEC, N>(a, ins.a, acc, ins.imm, file, t);
+      apply<N>(ins.op, a, acc, acc);
     } else {
-      float a[kPerThread], b[kPerThread];
-      fetch<VEC>(a, ins.a, acc, ins.imm, file, t);
-      fetch<VEC>(b, ins.b, acc, ins.imm, file, t);
-      apply(ins.op, a, b, acc);
+      float a[N], b[N];
+      fetch<VEC, N>(a, ins.a, acc, ins.imm, file, t);
+      fetch<VEC, N>(b, ins.b, acc, ins.imm, file, t);
+      apply<N>(ins.op, a, b, acc);
     }
-    if (ins.dst != EW_NODST) put<VEC>(acc, ins.dst, file, t);
+    if (ins.dst != EW_NODST) put<VEC, N>(acc, ins.dst, file, t);
   }
 }
 
-template <bool VEC>
-__device__ __forceinline__ void write_outputs(const EwProgram& prog, const float (&acc)[kPerThread], float* file, int t, int64_t base) {
-  constexpr int W = VEC ? 4 : 1, U = kPerThread / W;
+template <bool VEC, int N>
+__device__ __forceinline__ void write_outputs(const EwProgram& prog, const float (&acc)[N], float* file, int t, int64_t base) {
+  constexpr int W = VEC ? 4 : 1, U = N / W;
   for (int o = 0; o < prog.n_outputs; ++o) {
     const EwOutput& out = prog.out[o];
-    float v[kPerThread];
-    fetch<VEC>(v, out.src, acc, 0.0f, file, t);
+    float v[N];
+    fetch<VEC, N>(v, out.src, acc, 0.0f, file, t);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t e = base + (int64_t)(u * kThreads + t) * W;
@@ -223,11 +223,12 @@ __device__ __forceinline__ void write_outputs(const EwProgram& prog, const float
 // every operand offset below 2^31.  Operand descriptors (pointer, 32-bit strides, staging
 // mode) are read once per CTA into registers; the per-tile work is RANK-1 multiply-shift
 // divisions per vector and one 32-bit multiply-add per operand and dimension.
-template <int MAXIN, int RANK, bool VEC>
+template <int MAXIN, int RANK, bool VEC, int N>
 __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs) {
   extern __shared__ __align__(16) float file[];
   const int t = threadIdx.x;
-  constexpr int W = VEC ? 4 : 1, U = kPerThread / W;
+  constexpr int W = VEC ? 4 : 1, U = N / W;
+  constexpr int kTileN = kThreads * N;
   const char* ptr[MAXIN];
   uint32_t stride[MAXIN][RANK];
   int mode[MAXIN], dtype[MAXIN];
@@ -242,9 +243,9 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
     for (int d = 0; d < RANK; ++d) stride[k][d] = live ? (uint32_t)prog.in[k].stride[d] : 0u;
     convert |= mode[k] == EW_STAGE_ASYNC_HALF4;
   }
-  const int64_t ntiles = (prog.total + kTile - 1) / kTile;
+  const int64_t ntiles = (prog.total + kTileN - 1) / kTileN;
   for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-    const int64_t base = tile * kTile;
+    const int64_t base = tile * kTileN;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t e = base + (int64_t)(u * kThreads + t) * W;
@@ -264,7 +265,7 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
         uint32_t off = 0;
 #pragma unroll
         for (int d = 0; d < RANK; ++d) off += coord[d] * stride[k][d];
-        float* dst = slot_ptr<VEC>(file, k, u * W, t);
+        float* dst = slot_ptr<VEC, N>(file, k, u * W, t);
         switch (mode[k]) {
           case EW_STAGE_ASYNC_F32X4: cp_async16(dst, reinterpret_cast<const float*>(ptr[k]) + off); break;
           case EW_STAGE_ASYNC_HALF4: cp_async8(dst, reinterpret_cast<const uint16_t*>(ptr[k]) + off); break;
@@ -292,7 +293,7 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
         if (mode[k] != EW_STAGE_ASYNC_HALF4) continue;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          float* dst = slot_ptr<VEC>(file, k, u * W, t);
+          float* dst = slot_ptr<VEC, N>(file, k, u * W, t);
           float v[4];
           if (dtype[k] == IB200_BF16) load4<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(dst), v);
           else load4<__half>(reinterpret_cast<const __half*>(dst), v);
@@ -300,9 +301,9 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
         }
       }
     }
-    float acc[kPerThread];
-    run_chain<VEC>(prog, acc, file, t);
-    write_outputs<VEC>(prog, acc, file, t, base);
+    float acc[N];
+    run_chain<VEC, N>(prog, acc, file, t);
+    write_outputs<VEC, N>(prog, acc, file, t, base);
   }
 }
 
@@ -334,7 +335,7 @@ __global__ void __launch_bounds__(kThreads) ew_kernel(const __grid_constant__ Ew
         const EwInput& in = prog.in[k];
         int64_t off = 0;
         for (int d = 0; d < prog.rank; ++d) off += (int64_t)coord[d] * in.stride[d];
-        float* dst = slot_ptr<VEC>(file, k, u * W, t);
+        float* dst = slot_ptr<VEC, kPerThread>(file, k, u * W, t);
         if (in.kind == EW_IN_IOTA) {
           const int64_t step = in.stride[prog.rank - 1];
 #pragma unroll
@@ -372,7 +373,7 @@ __global__ void __launch_bounds__(kThreads) ew_kernel(const __grid_constant__ Ew
         if (!(in.vec_ok && in.kind == EW_IN_TENSOR && (in.dtype == IB200_BF16 || in.dtype == IB200_F16))) continue;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          float* dst = slot_ptr<VEC>(file, k, u * W, t);
+          float* dst = slot_ptr<VEC, kPerThread>(file, k, u * W, t);
           float v[4];
           if (in.dtype == IB200_BF16) load4<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(dst), v);
           else load4<__half>(reinterpret_cast<const __half*>(dst), v);
@@ -383,9 +384,9 @@ __global__ void __launch_bounds__(kThreads) ew_kernel(const __grid_constant__ Ew
 
     // ---- run the chain ---------------------------------------------------------------------
     float acc[kPerThread];
-    run_chain<VEC>(prog, acc, file, t);
+    run_chain<VEC, kPerThread>(prog, acc, file, t);
 
-    write_outputs<VEC>(prog, acc, file, t, base);
+    write_outputs<VEC, kPerThread>(prog, acc, file, t, base);
   }
 }
 
@@ -399,11 +400,6 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
     return fail(IB200_ERR_INVALID, "elementwise: malformed program");
   EwDivs divs;
   for (int d = 0; d < prog.rank; ++d) divs.d[d] = FastDiv(prog.dim[d]);
-  const size_t smem = (size_t)(prog.n_slots > 0 ? prog.n_slots : 1) * kTile * sizeof(float);
-  const int64_t tiles = (prog.total + kTile - 1) / kTile;
-  const int per_sm = (int)(220 * 1024 / smem) < 8 ? (int)(220 * 1024 / smem) : 8;
-  const int64_t cap = (int64_t)kSmCount * (per_sm > 0 ? per_sm : 1) * 4;
-  const int grid = (int)(tiles < cap ? tiles : cap);
   // staging mode per operand, and whether the specialised kernel applies
   EwProgram p = prog;
   bool fast = p.n_inputs <= 4 && p.rank <= 3;
@@ -427,13 +423,24 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
     }
   }
   void (*kern)(const EwProgram, const EwDivs) = p.vec ? ew_kernel<true> : ew_kernel<false>;
+  int per_thread = kPerThread;
   if (fast) {
     const int mi = p.n_inputs <= 2 ? 2 : 4;
-#define IB200_EW(MI, R)                                                                       \
-  if (mi == MI && p.rank == R) kern = p.vec ? ew_kernel_fast<MI, R, true> : ew_kernel_fast<MI, R, false>;
+    // 16 elements per thread for large vectorised problems: halves the interpretive overhead per element
+    const bool wide = p.vec && p.total >= (int64_t)kSmCount * kThreads * 16 * 4 && p.n_slots <= 12;
+    if (wide) per_thread = 16;
+#define IB200_EW(MI, R)                                                                                   \
+  if (mi == MI && p.rank == R)                                                                            \
+    kern = wide ? ew_kernel_fast<MI, R, true, 16> : (p.vec ? ew_kernel_fast<MI, R, true, 8> : ew_kernel_fast<MI, R, false, 8>);
     IB200_EW(2, 1) IB200_EW(2, 2) IB200_EW(2, 3) IB200_EW(4, 1) IB200_EW(4, 2) IB200_EW(4, 3)
 #undef IB200_EW
   }
+  const int tile_elems = kThreads * per_thread;
+  const size_t smem = (size_t)(p.n_slots > 0 ? p.n_slots : 1) * tile_elems * sizeof(float);
+  const int64_t tiles = (p.total + tile_elems - 1) / tile_elems;
+  const int per_sm = (int)(220 * 1024 / smem) < 8 ? (int)(220 * 1024 / smem) : 8;
+  const int64_t cap = (int64_t)kSmCount * (per_sm > 0 ? per_sm : 1) * 4;
+  const int grid = (int)(tiles < cap ? tiles : cap);
   if (smem > 48 * 1024) IB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<grid, kThreads, smem, s>>>(p, divs);
   return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "elementwise launch");

@@ -1,6 +1,8 @@
 // Layout kernels that are not arithmetic: 2-D transpose through a padded shared-memory
 // tile (coalesced 128-byte rows on both sides).  Replaces the generated transpose2d kernel
 // of the reference (backends/cuda/codegen/intentir_to_cuda.py:1487-1550).
+#include <cstring>
+
 #include "common.cuh"
 
 namespace ib200 {
@@ -28,7 +30,51 @@ __global__ void __launch_bounds__(256) transpose_kernel(const T* __restrict__ x,
   }
 }
 
+template <typename T, typename I>
+__global__ void __launch_bounds__(256) gather_kernel(const T* __restrict__ data, GatherArgs a, T* __restrict__ out, T other) {
+  for (int64_t l = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; l < a.n; l += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off = 0;
+    bool inside = true;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (k >= a.n_idx) break;
+      int64_t i = (int64_t)static_cast<const I*>(a.idx[k])[l];
+      if (i < 0) i += a.dim[k];  // numpy wraps negative indices
+      inside &= i >= 0 && i < a.dim[k];
+      off += i * a.stride[k];
+    }
+    out[l] = inside ? data[off] : other;
+  }
+}
+
+template <typename T> int run_gather(const void* data, const GatherArgs& a, void* out, double other, cudaStream_t s) {
+  const int64_t blocks = (a.n + 255) / 256;
+  const int grid = (int)(blocks < (int64_t)kSmCount * 16 ? blocks : (int64_t)kSmCount * 16);
+  T fill;
+  if (sizeof(T) == 4) { float f = (float)other; std::memcpy(&fill, &f, sizeof(T)); }
+  else if (sizeof(T) == 2) { __nv_bfloat16 h = __float2bfloat16_rn((float)other); std::memcpy(&fill, &h, sizeof(T)); }
+  else std::memset(&fill, other != 0.0, sizeof(T));
+  if (a.idx_is_64) gather_kernel<T, long long><<<grid, 256, 0, s>>>(static_cast<const T*>(data), a, static_cast<T*>(out), fill);
+  else gather_kernel<T, int><<<grid, 256, 0, s>>>(static_cast<const T*>(data), a, static_cast<T*>(out), fill);
+  return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "gather launch");
+}
+
 }  // namespace
+
+// out[l] = data[idx0[l], idx1[l], ...] (one index tensor per data axis; numpy fancy indexing,
+// verify/interpreter.py:284-291).  Out-of-range positions, which numpy rejects, read `other`
+// (the reference CUDA backend's gather2d convention, intentir_to_cuda.py:1779-1832).
+// `other` is converted as f32 / bf16 for 4- / 2-byte elements.
+int launch_gather(const void* data, const GatherArgs& a, void* out, int elem_bytes, double other, cudaStream_t s) {
+  if (a.n < 0 || a.n_idx < 1 || a.n_idx > 4) return fail(IB200_ERR_INVALID, "gather: bad arguments");
+  if (a.n == 0) return IB200_OK;
+  switch (elem_bytes) {
+    case 4: return run_gather<uint32_t>(data, a, out, other, s);
+    case 2: return run_gather<uint16_t>(data, a, out, other, s);
+    case 1: return run_gather<uint8_t>(data, a, out, other, s);
+    default: return fail(IB200_ERR_UNSUPPORTED, "gather: element size must be 1, 2 or 4 bytes");
+  }
+}
 
 int launch_transpose2d(const void* x, void* out, int elem_bytes, int64_t rows, int64_t cols, cudaStream_t s) {
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "transpose2d: negative extent");

@@ -20,6 +20,12 @@
 //   larger      : one CTA per row streaming the row three times (passes 2 and 3 hit L2).
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "async.cuh"
 #include "common.cuh"
 #include "rowio.cuh"
 
@@ -226,6 +232,104 @@ __global__ void __launch_bounds__(THREADS) norm_cluster(const T* __restrict__ x,
   }
 }
 
+// Persistent, software-pipelined variant for rows of up to 8 x 4096 elements: a group of
+// `csize` CTAs (a thread-block cluster when csize > 1) owns rows group, group + n_groups, ...
+// Each CTA stages its segment of the NEXT row into shared memory with one bulk asynchronous
+// copy (TMA, completion on an mbarrier) while it reduces, merges and writes the CURRENT row,
+// so the latency of the reductions and of the cluster barrier is hidden behind the copy
+// instead of leaving the memory system idle.  Two stages of shared memory, two sets of the
+// exchange slots (a peer can run at most one row ahead).  Statistics are those of norm_cluster;
+// they travel between the CTAs as asynchronous shared-memory stores that count bytes on the
+// receiver's mbarrier, so no cluster-wide barrier (and no fence on the row stores still in
+// flight) is needed per row.
+template <typename T, typename TW, int AFF, bool CLUSTER>
+__global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
+                                                 T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                 int64_t rows, int cols, int seg, int stage_bytes, float eps, AffineMap map,
+                                                 int32_t* status) {
+  constexpr int THREADS = 256, NV = 4;
+  extern __shared__ __align__(128) unsigned char stage_mem[];
+  __shared__ uint64_t bar[2];   // staged row segments
+  __shared__ uint64_t xbar[2];  // statistics received from the peers
+  __shared__ float slots[2][32];
+  __shared__ float part[2][8][3];
+  int csize = 1, rank = 0;
+  if (CLUSTER) {
+    cg::cluster_group cluster = cg::this_cluster();
+    csize = (int)cluster.num_blocks();
+    rank = (int)cluster.block_rank();
+  }
+  const int64_t n_groups = gridDim.x / csize, group = blockIdx.x / csize;
+  const int col0 = rank * seg;
+  const int mine = min(seg, cols - col0) > 0 ? min(seg, cols - col0) : 0;
+  const uint32_t bytes = (uint32_t)mine * sizeof(T);
+  if (threadIdx.x == 0) {
+    mbarrier_init(&bar[0], 1);
+    mbarrier_init(&bar[1], 1);
+    mbarrier_init(&xbar[0], 1);
+    mbarrier_init(&xbar[1], 1);
+    mbarrier_init_fence();
+  }
+  __syncthreads();
+  if (CLUSTER) cluster_arrive();
+  if (threadIdx.x == 0 && bytes && group < rows) {
+    mbarrier_expect_tx(&bar[0], bytes);
+    bulk_load(stage_mem, x + group * cols + col0, bytes, &bar[0]);
+  }
+  int it = 0;
+  for (int64_t r = group; r < rows; r += n_groups, ++it) {
+    const int st = it & 1;
+    if (threadIdx.x == 0 && bytes && r + n_groups < rows) {  // every thread finished reading stage st^1 one iteration ago
+      mbarrier_expect_tx(&bar[st ^ 1], bytes);
+      bulk_load(stage_mem + (st ^ 1) * stage_bytes, x + (r + n_groups) * cols + col0, bytes, &bar[st ^ 1]);
+    }
+    if (bytes && !mbarrier_wait_bounded(&bar[st], (it >> 1) & 1) && status) atomicCAS(status, 0, 5);
+    float v[NV][4];
+    load_row<T, NV, true>(reinterpret_cast<const T*>(stage_mem + st * stage_bytes), mine, threadIdx.x, THREADS, 0.0f, v);
+
+    const float s = block_reduce<SumOp>(local_sum<NV>(v), slots[0]);
+    float mean = mine > 0 ? s / (float)mine : 0.0f;
+    const float q = block_reduce<SumOp>(centre_and_square<NV, true>(v, mean, mine, threadIdx.x, THREADS), slots[1]);
+    float m2 = q;
+    if (CLUSTER) {
+      const float mean_k = mean;
+      if (it == 0) cluster_wait();  // all CTAs of the cluster are running and have initialised their barriers
+      // every CTA sends its (mean, M2, count) to every peer with stores that count bytes on the
+      // receiver's mbarrier; no cluster-wide barrier, no fence on the row stores in flight
+      if (threadIdx.x == 0) mbarrier_expect_tx(&xbar[st], (uint32_t)csize * 12u);
+      if (threadIdx.x < csize) {
+        const uint32_t dst = cluster_map(&part[st][rank][0], threadIdx.x), rbar = cluster_map(&xbar[st], threadIdx.x);
+        remote_store_signal(dst, mean_k, rbar);
+        remote_store_signal(dst + 4, q, rbar);
+        remote_store_signal(dst + 8, (float)mine, rbar);
+      }
+      if (!mbarrier_wait_bounded(&xbar[st], (it >> 1) & 1) && status) atomicCAS(status, 0, 6);
+      mean = 0.0f;
+      for (int k = 0; k < csize; ++k) mean += part[st][k][2] * part[st][k][0];
+      mean /= (float)cols;
+      m2 = 0.0f;
+      for (int k = 0; k < csize; ++k) {
+        const float d = part[st][k][0] - mean;
+        m2 += part[st][k][1] + part[st][k][2] * d * d;
+      }
+      const float shift = mean_k - mean;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[i][k] += shift;
+    }
+    const float rstd = 1.0f / sqrtf(m2 / (float)cols + eps);
+    uint32_t lq = 0, lr = 0;
+    if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
+    normalise<TW, NV, true, AFF>(v, rstd, w, b, mine, col0, threadIdx.x, THREADS, map, lq, lr);
+    store_row<T, NV, true>(y + r * cols + col0, mine, threadIdx.x, THREADS, v);
+    if (rank == 0 && threadIdx.x == 0) {
+      if (mean_out) mean_out[r] = mean;
+      if (rstd_out) rstd_out[r] = rstd;
+    }
+  }
+}
+
 template <typename T, typename TW, int AFF>
 __global__ void __launch_bounds__(1024) norm_stream(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                                                     T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -266,7 +370,65 @@ struct Args {
   int64_t rows, cols, inner, period;
   float eps;
   cudaStream_t s;
+  int32_t* status;
 };
+
+// how many groups of `csize` CTAs of a kernel can be resident at once (cached per kernel)
+template <typename K> int resident_groups(K kernel, int csize, int smem) {
+  static std::mutex mu;
+  static std::map<std::tuple<const void*, int, int, int>, int> cache;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const auto key = std::make_tuple(reinterpret_cast<const void*>(kernel), csize, smem, dev);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  int n = 0;
+  if (csize > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(csize * kSmCount);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  } else {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, smem) != cudaSuccess) { cudaGetLastError(); per_sm = 0; }
+    n = per_sm * kSmCount;
+  }
+  if (n <= 0) n = kSmCount / csize;
+  cache[key] = n;
+  return n;
+}
+
+template <typename T, typename TW, int AFF, bool CLUSTER> int launch_pipe(const Args& a, const AffineMap& map, int csize, int seg) {
+  auto kernel = norm_pipe<T, TW, AFF, CLUSTER>;
+  const int stage_bytes = (int)(((size_t)seg * sizeof(T) + 127) & ~(size_t)127);
+  const int smem = 2 * stage_bytes;
+  const int64_t resident = resident_groups(kernel, csize, smem);
+  const int64_t groups = a.rows < resident ? a.rows : resident;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(groups * csize));
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = a.s;
+  cudaLaunchAttribute attr[1];
+  if (CLUSTER) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<const T*>(a.x), static_cast<const TW*>(a.w), static_cast<const TW*>(a.b),
+                                     static_cast<T*>(a.y), a.mean, a.rstd, a.rows, (int)a.cols, seg, stage_bytes, a.eps, map, a.status);
+  return e == cudaSuccess ? IB200_OK : cuda_fail(e, "norm pipelined launch");
+}
 
 template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a) {
   const T* x = static_cast<const T*>(a.x);
@@ -278,6 +440,15 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
     map.period = FastDiv((uint32_t)a.period);
   }
   const int c = (int)a.cols;
+  if (VEC && a.cols > 4096 && a.cols <= 32768 && (a.cols * sizeof(T)) % 16 == 0) {
+    static const bool enabled = !(std::getenv("IB200_NORM_PIPE") && std::getenv("IB200_NORM_PIPE")[0] == '0');
+    int csize = 1;
+    while ((int64_t)csize * 4096 < a.cols) csize *= 2;
+    int seg = (int)((a.cols + csize - 1) / csize);
+    seg = (seg + 7) & ~7;  // segment starts and sizes stay multiples of 16 bytes for 2- and 4-byte elements
+    if (enabled && ((size_t)seg * sizeof(T)) % 16 == 0)
+      return csize == 1 ? launch_pipe<T, TW, AFF, false>(a, map, 1, seg) : launch_pipe<T, TW, AFF, true>(a, map, csize, seg);
+  }
 #define IB200_WARP(NV)                                                                                            \
   {                                                                                                               \
     const int64_t blocks = (a.rows + 3) / 4;                                                                      \
@@ -361,14 +532,33 @@ template <typename T, typename TW> int pick_mode(const Args& a) {
 
 }  // namespace
 
+// A status word for callers of the direct entry points, which pass none: set non-zero if a
+// bounded wait for a bulk copy ever ran out (read by ib200_check_status(NULL, stream)).
+static __device__ int32_t g_norm_status;
+
+int32_t* norm_default_status() {
+  static std::mutex mu;
+  static int32_t* addr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_norm_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    addr[dev] = static_cast<int32_t*>(p);
+  }
+  return addr[dev];
+}
+
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype,
                      int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps,
-                     cudaStream_t s) {
+                     cudaStream_t s, int32_t* status) {
+  if (!status) status = norm_default_status();
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "norm: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
   if (!x || !y) return fail(IB200_ERR_INVALID, "norm: null pointer");
   if ((w || b) && (affine_inner < 1 || affine_period < 1)) return fail(IB200_ERR_INVALID, "norm: affine_inner and affine_period must be >= 1");
-  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s};
+  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status};
   const int adt = (w || b) ? affine_dtype : dtype;
   switch (dtype) {
     case IB200_F32:

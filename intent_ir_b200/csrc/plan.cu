@@ -155,7 +155,7 @@ struct Buffer {
 };
 
 struct Step {
-  enum Kind { REDUCE, SOFTMAX, NORM, GEMM, ELEMENTWISE, TRANSPOSE } kind;
+  enum Kind { REDUCE, SOFTMAX, NORM, GEMM, ELEMENTWISE, TRANSPOSE, GATHER } kind;
   std::string label;
   int in[3] = {-1, -1, -1};
   int out[3] = {-1, -1, -1};
@@ -165,6 +165,10 @@ struct Step {
   float scale = 1.0f, eps = 0.0f;
   int dtype = IB200_F32, dtype2 = IB200_F32;
   int transpose_b = 0, act = 0;
+  int64_t batch = 1, batch_stride[3] = {0, 0, 0};  // batched matmul: elements between consecutive A / B / C matrices
+  std::vector<int> idx_buf;                         // gather: index buffers
+  Shape g_dim, g_stride;
+  double other = 0.0;
   EwProgram ew;
   std::vector<int> ew_in_buf, ew_out_buf;
   std::vector<int64_t> ew_in_off;  // element offsets into the input buffers
@@ -595,11 +599,13 @@ class Planner {
         n.ta = flag("transpose_a");
         n.tb = flag("transpose_b");
         Shape a = nodes_[in[0]].shape, b = nodes_[in[1]].shape;
-        if (a.size() != 2 || b.size() != 2) throw Unsupported(where + ": only rank-2 operands are covered (got " + shape_str(a) + " x " + shape_str(b) + ")");
-        if (n.ta) std::swap(a[0], a[1]);
-        if (n.tb) std::swap(b[0], b[1]);
-        if (a[1] != b[0]) throw Invalid(where + ": inner extents differ: " + shape_str(a) + " x " + shape_str(b));
-        n.shape = {a[0], b[1]};
+        if (a.size() < 2 || b.size() < 2) throw Unsupported(where + ": rank-1 operands are not covered (got " + shape_str(a) + " x " + shape_str(b) + ")");
+        if (n.ta) std::swap(a[a.size() - 1], a[a.size() - 2]);
+        if (n.tb) std::swap(b[b.size() - 1], b[b.size() - 2]);
+        if (a.back() != b[b.size() - 2]) throw Invalid(where + ": inner extents differ: " + shape_str(a) + " x " + shape_str(b));
+        n.shape = broadcast(Shape(a.begin(), a.end() - 2), Shape(b.begin(), b.end() - 2), op);  // np.matmul broadcasts the batch axes
+        n.shape.push_back(a[a.size() - 2]);
+        n.shape.push_back(b.back());
         const Json* ep = attrs->find("epilogue");
         if (ep && !ep->is_null() && !(ep->is_str() && ep->s.empty()) && !(ep->is_obj() && ep->obj.empty())) {
           const int mm = add(n);
@@ -613,6 +619,17 @@ class Planner {
           n.name = out;
           id = add(n);
         }
+      } else if (op == "gather") {
+        if (in.size() < 2) throw Invalid(where + " requires data + index tensors");
+        Node n; n.name = out; n.op = op; n.in = in; n.dclass = nodes_[in[0]].dclass;
+        if (in.size() - 1 != nodes_[in[0]].shape.size() || in.size() - 1 > 4)
+          throw Unsupported(where + ": one index tensor per data axis (at most 4) is what the gather kernel covers");
+        n.shape = nodes_[in[1]].shape;
+        for (size_t k = 2; k < in.size(); ++k)
+          if (nodes_[in[k]].shape != n.shape) throw Unsupported(where + ": index tensors of different shapes are not covered");
+        const Json* ov = attrs->find("other_value");
+        n.cval = ov && ov->is_num() ? ov->num : 0.0;
+        id = add(n);
       } else {
         throw Unsupported("op '" + op + "' is not covered by the B200 kernels (name=" + plan_->kernel_name + ")");
       }
@@ -1047,6 +1064,7 @@ class Planner {
         else if (o == rs) { s.out[2] = buf; covered[other] = 2; }
       }
       if (!all_outputs_in(covered)) continue;
+      plan_->uses_status = true;
       plan_->steps.push_back(s);
       return true;
     }
@@ -1072,7 +1090,7 @@ class Planner {
       return false;
     }
     const Node& m = nodes_[mm];
-    if (m.ta) return false;  // A^T needs a transposition pass: left to the general path
+    if (m.ta || m.shape.size() != 2) return false;  // A^T and batched products: left to the general path
     const int a = m.in[0], b = m.in[1];
     if (!is_input(a) || !is_input(b)) return false;
     const int in_dt = nodes_[a].decl_dtype;
@@ -1236,7 +1254,25 @@ class Planner {
     }
     if (op == "matmul") {
       int a = n.in[0], b = n.in[1];
+      bool tb = n.tb;
       if (n.ta) a = transposed_copy(a);
+      // a B that is a swapped-last-two-axes view of a dense tensor is consumed as stored
+      materialise(b);
+      {
+        const View& v = nodes_[b].view;
+        const size_t r = v.shape.size();
+        View sw = v;
+        std::swap(sw.shape[r - 1], sw.shape[r - 2]);
+        std::swap(sw.strides[r - 1], sw.strides[r - 2]);
+        if (!v.contiguous() && sw.contiguous()) {
+          Node alias; alias.op = "identity"; alias.in = {b}; alias.shape = sw.shape; alias.dclass = nodes_[b].dclass;
+          const int id2 = add(alias);
+          nodes_[id2].repr = Node::STRIDED;
+          nodes_[id2].view = sw;
+          b = id2;
+          tb = !tb;
+        }
+      }
       materialise_contiguous(a);
       materialise_contiguous(b);
       int adt = plan_->buffers[nodes_[a].view.buffer].dtype, bdt = plan_->buffers[nodes_[b].view.buffer].dtype;
@@ -1245,16 +1281,27 @@ class Planner {
         b = converted_copy(b, IB200_F32);
         adt = IB200_F32;
       }
+      const Shape &as = nodes_[a].shape, &bs = nodes_[b].shape;
       Step s;
       s.kind = Step::GEMM;
       s.label = "gemm";
-      s.d[0] = n.shape[0];
-      s.d[1] = n.shape[1];
-      s.d[2] = n.tb ? nodes_[b].shape[1] : nodes_[b].shape[0];
+      s.d[0] = n.shape[n.shape.size() - 2];
+      s.d[1] = n.shape.back();
+      s.d[2] = as.back();
+      s.batch = numel(n.shape) / std::max<int64_t>(1, s.d[0] * s.d[1]);
+      const int64_t abatch = numel(as) / std::max<int64_t>(1, as.back() * as[as.size() - 2]);
+      const int64_t bbatch = numel(bs) / std::max<int64_t>(1, bs.back() * bs[bs.size() - 2]);
+      if (s.d[0] * s.d[1] == 0) s.batch = 0;
+      if ((abatch != s.batch && abatch != 1) || (bbatch != s.batch && bbatch != 1))
+        throw Unsupported("matmul: partially broadcast batch axes are not covered (" + shape_str(as) + " x " + shape_str(bs) + ")");
+      s.batch_stride[0] = abatch == 1 ? 0 : s.d[0] * s.d[2];
+      s.batch_stride[1] = bbatch == 1 ? 0 : s.d[1] * s.d[2];
+      s.batch_stride[2] = s.d[0] * s.d[1];
+      if (s.batch > 1) s.label = "gemm x" + std::to_string(s.batch);
       s.in[0] = nodes_[a].view.buffer;
       s.in[1] = nodes_[b].view.buffer;
       s.dtype = adt;
-      s.transpose_b = n.tb;
+      s.transpose_b = tb;
       s.out[0] = result_buffer(id, IB200_F32);
       s.dtype2 = plan_->buffers[s.out[0]].dtype;
       if (!(s.dtype2 == IB200_F32 || s.dtype2 == IB200_BF16)) {
@@ -1263,6 +1310,38 @@ class Planner {
         s.dtype2 = IB200_F32;
       }
       plan_->uses_status = true;
+      plan_->steps.push_back(s);
+      set_strided(id, s.out[0]);
+      return;
+    }
+    if (op == "gather") {
+      materialise_contiguous(n.in[0]);
+      const Node& data = nodes_[n.in[0]];
+      Step s;
+      s.kind = Step::GATHER;
+      s.label = "gather";
+      s.in[0] = data.view.buffer;
+      s.dtype = plan_->buffers[s.in[0]].dtype;
+      s.g_dim = data.shape;
+      s.g_stride = contiguous_strides(data.shape);
+      s.other = n.cval;
+      s.d[0] = numel(n.shape);
+      int idx_dtype = -1;
+      for (size_t k = 1; k < n.in.size(); ++k) {
+        materialise_contiguous(n.in[k]);
+        const int buf = nodes_[n.in[k]].view.buffer;
+        const int dt = plan_->buffers[buf].dtype;
+        if (dt != IB200_I32 && dt != IB200_I64) throw Unsupported("gather: index tensors must be i32 or i64");
+        if (idx_dtype >= 0 && dt != idx_dtype) throw Unsupported("gather: index tensors of mixed integer types are not covered");
+        idx_dtype = dt;
+        s.idx_buf.push_back(buf);
+      }
+      s.dtype2 = idx_dtype;
+      s.out[0] = result_buffer(id, s.dtype);
+      if (plan_->buffers[s.out[0]].dtype != s.dtype) {
+        out_written_.erase(n.name);
+        s.out[0] = new_workspace_buffer(s.dtype, numel(n.shape), n.name);
+      }
       plan_->steps.push_back(s);
       set_strided(id, s.out[0]);
       return;
@@ -1431,6 +1510,15 @@ class Planner {
     }
     Shape st;
     if (!broadcast_strides(v, root_shape, st)) throw Invalid("cannot broadcast " + shape_str(v.shape) + " onto " + shape_str(root_shape));
+    // the same memory seen through the same strides is one operand, however many view nodes name it
+    for (int k = 0; k < g.prog.n_inputs; ++k)
+      if (g.prog.in[k].kind == in.kind && g.in_buf[k] == g.in_buf.back() && g.in_off[k] == g.in_off.back() && leaf_strides_[k] == st &&
+          (in.kind == EW_IN_TENSOR || true)) {
+        g.in_buf.pop_back();
+        g.in_off.pop_back();
+        g.leaf_slot[id] = k;
+        return k;
+      }
     leaf_strides_.push_back(st);
     const int slot = g.prog.n_inputs++;
     g.leaf_slot[id] = slot;
@@ -1712,7 +1800,11 @@ int ib200_plan_json(const char* intent_json, const char* bindings_json, char* ou
 
 int ib200_plan_num_args(const ib200_plan_t* plan) { return plan ? (int)plan->arg_names.size() : 0; }
 size_t ib200_plan_workspace_bytes(const ib200_plan_t* plan) { return plan ? plan->workspace_bytes : 0; }
-int ib200_plan_num_launches(const ib200_plan_t* plan) { return plan ? (int)plan->steps.size() : 0; }
+int ib200_plan_num_launches(const ib200_plan_t* plan) {
+  int n = 0;
+  if (plan) for (const Step& st : plan->steps) n += st.kind == Step::GEMM ? (int)st.batch : 1;
+  return n;
+}
 
 int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, void* workspace, size_t workspace_bytes, void* stream) {
   if (!plan) return fail(IB200_ERR_INVALID, "plan_launch: null plan");
@@ -1738,12 +1830,24 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
       case Step::NORM:
         rc = launch_norm_rows(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), static_cast<float*>(P(st.out[1])),
                               static_cast<float*>(P(st.out[2])), st.dtype, st.dtype2, st.d[0], st.d[1], st.aff_inner, st.aff_period,
-                              st.eps, s);
+                              st.eps, s, status);
         break;
       case Step::GEMM:
-        rc = launch_gemm(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), st.dtype, st.dtype2, st.d[0], st.d[1], st.d[2],
-                         st.transpose_b, st.act, status, s);
+        for (int64_t bi = 0; bi < st.batch && rc == IB200_OK; ++bi)
+          rc = launch_gemm(static_cast<const char*>(P(st.in[0])) + bi * st.batch_stride[0] * dtype_size(st.dtype),
+                           static_cast<const char*>(P(st.in[1])) + bi * st.batch_stride[1] * dtype_size(st.dtype), P(st.in[2]),
+                           static_cast<char*>(P(st.out[0])) + bi * st.batch_stride[2] * dtype_size(st.dtype2), st.dtype, st.dtype2,
+                           st.d[0], st.d[1], st.d[2], st.transpose_b, st.act, status, s);
         break;
+      case Step::GATHER: {
+        GatherArgs ga{};
+        ga.n = st.d[0];
+        ga.n_idx = (int)st.idx_buf.size();
+        ga.idx_is_64 = st.dtype2 == IB200_I64;
+        for (int k = 0; k < ga.n_idx; ++k) { ga.idx[k] = P(st.idx_buf[k]); ga.dim[k] = st.g_dim[k]; ga.stride[k] = st.g_stride[k]; }
+        rc = launch_gather(P(st.in[0]), ga, P(st.out[0]), dtype_size(st.dtype), st.other, s);
+        break;
+      }
       case Step::TRANSPOSE:
         rc = launch_transpose2d(P(st.in[0]), P(st.out[0]), dtype_size(st.dtype), st.d[0], st.d[1], s);
         break;

@@ -47,7 +47,8 @@ EXPECTED_KERNELS = {
     "softmax_inner": ["softmax"], "softmax_inner__cuda_pipeline_form": ["softmax"], "softmax_like_rowvec": ["softmax"],
     "layer_norm_persistent": ["layernorm"], "layer_norm_persistent__cuda_pipeline_form": ["layernorm"],
     "group_norm_kernel": ["groupnorm"], "matmul_bias_relu2d": ["gemm+bias+relu"], "matmul_relu2d": ["gemm+relu"],
-    "row_sum": ["reduce_sum"], "row_max": ["reduce_max"], "transpose2d": ["transpose2d"],
+    "row_sum": ["reduce_sum"], "row_max": ["reduce_max"], "transpose2d": ["transpose2d"], "gather2d": ["gather"],
+    "_attn_fwd": ["gemm", "elementwise(2 ops, 3 in, 1 out)", "softmax", "gemm"],
 }
 
 
@@ -81,8 +82,11 @@ def test_planner_general_path_and_workspace(golden_graphs):
 
 
 def test_planner_rejects_what_it_does_not_cover(golden_graphs):
-    with pytest.raises(B200LoweringError, match="gather"):
-        plan_json(golden_graphs["gather2d"]["intent"], golden_graphs["gather2d"]["shapes"])
+    rope = {"name": "r", "tensors": {n: {"dtype": "f32", "shape": s} for n, s in
+                                      {"x": ["S", "B", "H", "D"], "c": ["S", "D2"], "s": ["S", "D2"], "y": ["S", "B", "H", "D"]}.items()},
+            "ops": [{"op": "rope", "inputs": ["x", "c", "s"], "output": "y"}], "outputs": ["y"]}
+    with pytest.raises(B200LoweringError, match="rope"):
+        plan_json(rope, {"S": 4, "B": 1, "H": 2, "D": 8, "D2": 4})
     g = golden_graphs["softmax_inner"]
     with pytest.raises(B200LoweringError, match="unbound symbolic dim"):
         plan_json(g["intent"], {"M": 4})

@@ -24,8 +24,7 @@ torch = pytest.importorskip("torch")
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 with open(os.path.join(GOLDEN, "intents.json")) as _f:
     _GRAPHS = json.load(_f)
-UNCOVERED = {"gather2d": "gather", "_attn_fwd": "rank-2"}  # raise B200LoweringError (see test below)
-KEYS = sorted(k for k in _GRAPHS if k not in UNCOVERED)
+KEYS = sorted(_GRAPHS)
 
 
 def _lower_and_run(intent, bindings, inputs):
@@ -250,15 +249,40 @@ def test_config_matmul_bias_relu_bf16_4096(golden_graphs):
 
 # ---- error behaviour ---------------------------------------------------------------------------
 
-@pytest.mark.parametrize("key", sorted(UNCOVERED))
-def test_uncovered_graphs_fail_loudly(key, golden_graphs):
+def _t0(shape, dtype="f32"):
+    return {"dtype": dtype, "shape": shape, "layout": "row_major"}
+
+
+@pytest.mark.parametrize("name,js", [
+    ("rope", {"name": "r", "tensors": {"x": _t0(["S", "B", "H", "D"]), "c": _t0(["S", "D2"]), "s": _t0(["S", "D2"]), "y": _t0(["S", "B", "H", "D"])},
+              "ops": [{"op": "rope", "inputs": ["x", "c", "s"], "output": "y"}], "outputs": ["y"]}),
+    ("dropout", {"name": "d", "tensors": {"x": _t0(["M"]), "p": _t0([]), "seed": _t0([], "i32"), "y": _t0(["M"])},
+                 "ops": [{"op": "dropout", "inputs": ["x", "p", "seed"], "output": "y"}], "outputs": ["y"]}),
+    ("non-trailing", {"name": "s", "tensors": {"x": _t0(["M", "N"]), "y": _t0(["M", "N"])},
+                      "ops": [{"op": "softmax", "inputs": ["x"], "output": "y", "attrs": {"axis": 0}}], "outputs": ["y"]}),
+])
+def test_uncovered_graphs_fail_loudly(name, js):
     from intent_ir_b200.errors import B200LoweringError
     from intent_ir_b200.lowering import lower_intent_to_b200_kernel
 
-    g = golden_graphs[key]
     with pytest.raises(B200LoweringError) as e:
-        lower_intent_to_b200_kernel(IntentFunction.from_json_dict(g["intent"]), shape_bindings=g["shapes"])
-    assert UNCOVERED[key] in str(e.value)
+        lower_intent_to_b200_kernel(IntentFunction.from_json_dict(js), shape_bindings={"S": 4, "B": 2, "H": 2, "D": 8, "D2": 4, "M": 8, "N": 8})
+    assert name in str(e.value)
+
+
+def test_gather_wraps_negative_indices_and_fills_out_of_range(golden_graphs):
+    js = json.loads(json.dumps(golden_graphs["gather2d"]["intent"]))
+    js["ops"][0]["attrs"] = {"other_value": -1.0}
+    rng = np.random.default_rng(0)
+    A = rng.standard_normal((7, 9), dtype=np.float32)
+    row = rng.integers(-9, 9, size=32).astype(np.int32)
+    col = rng.integers(-11, 11, size=32).astype(np.int32)
+    out, _ = _lower_and_run(IntentFunction.from_json_dict(js), {"M": 7, "N": 9, "L": 32}, {"inp": A, "row_idx": row, "col_idx": col})
+    want = np.full(32, -1.0, np.float32)
+    for i in range(32):
+        if -7 <= row[i] < 7 and -9 <= col[i] < 9:
+            want[i] = A[row[i], col[i]]  # numpy semantics where numpy accepts the index
+    assert np.array_equal(out["out"], want)
 
 
 def test_missing_input_and_wrong_shape_raise(golden_graphs):
@@ -274,3 +298,25 @@ def test_missing_input_and_wrong_shape_raise(golden_graphs):
         run_b200_kernel(inputs_np={"A": np.zeros((4, 4), np.float32)}, **kw)
     with pytest.raises(B200RuntimeError, match="shape"):
         run_b200_kernel(inputs_np={"A": np.zeros((4, 5), np.float32), "B": np.zeros((4, 4), np.float32)}, **kw)
+
+
+@pytest.mark.parametrize("m,n,dtype", [(2048, 2048, "f32"), (1536, 4100, "f32"), (3000, 1024, "bf16"), (1031, 2053, "f32")])
+def test_large_broadcast_chain_matches_oracle(m, n, dtype):
+    """Large enough for the 16-elements-per-thread staging (and a ragged shape that is not)."""
+    from intent_ir_b200.backend import round_to_bf16
+
+    t = lambda s, d=dtype: {"dtype": d, "shape": s, "layout": "row_major"}  # noqa: E731
+    js = {"name": "chain", "tensors": {"x": t(["M", "N"]), "col": t(["N"]), "row": t(["M", 1]), "y": t(["M", "N"], "f32")},
+          "ops": [{"op": "mul", "inputs": ["x", "col"], "output": "a"}, {"op": "add", "inputs": ["a", "row"], "output": "b"},
+                  {"op": "mul", "inputs": ["b"], "output": "c", "attrs": {"mul_factor": 0.5}},
+                  {"op": "sub", "inputs": ["c", "col"], "output": "d"}, {"op": "mul", "inputs": ["d", "d"], "output": "e"},
+                  {"op": "max", "inputs": ["e", "x"], "output": "y"}], "outputs": ["y"]}
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(m + n)
+    q = round_to_bf16 if dtype == "bf16" else (lambda a: a)
+    ins = {"x": q(rng.standard_normal((m, n), dtype=np.float32)), "col": q(rng.standard_normal(n, dtype=np.float32)),
+           "row": q(rng.standard_normal((m, 1), dtype=np.float32))}
+    out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
+    assert lowered.n_launches == 1
+    want = execute_intent(intent, ins, {"M": m, "N": n})["y"]
+    _agree(out["y"], want, infer_tolerances(intent).to_dict(), "y")
