@@ -16,6 +16,8 @@
 // HBM-bound: bytes moved = each distinct operand once + each output once.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ew_program.h"
 
@@ -121,6 +123,9 @@ __device__ __forceinline__ void apply(uint8_t op, const float (&a)[N], const flo
     EW_CASE(EW_TO_INT, truncf(x))
     EW_CASE(EW_ROUND_BF16, __bfloat162float(__float2bfloat16_rn(x)))
     EW_CASE(EW_ROUND_F16, __half2float(__float2half_rn(x)))
+    EW_CASE(EW_RSUB, y - x)
+    EW_CASE(EW_RDIV, y / x)
+    EW_CASE(EW_LOADB, y)
     default: break;
   }
 #undef EW_CASE
@@ -307,6 +312,153 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
   }
 }
 
+// ---- register path -------------------------------------------------------------------------
+// Linear chains over at most three f32 operands (the common case: y = f(x, col, row, consts))
+// never touch shared memory: every operand vector is loaded straight into registers with one
+// 128-bit load (or one scalar load when the operand is constant along the innermost axis),
+// all loads are issued before the first use, and each micro-op is acc = op(acc, B) with B an
+// operand register set, an immediate or acc itself.  Operand count, which operands are
+// inner-broadcast, and the collapsed rank are template parameters, so staging is branch-free.
+struct EwRegInstr {
+  uint8_t op, src, pad[2];  // src: 0..2 operand, 3 immediate, 4 acc
+  float imm;
+};
+struct EwRegCode {
+  int32_t n_instr;
+  EwRegInstr ins[kEwMaxInstr + 1];
+};
+
+template <int NIN, int BMASK, int RANK>
+__global__ void __launch_bounds__(kThreads, 4) ew_kernel_reg(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
+                                                             const __grid_constant__ EwRegCode code) {
+  constexpr int N = 8, U = 2;
+  const int t = threadIdx.x;
+  const float* ptr[NIN > 0 ? NIN : 1];
+  uint32_t stride[NIN > 0 ? NIN : 1][RANK];
+#pragma unroll
+  for (int k = 0; k < NIN; ++k) {
+    ptr[k] = static_cast<const float*>(prog.in[k].ptr);
+#pragma unroll
+    for (int d = 0; d < RANK; ++d) stride[k][d] = (uint32_t)prog.in[k].stride[d];
+  }
+  const int64_t ntiles = (prog.total + kTile - 1) / kTile;
+  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t base = tile * kTile;
+    float in[NIN > 0 ? NIN : 1][N];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = base + (int64_t)(u * kThreads + t) * 4;
+      const bool live = e < prog.total;
+      uint32_t coord[RANK];
+      uint32_t rem = live ? (uint32_t)e : 0u;
+#pragma unroll
+      for (int d = RANK - 1; d > 0; --d) {
+        uint32_t q;
+        divs.d[d].divmod(rem, q, coord[d]);
+        rem = q;
+      }
+      coord[0] = rem;
+#pragma unroll
+      for (int k = 0; k < NIN; ++k) {
+        uint32_t off = 0;
+#pragma unroll
+        for (int d = 0; d < RANK; ++d) off += coord[d] * stride[k][d];
+        if ((BMASK >> k) & 1) {
+          const float v = live ? __ldg(ptr[k] + off) : 0.0f;
+          in[k][4 * u] = in[k][4 * u + 1] = in[k][4 * u + 2] = in[k][4 * u + 3] = v;
+        } else {
+          const float4 q = live ? __ldg(reinterpret_cast<const float4*>(ptr[k] + off)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          in[k][4 * u] = q.x; in[k][4 * u + 1] = q.y; in[k][4 * u + 2] = q.z; in[k][4 * u + 3] = q.w;
+        }
+      }
+    }
+    float acc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = 0.0f;
+    for (int ip = 0; ip < code.n_instr; ++ip) {
+      const EwRegInstr ins = code.ins[ip];
+      switch (ins.src) {
+        case 0: apply<N>(ins.op, acc, in[0], acc); break;
+        case 1: if (NIN > 1) apply<N>(ins.op, acc, in[NIN > 1 ? 1 : 0], acc); break;
+        case 2: if (NIN > 2) apply<N>(ins.op, acc, in[NIN > 2 ? 2 : 0], acc); break;
+        case 3: {
+          float b[N];
+#pragma unroll
+          for (int j = 0; j < N; ++j) b[j] = ins.imm;
+          apply<N>(ins.op, acc, b, acc);
+          break;
+        }
+        default: apply<N>(ins.op, acc, acc, acc);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = base + (int64_t)(u * kThreads + t) * 4;
+      if (e >= prog.total) continue;
+      const float q[4] = {acc[4 * u], acc[4 * u + 1], acc[4 * u + 2], acc[4 * u + 3]};
+      store_vec4(prog.out[0].ptr, prog.out[0].dtype, e, q);
+    }
+  }
+}
+
+// Translate a slot-file program into the register form, if it is a linear chain.
+bool to_register_code(const EwProgram& p, EwRegCode& code) {
+  if (!p.vec || p.n_inputs > 3 || p.n_slots != p.n_inputs || p.n_outputs != 1 || p.rank > 2) return false;
+  for (int k = 0; k < p.n_inputs; ++k) {
+    const EwInput& in = p.in[k];
+    if (in.kind != EW_IN_TENSOR || in.dtype != IB200_F32) return false;
+    if (in.mode != EW_STAGE_ASYNC_F32X4 && in.mode != EW_STAGE_BROADCAST) return false;
+  }
+  code.n_instr = 0;
+  auto emit = [&](uint8_t op, uint8_t src, float imm) {
+    EwRegInstr& r = code.ins[code.n_instr++];
+    r.op = op; r.src = src; r.imm = imm; r.pad[0] = r.pad[1] = 0;
+  };
+  auto src_of = [&](uint8_t c) -> int { return c == EW_ACC ? 4 : c == EW_IMM ? 3 : (c < p.n_inputs ? c : -1); };
+  auto reversed = [](uint8_t op) -> int {
+    switch (op) {
+      case EW_SUB: return EW_RSUB;
+      case EW_DIV: return EW_RDIV;
+      case EW_LT: return EW_GT;
+      case EW_GT: return EW_LT;
+      case EW_LE: return EW_GE;
+      case EW_GE: return EW_LE;
+      case EW_ADD: case EW_MUL: case EW_MAX: case EW_MIN: case EW_NE: case EW_AND: case EW_OR: return op;
+      default: return -1;
+    }
+  };
+  if (p.n_instr == 0) {  // a plain copy / broadcast of operand 0
+    if (p.out[0].src >= p.n_inputs) return false;
+    emit(EW_LOADB, p.out[0].src, 0.0f);
+    return true;
+  }
+  if (p.out[0].src != EW_ACC) return false;
+  for (int ip = 0; ip < p.n_instr; ++ip) {
+    const EwInstr& ins = p.instr[ip];
+    if (ins.op == EW_WHERE || ins.dst != EW_NODST || ins.op >= EW_RSUB) return false;
+    const int a = src_of(ins.a), b = src_of(ins.b);
+    if (a < 0 || b < 0) return false;
+    const bool unary = ins.op == EW_MOV || ins.op == EW_RELU || ins.op == EW_EXP || ins.op == EW_RSQRT || ins.op == EW_ABS ||
+                       ins.op == EW_FLOOR || ins.op == EW_NOT || ins.op == EW_TO_BOOL || ins.op == EW_TO_INT ||
+                       ins.op == EW_ROUND_BF16 || ins.op == EW_ROUND_F16;
+    if (unary) {
+      if (a != 4) emit(EW_LOADB, (uint8_t)a, ins.imm);
+      emit(ins.op, 4, 0.0f);
+    } else if (a == 4) {
+      emit(ins.op, (uint8_t)b, ins.imm);
+    } else if (b == 4) {
+      const int r = reversed(ins.op);
+      if (r < 0) return false;
+      emit((uint8_t)r, (uint8_t)a, ins.imm);
+    } else {  // neither operand is the running value: only legal where nothing is running yet
+      if (ip != 0) return false;
+      emit(EW_LOADB, (uint8_t)a, ins.imm);
+      emit(ins.op, (uint8_t)b, ins.imm);
+    }
+  }
+  return true;
+}
+
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads) ew_kernel(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs) {
   extern __shared__ __align__(16) float file[];
@@ -420,6 +572,27 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
       else in.mode = EW_STAGE_GATHER;
     } else {
       in.mode = in.dtype == IB200_F32 ? EW_STAGE_ASYNC_F32 : EW_STAGE_GATHER;
+    }
+  }
+  {
+    static const bool reg_path = !(std::getenv("IB200_EW_REG") && std::getenv("IB200_EW_REG")[0] == '0');
+    EwRegCode code;
+    if (reg_path && fast && to_register_code(p, code)) {
+      int bmask = 0;
+      for (int k = 0; k < p.n_inputs; ++k) bmask |= (p.in[k].mode == EW_STAGE_BROADCAST) << k;
+      void (*rk)(const EwProgram, const EwDivs, const EwRegCode) = nullptr;
+#define IB200_REG(NIN, BM, R) if (p.n_inputs == NIN && bmask == BM && p.rank == R) rk = ew_kernel_reg<NIN, BM, R>;
+#define IB200_REG_R(NIN, BM) IB200_REG(NIN, BM, 1) IB200_REG(NIN, BM, 2)
+      IB200_REG_R(0, 0) IB200_REG_R(1, 0) IB200_REG_R(1, 1) IB200_REG_R(2, 0) IB200_REG_R(2, 1) IB200_REG_R(2, 2) IB200_REG_R(2, 3)
+      IB200_REG_R(3, 0) IB200_REG_R(3, 1) IB200_REG_R(3, 2) IB200_REG_R(3, 3) IB200_REG_R(3, 4) IB200_REG_R(3, 5) IB200_REG_R(3, 6) IB200_REG_R(3, 7)
+#undef IB200_REG_R
+#undef IB200_REG
+      if (rk) {
+        const int64_t tiles = (p.total + kTile - 1) / kTile;
+        const int64_t cap = (int64_t)kSmCount * 4 * 4;
+        rk<<<(int)(tiles < cap ? tiles : cap), kThreads, 0, s>>>(p, divs, code);
+        return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "elementwise launch");
+      }
     }
   }
   void (*kern)(const EwProgram, const EwDivs) = p.vec ? ew_kernel<true> : ew_kernel<false>;

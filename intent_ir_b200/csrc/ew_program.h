@@ -27,6 +27,7 @@ enum EwOp : uint8_t {
   EW_AND, EW_OR, EW_NOT,                                     // operands are "!= 0"
   EW_WHERE,                                                  // acc = (a != 0) ? b : c
   EW_TO_BOOL, EW_TO_INT, EW_ROUND_BF16, EW_ROUND_F16,        // casts (to f32 is EW_MOV)
+  EW_RSUB, EW_RDIV, EW_LOADB,                                // b - a, b / a, acc = b (register-path forms)
   EW_NUM_OPS
 };
 
