@@ -38,6 +38,7 @@ enum Affine { AFF_NONE = 0, AFF_COL = 1, AFF_GENERIC = 2 };
 
 struct AffineMap {  // widx = (linear / inner) % period, evaluated without 64-bit division per element
   FastDiv inner, period;
+  int nowrap;  // rows start on a multiple of `inner` and never run past `period`: no modulo per element
 };
 
 template <int NV> __device__ __forceinline__ float local_sum(const float (&v)[NV][4]) {
@@ -90,8 +91,8 @@ __device__ __forceinline__ void normalise(float (&v)[NV][4], float rstd, const T
     } else if (AFF == AFF_GENERIC) {
       if (VEC && (map.inner.d & 3u) == 0) {  // the 4 elements share one channel
         const uint32_t ch = map.period.d == 1 ? 0u : (lin_q + map.inner.div(lin_r + col_offset + c));
-        uint32_t qq, idx;
-        map.period.divmod(ch, qq, idx);
+        uint32_t qq, idx = ch;
+        if (!map.nowrap) map.period.divmod(ch, qq, idx);
         const float ws = w ? to_f32<TW>(w[idx]) : 1.f, bs = b ? to_f32<TW>(b[idx]) : 0.f;
 #pragma unroll
         for (int k = 0; k < 4; ++k) { wv[k] = ws; bv[k] = bs; }
@@ -242,17 +243,18 @@ __global__ void __launch_bounds__(THREADS) norm_cluster(const T* __restrict__ x,
 // they travel between the CTAs as asynchronous shared-memory stores that count bytes on the
 // receiver's mbarrier, so no cluster-wide barrier (and no fence on the row stores still in
 // flight) is needed per row.
-template <typename T, typename TW, int AFF, bool CLUSTER>
+template <typename T, typename TW, int AFF, bool CLUSTER, int NV>
 __global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                                                  T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                  int64_t rows, int cols, int seg, int stage_bytes, float eps, AffineMap map,
                                                  int32_t* status) {
-  constexpr int THREADS = 256, NV = 4;
+  constexpr int THREADS = 256;
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ uint64_t bar[2];   // staged row segments
   __shared__ uint64_t xbar[2];  // statistics received from the peers
   __shared__ float slots[2][32];
   __shared__ float part[2][8][3];
+  __shared__ float merged[2][2];
   int csize = 1, rank = 0;
   if (CLUSTER) {
     cg::cluster_group cluster = cg::this_cluster();
@@ -283,7 +285,9 @@ __global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const 
       mbarrier_expect_tx(&bar[st ^ 1], bytes);
       bulk_load(stage_mem + (st ^ 1) * stage_bytes, x + (r + n_groups) * cols + col0, bytes, &bar[st ^ 1]);
     }
-    if (bytes && !mbarrier_wait_bounded(&bar[st], (it >> 1) & 1) && status) atomicCAS(status, 0, 5);
+    // one warp watches the mbarrier; the others sleep at the block barrier instead of spinning
+    if (threadIdx.x < 32 && bytes && !mbarrier_wait_bounded(&bar[st], (it >> 1) & 1) && status) atomicCAS(status, 0, 5);
+    __syncthreads();
     float v[NV][4];
     load_row<T, NV, true>(reinterpret_cast<const T*>(stage_mem + st * stage_bytes), mine, threadIdx.x, THREADS, 0.0f, v);
 
@@ -303,15 +307,21 @@ __global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const 
         remote_store_signal(dst + 4, q, rbar);
         remote_store_signal(dst + 8, (float)mine, rbar);
       }
-      if (!mbarrier_wait_bounded(&xbar[st], (it >> 1) & 1) && status) atomicCAS(status, 0, 6);
-      mean = 0.0f;
-      for (int k = 0; k < csize; ++k) mean += part[st][k][2] * part[st][k][0];
-      mean /= (float)cols;
-      m2 = 0.0f;
-      for (int k = 0; k < csize; ++k) {
-        const float d = part[st][k][0] - mean;
-        m2 += part[st][k][1] + part[st][k][2] * d * d;
+      // warp 0 waits for the peers' statistics and merges them (lane k owns peer k, two shuffle
+      // reductions); the other warps sleep at the block barrier and read the two merged numbers
+      if (threadIdx.x < 32) {
+        if (!mbarrier_wait_bounded(&xbar[st], (it >> 1) & 1) && status) atomicCAS(status, 0, 6);
+        const bool have = threadIdx.x < csize;
+        const float mk = have ? part[st][threadIdx.x][0] : 0.0f, qk = have ? part[st][threadIdx.x][1] : 0.0f,
+                    nk = have ? part[st][threadIdx.x][2] : 0.0f;
+        const float mu = warp_reduce<SumOp>(nk * mk) / (float)cols;
+        const float d = mk - mu;
+        const float total = warp_reduce<SumOp>(qk + nk * d * d);
+        if (threadIdx.x == 0) { merged[st][0] = mu; merged[st][1] = total; }
       }
+      __syncthreads();
+      mean = merged[st][0];
+      m2 = merged[st][1];
       const float shift = mean_k - mean;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
@@ -406,8 +416,8 @@ template <typename K> int resident_groups(K kernel, int csize, int smem) {
   return n;
 }
 
-template <typename T, typename TW, int AFF, bool CLUSTER> int launch_pipe(const Args& a, const AffineMap& map, int csize, int seg) {
-  auto kernel = norm_pipe<T, TW, AFF, CLUSTER>;
+template <typename T, typename TW, int AFF, bool CLUSTER, int NV> int launch_pipe(const Args& a, const AffineMap& map, int csize, int seg) {
+  auto kernel = norm_pipe<T, TW, AFF, CLUSTER, NV>;
   const int stage_bytes = (int)(((size_t)seg * sizeof(T) + 127) & ~(size_t)127);
   const int smem = 2 * stage_bytes;
   const int64_t resident = resident_groups(kernel, csize, smem);
@@ -435,9 +445,11 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   T* y = static_cast<T*>(a.y);
   const TW *w = static_cast<const TW*>(a.w), *b = static_cast<const TW*>(a.b);
   AffineMap map;
+  map.nowrap = 0;
   if (AFF == AFF_GENERIC) {
     map.inner = FastDiv((uint32_t)a.inner);
     map.period = FastDiv((uint32_t)a.period);
+    map.nowrap = a.cols % a.inner == 0 && a.period % (a.cols / a.inner) == 0;
   }
   const int c = (int)a.cols;
   if (VEC && a.cols > 4096 && a.cols <= 32768 && (a.cols * sizeof(T)) % 16 == 0) {
@@ -447,7 +459,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
     int seg = (int)((a.cols + csize - 1) / csize);
     seg = (seg + 7) & ~7;  // segment starts and sizes stay multiples of 16 bytes for 2- and 4-byte elements
     if (enabled && ((size_t)seg * sizeof(T)) % 16 == 0)
-      return csize == 1 ? launch_pipe<T, TW, AFF, false>(a, map, 1, seg) : launch_pipe<T, TW, AFF, true>(a, map, csize, seg);
+      return csize == 1 ? launch_pipe<T, TW, AFF, false, 4>(a, map, 1, seg) : launch_pipe<T, TW, AFF, true, 4>(a, map, csize, seg);
   }
 #define IB200_WARP(NV)                                                                                            \
   {                                                                                                               \
