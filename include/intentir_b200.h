@@ -140,6 +140,11 @@ IB200_API int ib200_reduce_any_f32(const float* x, uint8_t* out, int64_t rows, i
 IB200_API int ib200_softmax(const void* x, void* y, float* row_max, float* row_sum, int dtype, int64_t rows,
                   int64_t cols, void* stream);
 
+/* Same kernel with separate input and output types: y may be IB200_F32 for bf16 / f16 inputs
+ * (a bf16 result above 0.5 cannot meet the verifier's 1e-3 tolerance, verify/tolerances.py:111-113). */
+IB200_API int ib200_softmax_io(const void* x, void* y, float* row_max, float* row_sum, int in_dtype, int out_dtype,
+                     int64_t rows, int64_t cols, void* stream);
+
 /* Normalisation over contiguous rows of `cols` elements with centred (two-pass) variance:
  *   mean = sum(x)/cols; var = sum((x-mean)^2)/cols; rstd = 1/sqrt(var+eps);
  *   y[r, j] = (x[r, j]-mean)*rstd * w[widx] + b[widx],  widx = ((r*cols + j) / affine_inner) % affine_period

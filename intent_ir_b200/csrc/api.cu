@@ -40,6 +40,11 @@ int ib200_softmax(const void* x, void* y, float* row_max, float* row_sum, int dt
   return launch_softmax(x, y, row_max, row_sum, dtype, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
+int ib200_softmax_io(const void* x, void* y, float* row_max, float* row_sum, int in_dtype, int out_dtype, int64_t rows, int64_t cols,
+                     void* stream) {
+  return launch_softmax(x, y, row_max, row_sum, in_dtype, rows, cols, static_cast<cudaStream_t>(stream), out_dtype);
+}
+
 int ib200_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int affine_dtype,
                     int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps, void* stream) {
   return launch_norm_rows(x, w, b, y, mean, rstd, dtype, affine_dtype, rows, cols, affine_inner, affine_period, eps,

@@ -949,7 +949,8 @@ class Planner {
       s.in[0] = nodes_[x].view.buffer;
       s.out[0] = out_buffer_[oname];
       s.dtype = nodes_[x].decl_dtype;
-      if (plan_->buffers[s.out[0]].dtype != s.dtype) continue;
+      s.dtype2 = plan_->buffers[s.out[0]].dtype;
+      if (s.dtype2 != s.dtype && !(s.dtype2 == IB200_F32 && s.dtype != IB200_F32)) continue;
       for (auto& other : outputs_) {
         if (other == oname) continue;
         const int o = skip_reshapes(by_name_[other]);
@@ -1243,10 +1244,12 @@ class Planner {
       s.d[0] = s.d[1] ? numel(n.shape) / s.d[1] : 0;
       s.in[0] = x.view.buffer;
       s.dtype = xdt;
-      s.out[0] = result_buffer(id, xdt);
-      if (plan_->buffers[s.out[0]].dtype != xdt) {
+      s.out[0] = result_buffer(id, IB200_F32);  // intermediates are kept in f32
+      s.dtype2 = plan_->buffers[s.out[0]].dtype;
+      if (s.dtype2 != xdt && s.dtype2 != IB200_F32) {
         out_written_.erase(n.name);
-        s.out[0] = new_workspace_buffer(xdt, numel(n.shape), n.name);
+        s.out[0] = new_workspace_buffer(IB200_F32, numel(n.shape), n.name);
+        s.dtype2 = IB200_F32;
       }
       plan_->steps.push_back(s);
       set_strided(id, s.out[0]);
@@ -1825,7 +1828,7 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
         break;
       case Step::SOFTMAX:
         rc = launch_softmax(P(st.in[0]), P(st.out[0]), static_cast<float*>(P(st.out[1])), static_cast<float*>(P(st.out[2])), st.dtype,
-                            st.d[0], st.d[1], s);
+                            st.d[0], st.d[1], s, st.dtype2);
         break;
       case Step::NORM:
         rc = launch_norm_rows(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), static_cast<float*>(P(st.out[1])),

@@ -47,8 +47,8 @@ template <int NV> __device__ __forceinline__ void scale(float (&v)[NV][4], float
     for (int k = 0; k < 4; ++k) v[i][k] = v[i][k] / s;
 }
 
-template <typename T, int NV, bool VEC>
-__global__ void __launch_bounds__(128) softmax_warp(const T* __restrict__ x, T* __restrict__ y, float* __restrict__ row_max,
+template <typename T, typename TO, int NV, bool VEC>
+__global__ void __launch_bounds__(128) softmax_warp(const T* __restrict__ x, TO* __restrict__ y, float* __restrict__ row_max,
                                                     float* __restrict__ row_sum, int64_t rows, int cols) {
   const int lane = threadIdx.x & 31;
   const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(128) softmax_warp(const T* __restrict__ x, T* 
     const float m = warp_reduce<MaxOp>(local_max<NV>(v));
     const float s = warp_reduce<SumOp>(exp_and_sum<NV>(v, m));
     scale<NV>(v, s);
-    store_row<T, NV, VEC>(y + r * cols, cols, lane, 32, v);
+    store_row<TO, NV, VEC>(y + r * cols, cols, lane, 32, v);
     if (lane == 0) {
       if (row_max) row_max[r] = m;
       if (row_sum) row_sum[r] = s;
@@ -66,8 +66,8 @@ __global__ void __launch_bounds__(128) softmax_warp(const T* __restrict__ x, T* 
   }
 }
 
-template <typename T, int THREADS, int NV, bool VEC>
-__global__ void __launch_bounds__(THREADS) softmax_block(const T* __restrict__ x, T* __restrict__ y,
+template <typename T, typename TO, int THREADS, int NV, bool VEC>
+__global__ void __launch_bounds__(THREADS) softmax_block(const T* __restrict__ x, TO* __restrict__ y,
                                                          float* __restrict__ row_max, float* __restrict__ row_sum,
                                                          int64_t rows, int cols) {
   __shared__ float slots[2][32];
@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(THREADS) softmax_block(const T* __restrict__ x
     const float m = block_reduce<MaxOp>(local_max<NV>(v), slots[0]);
     const float s = block_reduce<SumOp>(exp_and_sum<NV>(v, m), slots[1]);
     scale<NV>(v, s);
-    store_row<T, NV, VEC>(y + r * cols, cols, threadIdx.x, THREADS, v);
+    store_row<TO, NV, VEC>(y + r * cols, cols, threadIdx.x, THREADS, v);
     if (threadIdx.x == 0) {
       if (row_max) row_max[r] = m;
       if (row_sum) row_sum[r] = s;
@@ -86,20 +86,20 @@ __global__ void __launch_bounds__(THREADS) softmax_block(const T* __restrict__ x
 }
 
 // Rows too long for registers: three passes over the row (max, sum, write).
-template <typename T>
-__global__ void __launch_bounds__(1024) softmax_stream(const T* __restrict__ x, T* __restrict__ y, float* __restrict__ row_max,
+template <typename T, typename TO>
+__global__ void __launch_bounds__(1024) softmax_stream(const T* __restrict__ x, TO* __restrict__ y, float* __restrict__ row_max,
                                                        float* __restrict__ row_sum, int64_t rows, int64_t cols) {
   __shared__ float slots[2][32];
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const T* xr = x + r * cols;
-    T* yr = y + r * cols;
+    TO* yr = y + r * cols;
     float m = -INFINITY;
     for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) m = max_nan(m, to_f32<T>(xr[c]));
     m = block_reduce<MaxOp>(m, slots[0]);
     float s = 0.0f;
     for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += expf(to_f32<T>(xr[c]) - m);
     s = block_reduce<SumOp>(s, slots[1]);
-    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) yr[c] = from_f32<T>(expf(to_f32<T>(xr[c]) - m) / s);
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) yr[c] = from_f32<TO>(expf(to_f32<T>(xr[c]) - m) / s);
     if (threadIdx.x == 0) {
       if (row_max) row_max[r] = m;
       if (row_sum) row_sum[r] = s;
@@ -107,61 +107,62 @@ __global__ void __launch_bounds__(1024) softmax_stream(const T* __restrict__ x, 
   }
 }
 
-template <typename T, int NV, bool VEC>
-void launch_warp(const T* x, T* y, float* mx, float* sm, int64_t rows, int cols, cudaStream_t s) {
+template <typename T, typename TO, int NV, bool VEC>
+void launch_warp(const T* x, TO* y, float* mx, float* sm, int64_t rows, int cols, cudaStream_t s) {
   const int64_t blocks = (rows + 3) / 4;
   const int grid = (int)(blocks < (int64_t)kSmCount * 32 ? blocks : (int64_t)kSmCount * 32);
-  softmax_warp<T, NV, VEC><<<grid, 128, 0, s>>>(x, y, mx, sm, rows, cols);
+  softmax_warp<T, TO, NV, VEC><<<grid, 128, 0, s>>>(x, y, mx, sm, rows, cols);
 }
-template <typename T, int THREADS, int NV, bool VEC>
-void launch_block(const T* x, T* y, float* mx, float* sm, int64_t rows, int cols, cudaStream_t s) {
+template <typename T, typename TO, int THREADS, int NV, bool VEC>
+void launch_block(const T* x, TO* y, float* mx, float* sm, int64_t rows, int cols, cudaStream_t s) {
   const int per_sm = 2048 / THREADS;
   const int64_t cap = (int64_t)kSmCount * per_sm * 2;
   const int grid = (int)(rows < cap ? rows : cap);
-  softmax_block<T, THREADS, NV, VEC><<<grid, THREADS, 0, s>>>(x, y, mx, sm, rows, cols);
+  softmax_block<T, TO, THREADS, NV, VEC><<<grid, THREADS, 0, s>>>(x, y, mx, sm, rows, cols);
 }
 
-template <typename T, bool VEC>
-void dispatch(const T* x, T* y, float* mx, float* sm, int64_t rows, int64_t cols, cudaStream_t s) {
+template <typename T, typename TO, bool VEC>
+void dispatch(const T* x, TO* y, float* mx, float* sm, int64_t rows, int64_t cols, cudaStream_t s) {
   const int c = (int)cols;
-  if (cols <= 128) launch_warp<T, 1, VEC>(x, y, mx, sm, rows, c, s);
-  else if (cols <= 256) launch_warp<T, 2, VEC>(x, y, mx, sm, rows, c, s);
-  else if (cols <= 512) launch_warp<T, 4, VEC>(x, y, mx, sm, rows, c, s);
-  else if (cols <= 1024) launch_warp<T, 8, VEC>(x, y, mx, sm, rows, c, s);
-  else if (cols <= 2048) launch_block<T, 256, 2, VEC>(x, y, mx, sm, rows, c, s);
-  else if (cols <= 4096) launch_block<T, 256, 4, VEC>(x, y, mx, sm, rows, c, s);
-  else if (cols <= 8192) launch_block<T, 512, 4, VEC>(x, y, mx, sm, rows, c, s);
-  else if (cols <= 16384) launch_block<T, 1024, 4, VEC>(x, y, mx, sm, rows, c, s);
+  if (cols <= 128) launch_warp<T, TO, 1, VEC>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 256) launch_warp<T, TO, 2, VEC>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 512) launch_warp<T, TO, 4, VEC>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 1024) launch_warp<T, TO, 8, VEC>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 2048) launch_block<T, TO, 256, 2, VEC>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 4096) launch_block<T, TO, 256, 4, VEC>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 8192) launch_block<T, TO, 512, 4, VEC>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 16384) launch_block<T, TO, 1024, 4, VEC>(x, y, mx, sm, rows, c, s);
   else {
     const int grid = (int)(rows < (int64_t)kSmCount * 2 ? rows : (int64_t)kSmCount * 2);
-    softmax_stream<T><<<grid, 1024, 0, s>>>(x, y, mx, sm, rows, cols);
+    softmax_stream<T, TO><<<grid, 1024, 0, s>>>(x, y, mx, sm, rows, cols);
   }
 }
 
-template <typename T>
+template <typename T, typename TO>
 int run(const void* xv, void* yv, float* mx, float* sm, int64_t rows, int64_t cols, cudaStream_t s) {
   const T* x = static_cast<const T*>(xv);
-  T* y = static_cast<T*>(yv);
+  TO* y = static_cast<TO*>(yv);
   // every row start is aligned to a 4-element vector when the bases are and cols % 4 == 0
   const bool vec = aligned16(x) && aligned16(y) && cols % 4 == 0;
-  if (vec) dispatch<T, true>(x, y, mx, sm, rows, cols, s);
-  else dispatch<T, false>(x, y, mx, sm, rows, cols, s);
+  if (vec) dispatch<T, TO, true>(x, y, mx, sm, rows, cols, s);
+  else dispatch<T, TO, false>(x, y, mx, sm, rows, cols, s);
   return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "softmax launch");
 }
 
 }  // namespace
 
 int launch_softmax(const void* x, void* y, float* row_max, float* row_sum, int dtype, int64_t rows, int64_t cols,
-                   cudaStream_t s) {
+                   cudaStream_t s, int out_dtype) {
+  if (out_dtype < 0) out_dtype = dtype;
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "softmax: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
   if (!x || !y) return fail(IB200_ERR_INVALID, "softmax: null pointer");
-  switch (dtype) {
-    case IB200_F32: return run<float>(x, y, row_max, row_sum, rows, cols, s);
-    case IB200_BF16: return run<__nv_bfloat16>(x, y, row_max, row_sum, rows, cols, s);
-    case IB200_F16: return run<__half>(x, y, row_max, row_sum, rows, cols, s);
-    default: return fail(IB200_ERR_UNSUPPORTED, "softmax: dtype must be f32, bf16 or f16");
-  }
+  if (dtype == IB200_F32 && out_dtype == IB200_F32) return run<float, float>(x, y, row_max, row_sum, rows, cols, s);
+  if (dtype == IB200_BF16 && out_dtype == IB200_BF16) return run<__nv_bfloat16, __nv_bfloat16>(x, y, row_max, row_sum, rows, cols, s);
+  if (dtype == IB200_F16 && out_dtype == IB200_F16) return run<__half, __half>(x, y, row_max, row_sum, rows, cols, s);
+  if (dtype == IB200_BF16 && out_dtype == IB200_F32) return run<__nv_bfloat16, float>(x, y, row_max, row_sum, rows, cols, s);
+  if (dtype == IB200_F16 && out_dtype == IB200_F32) return run<__half, float>(x, y, row_max, row_sum, rows, cols, s);
+  return fail(IB200_ERR_UNSUPPORTED, "softmax: x must be f32, bf16 or f16; y the same type, or f32 for 16-bit inputs");
 }
 
 }  // namespace ib200

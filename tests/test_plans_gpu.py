@@ -320,3 +320,77 @@ def test_large_broadcast_chain_matches_oracle(m, n, dtype):
     assert lowered.n_launches == 1
     want = execute_intent(intent, ins, {"M": m, "N": n})["y"]
     _agree(out["y"], want, infer_tolerances(intent).to_dict(), "y")
+
+
+def test_softmax_bf16_input_f32_output(golden_graphs):
+    from intent_ir_b200.backend import round_to_bf16
+
+    js = json.loads(json.dumps(golden_graphs["softmax_inner"]["intent"]))
+    js["tensors"]["input_ptr"]["dtype"] = "bf16"
+    intent = IntentFunction.from_json_dict(js)
+    x = round_to_bf16(3 * np.random.default_rng(8).standard_normal((300, 31), dtype=np.float32))
+    out, lowered = _lower_and_run(intent, {"M": 300, "N": 31}, {"input_ptr": x})
+    assert [s["kernel"] for s in lowered.steps] == ["softmax"]
+    want = execute_intent(intent, {"input_ptr": x})["output_ptr"]
+    assert (want > 0.5).any()  # the regime a bf16 result could not meet
+    _agree(out["output_ptr"], want, infer_tolerances(intent).to_dict(), "softmax bf16->f32")
+
+
+# ---- stage-C style checks through the same runner (verify/metamorphic.py) --------------------
+
+def _runner(key, golden_graphs):
+    from intent_ir_b200.backend import make_run_ref_fn
+
+    intent = IntentFunction.from_json_dict(golden_graphs[key]["intent"])
+    return intent, make_run_ref_fn(intent)
+
+
+def test_metamorphic_relations(golden_graphs):
+    rng = np.random.default_rng(12)
+    # any: invariant under a column permutation (metamorphic.py:309-329)
+    intent, run = _runner("any_kernel_dim", golden_graphs)
+    x = np.where(rng.random((40, 300)) < 0.01, np.float32(1), np.float32(0))
+    base = run(TestCase(shapes={"M": 40, "N": 300}, dtypes={}, seed=0, inputs={"inp": x}))["out"]
+    perm = run(TestCase(shapes={"M": 40, "N": 300}, dtypes={}, seed=0, inputs={"inp": x[:, rng.permutation(300)]}))["out"]
+    assert np.array_equal(base, perm) and base.any() and not base.all()
+    # softmax: shift invariance and column reversal (:360-420)
+    intent, run = _runner("softmax_inner", golden_graphs)
+    x = rng.standard_normal((33, 500), dtype=np.float32)
+    case = lambda a: TestCase(shapes={"M": 33, "N": 500}, dtypes={}, seed=0, inputs={"input_ptr": a})  # noqa: E731
+    y0 = run(case(x))["output_ptr"]
+    assert np.allclose(run(case(x + np.float32(0.37)))["output_ptr"], y0, atol=1e-4, rtol=1e-4)
+    assert np.allclose(run(case(x[:, ::-1].copy()))["output_ptr"][:, ::-1], y0, atol=1e-6, rtol=1e-6)
+    # layernorm / groupnorm: Y and rstd invariant under a shift of the input, mean shifts (:330-358, :460-482)
+    intent, run = _runner("layer_norm_persistent", golden_graphs)
+    w, b = rng.standard_normal(700, dtype=np.float32), rng.standard_normal(700, dtype=np.float32)
+    x = rng.standard_normal((20, 700), dtype=np.float32)
+    case = lambda a: TestCase(shapes={"M": 20, "N": 700}, dtypes={}, seed=0, inputs={"in_ptr": a, "weight_ptr": w, "bias_ptr": b})  # noqa: E731
+    o0, o1 = run(case(x)), run(case(x + np.float32(0.37)))
+    assert np.allclose(o0["out_ptr"], o1["out_ptr"], atol=1e-3, rtol=1e-3)
+    assert np.allclose(o0["out_mean_ptr"] + 0.37, o1["out_mean_ptr"], atol=1e-3) and np.allclose(o0["out_rstd_ptr"], o1["out_rstd_ptr"], rtol=1e-3)
+    intent, run = _runner("group_norm_kernel", golden_graphs)
+    shapes = {"N": 3, "C": 16, "HW": 4608, "num_groups": 2}  # rows of 36864 elements: the clustered kernel
+    x = rng.standard_normal((3, 16, 4608), dtype=np.float32)
+    w, b = rng.standard_normal(16, dtype=np.float32), rng.standard_normal(16, dtype=np.float32)
+    case = lambda a: TestCase(shapes=shapes, dtypes={}, seed=0, inputs={"X": a, "W": w, "B": b})  # noqa: E731
+    o0, o1 = run(case(x)), run(case(x + np.float32(0.37)))
+    assert np.allclose(o0["Y"], o1["Y"], atol=1e-3, rtol=1e-3)
+    assert np.allclose(o0["Mean"] + 0.37, o1["Mean"], atol=1e-3) and np.allclose(o0["Rstd"], o1["Rstd"], rtol=1e-3)
+
+
+def test_bounded_exhaustive_tiny_domains(golden_graphs):
+    """Every input over a tiny domain, as verify/metamorphic.py:664-701 enumerates them."""
+    from itertools import product
+
+    def sweep(key, shapes, name, shape, domain, fixed):
+        intent, run = _runner(key, golden_graphs)
+        cases = [TestCase(shapes=shapes, dtypes={}, seed=0, inputs={**fixed, name: np.array(v, np.float32).reshape(shape)})
+                 for v in product(domain, repeat=int(np.prod(shape)))]
+        diffs, cex = run_diff(intent, run, cases, tolerances=infer_tolerances(intent).to_dict())
+        assert len(diffs) == len(cases) and all(d.ok for d in diffs), [(c.case.inputs[name].tolist(), c.diff.summary) for c in cex[:3]]
+
+    sweep("any_kernel_dim", {"M": 2, "N": 3}, "inp", (2, 3), [0.0, 1.0], {})
+    sweep("softmax_inner", {"M": 1, "N": 2}, "input_ptr", (1, 2), [-1.0, 0.0, 1.0], {})
+    one2 = np.ones(2, np.float32)
+    sweep("layer_norm_persistent", {"M": 1, "N": 2}, "in_ptr", (1, 2), [-1.0, 0.0, 1.0], {"weight_ptr": one2, "bias_ptr": 0 * one2})
+    sweep("group_norm_kernel", {"N": 1, "C": 2, "HW": 2, "num_groups": 2}, "X", (1, 2, 2), [-1.0, 0.0, 1.0], {"W": one2, "B": 0 * one2})
