@@ -27,7 +27,7 @@ from .errors import B200LoweringError, B200RuntimeError
 from .lowering import B200LoweredKernel, lookup_plan
 from .ops import TORCH_OF_DTYPE
 
-__all__ = ["run_b200_kernel", "run_lowered", "run_lowered_pinned", "launch_lowered", "bind_lowered", "check_plan_status"]
+__all__ = ["run_b200_kernel", "run_lowered", "run_lowered_pinned", "HostPipeline", "launch_lowered", "bind_lowered", "check_plan_status"]
 
 _WORKSPACES: Dict[Any, torch.Tensor] = {}
 
@@ -212,6 +212,53 @@ def run_lowered_pinned(lowered: B200LoweredKernel, host_inputs: Mapping[str, tor
     torch.cuda.current_stream().synchronize()
     check_plan_status(lowered)
     return dict(host_outputs)
+
+
+class HostPipeline:
+    """Host buffers in, host buffers out, with the copies of consecutive calls overlapped.
+
+    ``submit(host_inputs, host_outputs)`` enqueues one run of the plan: host->device copies and
+    the kernels on one stream, the device->host copies on a second stream that waits for the
+    kernels.  With ``depth`` device buffer sets in rotation, the upload of call i+1 travels
+    while the download of call i is still on the wire (PCIe is full duplex).  ``wait()`` blocks
+    until everything submitted has landed in its host buffers and checks the plan's status word.
+    Host tensors should be pinned; a host output buffer must not be reused before ``wait()``.
+    """
+
+    def __init__(self, lowered: B200LoweredKernel, depth: int = 2, device: str = "cuda"):
+        _require_cuda()
+        self.lowered, self.depth = lowered, max(1, int(depth))
+        specs, outs = lowered.io_spec["tensors"], set(lowered.output_names)
+        self._in_names = [n for n in lowered.io_spec["arg_names"] if n not in outs]
+        mk = lambda n: torch.empty([int(d) for d in specs[n]["shape"]], dtype=TORCH_OF_DTYPE[specs[n]["dtype"]], device=device)  # noqa: E731
+        self._slots = []
+        for _ in range(self.depth):
+            ins = {n: mk(n) for n in self._in_names}
+            res = {n: mk(n) for n in lowered.output_names}
+            launch, _ = bind_lowered(lowered, ins, res)
+            self._slots.append((ins, res, launch, torch.cuda.Event(), torch.cuda.Event()))
+        self._compute, self._download = torch.cuda.Stream(), torch.cuda.Stream()
+        self._i = 0
+
+    def submit(self, host_inputs: Mapping[str, torch.Tensor], host_outputs: Mapping[str, torch.Tensor]) -> None:
+        ins, res, launch, computed, drained = self._slots[self._i % self.depth]
+        self._i += 1
+        with torch.cuda.stream(self._compute):
+            self._compute.wait_event(drained)  # this slot's previous download has finished
+            for n in self._in_names:
+                ins[n].copy_(host_inputs[n], non_blocking=True)
+            launch()
+            computed.record(self._compute)
+        with torch.cuda.stream(self._download):
+            self._download.wait_event(computed)
+            for n, t in res.items():
+                host_outputs[n].copy_(t, non_blocking=True)
+            drained.record(self._download)
+
+    def wait(self) -> None:
+        self._compute.synchronize()
+        self._download.synchronize()
+        check_plan_status(self.lowered)
 
 
 def run_b200_kernel(*, kernel_name: str = "", cuda_src: str = "", io_spec: Mapping[str, Any], launch: Any = None,
