@@ -25,8 +25,12 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint64_t* bar, uint32_t parity
 // false when the (generous) try limit ran out; the caller records that and carries on so that
 // no barrier shared with other threads or CTAs is abandoned
 __device__ __forceinline__ bool mbarrier_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t tries = 0; tries < (1u << 24); ++tries)
+  if (mbarrier_try_wait(bar, parity)) return true;
+  // back off between polls: a spinning warp would take issue slots from the warps doing the work
+  for (uint32_t tries = 0; tries < (1u << 22); ++tries) {
+    __nanosleep(tries < 8 ? 32 : 128);
     if (mbarrier_try_wait(bar, parity)) return true;
+  }
   return false;
 }
 // contiguous copy; both addresses 16-byte aligned, bytes a multiple of 16

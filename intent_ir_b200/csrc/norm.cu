@@ -39,6 +39,7 @@ enum Affine { AFF_NONE = 0, AFF_COL = 1, AFF_GENERIC = 2 };
 struct AffineMap {  // widx = (linear / inner) % period, evaluated without 64-bit division per element
   FastDiv inner, period;
   int nowrap;  // rows start on a multiple of `inner` and never run past `period`: no modulo per element
+  int small;   // rows*cols < 2^31: the row origin needs no 64-bit division
 };
 
 template <int NV> __device__ __forceinline__ float local_sum(const float (&v)[NV][4]) {
@@ -114,6 +115,13 @@ __device__ __forceinline__ void normalise(float (&v)[NV][4], float rstd, const T
 
 // quotient (mod period) and remainder of a row's first linear index by affine_inner
 __device__ __forceinline__ void row_origin(int64_t row, int64_t cols, const AffineMap& map, uint32_t& q, uint32_t& r) {
+  if (map.small) {  // multiply-shift division: a 64-bit division here would cost more than the row's arithmetic
+    const uint32_t lin = (uint32_t)row * (uint32_t)cols;
+    uint32_t qq, dummy;
+    map.inner.divmod(lin, qq, r);
+    map.period.divmod(qq, dummy, q);
+    return;
+  }
   const uint64_t lin = (uint64_t)row * (uint64_t)cols;
   const uint64_t qq = lin / map.inner.d;
   r = (uint32_t)(lin - qq * map.inner.d);
@@ -446,6 +454,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   const TW *w = static_cast<const TW*>(a.w), *b = static_cast<const TW*>(a.b);
   AffineMap map;
   map.nowrap = 0;
+  map.small = a.rows * a.cols < ((int64_t)1 << 31);
   if (AFF == AFF_GENERIC) {
     map.inner = FastDiv((uint32_t)a.inner);
     map.period = FastDiv((uint32_t)a.period);
