@@ -1,15 +1,16 @@
 // C[M,N] = act(A[M,K] · B + bias), fp32 accumulation.
 //
 // Tensor-core path (bf16 operands; K and N multiples of 8): a persistent, warp-specialised
-// sm_100a kernel, one CTA per SM, 128x256 output tiles, K in blocks of 64:
-//   warp 0   : TMA producer — cp.async.bulk.tensor (128-byte swizzle) into a 4-stage
+// sm_100a kernel, one CTA per SM, 128 x BN output tiles (BN = 256, 192 or 128, chosen per
+// problem to waste the fewest SM-waves), K in blocks of 64:
+//   warp 0   : TMA producer — cp.async.bulk.tensor (128-byte swizzle) into a 4..6-stage
 //              shared-memory ring, completion on mbarriers;
 //   warp 1   : allocates tensor memory and issues tcgen05.mma (cta_group::1, kind::f16,
-//              M=128 N=256 K=16) from one elected thread; tcgen05.commit releases ring
+//              M=128 N=BN K=16) from one elected thread; tcgen05.commit releases ring
 //              stages back to the producer and publishes finished accumulators;
 //   warps 2-5: epilogue — tcgen05.ld of the fp32 accumulator (one row per thread), + bias,
 //              activation, conversion, 16-byte stores.
-// Two 256-column accumulators fill the 512 TMEM columns, so the epilogue of tile i overlaps
+// Two accumulators of up to 256 columns share the 512 TMEM columns, so the epilogue of tile i overlaps
 // the main loop of tile i+1.  A is K-major; B is read as stored: [K,N] row-major is the
 // MN-major operand form (the descriptor's major bit), [N,K] (transpose_b) is K-major — no
 // transposition pass either way.  Every mbarrier wait is bounded: on expiry the thread
@@ -24,18 +25,26 @@
 // thread, operands staged through shared memory.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ib200 {
 namespace {
 
 // ============================== tcgen05 path ==========================================
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_STAGE_BYTES = BM * BK * 2;          // 16 KiB
-constexpr int B_STAGE_BYTES = BK * BN * 2;          // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+// The N extent of a tile is a template parameter (256, 192 or 128): the launcher picks the one
+// that minimises waves x time-per-tile for the problem at hand (narrow N, ragged tile counts).
+template <int BN> struct TileCfg {
+  static constexpr int B_STAGE_BYTES = BK * BN * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;      // 48 / 40 / 32 KiB, multiples of 1 KiB
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);     // 192 / 200 / 192 KiB of ring
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+constexpr int ACC_COLS = 256;  // TMEM columns reserved per accumulator buffer (two buffers = all 512)
 constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait, then give up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -130,9 +139,10 @@ struct GemmParams {
   int32_t* status;
 };
 
-template <typename TOut>
+template <typename TOut, int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  constexpr int STAGES = TileCfg<BN>::STAGES, STAGE_BYTES = TileCfg<BN>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -179,10 +189,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           mbar_expect_tx(&full[s], STAGE_BYTES);
           tma_load_2d(sa, &map_a, &full[s], kb * BK, m0);
           if (p.b_kmajor) {
-            tma_load_2d(sb, &map_b, &full[s], kb * BK, n0);  // one 64(K) x 256(N rows) box
+            tma_load_2d(sb, &map_b, &full[s], kb * BK, n0);  // one 64(K) x BN(N rows) box
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)  // four 64(N) x 64(K rows) boxes
+            for (int j = 0; j < BN / 64; ++j)  // BN/64 boxes of 64(N) x 64(K rows)
               tma_load_2d(sb + j * (BK * 128), &map_b, &full[s], n0 + j * 64, kb * BK);
           }
         }
@@ -210,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t acc_ph = (t_local >> 1) & 1;
         if (!(ok = mbar_wait(&acc_empty[buf], acc_ph ^ 1, abort_flag, p.status, 2))) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
+        const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -252,7 +262,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c * 32, r);
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS + c * 32, r);
         const int col0 = n0 + c * 32;
         if (row < p.M) {
 #pragma unroll
@@ -324,24 +334,50 @@ int make_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, int64_t rows
   return IB200_OK;
 }
 
-int run_tcgen05(const void* a, const void* b, const void* bias, void* c, int out_dtype, int64_t m, int64_t n, int64_t k,
+template <int BN>
+int launch_tile(const void* a, const void* b, const void* bias, void* c, int out_dtype, int64_t m, int64_t n, int64_t k,
                 int transpose_b, int act, int32_t* status, cudaStream_t s) {
   EncodeTiledFn enc;
   if (int rc = get_encoder(&enc)) return rc;
   CUtensorMap map_a, map_b;
   if (int rc = make_map(enc, &map_a, a, m, k, BM, BK)) return rc;
   if (transpose_b) {
-    if (int rc = make_map(enc, &map_b, b, n, k, BN, BK)) return rc;  // [N,K]: box 256 rows x 64 K
+    if (int rc = make_map(enc, &map_b, b, n, k, BN, BK)) return rc;  // [N,K]: box BN rows x 64 K
   } else {
     if (int rc = make_map(enc, &map_b, b, k, n, BK, 64)) return rc;  // [K,N]: box 64 K rows x 64 N
   }
   GemmParams p{(int)m, (int)n, (int)k, transpose_b ? 1 : 0, act, bias, c, status};
   const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
-  auto kern = out_dtype == IB200_BF16 ? gemm_tcgen05_kernel<__nv_bfloat16> : gemm_tcgen05_kernel<float>;
-  IB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(map_a, map_b, p);
+  auto kern = out_dtype == IB200_BF16 ? gemm_tcgen05_kernel<__nv_bfloat16, BN> : gemm_tcgen05_kernel<float, BN>;
+  IB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN>::SMEM));
+  kern<<<grid, GEMM_THREADS, TileCfg<BN>::SMEM, s>>>(map_a, map_b, p);
   return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "gemm tcgen05 launch");
+}
+
+int run_tcgen05(const void* a, const void* b, const void* bias, void* c, int out_dtype, int64_t m, int64_t n, int64_t k,
+                int transpose_b, int act, int32_t* status, cudaStream_t s) {
+  // tile width: fewest (waves of 148 CTAs) x (time per tile).  Time per output column, measured
+  // on 4096^3: 1.00 / 1.18 / 1.58 for 256 / 192 / 128 — narrower tiles re-read A more often and
+  // the main loop is bound by operand traffic into shared memory, so they only win when they
+  // save whole waves (small or ragged N)
+  const int64_t tiles_m = (m + BM - 1) / BM;
+  int best = 256;
+  double best_cost = 0.0;
+  const int widths[3] = {256, 192, 128};
+  const double penalty[3] = {1.0, 1.18, 1.58};
+  for (int i = 0; i < 3; ++i) {
+    const int64_t tiles = tiles_m * ((n + widths[i] - 1) / widths[i]);
+    const double cost = (double)((tiles + kSmCount - 1) / kSmCount) * widths[i] * penalty[i];
+    if (i == 0 || cost < best_cost) { best = widths[i]; best_cost = cost; }
+  }
+  static const char* force = std::getenv("IB200_GEMM_BN");
+  if (force) best = std::atoi(force);
+  switch (best) {
+    case 192: return launch_tile<192>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
+    case 128: return launch_tile<128>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
+    default: return launch_tile<256>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
+  }
 }
 
 // ============================== FMA path ==============================================

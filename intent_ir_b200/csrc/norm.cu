@@ -478,7 +478,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   }
 #define IB200_BLOCK(TH, NV)                                                                                       \
   {                                                                                                               \
-    const int64_t cap = (int64_t)kSmCount * (2048 / TH) * 4;                                                      \
+    const int64_t cap = (int64_t)kSmCount * (2048 / TH) * 8;                                                      \
     const int grid = (int)(a.rows < cap ? a.rows : cap);                                                          \
     norm_block<T, TW, TH, NV, VEC, AFF><<<grid, TH, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
   }

@@ -129,7 +129,7 @@ template <typename T, typename TO, int THREADS, int NV, bool VEC>
 void launch_block(const T* x, TO* y, float* mx, float* sm, int64_t rows, int cols, cudaStream_t s) {
   const int per_sm = 2048 / THREADS;
   // about one row per CTA (measured best: the hardware scheduler balances better than a grid-stride loop)
-  const int64_t cap = (int64_t)kSmCount * per_sm * 4;
+  const int64_t cap = (int64_t)kSmCount * per_sm * 8;
   const int grid = (int)(rows < cap ? rows : cap);
   softmax_block<T, TO, THREADS, NV, VEC><<<grid, THREADS, 0, s>>>(x, y, mx, sm, rows, cols);
 }
