@@ -233,6 +233,22 @@ def measure_op(name, steps, warmup, peaks):
     per = ms / steps
     out = {"workload": label, "us_per_launch": round(per * 1e3, 3), "launches_per_step": lowered.n_launches,
            "kernels": [s["kernel"] for s in lowered.steps]}
+    if nbytes < (1 << 20):  # launch-latency bound: the same plan replayed from a CUDA graph
+        import torch
+
+        from intent_ir_b200.runtime import graph_lowered
+
+        replay, _ = graph_lowered(lowered, sets[0][0], sets[0][1])
+        for _ in range(warmup):
+            replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            replay()
+        e1.record()
+        torch.cuda.synchronize()
+        out["us_per_graph_replay"] = round(e0.elapsed_time(e1) / steps * 1e3, 3)
     if flops:
         tf = flops / (per * 1e-3) / 1e12
         out.update({"tflops": round(tf, 1), "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),

@@ -114,18 +114,19 @@ def reduce(x: torch.Tensor, kind: str, dims: Sequence[int], keepdims: bool = Fal
 
 
 def softmax(x: torch.Tensor, out: Optional[torch.Tensor] = None, row_max: Optional[torch.Tensor] = None,
-            row_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Softmax over the last axis."""
+            row_sum: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Softmax over the last axis.  ``out_dtype`` (or the dtype of ``out``) may be float32 for
+    bf16 / f16 inputs."""
     _dev(x, "x")
     cols = x.shape[-1] if x.dim() else 1
     rows = x.numel() // cols if cols else 0
     if out is None:
-        out = torch.empty_like(x)
+        out = torch.empty_like(x, dtype=out_dtype or x.dtype)
     _dev(out, "out")
     for t, n in ((row_max, "row_max"), (row_sum, "row_sum")):
         if t is not None and (_dev(t, n).dtype != torch.float32 or t.numel() != rows):
             raise B200RuntimeError(f"{n} must be f32 with one element per row")
-    rc = _lib.load().ib200_softmax(_ptr(x), _ptr(out), _ptr(row_max), _ptr(row_sum), code_of(x), rows, cols, _stream())
+    rc = _lib.load().ib200_softmax_io(_ptr(x), _ptr(out), _ptr(row_max), _ptr(row_sum), code_of(x), code_of(out), rows, cols, _stream())
     _check(rc, "softmax")
     return out
 

@@ -27,7 +27,7 @@ from .errors import B200LoweringError, B200RuntimeError
 from .lowering import B200LoweredKernel, lookup_plan
 from .ops import TORCH_OF_DTYPE
 
-__all__ = ["run_b200_kernel", "run_lowered", "run_lowered_pinned", "HostPipeline", "launch_lowered", "bind_lowered", "check_plan_status"]
+__all__ = ["run_b200_kernel", "run_lowered", "run_lowered_pinned", "HostPipeline", "launch_lowered", "bind_lowered", "graph_lowered", "check_plan_status"]
 
 _WORKSPACES: Dict[Any, torch.Tensor] = {}
 
@@ -128,6 +128,25 @@ def bind_lowered(lowered: B200LoweredKernel, tensors: Mapping[str, torch.Tensor]
             raise B200RuntimeError(f"B200 plan launch failed: {_lib.last_error()} (status {rc})")
 
     return launch, outs
+
+
+def graph_lowered(lowered: B200LoweredKernel, tensors: Mapping[str, torch.Tensor],
+                  outputs: Optional[Mapping[str, torch.Tensor]] = None):
+    """Capture the plan's launches into a CUDA graph: returns ``(replay, outputs)``.  For plans
+    whose kernels are shorter than the cost of launching them (the reference's harness offers
+    the same replay mode, scripts/experiments/triton_gpu_vs_intentir_cuda.py:106-145).  The
+    bound tensors are baked into the graph; write new inputs into them before ``replay()``."""
+    launch, outs = bind_lowered(lowered, tensors, outputs)
+    launch()  # first use outside capture: module load, function attributes, workspace zero-fill
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        launch()
+
+    def replay(_keep=(launch, outs, tensors)):
+        graph.replay()
+
+    return replay, outs
 
 
 def check_plan_status(lowered: B200LoweredKernel) -> None:

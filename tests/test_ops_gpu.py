@@ -267,3 +267,40 @@ def test_transpose2d():
     from intent_ir_b200 import ops
     x = np.random.default_rng(0).standard_normal((70, 33), dtype=np.float32)
     assert np.array_equal(ops.transpose2d(_dev(x)).cpu().numpy(), x.T)
+
+
+def test_direct_c_entry_points_through_ctypes():
+    """Every convenience entry point of the header, called with raw pointers."""
+    import ctypes as C
+
+    from intent_ir_b200 import _lib
+
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((12, 96), dtype=np.float32)
+    xd = _dev(x)
+    y = torch.empty_like(xd)
+    assert lib.ib200_softmax(xd.data_ptr(), y.data_ptr(), None, None, _lib.F32, 12, 96, stream) == 0
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    _agree(y.cpu().numpy(), e / e.sum(axis=1, keepdims=True), 1e-4, 1e-4)
+    flags = torch.empty(12, dtype=torch.bool, device="cuda")
+    z = _dev(np.where(rng.random((12, 96)) < 0.02, x, np.float32(0)))
+    assert lib.ib200_reduce_any_f32(z.data_ptr(), flags.data_ptr(), 12, 96, stream) == 0
+    assert np.array_equal(flags.cpu().numpy(), (z.cpu().numpy() != 0).any(axis=1))
+    w, b = _dev(rng.standard_normal(96, dtype=np.float32)), _dev(rng.standard_normal(96, dtype=np.float32))
+    mean, rstd = torch.empty(12, device="cuda"), torch.empty(12, device="cuda")
+    assert lib.ib200_layernorm(xd.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), _lib.F32, 12, 96, 1e-5, stream) == 0
+    wy, wm, wr = _ln_ref(x, w.cpu().numpy(), b.cpu().numpy())
+    _agree(y.cpu().numpy(), wy, 1e-3, 1e-3)
+    _agree(mean.cpu().numpy(), wm, 1e-3, 1e-3)
+    g = _dev(rng.standard_normal((2, 6, 16), dtype=np.float32))
+    gy = torch.empty_like(g)
+    gm, gr = torch.empty(4, device="cuda"), torch.empty(4, device="cuda")
+    w6, b6 = _dev(np.ones(6, np.float32)), _dev(np.zeros(6, np.float32))
+    assert lib.ib200_groupnorm(g.data_ptr(), w6.data_ptr(), b6.data_ptr(), gy.data_ptr(), gm.data_ptr(), gr.data_ptr(), _lib.F32, 2, 6, 16, 2, 1e-5, stream) == 0
+    g4 = g.cpu().numpy().reshape(2, 2, 48).astype(np.float64)
+    _agree(gm.cpu().numpy(), g4.mean(axis=2).reshape(4), 1e-3, 1e-3)
+    assert lib.ib200_check_status(None, stream) == 0  # the library's own status word is clean
+    assert lib.ib200_groupnorm(g.data_ptr(), None, None, gy.data_ptr(), None, None, _lib.F32, 2, 6, 16, 4, 1e-5, stream) == _lib.ERR_INVALID
+    assert b"multiple" in lib.ib200_last_error()

@@ -394,3 +394,104 @@ def test_bounded_exhaustive_tiny_domains(golden_graphs):
     one2 = np.ones(2, np.float32)
     sweep("layer_norm_persistent", {"M": 1, "N": 2}, "in_ptr", (1, 2), [-1.0, 0.0, 1.0], {"weight_ptr": one2, "bias_ptr": 0 * one2})
     sweep("group_norm_kernel", {"N": 1, "C": 2, "HW": 2, "num_groups": 2}, "X", (1, 2, 2), [-1.0, 0.0, 1.0], {"W": one2, "B": 0 * one2})
+
+
+def test_bound_graphed_and_pipelined_launchers_agree_with_the_plain_runner(golden_graphs):
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+    from intent_ir_b200.runtime import HostPipeline, bind_lowered, graph_lowered, run_lowered
+
+    intent = IntentFunction.from_json_dict(golden_graphs["layer_norm_residual2d"]["intent"])  # a multi-kernel plan with a workspace
+    shapes = {"M": 64, "N": 192}
+    lowered = lower_intent_to_b200_kernel(intent, shape_bindings=shapes)
+    assert lowered.n_launches > 1 and lowered.workspace_bytes > 0
+    rng = np.random.default_rng(2)
+    specs, outs = lowered.io_spec["tensors"], lowered.output_names
+
+    def inputs():
+        return {n: rng.standard_normal([int(d) for d in specs[n]["shape"]]).astype(np.float32)
+                for n in lowered.io_spec["arg_names"] if n not in outs}
+
+    a, b = inputs(), inputs()
+    want_a, want_b = run_lowered(lowered, a), run_lowered(lowered, b)
+    dev = {k: torch.from_numpy(v).cuda() for k, v in a.items()}
+    launch, res = bind_lowered(lowered, dev)
+    launch()
+    torch.cuda.synchronize()
+    for n in outs:
+        assert np.array_equal(res[n].cpu().numpy(), want_a[n])
+    replay, gres = graph_lowered(lowered, dev)
+    for k, v in b.items():
+        dev[k].copy_(torch.from_numpy(v))
+    replay()
+    torch.cuda.synchronize()
+    for n in outs:
+        assert np.array_equal(gres[n].cpu().numpy(), want_b[n])
+    pipe = HostPipeline(lowered, depth=2)
+    host_in = [{k: torch.from_numpy(v).pin_memory() for k, v in d.items()} for d in (a, b, a)]
+    host_out = [{n: torch.empty([int(d) for d in specs[n]["shape"]], dtype=torch.float32).pin_memory() for n in outs} for _ in range(3)]
+    for i in range(3):
+        pipe.submit(host_in[i], host_out[i])
+    pipe.wait()
+    for i, want in enumerate((want_a, want_b, want_a)):
+        for n in outs:
+            assert np.array_equal(host_out[i][n].numpy(), want[n]), (i, n)
+
+
+@pytest.mark.parametrize("key,primary,shapes", [
+    ("softmax_inner", "input_ptr", {"M": 9, "N": 300}),
+    ("layer_norm_persistent", "in_ptr", {"M": 9, "N": 300}),
+    ("group_norm_kernel", "X", {"N": 2, "C": 8, "HW": 40, "num_groups": 2}),
+    ("matmul_bias_relu2d", "A", {"M": 16, "N": 24, "K": 40}),
+    ("add_bias2d", "inp", {"M": 9, "N": 300}),
+    ("row_max", "inp", {"M": 9, "N": 300}),
+])
+def test_numerical_stability_probes(key, primary, shapes, golden_graphs):
+    """The three probes of verify/numerical_stability.py:136-164 — a NaN, a +Inf/-Inf pair and a
+    1e4 scale injected into the primary input — with NaN positions compared explicitly (the
+    reference's comparison cannot accept any NaN) and everything else through the oracle."""
+    from intent_ir_b200.backend import default_inputs, make_run_ref_fn
+
+    intent = IntentFunction.from_json_dict(golden_graphs[key]["intent"])
+    bindings = derive_bindings(shapes)
+    base = default_inputs(intent, bindings, seed=4)
+    run = make_run_ref_fn(intent)
+    tol = infer_tolerances(intent).to_dict()
+    probes = {}
+    m = base[primary].copy(); m.reshape(-1)[0] = np.nan; probes["nan"] = m
+    m = base[primary].copy(); m.reshape(-1)[0] = np.inf; m.reshape(-1)[1] = -np.inf; probes["inf"] = m
+    probes["scale_1e4"] = (base[primary] * np.float32(1e4)).astype(np.float32)
+    for tag, arr in probes.items():
+        ins = {**base, primary: arr}
+        got = run(TestCase(shapes=shapes, dtypes={}, seed=4, inputs=ins))
+        with np.errstate(all="ignore"):
+            want = execute_intent(intent, ins, bindings)
+        for name in intent.outputs:
+            _agree(got[name], want[name], tol, f"{key}/{tag}/{name}")
+
+
+def test_mutants_are_killed(golden_graphs):
+    """verify/mutation.py in miniature: the interpreter runs a wrong variant of the graph, the
+    backend runs the original, and the diff must reject every mutant."""
+    from intent_ir_b200.backend import make_run_ref_fn
+
+    def mutate(js, fn):
+        js = json.loads(json.dumps(js))
+        fn(js)
+        return IntentFunction.from_json_dict(js)
+
+    ln = golden_graphs["layer_norm_persistent"]["intent"]
+    mm = golden_graphs["matmul_bias_relu2d"]["intent"]
+    sm = golden_graphs["softmax_inner__cuda_pipeline_form"]["intent"]
+    mutants = [
+        (ln, {"M": 8, "N": 64}, lambda j: j["ops"][6]["attrs"].update(value=1e-1)),                      # eps
+        (ln, {"M": 8, "N": 64}, lambda j: j["ops"][2].update(inputs=list(reversed(j["ops"][2]["inputs"])))),  # mean - x
+        (ln, {"M": 8, "N": 64}, lambda j: j["ops"][13].update(op="sub")),                                # - bias
+        (mm, {"M": 8, "N": 16, "K": 24}, lambda j: j["ops"][3].update(op="abs")),                         # relu -> abs
+        (mm, {"M": 8, "N": 16, "K": 24}, lambda j: j["ops"][2].update(op="sub")),                         # - bias
+        (sm, {"M": 8, "N": 64}, lambda j: j["ops"][6].update(op="mul")),                                  # div -> mul
+    ]
+    for original, shapes, fn in mutants:
+        run = make_run_ref_fn(IntentFunction.from_json_dict(original))
+        mutant = mutate(original, fn)
+        diffs, cex = run_diff(mutant, run, [TestCase(shapes=shapes, dtypes={}, seed=3)], tolerances=infer_tolerances(mutant).to_dict())
+        assert not diffs[0].ok and cex, mutant.ops
