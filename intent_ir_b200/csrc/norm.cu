@@ -66,12 +66,38 @@ __device__ __forceinline__ float centre_and_square(float (&v)[NV][4], float mean
   return q;
 }
 
+// groupnorm with large spatial extents: a thread block's whole segment [col_offset, col_offset +
+// cols) usually lies inside one channel; then w and b are two scalars per row, which can be
+// fetched before the reductions so that their latency is hidden
+struct UniformAffine {
+  bool valid = false;
+  float w = 1.0f, b = 0.0f;
+};
+template <typename TW, int AFF>
+__device__ __forceinline__ UniformAffine uniform_affine(const TW* __restrict__ w, const TW* __restrict__ b, int cols, int col_offset,
+                                                        const AffineMap& map, uint32_t lin_q, uint32_t lin_r) {
+  UniformAffine u;
+  if (AFF == AFF_GENERIC && cols > 0) {
+    const uint32_t first = map.inner.div(lin_r + col_offset), last = map.inner.div(lin_r + col_offset + cols - 1);
+    if (first == last) {
+      u.valid = true;
+      uint32_t qq, idx = lin_q + first;
+      if (!map.nowrap) map.period.divmod(lin_q + first, qq, idx);
+      if (w) u.w = to_f32<TW>(w[idx]);
+      if (b) u.b = to_f32<TW>(b[idx]);
+    }
+  }
+  return u;
+}
+
 // v <- v*rstd*w + b.  `col0` is the column of this thread's first element of the row segment,
 // `lin_q` / `lin_r` are quotient and remainder of the row's first linear index by affine_inner.
 template <typename TW, int NV, bool VEC, int AFF>
 __device__ __forceinline__ void normalise(float (&v)[NV][4], float rstd, const TW* __restrict__ w, const TW* __restrict__ b,
                                           int cols, int col_offset, int tid, int nthreads, const AffineMap& map,
-                                          uint32_t lin_q, uint32_t lin_r) {
+                                          uint32_t lin_q, uint32_t lin_r, const UniformAffine& uni) {
+  const bool uniform = uni.valid;
+  const float w_uni = uni.w, b_uni = uni.b;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int c = 4 * (i * nthreads + tid);
@@ -90,7 +116,10 @@ __device__ __forceinline__ void normalise(float (&v)[NV][4], float rstd, const T
           }
       }
     } else if (AFF == AFF_GENERIC) {
-      if (VEC && (map.inner.d & 3u) == 0) {  // the 4 elements share one channel
+      if (uniform) {  // the whole segment lies in one channel: scalars fetched once, above
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { wv[k] = w_uni; bv[k] = b_uni; }
+      } else if (VEC && (map.inner.d & 3u) == 0) {  // the 4 elements share one channel
         const uint32_t ch = map.period.d == 1 ? 0u : (lin_q + map.inner.div(lin_r + col_offset + c));
         uint32_t qq, idx = ch;
         if (!map.nowrap) map.period.divmod(ch, qq, idx);
@@ -142,7 +171,7 @@ __global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const 
     const float rstd = 1.0f / sqrtf(var + eps);
     uint32_t lq = 0, lr = 0;
     if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
-    normalise<TW, NV, VEC, AFF>(v, rstd, w, b, cols, 0, lane, 32, map, lq, lr);
+    normalise<TW, NV, VEC, AFF>(v, rstd, w, b, cols, 0, lane, 32, map, lq, lr, uniform_affine<TW, AFF>(w, b, cols, 0, map, lq, lr));
     store_row<T, NV, VEC>(y + r * cols, cols, lane, 32, v);
     if (lane == 0) {
       if (mean_out) mean_out[r] = mean;
@@ -165,7 +194,7 @@ __global__ void __launch_bounds__(THREADS) norm_block(const T* __restrict__ x, c
     const float rstd = 1.0f / sqrtf(var + eps);
     uint32_t lq = 0, lr = 0;
     if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
-    normalise<TW, NV, VEC, AFF>(v, rstd, w, b, cols, 0, threadIdx.x, THREADS, map, lq, lr);
+    normalise<TW, NV, VEC, AFF>(v, rstd, w, b, cols, 0, threadIdx.x, THREADS, map, lq, lr, uniform_affine<TW, AFF>(w, b, cols, 0, map, lq, lr));
     store_row<T, NV, VEC>(y + r * cols, cols, threadIdx.x, THREADS, v);
     if (threadIdx.x == 0) {
       if (mean_out) mean_out[r] = mean;
@@ -233,7 +262,8 @@ __global__ void __launch_bounds__(THREADS) norm_cluster(const T* __restrict__ x,
 
   uint32_t lq = 0, lr = 0;
   if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
-  normalise<TW, NV, VEC, AFF>(v, rstd, w, b, mine, col0, threadIdx.x, THREADS, map, lq, lr);
+  normalise<TW, NV, VEC, AFF>(v, rstd, w, b, mine, col0, threadIdx.x, THREADS, map, lq, lr,
+                              uniform_affine<TW, AFF>(w, b, mine, col0, map, lq, lr));
   store_row<T, NV, VEC>(y + r * cols + col0, mine, threadIdx.x, THREADS, v);
   if (rank == 0 && threadIdx.x == 0) {
     if (mean_out) mean_out[r] = mean;
@@ -293,6 +323,9 @@ __global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const 
       mbarrier_expect_tx(&bar[st ^ 1], bytes);
       bulk_load(stage_mem + (st ^ 1) * stage_bytes, x + (r + n_groups) * cols + col0, bytes, &bar[st ^ 1]);
     }
+    uint32_t lq = 0, lr = 0;
+    if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
+    const UniformAffine uni = uniform_affine<TW, AFF>(w, b, mine, col0, map, lq, lr);  // in flight during the reductions
     // one warp watches the mbarrier; the others sleep at the block barrier instead of spinning
     if (threadIdx.x < 32 && bytes && !mbarrier_wait_bounded(&bar[st], (it >> 1) & 1) && status) atomicCAS(status, 0, 5);
     __syncthreads();
@@ -337,9 +370,7 @@ __global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const 
         for (int k = 0; k < 4; ++k) v[i][k] += shift;
     }
     const float rstd = 1.0f / sqrtf(m2 / (float)cols + eps);
-    uint32_t lq = 0, lr = 0;
-    if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
-    normalise<TW, NV, true, AFF>(v, rstd, w, b, mine, col0, threadIdx.x, THREADS, map, lq, lr);
+    normalise<TW, NV, true, AFF>(v, rstd, w, b, mine, col0, threadIdx.x, THREADS, map, lq, lr, uni);
     store_row<T, NV, true>(y + r * cols + col0, mine, threadIdx.x, THREADS, v);
     if (rank == 0 && threadIdx.x == 0) {
       if (mean_out) mean_out[r] = mean;
