@@ -126,6 +126,22 @@ def workload(name):
                 lambda r: {"x": r.standard_normal((m, n), dtype=np.float32), "col": r.standard_normal(n, dtype=np.float32),
                            "row": r.standard_normal((m, 1), dtype=np.float32)},
                 2 * m * n * 4 + n * 4 + m * 4, 0, "broadcast mul/add chain, 4 ops, f32 [8192,4096]")
+    if name == "rmsnorm":
+        m, n = 8192, 4096
+        return (g["rms_norm2d"]["intent"], {"M": m, "N": n},
+                lambda r: {"inp": r.standard_normal((m, n), dtype=np.float32), "weight": r.uniform(0.5, 1.5, n).astype(np.float32)},
+                2 * m * n * 4 + n * 4 + m * 4, 0, "rms-norm f32 [8192,4096] + rstd (5 graph steps in one row program)")
+    if name == "layernorm_residual":
+        m, n = 8192, 4096
+        return (g["layer_norm_residual2d"]["intent"], {"M": m, "N": n},
+                lambda r: {"inp": r.standard_normal((m, n), dtype=np.float32), "residual": r.standard_normal((m, n), dtype=np.float32),
+                           "weight": r.uniform(0.5, 1.5, n).astype(np.float32), "bias": (0.1 * r.standard_normal(n)).astype(np.float32)},
+                3 * m * n * 4 + 2 * n * 4 + 2 * m * 4, 0, "residual add + layernorm f32 [8192,4096] + mean, rstd (one row program)")
+    if name == "masked_softmax":
+        m = n = 4096
+        return (g["masked_softmax2d"]["intent"], {"M": m, "N": n},
+                lambda r: {"inp": 3 * r.standard_normal((m, n), dtype=np.float32), "mask": r.random(n) > 0.2},
+                2 * m * n * 4 + n, 0, "masked softmax f32 [4096,4096], column mask (one row program)")
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -510,7 +526,7 @@ def main():
                                     "sample": f"{rows_sample} of {rows_full} rows, best of 3, numpy {np.__version__}, host has {os.cpu_count()} cores"}
         if not args.no_ops:
             ops = {}
-            for name in ("layernorm", "groupnorm", "matmul", "chain", "reduce_any_large", "reduce_any"):
+            for name in ("layernorm", "groupnorm", "matmul", "chain", "rmsnorm", "layernorm_residual", "masked_softmax", "reduce_any_large", "reduce_any"):
                 if name == args.workload:
                     continue
                 ops[name] = measure_op(name, max(20, min(args.steps, 100)), max(3, min(args.warmup, 10)), peaks)

@@ -19,6 +19,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "ew_device.cuh"
 #include "ew_program.h"
 
 namespace ib200 {
@@ -31,105 +32,6 @@ constexpr int kTile = kThreads * kPerThread;
 struct EwDivs {
   FastDiv d[kEwMaxRank];
 };
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
-}
-
-__device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t off) {
-  switch (dtype) {
-    case IB200_F32: return static_cast<const float*>(p)[off];
-    case IB200_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[off]);
-    case IB200_F16: return __half2float(static_cast<const __half*>(p)[off]);
-    case IB200_BOOL: case IB200_U8: return static_cast<const uint8_t*>(p)[off] ? 1.0f : 0.0f;
-    case IB200_I32: return (float)static_cast<const int32_t*>(p)[off];
-    case IB200_I64: return (float)static_cast<const long long*>(p)[off];
-    case IB200_I8: return (float)static_cast<const int8_t*>(p)[off];
-    case IB200_I16: return (float)static_cast<const int16_t*>(p)[off];
-    default: return 0.0f;
-  }
-}
-
-__device__ __forceinline__ void store_scalar(void* p, int dtype, int64_t off, float v) {
-  switch (dtype) {
-    case IB200_F32: static_cast<float*>(p)[off] = v; break;
-    case IB200_BF16: static_cast<__nv_bfloat16*>(p)[off] = __float2bfloat16_rn(v); break;
-    case IB200_F16: static_cast<__half*>(p)[off] = __float2half_rn(v); break;
-    case IB200_BOOL: case IB200_U8: static_cast<uint8_t*>(p)[off] = v != 0.0f ? 1 : 0; break;
-    case IB200_I32: static_cast<int32_t*>(p)[off] = __float2int_rz(v); break;
-    case IB200_I64: static_cast<long long*>(p)[off] = __float2ll_rz(v); break;
-    case IB200_I8: static_cast<int8_t*>(p)[off] = (int8_t)__float2int_rz(v); break;
-    case IB200_I16: static_cast<int16_t*>(p)[off] = (int16_t)__float2int_rz(v); break;
-    default: break;
-  }
-}
-
-__device__ __forceinline__ void store_vec4(void* p, int dtype, int64_t off, const float (&v)[4]) {
-  switch (dtype) {
-    case IB200_F32: store4<float>(static_cast<float*>(p) + off, v); break;
-    case IB200_BF16: store4<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p) + off, v); break;
-    case IB200_F16: store4<__half>(static_cast<__half*>(p) + off, v); break;
-    case IB200_BOOL: case IB200_U8: store4<uint8_t>(static_cast<uint8_t*>(p) + off, v); break;
-    case IB200_I32: store4<int32_t>(static_cast<int32_t*>(p) + off, v); break;
-    default:
-#pragma unroll
-      for (int k = 0; k < 4; ++k) store_scalar(p, dtype, off + k, v[k]);
-  }
-}
-
-// one micro-op over the thread's 8 values; the opcode is uniform across the grid, so the
-// switch is a single uniform branch per instruction, not per element
-template <int N>
-__device__ __forceinline__ void apply(uint8_t op, const float (&a)[N], const float (&b)[N], float (&acc)[N]) {
-#define EW_CASE(OP, EXPR)                      \
-  case OP:                                     \
-    _Pragma("unroll") for (int j = 0; j < N; ++j) { \
-      const float x = a[j], y = b[j];          \
-      (void)y;                                 \
-      acc[j] = (EXPR);                         \
-    }                                          \
-    break;
-  switch (op) {
-    EW_CASE(EW_MOV, x)
-    EW_CASE(EW_ADD, x + y)
-    EW_CASE(EW_SUB, x - y)
-    EW_CASE(EW_MUL, x * y)
-    EW_CASE(EW_DIV, x / y)
-    EW_CASE(EW_MAX, max_nan(x, y))
-    EW_CASE(EW_MIN, min_nan(x, y))
-    EW_CASE(EW_RELU, max_nan(x, 0.0f))
-    EW_CASE(EW_EXP, expf(x))
-    EW_CASE(EW_RSQRT, 1.0f / sqrtf(x))
-    EW_CASE(EW_ABS, fabsf(x))
-    EW_CASE(EW_FLOOR, floorf(x))
-    EW_CASE(EW_NE, x != y ? 1.0f : 0.0f)
-    EW_CASE(EW_LT, x < y ? 1.0f : 0.0f)
-    EW_CASE(EW_LE, x <= y ? 1.0f : 0.0f)
-    EW_CASE(EW_GT, x > y ? 1.0f : 0.0f)
-    EW_CASE(EW_GE, x >= y ? 1.0f : 0.0f)
-    EW_CASE(EW_AND, (x != 0.0f && y != 0.0f) ? 1.0f : 0.0f)
-    EW_CASE(EW_OR, (x != 0.0f || y != 0.0f) ? 1.0f : 0.0f)
-    EW_CASE(EW_NOT, x != 0.0f ? 0.0f : 1.0f)
-    EW_CASE(EW_TO_BOOL, x != 0.0f ? 1.0f : 0.0f)
-    EW_CASE(EW_TO_INT, truncf(x))
-    EW_CASE(EW_ROUND_BF16, __bfloat162float(__float2bfloat16_rn(x)))
-    EW_CASE(EW_ROUND_F16, __half2float(__float2half_rn(x)))
-    EW_CASE(EW_RSUB, y - x)
-    EW_CASE(EW_RDIV, y / x)
-    EW_CASE(EW_LOADB, y)
-    default: break;
-  }
-#undef EW_CASE
-}
 
 // Slot file: slot s, value j (0..N-1), thread t.  VEC: values 4u..4u+3 form one float4 at
 // ((s*N/4+u)*kThreads + t)*16 bytes; scalar: value j at ((s*N+j)*kThreads + t)*4 bytes.
@@ -285,6 +187,13 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
 #pragma unroll
             for (int j = 0; j < W; ++j) dst[j] = (float)(off + j * stride[k][RANK - 1]);
             break;
+          case EW_STAGE_BYTE4:
+            if (VEC) {
+              float v[4];
+              load4<uint8_t>(reinterpret_cast<const uint8_t*>(ptr[k]) + off, v);
+              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            }
+            break;
           default:  // EW_STAGE_GATHER
 #pragma unroll
             for (int j = 0; j < W; ++j) dst[j] = load_scalar(ptr[k], dtype[k], (int64_t)off + (int64_t)j * stride[k][RANK - 1]);
@@ -313,9 +222,9 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
 }
 
 // ---- register path -------------------------------------------------------------------------
-// Linear chains over at most three f32 operands (the common case: y = f(x, col, row, consts))
+// Linear chains over at most three f32 / bf16 / f16 operands (the common case: y = f(x, col, row, consts))
 // never touch shared memory: every operand vector is loaded straight into registers with one
-// 128-bit load (or one scalar load when the operand is constant along the innermost axis),
+// 128-bit (64-bit for 16-bit types) load (or one scalar load when the operand is constant along the innermost axis),
 // all loads are issued before the first use, and each micro-op is acc = op(acc, B) with B an
 // operand register set, an immediate or acc itself.  Operand count, which operands are
 // inner-broadcast, and the collapsed rank are template parameters, so staging is branch-free.
@@ -333,11 +242,13 @@ __global__ void __launch_bounds__(kThreads, 4) ew_kernel_reg(const __grid_consta
                                                              const __grid_constant__ EwRegCode code) {
   constexpr int N = 8, U = 2;
   const int t = threadIdx.x;
-  const float* ptr[NIN > 0 ? NIN : 1];
+  const char* ptr[NIN > 0 ? NIN : 1];
   uint32_t stride[NIN > 0 ? NIN : 1][RANK];
+  int half_kind[NIN > 0 ? NIN : 1];  // 0: f32, 1: bf16, 2: f16 (uniform over the grid)
 #pragma unroll
   for (int k = 0; k < NIN; ++k) {
-    ptr[k] = static_cast<const float*>(prog.in[k].ptr);
+    ptr[k] = static_cast<const char*>(prog.in[k].ptr);
+    half_kind[k] = prog.in[k].dtype == IB200_BF16 ? 1 : prog.in[k].dtype == IB200_F16 ? 2 : 0;
 #pragma unroll
     for (int d = 0; d < RANK; ++d) stride[k][d] = (uint32_t)prog.in[k].stride[d];
   }
@@ -363,12 +274,27 @@ __global__ void __launch_bounds__(kThreads, 4) ew_kernel_reg(const __grid_consta
         uint32_t off = 0;
 #pragma unroll
         for (int d = 0; d < RANK; ++d) off += coord[d] * stride[k][d];
+        float* dst = &in[k][4 * u];
         if ((BMASK >> k) & 1) {
-          const float v = live ? __ldg(ptr[k] + off) : 0.0f;
-          in[k][4 * u] = in[k][4 * u + 1] = in[k][4 * u + 2] = in[k][4 * u + 3] = v;
-        } else {
-          const float4 q = live ? __ldg(reinterpret_cast<const float4*>(ptr[k] + off)) : make_float4(0.f, 0.f, 0.f, 0.f);
-          in[k][4 * u] = q.x; in[k][4 * u + 1] = q.y; in[k][4 * u + 2] = q.z; in[k][4 * u + 3] = q.w;
+          float v = 0.0f;
+          if (live) {
+            if (half_kind[k] == 0) v = __ldg(reinterpret_cast<const float*>(ptr[k]) + off);
+            else if (half_kind[k] == 1) v = __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(ptr[k]) + off));
+            else v = __half2float(__ldg(reinterpret_cast<const __half*>(ptr[k]) + off));
+          }
+          dst[0] = dst[1] = dst[2] = dst[3] = v;
+        } else if (half_kind[k] == 0) {
+          const float4 q = live ? __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ptr[k]) + off)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          dst[0] = q.x; dst[1] = q.y; dst[2] = q.z; dst[3] = q.w;
+        } else {  // four 16-bit elements in one 64-bit load
+          const uint2 q = live ? __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(ptr[k]) + off)) : make_uint2(0u, 0u);
+          if (half_kind[k] == 1) {
+            dst[0] = __uint_as_float(q.x << 16); dst[1] = __uint_as_float(q.x & 0xffff0000u);
+            dst[2] = __uint_as_float(q.y << 16); dst[3] = __uint_as_float(q.y & 0xffff0000u);
+          } else {
+            const __half2 lo = *reinterpret_cast<const __half2*>(&q.x), hi = *reinterpret_cast<const __half2*>(&q.y);
+            dst[0] = __low2float(lo); dst[1] = __high2float(lo); dst[2] = __low2float(hi); dst[3] = __high2float(hi);
+          }
         }
       }
     }
@@ -406,8 +332,8 @@ bool to_register_code(const EwProgram& p, EwRegCode& code) {
   if (!p.vec || p.n_inputs > 3 || p.n_slots != p.n_inputs || p.n_outputs != 1 || p.rank > 2) return false;
   for (int k = 0; k < p.n_inputs; ++k) {
     const EwInput& in = p.in[k];
-    if (in.kind != EW_IN_TENSOR || in.dtype != IB200_F32) return false;
-    if (in.mode != EW_STAGE_ASYNC_F32X4 && in.mode != EW_STAGE_BROADCAST) return false;
+    if (in.kind != EW_IN_TENSOR || (in.dtype != IB200_F32 && in.dtype != IB200_BF16 && in.dtype != IB200_F16)) return false;
+    if (in.mode != EW_STAGE_ASYNC_F32X4 && in.mode != EW_STAGE_ASYNC_HALF4 && in.mode != EW_STAGE_BROADCAST) return false;
   }
   code.n_instr = 0;
   auto emit = [&](uint8_t op, uint8_t src, float imm) {
@@ -568,6 +494,7 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
     else if (p.vec) {
       if (in.vec_ok && in.dtype == IB200_F32) in.mode = EW_STAGE_ASYNC_F32X4;
       else if (in.vec_ok && (in.dtype == IB200_BF16 || in.dtype == IB200_F16)) in.mode = EW_STAGE_ASYNC_HALF4;
+      else if (in.vec_ok && (in.dtype == IB200_BOOL || in.dtype == IB200_U8)) in.mode = EW_STAGE_BYTE4;
       else if (inner == 0) in.mode = EW_STAGE_BROADCAST;
       else in.mode = EW_STAGE_GATHER;
     } else {

@@ -56,6 +56,7 @@ enum EwStageMode : int32_t {  // how an operand reaches the slot file
   EW_STAGE_BROADCAST,    // one scalar load, replicated (inner stride 0)
   EW_STAGE_GATHER,       // scalar loads with the inner stride
   EW_STAGE_IOTA,         // value = offset
+  EW_STAGE_BYTE4,        // one 32-bit load of 4 contiguous bool / u8 values, widened to 4 floats
 };
 
 struct EwInput {

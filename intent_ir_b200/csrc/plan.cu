@@ -23,17 +23,20 @@
 //      become single micro-op kernels (ew_program.h); reductions, softmax, matmul and
 //      transposes become their kernels; intermediates live in a caller-provided workspace.
 #include <algorithm>
+#include <cstdlib>
 #include <deque>
 #include <functional>
 #include <map>
 #include <memory>
 #include <set>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "common.cuh"
 #include "ew_program.h"
 #include "json.hpp"
+#include "row_program.h"
 
 namespace ib200 {
 namespace {
@@ -155,7 +158,7 @@ struct Buffer {
 };
 
 struct Step {
-  enum Kind { REDUCE, SOFTMAX, NORM, GEMM, ELEMENTWISE, TRANSPOSE, GATHER } kind;
+  enum Kind { REDUCE, SOFTMAX, NORM, GEMM, ELEMENTWISE, TRANSPOSE, GATHER, ROWFUSE } kind;
   std::string label;
   int in[3] = {-1, -1, -1};
   int out[3] = {-1, -1, -1};
@@ -172,6 +175,10 @@ struct Step {
   EwProgram ew;
   std::vector<int> ew_in_buf, ew_out_buf;
   std::vector<int64_t> ew_in_off;  // element offsets into the input buffers
+  // ROWFUSE: several of the steps above run as one row program
+  RowProgram row;
+  std::vector<int> row_in_buf, row_load_buf, row_out_buf;  // per RowInput / RowScalarLoad / RowOutput (-1: none)
+  std::vector<int64_t> row_in_off, row_load_off;
 };
 
 }  // namespace
@@ -207,6 +214,7 @@ class Planner {
     plan_->kernel_name = nm && nm->is_str() ? nm->s : "intent_fn";
     build();
     if (!match_fused()) lower_general();
+    fuse_rows();
     finish();
     return std::move(plan_);
   }
@@ -1690,7 +1698,555 @@ class Planner {
     return true;
   }
 
+  // =============================== row fusion ===============================================
+  // Runs of steps that all work row by row on one [R, C] problem (elementwise chains over
+  // [R, C] or over the R per-row results, reductions along the row, softmax) become one
+  // ROWFUSE step: see row_program.h.  The pass works on the finished step list, so it reuses
+  // every micro-op program the general lowering produced.
+  static void step_io(const Step& s, std::vector<int>& reads, std::vector<int>& writes) {
+    reads.clear();
+    writes.clear();
+    if (s.kind == Step::ELEMENTWISE) {
+      for (int b : s.ew_in_buf) if (b >= 0) reads.push_back(b);
+      writes = s.ew_out_buf;
+      return;
+    }
+    if (s.kind == Step::ROWFUSE) {
+      for (int b : s.row_in_buf) if (b >= 0) reads.push_back(b);
+      for (int b : s.row_load_buf) if (b >= 0) reads.push_back(b);
+      for (int b : s.row_out_buf) if (b >= 0) writes.push_back(b);
+      return;
+    }
+    for (int k = 0; k < 3; ++k) {
+      if (s.in[k] >= 0) reads.push_back(s.in[k]);
+      if (s.out[k] >= 0) writes.push_back(s.out[k]);
+    }
+    for (int b : s.idx_buf) reads.push_back(b);
+  }
+
+  static bool row_anchor(const Step& s, int64_t& R, int64_t& C) {
+    if (s.kind == Step::REDUCE && s.d[2] == 1) { R = s.d[0]; C = s.d[1]; }
+    else if (s.kind == Step::SOFTMAX && s.out[1] < 0 && s.out[2] < 0) { R = s.d[0]; C = s.d[1]; }
+    else return false;
+    return R >= 1 && C >= 2 && C < (1 << 24) && R * C < ((int64_t)1 << 31);
+  }
+  static bool row_candidate(const Step& s, int64_t R, int64_t C) {
+    int64_t r, c;
+    if (row_anchor(s, r, c)) return r == R && c == C;
+    if (s.kind != Step::ELEMENTWISE) return false;
+    return s.ew.total == R * C || s.ew.total == R;
+  }
+
+  struct RowBuild {
+    const std::vector<Step>& steps;
+    size_t b, e;
+    int64_t R, C;
+    Step out;
+    std::map<int, int> full_slot, scalar_of, last_read;
+    std::set<int> written, needed_after;
+    std::map<std::tuple<int, int64_t, int64_t, int64_t>, int> leaf_cache;
+    std::map<std::tuple<int, int64_t, int64_t>, int> load_cache;
+    bool busy[kRowMaxSlots] = {}, pinned[kRowMaxSlots] = {};
+    int slot_last[kRowMaxSlots] = {};
+    std::set<size_t> sunk;
+    int saved = 0;  // HBM round trips the fusion removes
+    RowBuild(const std::vector<Step>& st, size_t b_, size_t e_, int64_t r, int64_t c) : steps(st), b(b_), e(e_), R(r), C(c) {}
+
+    RowProgram& p() { return out.row; }
+    // a pinned slot (a row-invariant operand staged before the first row only) must be one no
+    // other value has used or will use: it keeps its contents from row to row
+    bool ever[kRowMaxSlots] = {};
+    int n_slots = 0;
+    int alloc(int last, bool pin = false) {
+      for (int s = 0; s < kRowMaxSlots; ++s)
+        if (!busy[s] && !(pin && ever[s])) {
+          busy[s] = true; pinned[s] = pin; slot_last[s] = last; ever[s] = true;
+          if (s + 1 > n_slots) n_slots = s + 1;
+          return s;
+        }
+      return -1;
+    }
+    int new_scalar() { return p().n_scalars < kRowMaxScalars ? p().n_scalars++ : -1; }
+    void release(int step) {
+      for (int s = 0; s < kRowMaxSlots; ++s)
+        if (busy[s] && !pinned[s] && slot_last[s] <= step) busy[s] = false;
+    }
+    RowPhase* begin_phase(uint8_t domain) {
+      if (p().n_phases >= kRowMaxPhases) return nullptr;
+      RowPhase& ph = p().phase[p().n_phases++];
+      ph = RowPhase{};
+      ph.domain = domain;
+      ph.first_input = (uint16_t)p().n_inputs; ph.first_load = (uint16_t)p().n_loads;
+      ph.first_output = (uint16_t)p().n_outputs; ph.first_instr = (uint16_t)p().n_instr;
+      return &ph;
+    }
+    EwInstr* add_instr(RowPhase& ph) {
+      if (p().n_instr >= kRowMaxInstr) return nullptr;
+      ph.n_instr++;
+      EwInstr& i = p().instr[p().n_instr++];
+      i = EwInstr{};
+      i.a = i.b = i.c = EW_ACC; i.dst = EW_NODST;
+      return &i;
+    }
+    RowOutput* add_output(RowPhase& ph, int buf) {
+      if (p().n_outputs >= kRowMaxOutputs || (ph.domain == ROW_FULL && ph.n_outputs >= kRowMaxSinks)) return nullptr;
+      ph.n_outputs++;
+      RowOutput& o = p().out[p().n_outputs++];
+      o = RowOutput{};
+      o.scalar = kRowNone; o.scale = 1.0f; o.src = EW_ACC;
+      out.row_out_buf.push_back(buf);
+      return &o;
+    }
+    // S[k] = buffer[off + row * stride], loaded once per row
+    int scalar_load(RowPhase& ph, int buf, int64_t off, int64_t stride, int dtype) {
+      auto key = std::make_tuple(buf, off, stride);
+      auto it = load_cache.find(key);
+      if (it != load_cache.end()) { ++saved; return it->second; }
+      const int k = new_scalar();
+      if (k < 0 || p().n_loads >= kRowMaxLoads) return -1;
+      RowScalarLoad& ld = p().load[p().n_loads++];
+      ld = RowScalarLoad{};
+      ld.row_stride = stride; ld.dtype = dtype; ld.scalar = k;
+      ph.n_loads++;
+      out.row_load_buf.push_back(buf);
+      out.row_load_off.push_back(off);
+      load_cache[key] = k;
+      return k;
+    }
+    // a slot holding buffer[off + row*rs + col*cs] for the current row
+    int leaf(RowPhase& ph, int buf, int64_t off, int64_t rs, int64_t cs, int dtype, int kind) {
+      auto key = std::make_tuple(buf, off, rs, cs);
+      if (kind == EW_IN_TENSOR) {
+        auto it = leaf_cache.find(key);
+        if (it != leaf_cache.end()) { ++saved; return it->second; }
+      }
+      if (p().n_inputs >= kRowMaxInputs || cs > INT32_MAX || cs < INT32_MIN) return -1;
+      const bool once = kind == EW_IN_TENSOR && rs == 0 && R > 1;
+      const int slot = alloc(kind == EW_IN_TENSOR ? last_read[buf] : cur, once);
+      if (slot < 0) return -1;
+      RowInput& in = p().in[p().n_inputs++];
+      in = RowInput{};
+      in.row_stride = rs; in.col_stride = (int32_t)cs; in.dtype = dtype; in.kind = (uint8_t)kind; in.slot = (uint8_t)slot; in.once = once;
+      ph.n_inputs++;
+      out.row_in_buf.push_back(kind == EW_IN_TENSOR ? buf : -1);
+      out.row_in_off.push_back(off);
+      if (kind == EW_IN_TENSOR) leaf_cache[key] = slot;
+      return slot;
+    }
+    int cur = 0;  // index of the step being translated
+
+    bool read_later_in_run(int buf, size_t after, bool skip_sunk) const {
+      std::vector<int> r, w;
+      for (size_t k = after + 1; k < e; ++k) {
+        if (skip_sunk && sunk.count(k)) continue;
+        step_io(steps[k], r, w);
+        if (std::find(r.begin(), r.end(), buf) != r.end()) return true;
+      }
+      return false;
+    }
+  };
+
+  bool build_row_program(size_t b, size_t e, int64_t R, int64_t C, Step& fused) {
+    const std::vector<Step>& steps = plan_->steps;
+    RowBuild rb(steps, b, e, R, C);
+    RowProgram& p = rb.p();
+    p = RowProgram{};
+    p.rows = R;
+    p.cols = (int32_t)C;
+    std::vector<int> reads, writes;
+    for (size_t k = b; k < e; ++k) {
+      step_io(steps[k], reads, writes);
+      for (int r : reads) rb.last_read[r] = (int)k;
+    }
+    for (size_t k = e; k < steps.size(); ++k) {
+      step_io(steps[k], reads, writes);
+      for (int r : reads) rb.needed_after.insert(r);
+    }
+    auto goes_to_hbm = [&](int buf) { return plan_->buffers[buf].is_arg || rb.needed_after.count(buf) > 0; };
+    auto dtype_of = [&](int buf) { return plan_->buffers[buf].dtype; };
+    bool has_reduce = false;
+
+    for (size_t k = b; k < e; ++k) {
+      if (rb.sunk.count(k)) continue;
+      const Step& st = steps[k];
+      rb.cur = (int)k;
+      if (st.kind == Step::ELEMENTWISE && st.ew.total == R * C) {
+        // ---------------- an elementwise chain over the full [R, C] problem ----------------
+        const EwProgram& q = st.ew;
+        const bool split = q.rank == 1;
+        if (!split && !(q.rank == 2 && (int64_t)q.dim[0] == R && (int64_t)q.dim[1] == C)) return false;
+        RowPhase* ph = rb.begin_phase(ROW_FULL);
+        if (!ph) return false;
+        std::vector<uint8_t> code(q.n_slots, 0);
+        for (int i = 0; i < q.n_inputs; ++i) {
+          const EwInput& in = q.in[i];
+          const int64_t rs = split ? in.stride[0] * C : in.stride[0], cs = split ? in.stride[0] : in.stride[1];
+          if (in.kind == EW_IN_IOTA) {
+            const int slot = rb.leaf(*ph, -1, 0, rs, cs, IB200_I32, EW_IN_IOTA);
+            if (slot < 0) return false;
+            code[i] = (uint8_t)slot;
+            continue;
+          }
+          const int buf = st.ew_in_buf[i];
+          const int64_t off = st.ew_in_off[i];
+          if (rb.scalar_of.count(buf)) {
+            if (off != 0 || cs != 0 || !(rs == 1 || R == 1)) return false;
+            code[i] = (uint8_t)(EW_ROWSCALAR + rb.scalar_of[buf]);
+          } else if (rb.full_slot.count(buf)) {
+            if (off != 0 || cs != 1 || !(rs == C || R == 1)) return false;
+            code[i] = (uint8_t)rb.full_slot[buf];
+          } else if (rb.written.count(buf)) {
+            return false;
+          } else if (cs == 0) {
+            const int sc = rb.scalar_load(*ph, buf, off, rs, in.dtype);
+            if (sc < 0) return false;
+            code[i] = (uint8_t)(EW_ROWSCALAR + sc);
+          } else {
+            if (rs < 0 || cs < 0) return false;
+            const int slot = rb.leaf(*ph, buf, off, rs, cs, in.dtype, EW_IN_TENSOR);
+            if (slot < 0) return false;
+            code[i] = (uint8_t)slot;
+          }
+        }
+        for (int i = q.n_inputs; i < q.n_slots; ++i) {
+          const int slot = rb.alloc((int)k);
+          if (slot < 0) return false;
+          code[i] = (uint8_t)slot;
+        }
+        auto remap = [&](uint8_t c) -> uint8_t { return c < kEwMaxSlots ? code[c] : c; };
+        for (int i = 0; i < q.n_instr; ++i) {
+          EwInstr* ins = rb.add_instr(*ph);
+          if (!ins) return false;
+          *ins = q.instr[i];
+          ins->a = remap(ins->a); ins->b = remap(ins->b); ins->c = remap(ins->c);
+          if (ins->dst != EW_NODST) {
+            ins->dst = remap(ins->dst);
+            if (ins->dst >= kRowMaxSlots) return false;
+          }
+        }
+        for (int o = 0; o < q.n_outputs; ++o) {
+          const int ob = st.ew_out_buf[o];
+          uint8_t src = remap(q.out[o].src);
+          // reductions of this value along the row fold into the phase that computes it
+          for (size_t k2 = k + 1; k2 < e; ++k2) {
+            const Step& r2 = steps[k2];
+            if (r2.kind != Step::REDUCE || r2.in[0] != ob || rb.sunk.count(k2) || ph->n_outputs >= kRowMaxSinks - 1) continue;
+            if (src == EW_ACC && o + 1 != q.n_outputs) continue;
+            RowOutput* ro = rb.add_output(*ph, goes_to_hbm(r2.out[0]) ? r2.out[0] : -1);
+            const int sc = rb.new_scalar();
+            if (!ro || sc < 0) return false;
+            ro->src = src; ro->reduce = (uint8_t)(r2.reduce_kind + 1); ro->scalar = (uint8_t)sc; ro->scale = r2.scale;
+            ro->dtype = r2.dtype2; ro->row_stride = 1;
+            rb.scalar_of[r2.out[0]] = sc;
+            rb.written.insert(r2.out[0]);
+            rb.sunk.insert(k2);
+            has_reduce = true;
+            ++rb.saved;
+          }
+          const bool resident = rb.read_later_in_run(ob, k, true);
+          if (resident) {
+            ++rb.saved;
+            if (src < kRowMaxSlots) {
+              rb.full_slot[ob] = src;
+              rb.slot_last[src] = std::max(rb.slot_last[src], rb.last_read[ob]);
+            } else if (src == EW_ACC) {
+              if (q.n_instr == 0) return false;
+              EwInstr& last = p.instr[p.n_instr - 1];
+              if (last.dst == EW_NODST) {
+                const int slot = rb.alloc(rb.last_read[ob]);
+                if (slot < 0) return false;
+                last.dst = (uint8_t)slot;
+              } else {
+                rb.slot_last[last.dst] = std::max(rb.slot_last[last.dst], rb.last_read[ob]);
+              }
+              rb.full_slot[ob] = last.dst;
+            } else {
+              return false;
+            }
+          }
+          if (goes_to_hbm(ob)) {
+            RowOutput* ro = rb.add_output(*ph, ob);
+            if (!ro) return false;
+            ro->src = src; ro->dtype = q.out[o].dtype; ro->row_stride = C;
+          }
+          rb.written.insert(ob);
+        }
+      } else if (st.kind == Step::ELEMENTWISE && st.ew.total == R) {
+        // ---------------- a chain over the per-row results ----------------------------------------
+        const EwProgram& q = st.ew;
+        if (q.rank != 1) return false;
+        RowPhase* ph = rb.begin_phase(ROW_SCALAR);
+        if (!ph) return false;
+        std::vector<uint8_t> code(q.n_slots, 0);
+        for (int i = 0; i < q.n_inputs; ++i) {
+          const EwInput& in = q.in[i];
+          if (in.kind != EW_IN_TENSOR) return false;
+          const int buf = st.ew_in_buf[i];
+          const int64_t off = st.ew_in_off[i], rs = in.stride[0];
+          int sc;
+          if (rb.scalar_of.count(buf)) {
+            if (off != 0 || !(rs == 1 || R == 1)) return false;
+            sc = rb.scalar_of[buf];
+          } else if (rb.written.count(buf)) {
+            return false;
+          } else {
+            sc = rb.scalar_load(*ph, buf, off, rs, in.dtype);
+            if (sc < 0) return false;
+          }
+          code[i] = (uint8_t)(EW_ROWSCALAR + sc);
+        }
+        for (int i = q.n_inputs; i < q.n_slots; ++i) {
+          const int sc = rb.new_scalar();
+          if (sc < 0) return false;
+          code[i] = (uint8_t)(EW_ROWSCALAR + sc);
+        }
+        auto remap = [&](uint8_t c) -> uint8_t { return c < kEwMaxSlots ? code[c] : c; };
+        for (int i = 0; i < q.n_instr; ++i) {
+          EwInstr* ins = rb.add_instr(*ph);
+          if (!ins) return false;
+          *ins = q.instr[i];
+          ins->a = remap(ins->a); ins->b = remap(ins->b); ins->c = remap(ins->c);
+          if (ins->dst != EW_NODST) ins->dst = remap(ins->dst);
+        }
+        for (int o = 0; o < q.n_outputs; ++o) {
+          const int ob = st.ew_out_buf[o];
+          const uint8_t src = remap(q.out[o].src);
+          const bool hbm = goes_to_hbm(ob);
+          if (src == EW_ACC) {
+            if (o + 1 != q.n_outputs) return false;
+            const int sc = rb.new_scalar();
+            RowOutput* ro = rb.add_output(*ph, hbm ? ob : -1);
+            if (sc < 0 || !ro) return false;
+            ro->src = src; ro->scalar = (uint8_t)sc; ro->dtype = q.out[o].dtype; ro->row_stride = 1;
+            rb.scalar_of[ob] = sc;
+          } else {
+            if (src < EW_ROWSCALAR || src >= EW_ACC) return false;
+            rb.scalar_of[ob] = src - EW_ROWSCALAR;
+            if (hbm) {
+              RowOutput* ro = rb.add_output(*ph, ob);
+              if (!ro) return false;
+              ro->src = src; ro->dtype = q.out[o].dtype; ro->row_stride = 1;
+            }
+          }
+          if (rb.read_later_in_run(ob, k, false)) ++rb.saved;
+          rb.written.insert(ob);
+        }
+      } else if (st.kind == Step::REDUCE) {
+        // ---------------- a reduction whose operand was not produced by a chain in this run ----
+        RowPhase* ph = rb.begin_phase(ROW_FULL);
+        if (!ph) return false;
+        const int xb = st.in[0];
+        int slot;
+        if (rb.full_slot.count(xb)) slot = rb.full_slot[xb];
+        else if (rb.written.count(xb)) return false;
+        else slot = rb.leaf(*ph, xb, 0, C, 1, st.dtype, EW_IN_TENSOR);
+        if (slot < 0) return false;
+        const int sc = rb.new_scalar();
+        RowOutput* ro = rb.add_output(*ph, goes_to_hbm(st.out[0]) ? st.out[0] : -1);
+        if (sc < 0 || !ro) return false;
+        ro->src = (uint8_t)slot; ro->reduce = (uint8_t)(st.reduce_kind + 1); ro->scalar = (uint8_t)sc; ro->scale = st.scale;
+        ro->dtype = st.dtype2; ro->row_stride = 1;
+        rb.scalar_of[st.out[0]] = sc;
+        rb.written.insert(st.out[0]);
+        if (rb.read_later_in_run(st.out[0], k, false)) ++rb.saved;
+        has_reduce = true;
+      } else if (st.kind == Step::SOFTMAX) {
+        // ---------------- softmax along the row: max, exp(x - max) and its sum, the quotient ----
+        const int xb = st.in[0], ob = st.out[0];
+        RowPhase* p1 = rb.begin_phase(ROW_FULL);
+        if (!p1) return false;
+        int sx;
+        if (rb.full_slot.count(xb)) sx = rb.full_slot[xb];
+        else if (rb.written.count(xb)) return false;
+        else sx = rb.leaf(*p1, xb, 0, C, 1, st.dtype, EW_IN_TENSOR);
+        if (sx < 0) return false;
+        const int m = rb.new_scalar(), sum = rb.new_scalar();
+        RowOutput* o1 = rb.add_output(*p1, -1);
+        if (m < 0 || sum < 0 || !o1) return false;
+        o1->src = (uint8_t)sx; o1->reduce = IB200_REDUCE_MAX + 1; o1->scalar = (uint8_t)m; o1->dtype = IB200_F32;
+        const bool resident = rb.read_later_in_run(ob, k, false);
+        const int se = rb.alloc(resident ? rb.last_read[ob] : (int)k);
+        if (se < 0) return false;
+        RowPhase* p2 = rb.begin_phase(ROW_FULL);
+        if (!p2) return false;
+        EwInstr *i1 = rb.add_instr(*p2), *i2 = rb.add_instr(*p2);
+        RowOutput* o2 = rb.add_output(*p2, -1);
+        if (!i1 || !i2 || !o2) return false;
+        i1->op = EW_SUB; i1->a = (uint8_t)sx; i1->b = (uint8_t)(EW_ROWSCALAR + m);
+        i2->op = EW_EXP; i2->dst = (uint8_t)se;
+        o2->src = EW_ACC; o2->reduce = IB200_REDUCE_SUM + 1; o2->scalar = (uint8_t)sum; o2->dtype = IB200_F32;
+        RowPhase* p3 = rb.begin_phase(ROW_FULL);
+        if (!p3) return false;
+        EwInstr* i3 = rb.add_instr(*p3);
+        if (!i3) return false;
+        i3->op = EW_DIV; i3->a = (uint8_t)se; i3->b = (uint8_t)(EW_ROWSCALAR + sum);
+        if (resident) {
+          i3->dst = (uint8_t)se;
+          rb.full_slot[ob] = se;
+          ++rb.saved;
+        }
+        if (goes_to_hbm(ob)) {
+          RowOutput* o3 = rb.add_output(*p3, ob);
+          if (!o3) return false;
+          o3->src = EW_ACC; o3->dtype = st.dtype2; o3->row_stride = C;
+        }
+        rb.written.insert(ob);
+        has_reduce = true;
+      } else {
+        return false;
+      }
+      rb.release((int)k);
+    }
+    if (!has_reduce || rb.saved == 0 || p.n_phases == 0) return false;
+    // Worth it?  Small problems are launch-bound: one launch beats several.  Large ones weigh the
+    // HBM round trips saved against the row kernel's interpretive cost.  The constants are
+    // microseconds per million elements measured on B200 (f32 [8192,4096] rms-norm, residual
+    // layernorm and masked softmax, fused and unfused): 0.82 per full-size tensor read or written
+    // by a separate kernel; in the row kernel 0.6 per micro-op, 1.4 more for exp / div / rsqrt,
+    // 0.5 per row reduction and 0.3 per staged operand or stored result.
+    if (R * C > (1 << 20)) {
+      double fused_cost = 0.0, unfused_cost = 0.0;
+      for (int ph = 0; ph < p.n_phases; ++ph) {
+        const RowPhase& f = p.phase[ph];
+        if (f.domain != ROW_FULL) continue;
+        for (int i = f.first_instr; i < f.first_instr + f.n_instr; ++i) {
+          const uint8_t op = p.instr[i].op;
+          fused_cost += 0.6 + ((op == EW_EXP || op == EW_DIV || op == EW_RDIV || op == EW_RSQRT) ? 1.4 : 0.0);
+        }
+        for (int i = f.first_input; i < f.first_input + f.n_inputs; ++i) fused_cost += p.in[i].once ? 0.0 : 0.3 * dtype_size(p.in[i].dtype) / 4.0;
+        for (int i = f.first_output; i < f.first_output + f.n_outputs; ++i)
+          fused_cost += p.out[i].reduce ? 0.5 : (rb.out.row_out_buf[i] >= 0 ? 0.3 * dtype_size(p.out[i].dtype) / 4.0 : 0.0);
+      }
+      for (size_t k = b; k < e; ++k) {
+        const Step& st = steps[k];
+        double tensors = 0.0;
+        if (st.kind == Step::ELEMENTWISE && st.ew.total == R * C) {
+          for (int i = 0; i < st.ew.n_inputs; ++i) {
+            bool full = st.ew.in[i].kind == EW_IN_TENSOR;
+            for (int d = 0; d < st.ew.rank; ++d) full &= st.ew.in[i].stride[d] != 0;
+            if (full) tensors += dtype_size(st.ew.in[i].dtype) / 4.0;
+          }
+          for (int o = 0; o < st.ew.n_outputs; ++o) tensors += dtype_size(st.ew.out[o].dtype) / 4.0;
+        } else if (st.kind == Step::REDUCE) {
+          tensors = dtype_size(st.dtype) / 4.0;
+        } else if (st.kind == Step::SOFTMAX) {
+          tensors = (dtype_size(st.dtype) + dtype_size(st.dtype2)) / 4.0;
+        }
+        unfused_cost += 0.82 * tensors;
+      }
+      if (fused_cost >= unfused_cost) return false;
+    }
+    // renumber the slots: the per-row ones first, then the row-invariant ones (one copy per CTA)
+    uint8_t perm[kRowMaxSlots];
+    int n_row = 0, n_once = 0;
+    for (int sl = 0; sl < rb.n_slots; ++sl)
+      if (!rb.pinned[sl]) perm[sl] = (uint8_t)n_row++;
+    for (int sl = 0; sl < rb.n_slots; ++sl)
+      if (rb.pinned[sl]) perm[sl] = (uint8_t)(n_row + n_once++);
+    auto renum = [&](uint8_t& c) { if (c < kRowMaxSlots) c = perm[c]; };
+    for (int i = 0; i < p.n_inputs; ++i) renum(p.in[i].slot);
+    for (int ph = 0; ph < p.n_phases; ++ph) {
+      const RowPhase& f = p.phase[ph];
+      if (f.domain != ROW_FULL) continue;
+      for (int i = f.first_instr; i < f.first_instr + f.n_instr; ++i) {
+        renum(p.instr[i].a); renum(p.instr[i].b); renum(p.instr[i].c);
+        if (p.instr[i].dst != EW_NODST) renum(p.instr[i].dst);
+      }
+      for (int i = f.first_output; i < f.first_output + f.n_outputs; ++i) renum(p.out[i].src);
+    }
+    p.n_row_slots = n_row;
+    p.n_once_slots = n_once;
+    if (!row_program_fits(n_row, n_once, (int)C)) return false;
+    fused = rb.out;
+    fused.kind = Step::ROWFUSE;
+    fused.d[0] = R;
+    fused.d[1] = C;
+    fused.label = "rowfused(" + std::to_string(e - b) + " steps, " + std::to_string(p.n_phases) + " phases)";
+    return true;
+  }
+
+  void fuse_rows() {
+    if (const char* env = std::getenv("IB200_ROWFUSE"))
+      if (env[0] == '0') return;
+    std::vector<Step>& steps = plan_->steps;
+    size_t floor = 0;  // steps before this index are final
+    for (size_t a = 0; a < steps.size(); ++a) {
+      int64_t R, C;
+      if (a < floor || !row_anchor(steps[a], R, C)) continue;
+      size_t b = a, e = a + 1;
+      while (b > floor && row_candidate(steps[b - 1], R, C)) --b;
+      while (e < steps.size() && row_candidate(steps[e], R, C)) ++e;
+      bool done = false;
+      for (size_t b2 = b; b2 <= a && !done; ++b2)
+        for (size_t e2 = e; e2 > a && e2 - b2 >= 2 && !done; --e2) {
+          Step fused;
+          if (!build_row_program(b2, e2, R, C, fused)) continue;
+          steps.erase(steps.begin() + b2, steps.begin() + e2);
+          steps.insert(steps.begin() + b2, fused);
+          floor = b2 + 1;
+          a = b2;  // the loop's ++a moves past the fused step
+          done = true;
+        }
+      if (!done) floor = std::max(floor, b);
+    }
+  }
+
   // =============================== description ==============================================
+  // the row program in readable form, so that the host side (and its tests) can inspect what
+  // a fused step does without a GPU
+  static Json describe_row_program(const Step& s) {
+    static const char* kOps[] = {"mov", "add", "sub", "mul", "div", "max", "min", "relu", "exp", "rsqrt", "abs", "floor", "ne", "lt", "le",
+                                 "gt", "ge", "and", "or", "not", "where", "to_bool", "to_int", "round_bf16", "round_f16", "rsub", "rdiv", "loadb"};
+    auto num = [](double v) { return Json::number(v); };
+    const RowProgram& p = s.row;
+    Json r = Json::object();
+    r.set("rows", num((double)p.rows));
+    r.set("cols", num(p.cols));
+    r.set("n_row_slots", num(p.n_row_slots));
+    r.set("n_once_slots", num(p.n_once_slots));
+    r.set("n_scalars", num(p.n_scalars));
+    Json phases = Json::array();
+    for (int ph = 0; ph < p.n_phases; ++ph) {
+      const RowPhase& f = p.phase[ph];
+      Json jp = Json::object(), ins = Json::array(), lds = Json::array(), code = Json::array(), outs = Json::array();
+      jp.set("domain", Json::string(f.domain == ROW_FULL ? "full" : "scalar"));
+      for (int k = f.first_input; k < f.first_input + f.n_inputs; ++k) {
+        Json j = Json::object();
+        j.set("buffer", num(s.row_in_buf[k])); j.set("offset", num((double)s.row_in_off[k]));
+        j.set("row_stride", num((double)p.in[k].row_stride)); j.set("col_stride", num(p.in[k].col_stride));
+        j.set("dtype", Json::string(dtype_name(p.in[k].dtype))); j.set("iota", num(p.in[k].kind == EW_IN_IOTA));
+        j.set("slot", num(p.in[k].slot)); j.set("once", num(p.in[k].once));
+        ins.push(j);
+      }
+      for (int k = f.first_load; k < f.first_load + f.n_loads; ++k) {
+        Json j = Json::object();
+        j.set("buffer", num(s.row_load_buf[k])); j.set("offset", num((double)s.row_load_off[k]));
+        j.set("row_stride", num((double)p.load[k].row_stride)); j.set("dtype", Json::string(dtype_name(p.load[k].dtype)));
+        j.set("scalar", num(p.load[k].scalar));
+        lds.push(j);
+      }
+      for (int k = f.first_instr; k < f.first_instr + f.n_instr; ++k) {
+        const EwInstr& i = p.instr[k];
+        Json j = Json::object();
+        j.set("op", Json::string(i.op < EW_NUM_OPS ? kOps[i.op] : "?"));
+        j.set("a", num(i.a)); j.set("b", num(i.b)); j.set("c", num(i.c)); j.set("dst", num(i.dst)); j.set("imm", num(i.imm));
+        code.push(j);
+      }
+      for (int k = f.first_output; k < f.first_output + f.n_outputs; ++k) {
+        const RowOutput& o = p.out[k];
+        Json j = Json::object();
+        j.set("buffer", num(s.row_out_buf[k])); j.set("row_stride", num((double)o.row_stride));
+        j.set("dtype", Json::string(dtype_name(o.dtype))); j.set("src", num(o.src)); j.set("reduce", num(o.reduce));
+        j.set("scalar", num(o.scalar)); j.set("scale", num(o.scale));
+        outs.push(j);
+      }
+      jp.set("inputs", ins); jp.set("loads", lds); jp.set("instr", code); jp.set("outputs", outs);
+      phases.push(jp);
+    }
+    r.set("phases", phases);
+    return r;
+  }
+
   void finish() {
     if (plan_->uses_status) {
       plan_->status_offset = plan_->workspace_bytes;
@@ -1733,9 +2289,20 @@ class Planner {
       for (int i = 0; i < 4; ++i) ext.push(Json::number((double)s.d[i]));
       if (s.kind == Step::ELEMENTWISE) { ext = Json::array(); for (int i = 0; i < s.ew.rank; ++i) ext.push(Json::number((double)s.ew.dim[i])); }
       j.set("extents", ext);
+      if (s.kind == Step::ROWFUSE) j.set("row_program", describe_row_program(s));
       steps.push(j);
     }
     d.set("steps", steps);
+    Json bufs = Json::array();
+    for (auto& b : plan_->buffers) {
+      Json j = Json::object();
+      j.set("name", Json::string(b.name));
+      j.set("arg", Json::number(b.is_arg ? b.arg_index : -1));
+      j.set("dtype", Json::string(dtype_name(b.dtype)));
+      j.set("bytes", Json::number((double)b.bytes));
+      bufs.push(j);
+    }
+    d.set("buffers", bufs);
     d.set("workspace_bytes", Json::number((double)plan_->workspace_bytes));
     d.set("status_offset", Json::number(plan_->uses_status ? (double)plan_->status_offset : -1.0));
     plan_->description = d;
@@ -1872,6 +2439,24 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
         }
         prog.vec = vec;
         rc = launch_elementwise(prog, s);
+        break;
+      }
+      case Step::ROWFUSE: {
+        RowProgram prog = st.row;
+        for (int k = 0; k < prog.n_inputs; ++k) {
+          RowInput& in = prog.in[k];
+          if (in.kind != EW_IN_TENSOR) continue;
+          in.ptr = static_cast<const char*>(P(st.row_in_buf[k])) + st.row_in_off[k] * dtype_size(in.dtype);
+          in.vec_ok = in.col_stride == 1 && aligned16(in.ptr) && in.row_stride % 4 == 0;
+        }
+        for (int k = 0; k < prog.n_loads; ++k)
+          prog.load[k].ptr = static_cast<const char*>(P(st.row_load_buf[k])) + st.row_load_off[k] * dtype_size(prog.load[k].dtype);
+        for (int k = 0; k < prog.n_outputs; ++k) {
+          RowOutput& o = prog.out[k];
+          o.ptr = st.row_out_buf[k] >= 0 ? P(st.row_out_buf[k]) : nullptr;
+          o.vec_ok = o.ptr && aligned16(o.ptr) && o.row_stride % 4 == 0;
+        }
+        rc = launch_row_program(prog, s);
         break;
       }
     }

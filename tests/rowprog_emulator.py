@@ -1,0 +1,141 @@
+"""A numpy emulator of the fused row programs the planner emits (intent_ir_b200/csrc/row_program.h),
+driven by the readable dump in the plan description.  It lets the CPU-only tests check the
+planner's fusion pass -- slot and scalar allocation, liveness, reduction sinks, which results
+reach global memory -- against the oracle without a GPU.  Test infrastructure only."""
+
+from __future__ import annotations
+
+from typing import Dict
+
+import numpy as np
+
+ACC, IMM, NODST, ROWSCALAR, NONE = 0x80, 0x81, 0xFF, 0x40, 0xFF
+
+_NP = {"f32": np.float32, "bf16": np.float32, "f16": np.float16, "i32": np.int32, "i64": np.int64, "bool": np.bool_,
+       "u8": np.uint8, "i8": np.int8, "i16": np.int16, "f64": np.float64}
+_SIZE = {"f32": 4, "bf16": 2, "f16": 2, "i32": 4, "i64": 8, "bool": 1, "u8": 1, "i8": 1, "i16": 2, "f64": 8}
+
+
+def _apply(op, a, b):
+    f = np.float32
+    with np.errstate(all="ignore"):
+        if op == "mov": return a
+        if op == "add": return a + b
+        if op == "sub": return a - b
+        if op == "mul": return a * b
+        if op == "div": return a / b
+        if op == "max": return np.maximum(a, b)
+        if op == "min": return np.minimum(a, b)
+        if op == "relu": return np.maximum(a, f(0))
+        if op == "exp": return np.exp(a)
+        if op == "rsqrt": return f(1) / np.sqrt(a)
+        if op == "abs": return np.abs(a)
+        if op == "floor": return np.floor(a)
+        if op in ("ne", "lt", "le", "gt", "ge"):
+            return {"ne": np.not_equal, "lt": np.less, "le": np.less_equal, "gt": np.greater, "ge": np.greater_equal}[op](a, b).astype(f)
+        if op == "and": return ((a != 0) & (b != 0)).astype(f)
+        if op == "or": return ((a != 0) | (b != 0)).astype(f)
+        if op == "not": return (a == 0).astype(f)
+        if op == "to_bool": return (a != 0).astype(f)
+        if op == "to_int": return np.trunc(a)
+        if op == "round_f16": return a.astype(np.float16).astype(f)
+        if op == "rsub": return b - a
+        if op == "rdiv": return b / a
+        if op == "loadb": return b
+    raise ValueError(f"emulator: op {op}")
+
+
+def _store(values, dtype):
+    if dtype == "bool":
+        return values != 0
+    if dtype in ("i32", "i64", "i8", "i16", "u8"):
+        return np.trunc(values).astype(_NP[dtype])
+    if dtype == "f16":
+        return values.astype(np.float16)
+    return values.astype(np.float32)  # bf16 buffers are modelled as f32 here
+
+
+def run_row_program(prog: dict, buffers: Dict[int, np.ndarray], buffer_table: list) -> None:
+    """Execute one fused step; `buffers` maps buffer id -> flat numpy array and is updated in place."""
+    rows, cols = int(prog["rows"]), int(prog["cols"])
+    once_done = set()
+    slots: Dict[int, np.ndarray] = {}
+    for row in range(rows):
+        S = np.full(32, np.nan, np.float32)
+        for pi, ph in enumerate(prog["phases"]):
+            for ld in ph["loads"]:
+                S[ld["scalar"]] = np.float32(buffers[ld["buffer"]][ld["offset"] + row * ld["row_stride"]])
+            scalar = ph["domain"] == "scalar"
+            width = 1 if scalar else cols
+            for k, inp in enumerate(ph["inputs"]):
+                if inp["once"]:
+                    if (pi, k) in once_done:
+                        continue
+                    once_done.add((pi, k))
+                idx = inp["offset"] + row * inp["row_stride"] + np.arange(cols) * inp["col_stride"]
+                slots[inp["slot"]] = idx.astype(np.float32) if inp["iota"] else buffers[inp["buffer"]][idx].astype(np.float32)
+            acc = np.zeros(width, np.float32)
+
+            def get(code, imm):
+                if code == ACC: return acc
+                if code == IMM: return np.full(width, imm, np.float32)
+                if code >= ROWSCALAR: return np.full(width, S[code - ROWSCALAR], np.float32)
+                assert not scalar, "slot operand in a scalar phase"
+                return slots[code]
+
+            for ins in ph["instr"]:
+                imm = np.float32(ins["imm"])
+                if ins["op"] == "where":
+                    acc = np.where(get(ins["a"], imm) != 0, get(ins["b"], imm), get(ins["c"], imm)).astype(np.float32)
+                else:
+                    acc = np.asarray(_apply(ins["op"], get(ins["a"], imm), get(ins["b"], imm)), np.float32)
+                if ins["dst"] != NODST:
+                    if scalar:
+                        S[ins["dst"] - ROWSCALAR] = acc[0]
+                    else:
+                        slots[ins["dst"]] = acc.copy()
+            for out in ph["outputs"]:
+                v = get(out["src"], np.float32(0))
+                if out["reduce"]:
+                    kind = out["reduce"] - 1
+                    with np.errstate(all="ignore"):
+                        r = v.sum(dtype=np.float32) if kind == 0 else v.max() if kind == 1 else np.float32((v != 0).any())
+                    r = np.float32(r * np.float32(out["scale"]))
+                    S[out["scalar"]] = r
+                    if out["buffer"] >= 0:
+                        _write(buffers, buffer_table, out["buffer"], row * out["row_stride"], np.asarray([r]), out["dtype"])
+                elif scalar:
+                    if out["scalar"] != NONE:
+                        S[out["scalar"]] = v[0]
+                    if out["buffer"] >= 0:
+                        _write(buffers, buffer_table, out["buffer"], row * out["row_stride"], v[:1], out["dtype"])
+                elif out["buffer"] >= 0:
+                    _write(buffers, buffer_table, out["buffer"], row * out["row_stride"], v, out["dtype"])
+
+
+def _write(buffers, table, buf, start, values, dtype):
+    if buf not in buffers:
+        t = table[buf]
+        n = int(t["bytes"]) // _SIZE[t["dtype"]]
+        buffers[buf] = np.zeros(n, _NP[t["dtype"]])
+    buffers[buf][start:start + len(values)] = _store(values, dtype)
+
+
+def run_plan_description(desc: dict, inputs: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
+    """Run a plan made only of fused row steps; returns the declared outputs by name."""
+    table = desc["buffers"]
+    names = desc["io_spec"]["arg_names"]
+    buffers: Dict[int, np.ndarray] = {}
+    for i, t in enumerate(table):
+        if t["arg"] >= 0 and names[t["arg"]] in inputs:
+            buffers[i] = np.ascontiguousarray(inputs[names[t["arg"]]]).reshape(-1)
+    for st in desc["steps"]:
+        if "row_program" not in st:
+            raise ValueError(f"emulator covers fused row steps only, not {st['kernel']}")
+        run_row_program(st["row_program"], buffers, table)
+    out = {}
+    for name in desc["output_names"]:
+        i = next(k for k, t in enumerate(table) if t["arg"] >= 0 and names[t["arg"]] == name)
+        shape = desc["io_spec"]["tensors"][name]["shape"]
+        out[name] = buffers[i].reshape(shape)
+    return out

@@ -48,7 +48,9 @@ EXPECTED_KERNELS = {
     "layer_norm_persistent": ["layernorm"], "layer_norm_persistent__cuda_pipeline_form": ["layernorm"],
     "group_norm_kernel": ["groupnorm"], "matmul_bias_relu2d": ["gemm+bias+relu"], "matmul_relu2d": ["gemm+relu"],
     "row_sum": ["reduce_sum"], "row_max": ["reduce_max"], "transpose2d": ["transpose2d"], "gather2d": ["gather"],
-    "_attn_fwd": ["gemm", "elementwise(2 ops, 3 in, 1 out)", "softmax", "gemm"],
+    "_attn_fwd": ["gemm", "rowfused(2 steps, 4 phases)", "gemm"],  # scale + mask + softmax in one row program
+    "masked_softmax2d": ["rowfused(2 steps, 4 phases)"], "rms_norm2d": ["rowfused(5 steps, 4 phases)"],
+    "rms_norm_residual2d": ["rowfused(5 steps, 4 phases)"], "layer_norm_residual2d": ["rowfused(8 steps, 6 phases)"],
 }
 
 
@@ -172,3 +174,49 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", text, re.M), f
+
+
+# ---- pipeline report artefacts (scripts/backend_codegen_smoke.py:81-146) --------------------------
+
+def _write_artifact(tmp_path, key, golden_graphs, golden_vectors, rename=None, expanded=True):
+    g = golden_graphs[key]
+    report = {"baseline": {"shapes": g["shapes"], "seed": 0}, "intent": g["intent"], "intent_expanded": g["intent"] if expanded else None}
+    (tmp_path / f"{key}.json").write_text(json.dumps(report))
+    arrays = {n: golden_vectors[f"{key}/in/{n}"] for n in g["inputs"]}
+    arrays.update({n: golden_vectors[f"{key}/out/{n}"] for n in g["outputs"]})
+    for old, new in (rename or {}).items():
+        arrays[new] = arrays.pop(old)
+    np.savez(tmp_path / f"{key}.baseline.npz", **arrays)
+    return str(tmp_path / f"{key}.json")
+
+
+def test_artifact_loader_reads_report_and_baseline(tmp_path, golden_graphs, golden_vectors):
+    from intent_ir_b200.artifacts import SMOKE_TOLERANCES, load_artifact
+
+    path = _write_artifact(tmp_path, "softmax_inner", golden_graphs, golden_vectors, rename={"input_ptr": "input", "output_ptr": "out"})
+    art = load_artifact(path)
+    assert art.kernel == "softmax_inner" and art.inputs == ["input_ptr"] and art.outputs == ["output_ptr"]
+    assert art.tolerances == SMOKE_TOLERANCES["softmax_inner"]
+    # recorded under other spellings, reachable under the graph's names
+    assert np.array_equal(art.baseline["input_ptr"], golden_vectors["softmax_inner/in/input_ptr"])
+    assert np.array_equal(art.baseline["output_ptr"], golden_vectors["softmax_inner/out/output_ptr"])
+    assert art.bindings == golden_graphs["softmax_inner"]["shapes"]
+
+    path = _write_artifact(tmp_path, "group_norm_kernel", golden_graphs, golden_vectors, expanded=False)
+    art = load_artifact(path)
+    assert art.bindings["group_size"] * art.bindings["num_groups"] == art.bindings["C"]
+    assert art.bindings["num_elements"] == art.bindings["group_size"] * art.bindings["HW"]
+
+
+def test_artifact_loader_errors(tmp_path):
+    from intent_ir_b200.artifacts import load_artifact
+    from intent_ir_b200.errors import B200RuntimeError
+
+    (tmp_path / "k.json").write_text(json.dumps({"baseline": {"shapes": {}}}))
+    with pytest.raises(B200RuntimeError, match="neither intent_expanded nor intent"):
+        load_artifact(str(tmp_path / "k.json"))
+    (tmp_path / "k2.json").write_text(json.dumps({"intent": {"name": "k2", "tensors": {"x": {"dtype": "f32", "shape": [2], "layout": "row_major"},
+                                                                                 "y": {"dtype": "f32", "shape": [2], "layout": "row_major"}},
+                                                             "ops": [{"op": "relu", "inputs": ["x"], "output": "y"}], "outputs": ["y"]}}))
+    with pytest.raises(B200RuntimeError, match="missing baseline npz"):
+        load_artifact(str(tmp_path / "k2.json"))

@@ -300,7 +300,8 @@ def test_missing_input_and_wrong_shape_raise(golden_graphs):
         run_b200_kernel(inputs_np={"A": np.zeros((4, 5), np.float32), "B": np.zeros((4, 4), np.float32)}, **kw)
 
 
-@pytest.mark.parametrize("m,n,dtype", [(2048, 2048, "f32"), (1536, 4100, "f32"), (3000, 1024, "bf16"), (1031, 2053, "f32")])
+@pytest.mark.parametrize("m,n,dtype", [(2048, 2048, "f32"), (1536, 4100, "f32"), (3000, 1024, "bf16"), (1031, 2053, "f32"),
+                                         (1000, 520, "f16"), (77, 36, "bf16"), (515, 1027, "bf16")])
 def test_large_broadcast_chain_matches_oracle(m, n, dtype):
     """Large enough for the 16-elements-per-thread staging (and a ragged shape that is not)."""
     from intent_ir_b200.backend import round_to_bf16
@@ -313,7 +314,7 @@ def test_large_broadcast_chain_matches_oracle(m, n, dtype):
                   {"op": "max", "inputs": ["e", "x"], "output": "y"}], "outputs": ["y"]}
     intent = IntentFunction.from_json_dict(js)
     rng = np.random.default_rng(m + n)
-    q = round_to_bf16 if dtype == "bf16" else (lambda a: a)
+    q = {"bf16": round_to_bf16, "f16": lambda a: a.astype(np.float16).astype(np.float32), "f32": lambda a: a}[dtype]
     ins = {"x": q(rng.standard_normal((m, n), dtype=np.float32)), "col": q(rng.standard_normal(n, dtype=np.float32)),
            "row": q(rng.standard_normal((m, 1), dtype=np.float32))}
     out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
@@ -400,8 +401,8 @@ def test_bound_graphed_and_pipelined_launchers_agree_with_the_plain_runner(golde
     from intent_ir_b200.lowering import lower_intent_to_b200_kernel
     from intent_ir_b200.runtime import HostPipeline, bind_lowered, graph_lowered, run_lowered
 
-    intent = IntentFunction.from_json_dict(golden_graphs["layer_norm_residual2d"]["intent"])  # a multi-kernel plan with a workspace
-    shapes = {"M": 64, "N": 192}
+    intent = IntentFunction.from_json_dict(golden_graphs["mlp2d"]["intent"])  # a multi-kernel plan with a workspace
+    shapes = {"M": 64, "K": 96, "H": 192, "N": 48}
     lowered = lower_intent_to_b200_kernel(intent, shape_bindings=shapes)
     assert lowered.n_launches > 1 and lowered.workspace_bytes > 0
     rng = np.random.default_rng(2)
@@ -495,3 +496,26 @@ def test_mutants_are_killed(golden_graphs):
         mutant = mutate(original, fn)
         diffs, cex = run_diff(mutant, run, [TestCase(shapes=shapes, dtypes={}, seed=3)], tolerances=infer_tolerances(mutant).to_dict())
         assert not diffs[0].ok and cex, mutant.ops
+
+
+# ---- pipeline report artefacts replayed on the GPU (scripts/backend_codegen_smoke.py:81-218) -------
+
+@pytest.mark.parametrize("key", ["softmax_inner", "group_norm_kernel", "_attn_fwd", "layer_norm_persistent", "any_kernel_dim",
+                                 "rms_norm_residual2d", "masked_softmax2d", "mlp2d"])
+def test_artifact_replay(key, tmp_path, golden_graphs, golden_vectors):
+    from intent_ir_b200.artifacts import run_artifact
+
+    g = golden_graphs[key]
+    report = {"baseline": {"shapes": g["shapes"], "seed": 0}, "intent": g["intent"], "intent_expanded": g["intent"]}
+    (tmp_path / f"{key}.json").write_text(json.dumps(report))
+    arrays = {n: golden_vectors[f"{key}/in/{n}"] for n in g["inputs"]}
+    arrays.update({n: golden_vectors[f"{key}/out/{n}"] for n in g["outputs"]})
+    np.savez(tmp_path / f"{key}.baseline.npz", **arrays)
+    res = run_artifact(str(tmp_path / f"{key}.json"))
+    assert res["ok"], res
+    # a corrupted recording must be reported, output by output
+    arrays[g["outputs"][0]] = np.where(arrays[g["outputs"][0]].astype(np.float32) > -1e30, 1, 0).astype(arrays[g["outputs"][0]].dtype) \
+        if arrays[g["outputs"][0]].dtype != np.bool_ else ~arrays[g["outputs"][0]]
+    np.savez(tmp_path / f"{key}.baseline.npz", **arrays)
+    res = run_artifact(str(tmp_path / f"{key}.json"))
+    assert not res["ok"] and g["outputs"][0] in res["failed"]
