@@ -130,18 +130,18 @@ def workload(name):
         m, n = 8192, 4096
         return (g["rms_norm2d"]["intent"], {"M": m, "N": n},
                 lambda r: {"inp": r.standard_normal((m, n), dtype=np.float32), "weight": r.uniform(0.5, 1.5, n).astype(np.float32)},
-                2 * m * n * 4 + n * 4 + m * 4, 0, "rms-norm f32 [8192,4096] + rstd (5 graph steps in one row program)")
+                2 * m * n * 4 + n * 4 + m * 4, 0, "rms-norm f32 [8192,4096] + rstd (5-op graph, pipeline/tilelang/core.py:735)")
     if name == "layernorm_residual":
         m, n = 8192, 4096
         return (g["layer_norm_residual2d"]["intent"], {"M": m, "N": n},
                 lambda r: {"inp": r.standard_normal((m, n), dtype=np.float32), "residual": r.standard_normal((m, n), dtype=np.float32),
                            "weight": r.uniform(0.5, 1.5, n).astype(np.float32), "bias": (0.1 * r.standard_normal(n)).astype(np.float32)},
-                3 * m * n * 4 + 2 * n * 4 + 2 * m * 4, 0, "residual add + layernorm f32 [8192,4096] + mean, rstd (one row program)")
+                3 * m * n * 4 + 2 * n * 4 + 2 * m * 4, 0, "residual add + layernorm f32 [8192,4096] + mean, rstd (pipeline/tilelang/core.py:1426)")
     if name == "masked_softmax":
         m = n = 4096
         return (g["masked_softmax2d"]["intent"], {"M": m, "N": n},
                 lambda r: {"inp": 3 * r.standard_normal((m, n), dtype=np.float32), "mask": r.random(n) > 0.2},
-                2 * m * n * 4 + n, 0, "masked softmax f32 [4096,4096], column mask (one row program)")
+                2 * m * n * 4 + n, 0, "masked softmax f32 [4096,4096], column mask (pipeline/tilelang/core.py:1050)")
     raise SystemExit(f"unknown workload {name}")
 
 

@@ -107,5 +107,38 @@ __device__ __forceinline__ void apply(uint8_t op, const float (&a)[N], const flo
 #undef EW_CASE
 }
 
+// acc = op(acc, y) for one value y shared by all N lanes of the thread (an immediate or a
+// per-row scalar): the binary opcodes only, no broadcast of y into registers
+template <int N> __device__ __forceinline__ void apply_scalar(uint8_t op, float (&acc)[N], float y) {
+#define EW_CASE(OP, EXPR)                      \
+  case OP:                                     \
+    _Pragma("unroll") for (int j = 0; j < N; ++j) { \
+      const float x = acc[j];                  \
+      (void)x;                                 \
+      acc[j] = (EXPR);                         \
+    }                                          \
+    break;
+  switch (op) {
+    EW_CASE(EW_ADD, x + y)
+    EW_CASE(EW_SUB, x - y)
+    EW_CASE(EW_MUL, x * y)
+    EW_CASE(EW_DIV, x / y)
+    EW_CASE(EW_MAX, max_nan(x, y))
+    EW_CASE(EW_MIN, min_nan(x, y))
+    EW_CASE(EW_NE, x != y ? 1.0f : 0.0f)
+    EW_CASE(EW_LT, x < y ? 1.0f : 0.0f)
+    EW_CASE(EW_LE, x <= y ? 1.0f : 0.0f)
+    EW_CASE(EW_GT, x > y ? 1.0f : 0.0f)
+    EW_CASE(EW_GE, x >= y ? 1.0f : 0.0f)
+    EW_CASE(EW_AND, (x != 0.0f && y != 0.0f) ? 1.0f : 0.0f)
+    EW_CASE(EW_OR, (x != 0.0f || y != 0.0f) ? 1.0f : 0.0f)
+    EW_CASE(EW_RSUB, y - x)
+    EW_CASE(EW_RDIV, y / x)
+    EW_CASE(EW_LOADB, y)
+    default: break;
+  }
+#undef EW_CASE
+}
+
 }  // namespace
 }  // namespace ib200

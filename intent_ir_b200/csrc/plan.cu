@@ -1846,6 +1846,53 @@ class Planner {
     }
   };
 
+  // FULL-phase instructions in accumulate form: every instruction but `where` is
+  // acc = op(acc, b) (or acc = b for EW_LOADB), so the kernel never materialises a first
+  // operand.  op(a, acc) becomes the reversed opcode; op(a, b) becomes a load and an op.
+  static bool emit_accumulate_form(RowBuild& rb, RowPhase& ph, EwInstr ins) {
+    auto push = [&](uint8_t op, uint8_t bcode, float imm, uint8_t dst) -> bool {
+      EwInstr* o = rb.add_instr(ph);
+      if (!o) return false;
+      o->op = op; o->a = EW_ACC; o->b = bcode; o->c = EW_ACC; o->imm = imm; o->dst = dst;
+      return true;
+    };
+    if (ins.op == EW_WHERE) {
+      EwInstr* o = rb.add_instr(ph);
+      if (!o) return false;
+      *o = ins;
+      return true;
+    }
+    const bool unary = ins.op == EW_MOV || ins.op == EW_RELU || ins.op == EW_EXP || ins.op == EW_RSQRT || ins.op == EW_ABS ||
+                       ins.op == EW_FLOOR || ins.op == EW_NOT || ins.op == EW_TO_BOOL || ins.op == EW_TO_INT ||
+                       ins.op == EW_ROUND_BF16 || ins.op == EW_ROUND_F16;
+    if (unary) {
+      if (ins.a != EW_ACC && !push(EW_LOADB, ins.a, ins.imm, EW_NODST)) return false;
+      if (ins.op == EW_MOV && ins.a != EW_ACC) {  // the load is the whole instruction
+        rb.p().instr[rb.p().n_instr - 1].dst = ins.dst;
+        return true;
+      }
+      return push(ins.op, EW_ACC, 0.0f, ins.dst);
+    }
+    if (ins.a == EW_ACC) return push(ins.op, ins.b, ins.imm, ins.dst);
+    if (ins.b == EW_ACC) {
+      uint8_t r;
+      switch (ins.op) {
+        case EW_SUB: r = EW_RSUB; break;
+        case EW_DIV: r = EW_RDIV; break;
+        case EW_RSUB: r = EW_SUB; break;
+        case EW_RDIV: r = EW_DIV; break;
+        case EW_LT: r = EW_GT; break;
+        case EW_GT: r = EW_LT; break;
+        case EW_LE: r = EW_GE; break;
+        case EW_GE: r = EW_LE; break;
+        case EW_ADD: case EW_MUL: case EW_MAX: case EW_MIN: case EW_NE: case EW_AND: case EW_OR: r = ins.op; break;
+        default: return false;
+      }
+      return push(r, ins.a, ins.imm, ins.dst);
+    }
+    return push(EW_LOADB, ins.a, ins.imm, EW_NODST) && push(ins.op, ins.b, ins.imm, ins.dst);
+  }
+
   bool build_row_program(size_t b, size_t e, int64_t R, int64_t C, Step& fused) {
     const std::vector<Step>& steps = plan_->steps;
     RowBuild rb(steps, b, e, R, C);
@@ -1915,14 +1962,13 @@ class Planner {
         }
         auto remap = [&](uint8_t c) -> uint8_t { return c < kEwMaxSlots ? code[c] : c; };
         for (int i = 0; i < q.n_instr; ++i) {
-          EwInstr* ins = rb.add_instr(*ph);
-          if (!ins) return false;
-          *ins = q.instr[i];
-          ins->a = remap(ins->a); ins->b = remap(ins->b); ins->c = remap(ins->c);
-          if (ins->dst != EW_NODST) {
-            ins->dst = remap(ins->dst);
-            if (ins->dst >= kRowMaxSlots) return false;
+          EwInstr ins = q.instr[i];
+          ins.a = remap(ins.a); ins.b = remap(ins.b); ins.c = remap(ins.c);
+          if (ins.dst != EW_NODST) {
+            ins.dst = remap(ins.dst);
+            if (ins.dst >= kRowMaxSlots) return false;
           }
+          if (!emit_accumulate_form(rb, *ph, ins)) return false;
         }
         for (int o = 0; o < q.n_outputs; ++o) {
           const int ob = st.ew_out_buf[o];
@@ -2069,19 +2115,20 @@ class Planner {
         if (se < 0) return false;
         RowPhase* p2 = rb.begin_phase(ROW_FULL);
         if (!p2) return false;
-        EwInstr *i1 = rb.add_instr(*p2), *i2 = rb.add_instr(*p2);
+        EwInstr i1{}, i2{};
+        i1.op = EW_SUB; i1.a = (uint8_t)sx; i1.b = (uint8_t)(EW_ROWSCALAR + m); i1.c = EW_ACC; i1.dst = EW_NODST;
+        i2.op = EW_EXP; i2.a = i2.b = i2.c = EW_ACC; i2.dst = (uint8_t)se;
+        if (!emit_accumulate_form(rb, *p2, i1) || !emit_accumulate_form(rb, *p2, i2)) return false;
         RowOutput* o2 = rb.add_output(*p2, -1);
-        if (!i1 || !i2 || !o2) return false;
-        i1->op = EW_SUB; i1->a = (uint8_t)sx; i1->b = (uint8_t)(EW_ROWSCALAR + m);
-        i2->op = EW_EXP; i2->dst = (uint8_t)se;
+        if (!o2) return false;
         o2->src = EW_ACC; o2->reduce = IB200_REDUCE_SUM + 1; o2->scalar = (uint8_t)sum; o2->dtype = IB200_F32;
         RowPhase* p3 = rb.begin_phase(ROW_FULL);
         if (!p3) return false;
-        EwInstr* i3 = rb.add_instr(*p3);
-        if (!i3) return false;
-        i3->op = EW_DIV; i3->a = (uint8_t)se; i3->b = (uint8_t)(EW_ROWSCALAR + sum);
+        EwInstr i3{};
+        i3.op = EW_DIV; i3.a = (uint8_t)se; i3.b = (uint8_t)(EW_ROWSCALAR + sum); i3.c = EW_ACC;
+        i3.dst = resident ? (uint8_t)se : EW_NODST;
+        if (!emit_accumulate_form(rb, *p3, i3)) return false;
         if (resident) {
-          i3->dst = (uint8_t)se;
           rb.full_slot[ob] = se;
           ++rb.saved;
         }
@@ -2102,16 +2149,17 @@ class Planner {
     // HBM round trips saved against the row kernel's interpretive cost.  The constants are
     // microseconds per million elements measured on B200 (f32 [8192,4096] rms-norm, residual
     // layernorm and masked softmax, fused and unfused): 0.82 per full-size tensor read or written
-    // by a separate kernel; in the row kernel 0.6 per micro-op, 1.4 more for exp / div / rsqrt,
+    // by a separate kernel; in the row kernel 0.4 per micro-op, 1.2 more for exp / div / rsqrt,
     // 0.5 per row reduction and 0.3 per staged operand or stored result.
-    if (R * C > (1 << 20)) {
+    const char* mode = std::getenv("IB200_ROWFUSE");  // "2": fuse whatever fits (for measurements)
+    if (R * C > (1 << 20) && !(mode && mode[0] == '2')) {
       double fused_cost = 0.0, unfused_cost = 0.0;
       for (int ph = 0; ph < p.n_phases; ++ph) {
         const RowPhase& f = p.phase[ph];
         if (f.domain != ROW_FULL) continue;
         for (int i = f.first_instr; i < f.first_instr + f.n_instr; ++i) {
           const uint8_t op = p.instr[i].op;
-          fused_cost += 0.6 + ((op == EW_EXP || op == EW_DIV || op == EW_RDIV || op == EW_RSQRT) ? 1.4 : 0.0);
+          fused_cost += 0.4 + ((op == EW_EXP || op == EW_DIV || op == EW_RDIV || op == EW_RSQRT) ? 1.2 : 0.0);
         }
         for (int i = f.first_input; i < f.first_input + f.n_inputs; ++i) fused_cost += p.in[i].once ? 0.0 : 0.3 * dtype_size(p.in[i].dtype) / 4.0;
         for (int i = f.first_output; i < f.first_output + f.n_outputs; ++i)

@@ -304,6 +304,8 @@ __global__ void __launch_bounds__(G <= 32 ? 256 : G) row_kernel(const __grid_con
         for (int j = 0; j < N; ++j) acc[j] = 0.0f;
         for (int ip = 0; ip < phase.n_instr; ++ip) {
           const EwInstr ins = P.instr[phase.first_instr + ip];
+          // accumulate form (the planner's emit_accumulate_form): acc = op(acc, b), b a slot,
+          // a scalar or acc itself; only `where` names three operands
           if (ins.op == EW_WHERE) {
             float a[N], b[N], c[N];
             fetch<G, VEC, NU, N>(a, ins.a, acc, ins.imm, f, S, pass, t);
@@ -311,20 +313,14 @@ __global__ void __launch_bounds__(G <= 32 ? 256 : G) row_kernel(const __grid_con
             fetch<G, VEC, NU, N>(c, ins.c, acc, ins.imm, f, S, pass, t);
 #pragma unroll
             for (int j = 0; j < N; ++j) acc[j] = a[j] != 0.0f ? b[j] : c[j];
-          } else if (ins.a == EW_ACC) {  // the usual link of a chain: acc = op(acc, b)
+          } else if (ins.b == EW_ACC) {
+            apply<N>(ins.op, acc, acc, acc);
+          } else if (ins.b < kRowMaxSlots) {
             float b[N];
             fetch<G, VEC, NU, N>(b, ins.b, acc, ins.imm, f, S, pass, t);
             apply<N>(ins.op, acc, b, acc);
           } else {
-            float a[N], b[N];
-            fetch<G, VEC, NU, N>(a, ins.a, acc, ins.imm, f, S, pass, t);
-            if (ins.b == ins.a) {
-#pragma unroll
-              for (int j = 0; j < N; ++j) b[j] = a[j];
-            } else {
-              fetch<G, VEC, NU, N>(b, ins.b, acc, ins.imm, f, S, pass, t);
-            }
-            apply<N>(ins.op, a, b, acc);
+            apply_scalar<N>(ins.op, acc, ins.b == EW_IMM ? ins.imm : S[ins.b - EW_ROWSCALAR]);
           }
           if (ins.dst != EW_NODST) put<G, VEC, NU, N>(acc, ins.dst, f, pass, t);
         }
@@ -429,7 +425,7 @@ constexpr size_t kSmemPerSm = 227 * 1024;
 
 // the launch shape for a program with `n_row` per-row and `n_once` row-invariant slots: the
 // smallest group that still leaves at least eight warps resident per SM, else the most warps
-bool row_launch_config(int n_row, int n_once, int cols, RowLaunch& best) {
+bool row_launch_config(int n_row, int n_once, int cols, int n_instr, RowLaunch& best) {
   bool found = false;
   // tuning overrides, read once: IB200_ROW_G in {32, 128, 512}, IB200_ROW_NU in {2, 4, 8}
   static const int force_g = std::getenv("IB200_ROW_G") ? std::atoi(std::getenv("IB200_ROW_G")) : 0;
@@ -440,8 +436,8 @@ bool row_launch_config(int n_row, int n_once, int cols, RowLaunch& best) {
     c.g = g;
     c.w = cols % 4 == 0 ? 4 : 1;
     const int raw = (cols + g * c.w - 1) / (g * c.w);
-    // 16 values per thread and pass: 32 (IB200_ROW_NU=8) costs 160 registers and, measured, more in occupancy than it saves in decoding
-    c.nu = c.w == 4 ? (raw >= 3 ? 4 : 2) : 8;
+    // 16 values per thread and pass; 32 (120 registers) pays off, measured, once a row runs six or more micro-ops
+    c.nu = c.w == 4 ? (raw >= 8 && n_instr >= 6 && g < 512 ? 8 : raw >= 3 ? 4 : 2) : 8;
     if (force_nu && c.w == 4 && (force_nu == 2 || force_nu == 4 || (force_nu == 8 && g < 512))) c.nu = force_nu;
     c.units = (raw + c.nu - 1) / c.nu * c.nu;
     const size_t slot = (size_t)c.units * g * c.w * sizeof(float);
@@ -479,7 +475,7 @@ bool row_launch_config(int n_row, int n_once, int cols, RowLaunch& best) {
 
 bool row_program_fits(int n_row_slots, int n_once_slots, int cols) {
   RowLaunch c;
-  return row_launch_config(n_row_slots > 0 ? n_row_slots : 1, n_once_slots, cols, c);
+  return row_launch_config(n_row_slots > 0 ? n_row_slots : 1, n_once_slots, cols, 0, c);
 }
 
 int launch_row_program(const RowProgram& prog, cudaStream_t s) {
@@ -491,7 +487,11 @@ int launch_row_program(const RowProgram& prog, cudaStream_t s) {
   for (int ph = 0; ph < prog.n_phases; ++ph)
     if (prog.phase[ph].domain == ROW_FULL && prog.phase[ph].n_outputs > kRowMaxSinks) return fail(IB200_ERR_INVALID, "row program: too many outputs in one phase");
   RowLaunch c;
-  if (!row_launch_config(prog.n_row_slots > 0 ? prog.n_row_slots : 1, prog.n_once_slots, prog.cols, c))
+  const int n_row = prog.n_row_slots > 0 ? prog.n_row_slots : 1;
+  int full_instr = 0;  // micro-ops executed per element
+  for (int ph = 0; ph < prog.n_phases; ++ph)
+    if (prog.phase[ph].domain == ROW_FULL) full_instr += prog.phase[ph].n_instr;
+  if (!row_launch_config(n_row, prog.n_once_slots, prog.cols, full_instr, c) && !row_launch_config(n_row, prog.n_once_slots, prog.cols, 0, c))
     return fail(IB200_ERR_UNSUPPORTED, "row program: rows of " + std::to_string(prog.cols) + " elements do not fit in shared memory");
   RowProgram p = prog;
   if (p.n_row_slots == 0) p.n_row_slots = 1;  // the layout always has one per-row slot
