@@ -58,6 +58,14 @@ struct GatherArgs {
   int n_idx, idx_is_64;
 };
 int launch_gather(const void* data, const GatherArgs& a, void* out, int elem_bytes, double other, cudaStream_t s);
+int launch_rope(const float* x, const float* cos, const float* sin, float* y, int64_t seq, int64_t rows_per_pos, int64_t d, cudaStream_t s);
+int launch_correlation(const int8_t* src0, const int8_t* src1, int8_t* out, int64_t in_c, int64_t out_c, int64_t h, int64_t w,
+                       const void* shift_ptr, int shift_dtype, int shift_value, cudaStream_t s);
+int launch_resize2x(const int8_t* src, int8_t* out, int64_t c, int64_t h, int64_t w, int hw_fl, cudaStream_t s);
+int launch_warp(const int8_t* src, const int16_t* offset, int8_t* out, int64_t c, int64_t h, int64_t w, cudaStream_t s);
+// p and seed come from device scalars when their pointers are given, else from the values
+int launch_dropout(const float* x, float* y, int64_t n, const void* p_ptr, int p_dtype, float p_value, const void* seed_ptr, int seed_dtype,
+                   long long seed_value, int rounds, cudaStream_t s);
 
 #ifdef __CUDACC__
 // ---- element conversion ---------------------------------------------------------------------

@@ -240,7 +240,7 @@ struct EwRegCode {
 template <int NIN, int BMASK, int RANK>
 __global__ void __launch_bounds__(kThreads, 4) ew_kernel_reg(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
                                                              const __grid_constant__ EwRegCode code) {
-  constexpr int N = 8, U = 2;
+  constexpr int N = 8, U = 2;  // 16 values per thread were measured slower (half the resident warps)
   const int t = threadIdx.x;
   const char* ptr[NIN > 0 ? NIN : 1];
   uint32_t stride[NIN > 0 ? NIN : 1][RANK];
@@ -307,13 +307,7 @@ __global__ void __launch_bounds__(kThreads, 4) ew_kernel_reg(const __grid_consta
         case 0: apply<N>(ins.op, acc, in[0], acc); break;
         case 1: if (NIN > 1) apply<N>(ins.op, acc, in[NIN > 1 ? 1 : 0], acc); break;
         case 2: if (NIN > 2) apply<N>(ins.op, acc, in[NIN > 2 ? 2 : 0], acc); break;
-        case 3: {
-          float b[N];
-#pragma unroll
-          for (int j = 0; j < N; ++j) b[j] = ins.imm;
-          apply<N>(ins.op, acc, b, acc);
-          break;
-        }
+        case 3: apply_scalar<N>(ins.op, acc, ins.imm); break;
         default: apply<N>(ins.op, acc, acc, acc);
       }
     }

@@ -158,7 +158,7 @@ struct Buffer {
 };
 
 struct Step {
-  enum Kind { REDUCE, SOFTMAX, NORM, GEMM, ELEMENTWISE, TRANSPOSE, GATHER, ROWFUSE } kind;
+  enum Kind { REDUCE, SOFTMAX, NORM, GEMM, ELEMENTWISE, TRANSPOSE, GATHER, ROWFUSE, ROPE, DROPOUT, CORRELATION, RESIZE, WARP } kind;
   std::string label;
   int in[3] = {-1, -1, -1};
   int out[3] = {-1, -1, -1};
@@ -171,7 +171,8 @@ struct Step {
   int64_t batch = 1, batch_stride[3] = {0, 0, 0};  // batched matmul: elements between consecutive A / B / C matrices
   std::vector<int> idx_buf;                         // gather: index buffers
   Shape g_dim, g_stride;
-  double other = 0.0;
+  double other = 0.0;     // gather: fill value; dropout: p when it is a constant
+  long long seed = 0;     // dropout: the seed when it is a constant
   EwProgram ew;
   std::vector<int> ew_in_buf, ew_out_buf;
   std::vector<int64_t> ew_in_off;  // element offsets into the input buffers
@@ -214,6 +215,7 @@ class Planner {
     plan_->kernel_name = nm && nm->is_str() ? nm->s : "intent_fn";
     build();
     if (!match_fused()) lower_general();
+    fuse_gemm_epilogues();
     fuse_rows();
     finish();
     return std::move(plan_);
@@ -638,6 +640,49 @@ class Planner {
         const Json* ov = attrs->find("other_value");
         n.cval = ov && ov->is_num() ? ov->num : 0.0;
         id = add(n);
+      } else if (op == "rope") {
+        // x[SEQ, B, H, D even], cos / sin [SEQ, D/2]  (verify/interpreter.py:455-477)
+        if (in.size() != 3) throw Invalid(where + " requires x, cos, sin");
+        const Shape &xs = nodes_[in[0]].shape, &cs = nodes_[in[1]].shape, &ss = nodes_[in[2]].shape;
+        if (xs.size() != 4 || cs.size() != 2 || ss.size() != 2 || xs[3] % 2)
+          throw Invalid(where + ": rope expects x[SEQ,B,H,D even] and cos/sin[SEQ,D/2]; got " + shape_str(xs) + " " + shape_str(cs) + " " + shape_str(ss));
+        if (cs[0] != xs[0] || cs[1] != xs[3] / 2 || ss != cs) throw Invalid(where + ": rope cos/sin shape mismatch");
+        Node n; n.name = out; n.op = op; n.in = in; n.shape = xs; n.dclass = DC_FLOAT;
+        id = add(n);
+      } else if (op == "correlation" || op == "resize" || op == "warp") {
+        // int8 image ops; the output shape is the declared one (verify/interpreter.py:330-454)
+        auto dd = decl_.find(out);
+        if (dd == decl_.end() || !dd->second.find("shape")) throw Invalid(where + ": the output tensor must be declared");
+        Node n; n.name = out; n.op = op; n.in = in; n.dclass = DC_INT;
+        n.shape = shape_of(*dd->second.find("shape"), where);
+        if (n.shape.size() != 3) throw Invalid(where + ": " + op + " output must be rank-3, got " + shape_str(n.shape));
+        const size_t want_in = op == "correlation" ? 3 : op == "resize" ? 1 : 2;
+        if (in.size() != want_in) throw Invalid(where + ": " + op + " requires " + std::to_string(want_in) + " input(s)");
+        const Shape& src = nodes_[in[0]].shape;
+        if (src.size() != 3) throw Invalid(where + ": " + op + " input must be rank-3, got " + shape_str(src));
+        if (op == "correlation") {
+          if (nodes_[in[1]].shape != src) throw Invalid(where + ": correlation inputs shape mismatch: " + shape_str(src) + " vs " + shape_str(nodes_[in[1]].shape));
+          if (src[1] != n.shape[1] || src[2] != n.shape[2]) throw Invalid(where + ": correlation spatial shape mismatch");
+          if (numel(nodes_[in[2]].shape) != 1) throw Invalid(where + ": out_shift must be a scalar");
+          if (numel(n.shape) > 0 && src[0] > 0 && n.shape[0] - 1 > n.shape[2]) throw Invalid(where + ": correlation output channels need shifts beyond the width");
+        } else if (op == "resize") {
+          if (n.shape[0] != src[0]) throw Invalid(where + ": resize channel mismatch");
+          if (n.shape[1] != 2 * src[1] || n.shape[2] != 2 * src[2]) throw Invalid(where + ": resize currently expects 2x upsample: src=" + shape_str(src) + " out=" + shape_str(n.shape));
+          const Json* fl = attrs->find("hw_fl");
+          n.axis = fl && fl->is_num() ? (int)fl->as_int() : 7;
+        } else {
+          if (n.shape != src) throw Invalid(where + ": warp output shape mismatch: src=" + shape_str(src) + " out=" + shape_str(n.shape));
+          if (nodes_[in[1]].shape != Shape{src[1], src[2]}) throw Invalid(where + ": warp offset shape mismatch");
+        }
+        id = add(n);
+      } else if (op == "dropout") {
+        // x, p (scalar), seed (scalar); attrs.n_rounds, default 10  (verify/interpreter.py:697-742)
+        if (in.size() != 3) throw Invalid(where + " requires x, p, seed");
+        if (numel(nodes_[in[1]].shape) != 1 || numel(nodes_[in[2]].shape) != 1) throw Invalid(where + ": p and seed must be scalars");
+        Node n; n.name = out; n.op = op; n.in = in; n.shape = nodes_[in[0]].shape; n.dclass = DC_FLOAT;
+        const Json* nr = attrs->find("n_rounds");
+        n.axis = nr && nr->is_num() && nr->as_int() > 0 ? (int)nr->as_int() : 10;
+        id = add(n);
       } else {
         throw Unsupported("op '" + op + "' is not covered by the B200 kernels (name=" + plan_->kernel_name + ")");
       }
@@ -1013,8 +1058,20 @@ class Planner {
       }
       // D = X - mean(X)
       const Node& dn = nodes_[d];
+      // X is an external input, or any float value computed from inputs (a residual sum, say):
+      // that value is then computed first, by the general lowering, into the workspace (or into
+      // its own output buffer when the graph also returns it)
       const int x = skip_reshapes(dn.in[0]);
-      if (!is_input(x) || float_dtype_of_input(x) < 0) continue;
+      const bool x_is_input = is_input(x);
+      int x_dtype = x_is_input ? float_dtype_of_input(x) : -1;
+      if (!x_is_input) {
+        if (nodes_[x].dclass != DC_FLOAT || nodes_[x].op == "const") continue;
+        x_dtype = IB200_F32;
+        for (auto& other : outputs_)
+          if (by_name_[other] == x) x_dtype = plan_->buffers[out_buffer_[other]].dtype;
+        if (!(x_dtype == IB200_F32 || x_dtype == IB200_BF16 || x_dtype == IB200_F16)) continue;
+      }
+      if (x_dtype < 0) continue;
       int z1, red1, z2, red2;
       int64_t L1, L2;
       if (!match_mean(dn.in[1], z1, red1, L1) || skip_reshapes(z1) != x) continue;
@@ -1043,9 +1100,9 @@ class Planner {
       if (b >= 0 && !affine_operand(b, nodes_[y].shape, b_in, inner2, period2)) continue;
       if (w >= 0 && b >= 0 && (inner != inner2 || period != period2)) continue;
       if (w < 0 && b >= 0) { inner = inner2; period = period2; }
-      const int wd = w_in >= 0 ? nodes_[w_in].decl_dtype : b_in >= 0 ? nodes_[b_in].decl_dtype : nodes_[x].decl_dtype;
+      const int wd = w_in >= 0 ? nodes_[w_in].decl_dtype : b_in >= 0 ? nodes_[b_in].decl_dtype : x_dtype;
       if (w_in >= 0 && b_in >= 0 && nodes_[w_in].decl_dtype != nodes_[b_in].decl_dtype) continue;
-      if (!(wd == nodes_[x].decl_dtype || wd == IB200_F32)) continue;
+      if (!(wd == x_dtype || wd == IB200_F32)) continue;
 
       std::map<std::string, int> covered;
       covered[oname] = 0;
@@ -1057,15 +1114,15 @@ class Planner {
       s.aff_inner = inner;
       s.aff_period = period;
       s.eps = (float)eps;
-      s.in[0] = nodes_[x].view.buffer;
       s.in[1] = w_in >= 0 ? nodes_[w_in].view.buffer : -1;
       s.in[2] = b_in >= 0 ? nodes_[b_in].view.buffer : -1;
       s.out[0] = out_buffer_[oname];
-      s.dtype = nodes_[x].decl_dtype;
+      s.dtype = x_dtype;
       s.dtype2 = wd;
       if (plan_->buffers[s.out[0]].dtype != s.dtype) continue;
       for (auto& other : outputs_) {
         if (other == oname) continue;
+        if (!x_is_input && by_name_[other] == x) { covered[other] = 3; continue; }  // written when X is computed
         const int o = skip_reshapes(by_name_[other]);
         const int buf = out_buffer_[other];
         if (plan_->buffers[buf].dtype != IB200_F32 || numel(nodes_[by_name_[other]].shape) != s.d[0]) continue;
@@ -1073,6 +1130,17 @@ class Planner {
         else if (o == rs) { s.out[2] = buf; covered[other] = 2; }
       }
       if (!all_outputs_in(covered)) continue;
+      if (!x_is_input) {  // everything checked: now emit the kernel(s) that compute X
+        std::function<void(int)> lower_deps = [&](int id) {
+          if (nodes_[id].repr != Node::NONE) return;
+          for (int c : nodes_[id].in) lower_deps(c);
+          lower_node(id);
+        };
+        lower_deps(x);
+        materialise_contiguous(x);
+        if (plan_->buffers[nodes_[x].view.buffer].dtype != x_dtype) throw Unsupported("internal: normalised value landed in an unexpected dtype");
+      }
+      s.in[0] = nodes_[x].view.buffer;
       plan_->uses_status = true;
       plan_->steps.push_back(s);
       return true;
@@ -1352,6 +1420,94 @@ class Planner {
       if (plan_->buffers[s.out[0]].dtype != s.dtype) {
         out_written_.erase(n.name);
         s.out[0] = new_workspace_buffer(s.dtype, numel(n.shape), n.name);
+      }
+      plan_->steps.push_back(s);
+      set_strided(id, s.out[0]);
+      return;
+    }
+    if (op == "rope" || op == "dropout") {
+      Step s;
+      s.kind = op == "rope" ? Step::ROPE : Step::DROPOUT;
+      s.label = op;
+      const int x = converted_copy(n.in[0], IB200_F32);  // the interpreter computes both in float32
+      s.in[0] = nodes_[x].view.buffer;
+      const Shape& xs = nodes_[id].shape;
+      if (op == "rope") {
+        const int c = converted_copy(nodes_[id].in[1], IB200_F32), sn = converted_copy(nodes_[id].in[2], IB200_F32);
+        s.in[1] = nodes_[c].view.buffer;
+        s.in[2] = nodes_[sn].view.buffer;
+        s.d[0] = xs[0];
+        s.d[1] = xs[1] * xs[2];
+        s.d[2] = xs[3];
+      } else {
+        s.d[0] = numel(xs);
+        s.d[1] = nodes_[id].axis;
+        const int pn = nodes_[id].in[1], sd = nodes_[id].in[2];
+        if (nodes_[pn].repr == Node::NONE) lower_node(pn);
+        if (nodes_[sd].repr == Node::NONE) lower_node(sd);
+        if (nodes_[pn].repr == Node::CONSTANT) {
+          s.other = nodes_[pn].cval;
+        } else {
+          materialise_contiguous(pn);
+          s.in[1] = nodes_[pn].view.buffer;
+          s.dtype = plan_->buffers[s.in[1]].dtype;
+          if (class_of_dtype(s.dtype) != DC_FLOAT) throw Unsupported("dropout: p must be a floating-point scalar");
+        }
+        if (nodes_[sd].repr == Node::CONSTANT) {
+          s.seed = (long long)nodes_[sd].cval;
+        } else {
+          materialise_contiguous(sd);
+          s.in[2] = nodes_[sd].view.buffer;
+          s.dtype2 = plan_->buffers[s.in[2]].dtype;
+          if (s.dtype2 != IB200_I32 && s.dtype2 != IB200_I64) throw Unsupported("dropout: seed must be an i32 or i64 scalar");
+        }
+      }
+      s.out[0] = result_buffer(id, IB200_F32);
+      if (plan_->buffers[s.out[0]].dtype != IB200_F32) {
+        out_written_.erase(nodes_[id].name);
+        s.out[0] = new_workspace_buffer(IB200_F32, numel(xs), nodes_[id].name);
+      }
+      plan_->steps.push_back(s);
+      set_strided(id, s.out[0]);
+      return;
+    }
+    if (op == "correlation" || op == "resize" || op == "warp") {
+      Step s;
+      s.kind = op == "correlation" ? Step::CORRELATION : op == "resize" ? Step::RESIZE : Step::WARP;
+      s.label = op;
+      auto dense_input = [&](int node, int dtype, const char* what) {
+        if (nodes_[node].repr == Node::NONE) lower_node(node);
+        materialise_contiguous(node);
+        const int buf = nodes_[node].view.buffer;
+        if (plan_->buffers[buf].dtype != dtype) throw Unsupported(op + ": " + what + " must be declared " + dtype_name(dtype));
+        return buf;
+      };
+      const std::vector<int> ins = nodes_[id].in;
+      const Shape src = nodes_[ins[0]].shape, os = nodes_[id].shape;
+      s.in[0] = dense_input(ins[0], IB200_I8, "the source");
+      s.d[0] = src[0]; s.d[1] = src[1]; s.d[2] = src[2]; s.d[3] = os[0];
+      if (op == "correlation") {
+        s.in[1] = dense_input(ins[1], IB200_I8, "the second source");
+        const int sh = ins[2];
+        if (nodes_[sh].repr == Node::NONE) lower_node(sh);
+        if (nodes_[sh].repr == Node::CONSTANT) {
+          s.seed = (long long)nodes_[sh].cval;
+          if (s.seed < 0) throw Invalid("correlation: negative out_shift");
+        } else {
+          materialise_contiguous(sh);
+          s.in[2] = nodes_[sh].view.buffer;
+          s.dtype2 = plan_->buffers[s.in[2]].dtype;
+          if (s.dtype2 != IB200_I32 && s.dtype2 != IB200_I64) throw Unsupported("correlation: out_shift must be an i32 or i64 scalar");
+        }
+      } else if (op == "resize") {
+        s.d[3] = nodes_[id].axis;  // hw_fl
+      } else {
+        s.in[1] = dense_input(ins[1], IB200_I16, "the offset");
+      }
+      s.out[0] = result_buffer(id, IB200_I8);
+      if (plan_->buffers[s.out[0]].dtype != IB200_I8) {
+        out_written_.erase(nodes_[id].name);
+        s.out[0] = new_workspace_buffer(IB200_I8, numel(os), nodes_[id].name);
       }
       plan_->steps.push_back(s);
       set_strided(id, s.out[0]);
@@ -1696,6 +1852,65 @@ class Planner {
       if (out_buffer_.count(nodes_[roots[i]].name) && out_buffer_[nodes_[roots[i]].name] == bufs[i]) out_written_.insert(nodes_[roots[i]].name);
     }
     return true;
+  }
+
+  // =============================== GEMM epilogues ===========================================
+  // A GEMM whose only consumer is an elementwise step computing [relu](gemm [+ bias[col]])
+  // takes that step into its epilogue: multi-matmul graphs (mlp, attention output) then run one
+  // kernel per matmul, as the single-matmul pattern of phase B already does.
+  void fuse_gemm_epilogues() {
+    std::vector<Step>& steps = plan_->steps;
+    std::vector<int> reads, writes;
+    for (size_t i = 0; i + 1 < steps.size(); ++i) {
+      Step& g = steps[i];
+      const Step& e = steps[i + 1];
+      if (g.kind != Step::GEMM || g.batch != 1 || g.in[2] >= 0 || g.act != IB200_ACT_NONE || e.kind != Step::ELEMENTWISE) continue;
+      const int gb = g.out[0];
+      if (plan_->buffers[gb].is_arg) continue;
+      bool used_elsewhere = false;
+      for (size_t k = i + 2; k < steps.size() && !used_elsewhere; ++k) {
+        step_io(steps[k], reads, writes);
+        used_elsewhere = std::find(reads.begin(), reads.end(), gb) != reads.end();
+      }
+      if (used_elsewhere) continue;
+      const EwProgram& q = e.ew;
+      const int64_t M = g.d[0], N = g.d[1];
+      if (q.n_outputs != 1 || q.total != M * N || q.n_inputs < 1 || q.n_inputs > 2 || M < 2 || N < 2) continue;
+      // operand roles: the GEMM result (dense) and, optionally, a vector along N
+      int slot_g = -1, slot_b = -1;
+      bool ok = true;
+      for (int k = 0; k < q.n_inputs && ok; ++k) {
+        const EwInput& in = q.in[k];
+        if (in.kind != EW_IN_TENSOR || e.ew_in_off[k] != 0) { ok = false; break; }
+        const bool dense = q.rank == 1 ? in.stride[0] == 1 : (q.rank == 2 && (int64_t)q.dim[0] == M && (int64_t)q.dim[1] == N && in.stride[0] == N && in.stride[1] == 1);
+        const bool colvec = q.rank == 2 && (int64_t)q.dim[0] == M && (int64_t)q.dim[1] == N && in.stride[0] == 0 && in.stride[1] == 1;
+        if (e.ew_in_buf[k] == gb && dense && slot_g < 0) slot_g = k;
+        else if (colvec && slot_b < 0) slot_b = k;
+        else ok = false;
+      }
+      if (!ok || slot_g < 0 || (q.n_inputs == 2 && slot_b < 0)) continue;
+      // program: [add(g, b)] [relu]
+      int ip = 0, act = IB200_ACT_NONE;
+      if (slot_b >= 0) {
+        if (q.n_instr < 1 || q.instr[0].op != EW_ADD) continue;
+        const uint8_t a = q.instr[0].a, b = q.instr[0].b;
+        if (!((a == slot_g && b == slot_b) || (a == slot_b && b == slot_g))) continue;
+        ip = 1;
+      }
+      if (ip < q.n_instr && q.instr[ip].op == EW_RELU && (ip == 0 ? q.instr[ip].a == slot_g : q.instr[ip].a == EW_ACC)) { act = IB200_ACT_RELU; ++ip; }
+      if (ip != q.n_instr || ip == 0) continue;
+      if (q.out[0].src != EW_ACC) continue;
+      const int ob = e.ew_out_buf[0];
+      const int out_dt = plan_->buffers[ob].dtype;
+      if (!(out_dt == IB200_F32 || out_dt == IB200_BF16)) continue;
+      if (slot_b >= 0 && plan_->buffers[e.ew_in_buf[slot_b]].dtype != out_dt) continue;
+      g.in[2] = slot_b >= 0 ? e.ew_in_buf[slot_b] : -1;
+      g.act = act;
+      g.out[0] = ob;
+      g.dtype2 = out_dt;
+      g.label = std::string("gemm") + (slot_b >= 0 ? "+bias" : "") + (act ? "+relu" : "");
+      steps.erase(steps.begin() + i + 1);
+    }
   }
 
   // =============================== row fusion ===============================================
@@ -2466,6 +2681,25 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
         rc = launch_gather(P(st.in[0]), ga, P(st.out[0]), dtype_size(st.dtype), st.other, s);
         break;
       }
+      case Step::ROPE:
+        rc = launch_rope(static_cast<const float*>(P(st.in[0])), static_cast<const float*>(P(st.in[1])), static_cast<const float*>(P(st.in[2])),
+                         static_cast<float*>(P(st.out[0])), st.d[0], st.d[1], st.d[2], s);
+        break;
+      case Step::DROPOUT:
+        rc = launch_dropout(static_cast<const float*>(P(st.in[0])), static_cast<float*>(P(st.out[0])), st.d[0], P(st.in[1]), st.dtype,
+                            (float)st.other, P(st.in[2]), st.dtype2, st.seed, (int)st.d[1], s);
+        break;
+      case Step::CORRELATION:
+        rc = launch_correlation(static_cast<const int8_t*>(P(st.in[0])), static_cast<const int8_t*>(P(st.in[1])), static_cast<int8_t*>(P(st.out[0])),
+                                st.d[0], st.d[3], st.d[1], st.d[2], P(st.in[2]), st.dtype2, (int)st.seed, s);
+        break;
+      case Step::RESIZE:
+        rc = launch_resize2x(static_cast<const int8_t*>(P(st.in[0])), static_cast<int8_t*>(P(st.out[0])), st.d[0], st.d[1], st.d[2], (int)st.d[3], s);
+        break;
+      case Step::WARP:
+        rc = launch_warp(static_cast<const int8_t*>(P(st.in[0])), static_cast<const int16_t*>(P(st.in[1])), static_cast<int8_t*>(P(st.out[0])),
+                         st.d[0], st.d[1], st.d[2], s);
+        break;
       case Step::TRANSPOSE:
         rc = launch_transpose2d(P(st.in[0]), P(st.out[0]), dtype_size(st.dtype), st.d[0], st.d[1], s);
         break;

@@ -51,7 +51,9 @@ def _workspace(lowered: B200LoweredKernel, device) -> Optional[torch.Tensor]:
         # written when a bounded wait expires
         ws = torch.zeros(lowered.workspace_bytes + 256, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = ws
-        if len(_WORKSPACES) > 256:
+        # oldest first out: at most 256 plans and 8 GiB of scratch stay cached (bound launchers
+        # keep their own reference, so eviction never frees memory that is still in use)
+        while len(_WORKSPACES) > 1 and (len(_WORKSPACES) > 256 or sum(t.numel() for t in _WORKSPACES.values()) > (8 << 30)):
             _WORKSPACES.pop(next(iter(_WORKSPACES)))
     return ws
 

@@ -50,7 +50,9 @@ EXPECTED_KERNELS = {
     "row_sum": ["reduce_sum"], "row_max": ["reduce_max"], "transpose2d": ["transpose2d"], "gather2d": ["gather"],
     "_attn_fwd": ["gemm", "rowfused(2 steps, 4 phases)", "gemm"],  # scale + mask + softmax in one row program
     "masked_softmax2d": ["rowfused(2 steps, 4 phases)"], "rms_norm2d": ["rowfused(5 steps, 4 phases)"],
-    "rms_norm_residual2d": ["rowfused(5 steps, 4 phases)"], "layer_norm_residual2d": ["rowfused(8 steps, 6 phases)"],
+    "rms_norm_residual2d": ["rowfused(5 steps, 4 phases)"],
+    "layer_norm_residual2d": ["elementwise(1 ops, 2 in, 1 out)", "layernorm"],  # the residual sum, then the dedicated kernel
+    "mlp2d": ["gemm+bias+relu", "gemm+bias"], "matmul_transposed_epilogue": ["transpose2d", "gemm+bias+relu"],  # epilogues folded per GEMM
 }
 
 
@@ -76,19 +78,24 @@ def test_planner_fuses_elementwise_chains_into_one_pass(golden_graphs):
 
 
 def test_planner_general_path_and_workspace(golden_graphs):
-    g = golden_graphs["mlp2d"]
+    g = golden_graphs["matmul_fused_epilogue2d"]  # an epilogue the GEMM kernel cannot absorb
     d = plan_json(g["intent"], g["shapes"])
     kinds = [s["kernel"].split("(")[0] for s in d["steps"]]
-    assert kinds == ["gemm", "elementwise", "gemm", "elementwise"]
+    assert kinds == ["gemm", "elementwise"]
     assert d["workspace_bytes"] > 0 and d["status_offset"] >= 0
 
 
 def test_planner_rejects_what_it_does_not_cover(golden_graphs):
+    conv = {"name": "r", "tensors": {n: {"dtype": "f32", "shape": s} for n, s in {"x": ["S", "D"], "w": ["D", "D"], "y": ["S", "D"]}.items()},
+            "ops": [{"op": "conv2d", "inputs": ["x", "w"], "output": "y"}], "outputs": ["y"]}
+    with pytest.raises((B200LoweringError, IntentIRValidationError), match="conv2d"):
+        plan_json(conv, {"S": 4, "D": 8})
     rope = {"name": "r", "tensors": {n: {"dtype": "f32", "shape": s} for n, s in
                                       {"x": ["S", "B", "H", "D"], "c": ["S", "D2"], "s": ["S", "D2"], "y": ["S", "B", "H", "D"]}.items()},
             "ops": [{"op": "rope", "inputs": ["x", "c", "s"], "output": "y"}], "outputs": ["y"]}
-    with pytest.raises(B200LoweringError, match="rope"):
-        plan_json(rope, {"S": 4, "B": 1, "H": 2, "D": 8, "D2": 4})
+    assert [s["kernel"] for s in plan_json(rope, {"S": 4, "B": 1, "H": 2, "D": 8, "D2": 4})["steps"]] == ["rope"]
+    with pytest.raises(B200LoweringError, match="cos/sin shape mismatch"):
+        plan_json(rope, {"S": 4, "B": 1, "H": 2, "D": 8, "D2": 3})
     g = golden_graphs["softmax_inner"]
     with pytest.raises(B200LoweringError, match="unbound symbolic dim"):
         plan_json(g["intent"], {"M": 4})

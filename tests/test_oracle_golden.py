@@ -138,3 +138,31 @@ def test_tolerance_known_answers():
         "C": {"dtype": "f32", "shape": ["M", "N"]}},
         "ops": [{"op": "matmul", "inputs": ["A", "B"], "output": "C"}], "outputs": ["C"]})
     assert infer_tolerances(mm).atol > 1e-3
+
+
+# ---- rope, dropout, correlation, resize, warp (tests/golden/make_golden_ops.py) ----------------------
+with open(os.path.join(GOLDEN, "op_intents.json")) as _f:
+    OP_KEYS = sorted(json.load(_f))
+
+
+@pytest.fixture(scope="module")
+def op_golden():
+    with open(os.path.join(GOLDEN, "op_intents.json")) as f:
+        graphs = json.load(f)
+    with np.load(os.path.join(GOLDEN, "op_vectors.npz")) as z:
+        return graphs, {k: z[k] for k in z.files}
+
+
+@pytest.mark.parametrize("key", OP_KEYS)
+def test_interpreter_reproduces_single_op_kernel_bits(key, op_golden):
+    graphs, vectors = op_golden
+    g = graphs[key]
+    intent = IntentFunction.from_json_dict(g["intent"])
+    ins = {n: vectors[f"{key}/in/{n}"] for n in g["inputs"]}
+    with np.errstate(all="ignore"):
+        got = execute_intent(intent, ins, shape_bindings=g["shapes"])
+    for n in g["outputs"]:
+        want = vectors[f"{key}/out/{n}"]
+        have = np.asarray(got[n])
+        assert have.shape == want.shape and have.dtype == want.dtype, n
+        assert np.array_equal(have, want, equal_nan=True), n

@@ -254,10 +254,8 @@ def _t0(shape, dtype="f32"):
 
 
 @pytest.mark.parametrize("name,js", [
-    ("rope", {"name": "r", "tensors": {"x": _t0(["S", "B", "H", "D"]), "c": _t0(["S", "D2"]), "s": _t0(["S", "D2"]), "y": _t0(["S", "B", "H", "D"])},
-              "ops": [{"op": "rope", "inputs": ["x", "c", "s"], "output": "y"}], "outputs": ["y"]}),
-    ("dropout", {"name": "d", "tensors": {"x": _t0(["M"]), "p": _t0([]), "seed": _t0([], "i32"), "y": _t0(["M"])},
-                 "ops": [{"op": "dropout", "inputs": ["x", "p", "seed"], "output": "y"}], "outputs": ["y"]}),
+    ("rank-1", {"name": "m", "tensors": {"a": _t0(["M"]), "b": _t0(["M", "N"]), "y": _t0(["N"])},
+                "ops": [{"op": "matmul", "inputs": ["a", "b"], "output": "y"}], "outputs": ["y"]}),
     ("non-trailing", {"name": "s", "tensors": {"x": _t0(["M", "N"]), "y": _t0(["M", "N"])},
                       "ops": [{"op": "softmax", "inputs": ["x"], "output": "y", "attrs": {"axis": 0}}], "outputs": ["y"]}),
 ])
@@ -519,3 +517,75 @@ def test_artifact_replay(key, tmp_path, golden_graphs, golden_vectors):
     np.savez(tmp_path / f"{key}.baseline.npz", **arrays)
     res = run_artifact(str(tmp_path / f"{key}.json"))
     assert not res["ok"] and g["outputs"][0] in res["failed"]
+
+
+# ---- rope, dropout and the int8 image ops against the reference interpreter's recorded outputs (tests/golden/make_golden_ops.py) ----
+
+with open(os.path.join(os.path.dirname(__file__), "golden", "op_intents.json")) as _f:
+    _OP_GRAPHS = json.load(_f)
+
+
+@pytest.mark.parametrize("key", sorted(_OP_GRAPHS))
+def test_single_op_kernels_are_bit_exact(key):
+    g = _OP_GRAPHS[key]
+    with np.load(os.path.join(os.path.dirname(__file__), "golden", "op_vectors.npz")) as z:
+        ins = {n: z[f"{key}/in/{n}"] for n in g["inputs"]}
+        want = {n: z[f"{key}/out/{n}"] for n in g["outputs"]}
+    intent = IntentFunction.from_json_dict(g["intent"])
+    out, lowered = _lower_and_run(intent, g["shapes"], ins)
+    assert [s["kernel"] for s in lowered.steps] == [key.split("_")[0]]
+    for n, w in want.items():
+        assert out[n].dtype == w.dtype and np.array_equal(out[n], w), (key, n)
+
+
+def test_dropout_mask_statistics_and_scaling_at_size():
+    """4M elements: the keep fraction matches 1 - p, kept values are exactly x / (1 - p), and the
+    mask equals the oracle's Philox stream."""
+    js = {"name": "dropout", "tensors": {"x": _t0(["M"]), "p": _t0([]), "seed": _t0([], "i64"), "y": _t0(["M"])},
+          "ops": [{"op": "dropout", "inputs": ["x", "p", "seed"], "output": "y"}], "outputs": ["y"]}
+    intent = IntentFunction.from_json_dict(js)
+    m = 1 << 22
+    x = np.random.default_rng(3).standard_normal(m, dtype=np.float32) + 3.0
+    ins = {"x": x, "p": np.array(0.3, np.float32), "seed": np.array(2 ** 33 + 17, np.int64)}
+    out, _ = _lower_and_run(intent, {"M": m}, ins)
+    want = execute_intent(intent, ins, {"M": m})["y"]
+    assert np.array_equal(out["y"], want)
+    assert abs((out["y"] != 0).mean() - 0.7) < 2e-3
+
+
+def test_rope_and_dropout_inside_larger_graphs():
+    js = {"name": "g", "tensors": {"x": _t0(["S", "B", "H", "D"]), "c": _t0(["S", "D2"]), "s": _t0(["S", "D2"]), "p": _t0([]),
+                                   "seed": _t0([], "i32"), "y": _t0(["S", "B", "H", "D"])},
+          "ops": [{"op": "mul", "inputs": ["x"], "output": "x2", "attrs": {"mul_factor": 0.5}},
+                  {"op": "rope", "inputs": ["x2", "c", "s"], "output": "r"},
+                  {"op": "dropout", "inputs": ["r", "p", "seed"], "output": "d", "attrs": {"n_rounds": 7}},
+                  {"op": "relu", "inputs": ["d"], "output": "y"}], "outputs": ["y"]}
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(9)
+    shapes = {"S": 5, "B": 2, "H": 3, "D": 16, "D2": 8}
+    ang = rng.uniform(-3, 3, (5, 8))
+    ins = {"x": rng.standard_normal((5, 2, 3, 16), dtype=np.float32), "c": np.cos(ang).astype(np.float32), "s": np.sin(ang).astype(np.float32),
+           "p": np.array(0.25, np.float32), "seed": np.array(77, np.int32)}
+    out, lowered = _lower_and_run(intent, shapes, ins)
+    want = execute_intent(intent, ins, shapes)["y"]
+    assert np.array_equal(out["y"], want), [s["kernel"] for s in lowered.steps]
+
+
+def test_image_ops_at_size_and_in_a_chain():
+    """correlation -> resize -> warp on a [8, 96, 160] int8 image: every stage integer-exact."""
+    t = _t0
+    js = {"name": "img", "tensors": {"a": t(["C", "H", "W"], "i8"), "b": t(["C", "H", "W"], "i8"), "sh": t([], "i32"), "off": t(["H2", "W2"], "i16"),
+                                     "corr": t(["OC", "H", "W"], "i8"), "up": t(["OC", "H2", "W2"], "i8"), "out": t(["OC", "H2", "W2"], "i8")},
+          "ops": [{"op": "correlation", "inputs": ["a", "b", "sh"], "output": "corr"},
+                  {"op": "resize", "inputs": ["corr"], "output": "up", "attrs": {"hw_fl": 7}},
+                  {"op": "warp", "inputs": ["up", "off"], "output": "out"}], "outputs": ["out", "corr"]}
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(12)
+    shapes = {"C": 8, "H": 96, "W": 160, "OC": 5, "H2": 192, "W2": 320}
+    ins = {"a": rng.integers(-128, 128, (8, 96, 160)).astype(np.int8), "b": rng.integers(-128, 128, (8, 96, 160)).astype(np.int8),
+           "sh": np.array(6, np.int32), "off": rng.integers(-1024, 1024, (192, 320)).astype(np.int16)}
+    out, lowered = _lower_and_run(intent, shapes, ins)
+    assert [s["kernel"] for s in lowered.steps] == ["correlation", "resize", "warp"]
+    want = execute_intent(intent, ins, shapes)
+    for n in ("out", "corr"):
+        assert out[n].dtype == np.int8 and np.array_equal(out[n], want[n]), n
