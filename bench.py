@@ -130,7 +130,7 @@ def workload(name):
         m, n = 8192, 4096
         return (g["rms_norm2d"]["intent"], {"M": m, "N": n},
                 lambda r: {"inp": r.standard_normal((m, n), dtype=np.float32), "weight": r.uniform(0.5, 1.5, n).astype(np.float32)},
-                2 * m * n * 4 + n * 4 + m * 4, 0, "rms-norm f32 [8192,4096] + rstd (5-op graph, pipeline/tilelang/core.py:735)")
+                2 * m * n * 4 + n * 4 + m * 4, 0, "rms-norm f32 [8192,4096] + rstd (pipeline/tilelang/core.py:735)")
     if name == "layernorm_residual":
         m, n = 8192, 4096
         return (g["layer_norm_residual2d"]["intent"], {"M": m, "N": n},

@@ -1,6 +1,7 @@
-// Row normalisation (layernorm, groupnorm) with centred two-pass statistics:
+// Row normalisation (layernorm, groupnorm, rms-norm) with centred two-pass statistics:
 //   mean = sum(x)/L, var = sum((x-mean)^2)/L, rstd = 1/sqrt(var + eps),
-//   y = (x-mean)*rstd * w[widx] + b[widx],
+//   y = (x-mean)*rstd * w[widx] + b[widx]      (rms-norm: the same with mean fixed at 0,
+//   the chain of pipeline/tilelang/core.py:735-776),
 // the arithmetic of the reference's primitive-op chains (pipeline/tilelang/core.py:1334-1374
 // for layernorm, :187-232 for groupnorm) as verify/interpreter.py executes them.  The
 // reference's own CUDA layernorm (kernels/layernorm.cuh) uses E[x^2]-mean^2; the centred
@@ -40,6 +41,7 @@ struct AffineMap {  // widx = (linear / inner) % period, evaluated without 64-bi
   FastDiv inner, period;
   int nowrap;  // rows start on a multiple of `inner` and never run past `period`: no modulo per element
   int small;   // rows*cols < 2^31: the row origin needs no 64-bit division
+  int centre;  // 1: subtract the row mean (layernorm / groupnorm); 0: rms-norm, y = x * rsqrt(mean(x^2) + eps)
 };
 
 template <int NV> __device__ __forceinline__ float local_sum(const float (&v)[NV][4]) {
@@ -166,7 +168,7 @@ __global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const 
   for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += stride) {
     float v[NV][4];
     load_row<T, NV, VEC>(x + r * cols, cols, lane, 32, 0.0f, v);
-    const float mean = warp_reduce<SumOp>(local_sum<NV>(v)) / (float)cols;
+    const float mean = map.centre ? warp_reduce<SumOp>(local_sum<NV>(v)) / (float)cols : 0.0f;
     const float var = warp_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, lane, 32)) / (float)cols;
     const float rstd = 1.0f / sqrtf(var + eps);
     uint32_t lq = 0, lr = 0;
@@ -189,7 +191,7 @@ __global__ void __launch_bounds__(THREADS) norm_block(const T* __restrict__ x, c
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     float v[NV][4];
     load_row<T, NV, VEC>(x + r * cols, cols, threadIdx.x, THREADS, 0.0f, v);
-    const float mean = block_reduce<SumOp>(local_sum<NV>(v), slots[0]) / (float)cols;
+    const float mean = map.centre ? block_reduce<SumOp>(local_sum<NV>(v), slots[0]) / (float)cols : 0.0f;
     const float var = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, threadIdx.x, THREADS), slots[1]) / (float)cols;
     const float rstd = 1.0f / sqrtf(var + eps);
     uint32_t lq = 0, lr = 0;
@@ -232,7 +234,7 @@ __global__ void __launch_bounds__(THREADS) norm_cluster(const T* __restrict__ x,
   load_row<T, NV, VEC>(x + r * cols + col0, mine, threadIdx.x, THREADS, 0.0f, v);
 
   const float s = block_reduce<SumOp>(local_sum<NV>(v), slots[0]);
-  const float mean_k = mine > 0 ? s / (float)mine : 0.0f;
+  const float mean_k = mine > 0 && map.centre ? s / (float)mine : 0.0f;
   const float q = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean_k, mine, threadIdx.x, THREADS), slots[1]);
 
   cluster_wait();  // every CTA of the cluster is running: remote shared memory may be written
@@ -333,7 +335,7 @@ __global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const 
     load_row<T, NV, true>(reinterpret_cast<const T*>(stage_mem + st * stage_bytes), mine, threadIdx.x, THREADS, 0.0f, v);
 
     const float s = block_reduce<SumOp>(local_sum<NV>(v), slots[0]);
-    float mean = mine > 0 ? s / (float)mine : 0.0f;
+    float mean = mine > 0 && map.centre ? s / (float)mine : 0.0f;
     const float q = block_reduce<SumOp>(centre_and_square<NV, true>(v, mean, mine, threadIdx.x, THREADS), slots[1]);
     float m2 = q;
     if (CLUSTER) {
@@ -382,14 +384,14 @@ __global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const 
 template <typename T, typename TW, int AFF>
 __global__ void __launch_bounds__(1024) norm_stream(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                                                     T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                                                    int64_t rows, int64_t cols, float eps, int64_t inner, int64_t period) {
+                                                    int64_t rows, int64_t cols, float eps, int64_t inner, int64_t period, int centre) {
   __shared__ float slots[2][32];
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const T* xr = x + r * cols;
     T* yr = y + r * cols;
     float s = 0.0f;
     for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += to_f32<T>(xr[c]);
-    const float mean = block_reduce<SumOp>(s, slots[0]) / (float)cols;
+    const float mean = centre ? block_reduce<SumOp>(s, slots[0]) / (float)cols : 0.0f;
     float q = 0.0f;
     for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
       const float d = to_f32<T>(xr[c]) - mean;
@@ -420,6 +422,7 @@ struct Args {
   float eps;
   cudaStream_t s;
   int32_t* status;
+  int centre;
 };
 
 // how many groups of `csize` CTAs of a kernel can be resident at once (cached per kernel)
@@ -484,6 +487,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   T* y = static_cast<T*>(a.y);
   const TW *w = static_cast<const TW*>(a.w), *b = static_cast<const TW*>(a.b);
   AffineMap map;
+  map.centre = a.centre;
   map.nowrap = 0;
   map.small = a.rows * a.cols < ((int64_t)1 << 31);
   if (AFF == AFF_GENERIC) {
@@ -553,7 +557,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   } else {
     if (AFF == AFF_GENERIC && (a.rows * a.cols) / a.inner >= (int64_t)1 << 62) return fail(IB200_ERR_UNSUPPORTED, "norm: extent too large");
     const int grid = (int)(a.rows < (int64_t)kSmCount * 2 ? a.rows : (int64_t)kSmCount * 2);
-    norm_stream<T, TW, AFF><<<grid, 1024, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, a.cols, a.eps, a.inner, a.period);
+    norm_stream<T, TW, AFF><<<grid, 1024, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, a.cols, a.eps, a.inner, a.period, a.centre);
   }
 #undef IB200_WARP
 #undef IB200_BLOCK
@@ -604,13 +608,13 @@ int32_t* norm_default_status() {
 
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype,
                      int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps,
-                     cudaStream_t s, int32_t* status) {
+                     cudaStream_t s, int32_t* status, bool centre) {
   if (!status) status = norm_default_status();
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "norm: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
   if (!x || !y) return fail(IB200_ERR_INVALID, "norm: null pointer");
   if ((w || b) && (affine_inner < 1 || affine_period < 1)) return fail(IB200_ERR_INVALID, "norm: affine_inner and affine_period must be >= 1");
-  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status};
+  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status, centre ? 1 : 0};
   const int adt = (w || b) ? affine_dtype : dtype;
   switch (dtype) {
     case IB200_F32:

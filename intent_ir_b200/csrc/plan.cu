@@ -1032,6 +1032,14 @@ class Planner {
           const int cand_d = skip_reshapes(n.in[k]), cand_rs = skip_views(n.in[1 - k]);
           if (nodes_[cand_d].op == "sub" && nodes_[cand_rs].op == "rsqrt") { d = cand_d; rs = cand_rs; xh_rs_operand_ = n.in[1 - k]; xh_node_ = id; return true; }
         }
+        // rms-norm: X * rsqrt(mean(X*X) + eps), nothing subtracted
+        for (int k = 0; k < 2; ++k) {
+          const int cand_d = skip_reshapes(n.in[k]), cand_rs = skip_views(n.in[1 - k]);
+          if (nodes_[cand_rs].op == "rsqrt" && nodes_[cand_d].op != "rsqrt" && numel(nodes_[cand_d].shape) == numel(n.shape)) {
+            d = cand_d; rs = cand_rs; xh_rs_operand_ = n.in[1 - k]; xh_node_ = id;
+            return true;
+          }
+        }
         return false;
       };
       int d = -1, rs = -1, xh = -1;
@@ -1056,12 +1064,13 @@ class Planner {
         }
         if (xh < 0) continue;
       }
-      // D = X - mean(X)
+      // D = X - mean(X); for rms-norm D is X itself
+      const bool centred = nodes_[d].op == "sub";
       const Node& dn = nodes_[d];
       // X is an external input, or any float value computed from inputs (a residual sum, say):
       // that value is then computed first, by the general lowering, into the workspace (or into
       // its own output buffer when the graph also returns it)
-      const int x = skip_reshapes(dn.in[0]);
+      const int x = centred ? skip_reshapes(dn.in[0]) : d;
       const bool x_is_input = is_input(x);
       int x_dtype = x_is_input ? float_dtype_of_input(x) : -1;
       if (!x_is_input) {
@@ -1073,9 +1082,9 @@ class Planner {
       }
       if (x_dtype < 0) continue;
       int z1, red1, z2, red2;
-      int64_t L1, L2;
-      if (!match_mean(dn.in[1], z1, red1, L1) || skip_reshapes(z1) != x) continue;
-      const int mu = skip_views(dn.in[1]);
+      int64_t L1 = -1, L2;
+      if (centred && (!match_mean(dn.in[1], z1, red1, L1) || skip_reshapes(z1) != x)) continue;
+      const int mu = centred ? skip_views(dn.in[1]) : -1;
       // RS = rsqrt(mean(D*D) + eps)
       const Node& rn = nodes_[rs];
       const int ve = skip_views(rn.in[0]);
@@ -1085,13 +1094,14 @@ class Planner {
       if (const_value(nodes_[ve].in[1], eps)) var = nodes_[ve].in[0];
       else if (const_value(nodes_[ve].in[0], eps)) var = nodes_[ve].in[1];
       else continue;
-      if (!match_mean(var, z2, red2, L2) || L2 != L1) continue;
+      if (!match_mean(var, z2, red2, L2) || (centred && L2 != L1)) continue;
+      if (!centred) L1 = L2;
       const int sq = skip_reshapes(z2);
       if (nodes_[sq].op != "mul" || skip_reshapes(nodes_[sq].in[0]) != d || skip_reshapes(nodes_[sq].in[1]) != d) continue;
       const int64_t L = L1, total = numel(nodes_[x].shape);
       if (L <= 0 || total % L != 0 || numel(dn.shape) != total || numel(nodes_[y].shape) != total) continue;
       // the mean and rstd operands must broadcast per row
-      if (!per_row_operand(dn.in[1], mu, dn.shape, L)) continue;
+      if (centred && !per_row_operand(dn.in[1], mu, dn.shape, L)) continue;
       if (!per_row_operand(xh_rs_operand_, rs, nodes_[xh_node_].shape, L)) continue;
       // row-major views only between X, D, XH and Y (no transposes): guaranteed by skip_reshapes
       int w_in = -1, b_in = -1;
@@ -1108,7 +1118,8 @@ class Planner {
       covered[oname] = 0;
       Step s;
       s.kind = Step::NORM;
-      s.label = (inner == 1 && period == L) || (w < 0 && b < 0) ? "layernorm" : "groupnorm";
+      s.label = !centred ? "rmsnorm" : (inner == 1 && period == L) || (w < 0 && b < 0) ? "layernorm" : "groupnorm";
+      s.act = centred ? 1 : 0;  // NORM steps: whether the row mean is subtracted
       s.d[0] = total / L;
       s.d[1] = L;
       s.aff_inner = inner;
@@ -1126,7 +1137,7 @@ class Planner {
         const int o = skip_reshapes(by_name_[other]);
         const int buf = out_buffer_[other];
         if (plan_->buffers[buf].dtype != IB200_F32 || numel(nodes_[by_name_[other]].shape) != s.d[0]) continue;
-        if (o == mu) { s.out[1] = buf; covered[other] = 1; }
+        if (centred && o == mu) { s.out[1] = buf; covered[other] = 1; }
         else if (o == rs) { s.out[2] = buf; covered[other] = 2; }
       }
       if (!all_outputs_in(covered)) continue;
@@ -2663,7 +2674,7 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
       case Step::NORM:
         rc = launch_norm_rows(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), static_cast<float*>(P(st.out[1])),
                               static_cast<float*>(P(st.out[2])), st.dtype, st.dtype2, st.d[0], st.d[1], st.aff_inner, st.aff_period,
-                              st.eps, s, status);
+                              st.eps, s, status, st.act != 0);
         break;
       case Step::GEMM:
         for (int64_t bi = 0; bi < st.batch && rc == IB200_OK; ++bi)

@@ -14,6 +14,7 @@ knobs that the reference carries inside ``shape_bindings`` (``SOFTMAX_THREADS``,
 from __future__ import annotations
 
 import ctypes as C
+import itertools
 import json
 import threading
 from collections import OrderedDict
@@ -78,6 +79,7 @@ class B200LoweredKernel:
 
 _CACHE: "OrderedDict[Tuple[str, str], B200LoweredKernel]" = OrderedDict()
 _CACHE_LIMIT = 512
+_PLAN_SERIAL = itertools.count()
 _LOCK = threading.Lock()
 _BY_ID: Dict[str, B200LoweredKernel] = {}
 
@@ -144,7 +146,7 @@ def lower_intent_to_b200_kernel(intent, *, shape_bindings: Mapping[str, Any], sc
             _raise(rc, "plan_describe")
         break
     d = json.loads(buf.value.decode())
-    plan_id = f"{d['kernel_name']}#{len(_BY_ID)}"
+    plan_id = f"{d['kernel_name']}#{next(_PLAN_SERIAL)}"  # never reused, even after cache eviction
     io_spec = dict(d["io_spec"])
     io_spec["plan_id"] = plan_id
     lowered = B200LoweredKernel(

@@ -46,6 +46,8 @@ def _workspace(lowered: B200LoweredKernel, device) -> Optional[torch.Tensor]:
         return None
     key = (lowered.io_spec["plan_id"], str(device))
     ws = _WORKSPACES.get(key)
+    if ws is not None and ws.numel() < lowered.workspace_bytes + 256:
+        ws = None  # never hand a plan less scratch than it asked for
     if ws is None:
         # zero-filled once: the tensor-core GEMM's status word lives in it and is only ever
         # written when a bounded wait expires

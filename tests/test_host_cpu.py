@@ -49,8 +49,8 @@ EXPECTED_KERNELS = {
     "group_norm_kernel": ["groupnorm"], "matmul_bias_relu2d": ["gemm+bias+relu"], "matmul_relu2d": ["gemm+relu"],
     "row_sum": ["reduce_sum"], "row_max": ["reduce_max"], "transpose2d": ["transpose2d"], "gather2d": ["gather"],
     "_attn_fwd": ["gemm", "rowfused(2 steps, 4 phases)", "gemm"],  # scale + mask + softmax in one row program
-    "masked_softmax2d": ["rowfused(2 steps, 4 phases)"], "rms_norm2d": ["rowfused(5 steps, 4 phases)"],
-    "rms_norm_residual2d": ["rowfused(5 steps, 4 phases)"],
+    "masked_softmax2d": ["rowfused(2 steps, 4 phases)"], "rms_norm2d": ["rmsnorm"],
+    "rms_norm_residual2d": ["elementwise(2 ops, 3 in, 1 out)", "rmsnorm"],  # the residual sum, then the norm kernel without centring
     "layer_norm_residual2d": ["elementwise(1 ops, 2 in, 1 out)", "layernorm"],  # the residual sum, then the dedicated kernel
     "mlp2d": ["gemm+bias+relu", "gemm+bias"], "matmul_transposed_epilogue": ["transpose2d", "gemm+bias+relu"],  # epilogues folded per GEMM
 }
@@ -227,3 +227,12 @@ def test_artifact_loader_errors(tmp_path):
                                                              "ops": [{"op": "relu", "inputs": ["x"], "output": "y"}], "outputs": ["y"]}}))
     with pytest.raises(B200RuntimeError, match="missing baseline npz"):
         load_artifact(str(tmp_path / "k2.json"))
+
+
+def test_plan_ids_stay_unique_when_the_plan_cache_evicts(golden_graphs):
+    """Workspaces are cached per plan id: an id handed out twice would give a plan another plan's scratch."""
+    g = golden_graphs["add2d"]["intent"]
+    ids = set()
+    for m in range(1, 560):  # more plans than the cache holds
+        ids.add(lower_intent_to_b200_kernel(g, shape_bindings={"M": m, "N": 8}).io_spec["plan_id"])
+    assert len(ids) == 559

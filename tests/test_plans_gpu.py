@@ -589,3 +589,36 @@ def test_image_ops_at_size_and_in_a_chain():
     want = execute_intent(intent, ins, shapes)
     for n in ("out", "corr"):
         assert out[n].dtype == np.int8 and np.array_equal(out[n], want[n]), n
+
+
+@pytest.mark.parametrize("m,n", [(7, 64), (33, 1000), (64, 4096), (16, 8192), (12, 20000), (6, 40000), (3, 200000), (5, 4099)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_rms_norm_through_every_norm_kernel_variant(m, n, residual, golden_graphs):
+    """rms-norm runs on the row-normalisation kernels with the mean fixed at zero: warp, block, pipelined
+    cluster, one-shot cluster and streaming variants, with and without a residual sum in front."""
+    key = "rms_norm_residual2d" if residual else "rms_norm2d"
+    intent = IntentFunction.from_json_dict(golden_graphs[key]["intent"])
+    rng = np.random.default_rng(n + m)
+    ins = {"inp": (2.0 + rng.standard_normal((m, n))).astype(np.float32), "weight": rng.uniform(0.5, 1.5, n).astype(np.float32)}
+    if residual:
+        ins["residual"] = rng.standard_normal((m, n)).astype(np.float32)
+        ins["bias"] = rng.standard_normal(n).astype(np.float32)
+    out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
+    assert lowered.steps[-1]["kernel"] == "rmsnorm"
+    want = execute_intent(intent, ins, {"M": m, "N": n})
+    tol = infer_tolerances(intent).to_dict()
+    for name in intent.outputs:
+        _agree(out[name], want[name], tol, name)
+    # a row of zeros stays finite (rstd = 1/sqrt(eps)) and an Inf poisons only its own row
+    ins["inp"][0] = 0.0
+    if m > 1:
+        ins["inp"][1, 0] = np.inf
+    if residual:
+        ins["residual"][:2] = 0.0
+    out, _ = _lower_and_run(intent, {"M": m, "N": n}, ins)
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, ins, {"M": m, "N": n})
+    for name in intent.outputs:
+        w, g = np.asarray(want[name]), out[name]
+        assert np.array_equal(np.isnan(w), np.isnan(g)), name
+        assert np.allclose(np.nan_to_num(g, nan=0.0, posinf=0.0, neginf=0.0), np.nan_to_num(w, nan=0.0, posinf=0.0, neginf=0.0), rtol=1e-3, atol=1e-3), name
