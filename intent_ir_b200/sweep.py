@@ -39,6 +39,9 @@ __all__ = ["SweepCase", "generate_sweep_cases", "split_rows", "run_sweep", "merg
 
 EDGE_SIZES = (1, 2, 3, 7, 8, 15, 16, 17, 31, 32, 33)
 KINDS = ("reduce_any", "reduce_sum", "reduce_max", "softmax", "layernorm", "groupnorm", "matmul_bias_relu", "chain")
+# the graphs either side of the headline path: normalisation variants, masked softmax, the single-op kernels
+EXTRA_KINDS = ("rmsnorm", "layernorm_residual", "masked_softmax", "rope", "dropout", "image")
+ALL_KINDS = KINDS + EXTRA_KINDS
 
 
 @dataclass
@@ -157,6 +160,57 @@ def g_chain(rng: np.random.Generator, dtype: str) -> Dict[str, Any]:
     return {"name": "sweep_chain", "tensors": tensors, "ops": ops, "outputs": ["y"]}
 
 
+def g_rmsnorm() -> Dict[str, Any]:
+    """y = x * rsqrt(mean(x^2) + 1e-5) * w, rstd returned (the chain of pipeline/tilelang/core.py:735-776)."""
+    return {"name": "sweep_rmsnorm", "tensors": {"x": _t(["M", "N"]), "w": _t(["N"]), "y": _t(["M", "N"]), "rstd": _t(["M"])},
+            "ops": [{"op": "mul", "inputs": ["x", "x"], "output": "sq"},
+                    {"op": "reduce_sum", "inputs": ["sq"], "output": "ss", "attrs": {"dims": [1], "keepdims": True, "scale": "1.0/N"}},
+                    {"op": "add", "inputs": ["ss"], "output": "ve", "attrs": {"addend": 1e-5}},
+                    {"op": "rsqrt", "inputs": ["ve"], "output": "r1"},
+                    {"op": "reshape", "inputs": ["r1"], "output": "rstd", "attrs": {"shape": ["M"]}},
+                    {"op": "mul", "inputs": ["x", "r1"], "output": "xn"},
+                    {"op": "mul", "inputs": ["xn", "w"], "output": "y"}], "outputs": ["y", "rstd"]}
+
+
+def g_layernorm_residual() -> Dict[str, Any]:
+    """layernorm of x + r (pipeline/tilelang/core.py:1426): the residual sum is computed first."""
+    g = g_layernorm()
+    g = {**g, "name": "sweep_layernorm_residual", "tensors": {**g["tensors"], "r": _t(["M", "N"]), "x0": _t(["M", "N"])}}
+    ops = [dict(o, inputs=["z" if i == "x" else i for i in o["inputs"]]) for o in g["ops"]]
+    g["ops"] = [{"op": "add", "inputs": ["x0", "r"], "output": "z"}] + ops
+    del g["tensors"]["x"]
+    return g
+
+
+def g_masked_softmax() -> Dict[str, Any]:
+    """softmax(where(mask[N], x, -1e9)) along the row (pipeline/tilelang/core.py:1050-1076)."""
+    return {"name": "sweep_masked_softmax", "tensors": {"x": _t(["M", "N"]), "mask": _t(["N"], "bool"), "y": _t(["M", "N"])},
+            "ops": [{"op": "const", "inputs": [], "output": "neg", "attrs": {"value": -1e9, "dtype": "f32"}},
+                    {"op": "broadcast_in_dim", "inputs": ["mask"], "output": "m2", "attrs": {"out_shape": ["M", "N"], "broadcast_dims": [1]}},
+                    {"op": "where", "inputs": ["m2", "x", "neg"], "output": "xm"},
+                    {"op": "softmax", "inputs": ["xm"], "output": "y", "attrs": {"axis": -1}}], "outputs": ["y"]}
+
+
+def g_rope() -> Dict[str, Any]:
+    return {"name": "sweep_rope", "tensors": {"x": _t(["S", "B", "H", "D"]), "cos": _t(["S", "D2"]), "sin": _t(["S", "D2"]), "y": _t(["S", "B", "H", "D"])},
+            "ops": [{"op": "rope", "inputs": ["x", "cos", "sin"], "output": "y"}], "outputs": ["y"]}
+
+
+def g_dropout(rounds: int) -> Dict[str, Any]:
+    return {"name": "sweep_dropout", "tensors": {"x": _t(["M", "N"]), "p": _t([]), "seed": _t([], "i64"), "y": _t(["M", "N"])},
+            "ops": [{"op": "dropout", "inputs": ["x", "p", "seed"], "output": "y", "attrs": {"n_rounds": rounds}}], "outputs": ["y"]}
+
+
+def g_image() -> Dict[str, Any]:
+    """correlation -> 2x resize -> warp on int8 planes (verify/interpreter.py:330-454)."""
+    return {"name": "sweep_image",
+            "tensors": {"a": _t(["C", "H", "W"], "i8"), "b": _t(["C", "H", "W"], "i8"), "sh": _t([], "i32"), "off": _t(["H2", "W2"], "i16"),
+                        "corr": _t(["OC", "H", "W"], "i8"), "up": _t(["OC", "H2", "W2"], "i8"), "out": _t(["OC", "H2", "W2"], "i8")},
+            "ops": [{"op": "correlation", "inputs": ["a", "b", "sh"], "output": "corr"},
+                    {"op": "resize", "inputs": ["corr"], "output": "up", "attrs": {"hw_fl": 7}},
+                    {"op": "warp", "inputs": ["up", "off"], "output": "out"}], "outputs": ["out", "corr"]}
+
+
 # ---- case generation ------------------------------------------------------------------------------------
 
 def _dim(rng: np.random.Generator, hi: int = 4096) -> int:
@@ -193,10 +247,23 @@ def generate_sweep_cases(n_cases: int, base_seed: int = 1000, max_elements: int 
             shapes = {"M": m, "N": n}
             intent = g_softmax(dtype) if kind == "softmax" else g_chain(rng, dtype) if kind == "chain" else g_reduce(kind, dtype)
             elements = m * n
-        elif kind == "layernorm":
+        elif kind in ("layernorm", "rmsnorm", "layernorm_residual", "masked_softmax", "dropout"):
             dtype = "f32"
             m, n = _fit([_dim(rng), _dim(rng)], max_elements)
-            shapes, intent, elements = {"M": m, "N": n}, g_layernorm(), m * n
+            intent = {"layernorm": g_layernorm, "rmsnorm": g_rmsnorm, "layernorm_residual": g_layernorm_residual,
+                      "masked_softmax": g_masked_softmax}[kind]() if kind != "dropout" else g_dropout(int(rng.choice((7, 10))))
+            shapes, elements = {"M": m, "N": n}, m * n
+        elif kind == "rope":
+            dtype = "f32"
+            seq, heads, half = _fit([_dim(rng, 1024), int(rng.integers(1, 17)), int(rng.integers(1, 65))], max_elements // 2)
+            shapes = {"S": seq, "B": int(rng.integers(1, 3)), "H": heads, "D": 2 * half, "D2": half}
+            intent, elements = g_rope(), seq * shapes["B"] * heads * 2 * half
+        elif kind == "image":
+            dtype = "i8"
+            c, h, w = _fit([int(rng.integers(1, 9)), _dim(rng, 128), _dim(rng, 300)], max_elements // 16)
+            oc = int(rng.integers(1, min(8, w + 1) + 1))
+            shapes = {"C": c, "H": h, "W": w, "OC": oc, "H2": 2 * h, "W2": 2 * w}
+            intent, elements = g_image(), 4 * oc * h * w
         elif kind == "groupnorm":
             dtype = "f32"
             if canonical_groupnorm_every and i % canonical_groupnorm_every == 0:
@@ -218,7 +285,7 @@ def generate_sweep_cases(n_cases: int, base_seed: int = 1000, max_elements: int 
 
 
 _ROW_AXIS = {"reduce_any": "M", "reduce_sum": "M", "reduce_max": "M", "softmax": "M", "layernorm": "M", "chain": "M",
-             "matmul_bias_relu": "M", "groupnorm": "N"}
+             "matmul_bias_relu": "M", "groupnorm": "N", "rmsnorm": "M", "layernorm_residual": "M", "masked_softmax": "M"}
 
 
 def split_rows(case: SweepCase, parts: int, id_stride: int = 1 << 20) -> List[SweepCase]:
@@ -268,6 +335,26 @@ def case_inputs(case: SweepCase) -> Dict[str, np.ndarray]:
         sc = np.float32(1.0 / np.sqrt(max(s["K"], 1)))
         return {"A": q(rng.standard_normal((s["M"], s["K"]), dtype=np.float32)), "B": q(sc * rng.standard_normal((s["K"], s["N"]), dtype=np.float32)),
                 "bias": q(0.1 * rng.standard_normal(s["N"], dtype=np.float32))}
+    if k == "rmsnorm":
+        return {"x": rng.standard_normal((s["M"], s["N"]), dtype=np.float32), "w": rng.uniform(0.5, 1.5, s["N"]).astype(np.float32)}
+    if k == "layernorm_residual":
+        return {"x0": rng.standard_normal((s["M"], s["N"]), dtype=np.float32), "r": rng.standard_normal((s["M"], s["N"]), dtype=np.float32),
+                "w": rng.uniform(0.5, 1.5, s["N"]).astype(np.float32), "b": (0.1 * rng.standard_normal(s["N"])).astype(np.float32)}
+    if k == "masked_softmax":
+        mask = rng.random(s["N"]) > 0.2
+        mask[int(rng.integers(0, s["N"]))] = True  # at least one column survives
+        return {"x": 3 * rng.standard_normal((s["M"], s["N"]), dtype=np.float32), "mask": mask}
+    if k == "rope":
+        ang = rng.uniform(-np.pi, np.pi, (s["S"], s["D2"]))
+        return {"x": rng.standard_normal((s["S"], s["B"], s["H"], s["D"]), dtype=np.float32), "cos": np.cos(ang).astype(np.float32),
+                "sin": np.sin(ang).astype(np.float32)}
+    if k == "dropout":
+        return {"x": rng.standard_normal((s["M"], s["N"]), dtype=np.float32), "p": np.array(rng.choice((0.1, 0.25, 0.5)), np.float32),
+                "seed": np.array(int(rng.integers(-2 ** 40, 2 ** 40)), np.int64)}
+    if k == "image":
+        i8 = lambda shape: rng.integers(-128, 128, size=shape).astype(np.int8)  # noqa: E731
+        return {"a": i8((s["C"], s["H"], s["W"])), "b": i8((s["C"], s["H"], s["W"])), "sh": np.array(int(rng.integers(0, 9)), np.int32),
+                "off": rng.integers(-1024, 1024, size=(s["H2"], s["W2"])).astype(np.int16)}
     raise ValueError(f"unknown sweep kind {k}")
 
 

@@ -622,3 +622,15 @@ def test_rms_norm_through_every_norm_kernel_variant(m, n, residual, golden_graph
         w, g = np.asarray(want[name]), out[name]
         assert np.array_equal(np.isnan(w), np.isnan(g)), name
         assert np.allclose(np.nan_to_num(g, nan=0.0, posinf=0.0, neginf=0.0), np.nan_to_num(w, nan=0.0, posinf=0.0, neginf=0.0), rtol=1e-3, atol=1e-3), name
+
+
+def test_seeded_sweep_over_every_graph_family():
+    """96 seeded cases over all fourteen graph families (random extents with the verifier's edge sizes, f32 and
+    bf16) lowered, run on the GPU and diffed by the oracle's run_diff, exactly as `bench.py --workload sweep` does."""
+    from intent_ir_b200.sweep import ALL_KINDS, generate_sweep_cases, run_sweep
+
+    cases = generate_sweep_cases(96, base_seed=4242, max_elements=1 << 18, kinds=ALL_KINDS)
+    recs = run_sweep(cases, diff_fn=run_diff, tolerances_fn=infer_tolerances, case_type=TestCase)
+    bad = [(r["kind"], r["shapes"], r["summary"]) for r in recs if not r["ok"]]
+    assert len(recs) == 96 and not bad, bad
+    assert {r["kind"] for r in recs} == set(ALL_KINDS)

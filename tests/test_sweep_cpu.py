@@ -115,3 +115,23 @@ def test_two_rank_sweep_over_gloo(tmp_path):
     assert s["cases"] == s["ok"] == 20 and s["per_rank"] == [10, 10]
     shards = sorted(p.name for p in tmp_path.iterdir() if p.name.startswith("sweep.rank"))
     assert shards == ["sweep.rank0.jsonl", "sweep.rank1.jsonl"]
+
+
+def test_extra_graph_families_are_valid_and_plannable(tmp_path):
+    """The graphs either side of the headline path (rms-norm, residual layernorm, masked softmax, rope, dropout,
+    the int8 image chain): valid IntentIR, executable by the oracle, accepted by the planner."""
+    from intent_ir_b200.lowering import plan_json
+    from intent_ir_b200.sweep import ALL_KINDS, EXTRA_KINDS
+
+    cases = generate_sweep_cases(120, base_seed=77, max_elements=1 << 12, kinds=ALL_KINDS)
+    assert {c.kind for c in cases} == set(ALL_KINDS)
+    extra = [c for c in cases if c.kind in EXTRA_KINDS]
+    recs = run_sweep(extra, out_dir=str(tmp_path), make_runner=numpy_runner, **CHECKER)
+    assert len(recs) == len(extra) and all(r["ok"] for r in recs), [(r["kind"], r["summary"]) for r in recs if not r["ok"]]
+    expected_last = {"rmsnorm": "rmsnorm", "layernorm_residual": "layernorm", "rope": "rope", "dropout": "dropout", "image": "warp"}
+    for c in extra:
+        kernels = [s["kernel"] for s in plan_json(c.intent, c.shapes)["steps"]]
+        if c.kind in expected_last:
+            assert kernels[-1] == expected_last[c.kind], (c.kind, c.shapes, kernels)
+        else:
+            assert kernels[-1] == "softmax" or kernels[-1].startswith("rowfused"), (c.kind, kernels)
