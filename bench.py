@@ -142,6 +142,40 @@ def workload(name):
         return (g["masked_softmax2d"]["intent"], {"M": m, "N": n},
                 lambda r: {"inp": 3 * r.standard_normal((m, n), dtype=np.float32), "mask": r.random(n) > 0.2},
                 2 * m * n * 4 + n, 0, "masked softmax f32 [4096,4096], column mask (pipeline/tilelang/core.py:1050)")
+    if name == "rowprog":
+        m, n = 8192, 4096
+        t = lambda sh: {"dtype": "f32", "shape": sh, "layout": "row_major"}  # noqa: E731
+        js = {"name": "rms_relu", "tensors": {"x": t(["M", "N"]), "w": t(["N"]), "y": t(["M", "N"]), "rstd": t(["M"])},
+              "ops": [{"op": "mul", "inputs": ["x", "x"], "output": "sq"},
+                      {"op": "reduce_sum", "inputs": ["sq"], "output": "ss", "attrs": {"dims": [1], "keepdims": True, "scale": "1.0/N"}},
+                      {"op": "add", "inputs": ["ss"], "output": "ve", "attrs": {"addend": 1e-5}},
+                      {"op": "rsqrt", "inputs": ["ve"], "output": "r1"},
+                      {"op": "reshape", "inputs": ["r1"], "output": "rstd", "attrs": {"shape": ["M"]}},
+                      {"op": "mul", "inputs": ["x", "r1"], "output": "xn"},
+                      {"op": "relu", "inputs": ["xn"], "output": "xr"},
+                      {"op": "mul", "inputs": ["xr", "w"], "output": "y"}], "outputs": ["y", "rstd"]}
+        return (js, {"M": m, "N": n},
+                lambda r: {"x": r.standard_normal((m, n), dtype=np.float32), "w": r.uniform(0.5, 1.5, n).astype(np.float32)},
+                2 * m * n * 4 + n * 4 + m * 4, 0, "rms-norm with a ReLU inside, f32 [8192,4096]: no dedicated kernel, one fused row program")
+    if name == "rope":
+        sq, b, h, d = 8192, 2, 16, 128
+        t = lambda sh: {"dtype": "f32", "shape": sh, "layout": "row_major"}  # noqa: E731
+        js = {"name": "rope", "tensors": {"x": t(["S", "B", "H", "D"]), "cos": t(["S", "D2"]), "sin": t(["S", "D2"]), "y": t(["S", "B", "H", "D"])},
+              "ops": [{"op": "rope", "inputs": ["x", "cos", "sin"], "output": "y"}], "outputs": ["y"]}
+
+        def gen(r):
+            ang = r.uniform(-np.pi, np.pi, (sq, d // 2))
+            return {"x": r.standard_normal((sq, b, h, d), dtype=np.float32), "cos": np.cos(ang).astype(np.float32), "sin": np.sin(ang).astype(np.float32)}
+        return (js, {"S": sq, "B": b, "H": h, "D": d, "D2": d // 2}, gen, 2 * sq * b * h * d * 4 + 2 * sq * (d // 2) * 4, 0,
+                "rope f32 [8192,2,16,128] (verify/interpreter.py:455-477), bit-exact")
+    if name == "dropout":
+        m, n = 8192, 4096
+        t = lambda sh, dt="f32": {"dtype": dt, "shape": sh, "layout": "row_major"}  # noqa: E731
+        js = {"name": "dropout", "tensors": {"x": t(["M", "N"]), "p": t([]), "seed": t([], "i64"), "y": t(["M", "N"])},
+              "ops": [{"op": "dropout", "inputs": ["x", "p", "seed"], "output": "y"}], "outputs": ["y"]}
+        return (js, {"M": m, "N": n},
+                lambda r: {"x": r.standard_normal((m, n), dtype=np.float32), "p": np.array(0.1, np.float32), "seed": np.array(1234, np.int64)},
+                2 * m * n * 4, 0, "dropout f32 [8192,4096], p = 0.1, 10 Philox rounds (verify/interpreter.py:697-742), bit-exact mask")
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -203,7 +237,7 @@ def device_sets(lowered, gen, n_sets, seed):
     specs = lowered.io_spec["tensors"]
     sets = []
     for _ in range(n_sets):
-        ins = {k: torch.from_numpy(np.ascontiguousarray(v)).cuda().to(TORCH_OF_DTYPE[specs[k]["dtype"]]) for k, v in gen(rng).items()}
+        ins = {k: torch.from_numpy(np.asarray(v, order="C")).cuda().to(TORCH_OF_DTYPE[specs[k]["dtype"]]) for k, v in gen(rng).items()}
         outs = {k: torch.empty([int(d) for d in specs[k]["shape"]], dtype=TORCH_OF_DTYPE[specs[k]["dtype"]], device="cuda")
                 for k in lowered.output_names}
         sets.append((ins, outs))
@@ -526,7 +560,8 @@ def main():
                                     "sample": f"{rows_sample} of {rows_full} rows, best of 3, numpy {np.__version__}, host has {os.cpu_count()} cores"}
         if not args.no_ops:
             ops = {}
-            for name in ("layernorm", "groupnorm", "matmul", "chain", "rmsnorm", "layernorm_residual", "masked_softmax", "reduce_any_large", "reduce_any"):
+            for name in ("layernorm", "groupnorm", "matmul", "chain", "rmsnorm", "layernorm_residual", "masked_softmax", "rowprog", "rope", "dropout",
+                         "reduce_any_large", "reduce_any"):
                 if name == args.workload:
                     continue
                 ops[name] = measure_op(name, max(20, min(args.steps, 100)), max(3, min(args.warmup, 10)), peaks)

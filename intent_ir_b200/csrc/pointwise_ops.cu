@@ -50,15 +50,19 @@ __global__ void __launch_bounds__(256) rope_kernel(const float* __restrict__ x, 
 
 // counter (index, 0, 0, 0), key (seed low, seed high): the first output word of Philox-4x32
 // (verify/interpreter.py:303-329)
+// ROUNDS > 0 unrolls completely: the zero counter words then cost nothing in the first round and
+// the second round's key-only product is hoisted out of the element loop by the compiler.
+template <int ROUNDS>
 __device__ __forceinline__ uint32_t philox_c0(uint32_t index, uint32_t k0, uint32_t k1, int rounds) {
   uint32_t c0 = index, c1 = 0, c2 = 0, c3 = 0;
-  for (int r = 0; r < rounds; ++r) {
-    const uint32_t hi_a = __umulhi(0xD2511F53u, c0), lo_a = 0xD2511F53u * c0;
-    const uint32_t hi_b = __umulhi(0xCD9E8D57u, c2), lo_b = 0xCD9E8D57u * c2;
-    c0 = hi_b ^ c1 ^ k0;
-    c1 = lo_b;
-    c2 = hi_a ^ c3 ^ k1;
-    c3 = lo_a;
+  const int n = ROUNDS > 0 ? ROUNDS : rounds;
+#pragma unroll
+  for (int r = 0; r < n; ++r) {
+    const uint64_t pa = (uint64_t)0xD2511F53u * c0, pb = (uint64_t)0xCD9E8D57u * c2;  // one wide multiply each
+    c0 = (uint32_t)(pb >> 32) ^ c1 ^ k0;
+    c1 = (uint32_t)pb;
+    c2 = (uint32_t)(pa >> 32) ^ c3 ^ k1;
+    c3 = (uint32_t)pa;
     k0 += 0x9E3779B9u;
     k1 += 0xBB67AE85u;
   }
@@ -76,6 +80,7 @@ struct DropoutArgs {
 
 // y = u > p ? x / (1 - p) : 0 with u = uniform(philox(seed, index)); p >= 1 gives zeros, p <= 0
 // gives x (verify/interpreter.py:697-742)
+template <int ROUNDS>
 __global__ void __launch_bounds__(256) dropout_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n, DropoutArgs a) {
   float p = a.p_value;
   if (a.p_ptr) p = a.p_dtype == IB200_F32 ? *static_cast<const float*>(a.p_ptr)
@@ -93,7 +98,7 @@ __global__ void __launch_bounds__(256) dropout_kernel(const float* __restrict__ 
     if (mode == 1) {
       v = x[i];
     } else if (mode == 2) {
-      int r = (int)philox_c0((uint32_t)i, k0, k1, a.rounds);
+      int r = (int)philox_c0<ROUNDS>((uint32_t)i, k0, k1, a.rounds);
       if (r < 0) r = ~r;
       const float u = __fmul_rn(__int2float_rn(r), 4.6566127342e-10f);
       v = u > p ? __fdiv_rn(x[i], keep) : 0.0f;
@@ -225,7 +230,9 @@ int launch_dropout(const float* x, float* y, int64_t n, const void* p_ptr, int p
   DropoutArgs a{p_ptr, seed_ptr, p_dtype, seed_dtype, p_value, seed_value, rounds > 0 ? rounds : 10};
   const int64_t blocks = (n + 255) / 256;
   const int grid = (int)(blocks < (int64_t)kSmCount * 32 ? blocks : (int64_t)kSmCount * 32);
-  dropout_kernel<<<grid, 256, 0, s>>>(x, y, n, a);
+  if (a.rounds == 10) dropout_kernel<10><<<grid, 256, 0, s>>>(x, y, n, a);
+  else if (a.rounds == 7) dropout_kernel<7><<<grid, 256, 0, s>>>(x, y, n, a);
+  else dropout_kernel<0><<<grid, 256, 0, s>>>(x, y, n, a);
   return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "dropout launch");
 }
 

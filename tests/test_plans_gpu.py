@@ -634,3 +634,13 @@ def test_seeded_sweep_over_every_graph_family():
     bad = [(r["kind"], r["shapes"], r["summary"]) for r in recs if not r["ok"]]
     assert len(recs) == 96 and not bad, bad
     assert {r["kind"] for r in recs} == set(ALL_KINDS)
+
+
+@pytest.mark.parametrize("rounds", [1, 5, 13])
+def test_dropout_with_other_round_counts(rounds):
+    js = {"name": "dropout", "tensors": {"x": _t0(["M"]), "p": _t0([]), "seed": _t0([], "i32"), "y": _t0(["M"])},
+          "ops": [{"op": "dropout", "inputs": ["x", "p", "seed"], "output": "y", "attrs": {"n_rounds": rounds}}], "outputs": ["y"]}
+    intent = IntentFunction.from_json_dict(js)
+    ins = {"x": np.random.default_rng(rounds).standard_normal(5000, dtype=np.float32), "p": np.array(0.4, np.float32), "seed": np.array(-3, np.int32)}
+    out, _ = _lower_and_run(intent, {"M": 5000}, ins)
+    assert np.array_equal(out["y"], execute_intent(intent, ins, {"M": 5000})["y"])
