@@ -222,14 +222,14 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
 }
 
 // ---- register path -------------------------------------------------------------------------
-// Linear chains over at most three f32 / bf16 / f16 operands (the common case: y = f(x, col, row, consts))
+// Linear chains over at most three f32 / bf16 / f16 / bool operands (the common case: y = f(x, col, row, consts))
 // never touch shared memory: every operand vector is loaded straight into registers with one
 // 128-bit (64-bit for 16-bit types) load (or one scalar load when the operand is constant along the innermost axis),
 // all loads are issued before the first use, and each micro-op is acc = op(acc, B) with B an
 // operand register set, an immediate or acc itself.  Operand count, which operands are
 // inner-broadcast, and the collapsed rank are template parameters, so staging is branch-free.
 struct EwRegInstr {
-  uint8_t op, src, pad[2];  // src: 0..2 operand, 3 immediate, 4 acc
+  uint8_t op, src, pad[2];  // src: 0..2 operand, 3 immediate, 4 acc; EW_WHERE: src = condition, pad = the two values
   float imm;
 };
 struct EwRegCode {
@@ -237,18 +237,22 @@ struct EwRegCode {
   EwRegInstr ins[kEwMaxInstr + 1];
 };
 
-template <int NIN, int BMASK, int RANK>
-__global__ void __launch_bounds__(kThreads, 4) ew_kernel_reg(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
+// EXT adds `where` and bool / u8 operands; it is a separate instantiation because that code costs
+// the plain arithmetic chains registers.  Occupancy is what this kernel lives on: the plain form
+// is held to 32 registers so that eight CTAs (all 64 warps) are resident per SM -- measured on the
+// 4-op broadcast chain: 0.68 of HBM peak at four CTAs per SM, 0.79 at six, 0.83 at eight.
+template <int NIN, int BMASK, int RANK, bool EXT>
+__global__ void __launch_bounds__(kThreads, EXT ? 4 : 8) ew_kernel_reg(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
                                                              const __grid_constant__ EwRegCode code) {
   constexpr int N = 8, U = 2;  // 16 values per thread were measured slower (half the resident warps)
   const int t = threadIdx.x;
   const char* ptr[NIN > 0 ? NIN : 1];
   uint32_t stride[NIN > 0 ? NIN : 1][RANK];
-  int half_kind[NIN > 0 ? NIN : 1];  // 0: f32, 1: bf16, 2: f16 (uniform over the grid)
+  int half_kind[NIN > 0 ? NIN : 1];  // 0: f32, 1: bf16, 2: f16, 3: bool / u8 (uniform over the grid)
 #pragma unroll
   for (int k = 0; k < NIN; ++k) {
     ptr[k] = static_cast<const char*>(prog.in[k].ptr);
-    half_kind[k] = prog.in[k].dtype == IB200_BF16 ? 1 : prog.in[k].dtype == IB200_F16 ? 2 : 0;
+    half_kind[k] = prog.in[k].dtype == IB200_BF16 ? 1 : prog.in[k].dtype == IB200_F16 ? 2 : (EXT && (prog.in[k].dtype == IB200_BOOL || prog.in[k].dtype == IB200_U8)) ? 3 : 0;
 #pragma unroll
     for (int d = 0; d < RANK; ++d) stride[k][d] = (uint32_t)prog.in[k].stride[d];
   }
@@ -280,12 +284,16 @@ __global__ void __launch_bounds__(kThreads, 4) ew_kernel_reg(const __grid_consta
           if (live) {
             if (half_kind[k] == 0) v = __ldg(reinterpret_cast<const float*>(ptr[k]) + off);
             else if (half_kind[k] == 1) v = __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(ptr[k]) + off));
-            else v = __half2float(__ldg(reinterpret_cast<const __half*>(ptr[k]) + off));
+            else if (!EXT || half_kind[k] == 2) v = __half2float(__ldg(reinterpret_cast<const __half*>(ptr[k]) + off));
+            else v = __ldg(reinterpret_cast<const uint8_t*>(ptr[k]) + off) ? 1.0f : 0.0f;
           }
           dst[0] = dst[1] = dst[2] = dst[3] = v;
         } else if (half_kind[k] == 0) {
           const float4 q = live ? __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ptr[k]) + off)) : make_float4(0.f, 0.f, 0.f, 0.f);
           dst[0] = q.x; dst[1] = q.y; dst[2] = q.z; dst[3] = q.w;
+        } else if (EXT && half_kind[k] == 3) {  // four bytes in one 32-bit load
+          const uchar4 q = live ? __ldg(reinterpret_cast<const uchar4*>(reinterpret_cast<const uint8_t*>(ptr[k]) + off)) : make_uchar4(0, 0, 0, 0);
+          dst[0] = q.x ? 1.0f : 0.0f; dst[1] = q.y ? 1.0f : 0.0f; dst[2] = q.z ? 1.0f : 0.0f; dst[3] = q.w ? 1.0f : 0.0f;
         } else {  // four 16-bit elements in one 64-bit load
           const uint2 q = live ? __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(ptr[k]) + off)) : make_uint2(0u, 0u);
           if (half_kind[k] == 1) {
@@ -303,6 +311,19 @@ __global__ void __launch_bounds__(kThreads, 4) ew_kernel_reg(const __grid_consta
     for (int j = 0; j < N; ++j) acc[j] = 0.0f;
     for (int ip = 0; ip < code.n_instr; ++ip) {
       const EwRegInstr ins = code.ins[ip];
+      if (EXT && ins.op == EW_WHERE) {  // acc = cond != 0 ? b : c, each an operand, the immediate or acc
+        float sel[3][N];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+          const uint8_t src = q == 0 ? ins.src : ins.pad[q - 1];
+#pragma unroll
+          for (int j = 0; j < N; ++j)
+            sel[q][j] = src == 0 ? in[0][j] : src == 1 ? in[NIN > 1 ? 1 : 0][j] : src == 2 ? in[NIN > 2 ? 2 : 0][j] : src == 3 ? ins.imm : acc[j];
+        }
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = sel[0][j] != 0.0f ? sel[1][j] : sel[2][j];
+        continue;
+      }
       switch (ins.src) {
         case 0: apply<N>(ins.op, acc, in[0], acc); break;
         case 1: if (NIN > 1) apply<N>(ins.op, acc, in[NIN > 1 ? 1 : 0], acc); break;
@@ -326,8 +347,9 @@ bool to_register_code(const EwProgram& p, EwRegCode& code) {
   if (!p.vec || p.n_inputs > 3 || p.n_slots != p.n_inputs || p.n_outputs != 1 || p.rank > 2) return false;
   for (int k = 0; k < p.n_inputs; ++k) {
     const EwInput& in = p.in[k];
-    if (in.kind != EW_IN_TENSOR || (in.dtype != IB200_F32 && in.dtype != IB200_BF16 && in.dtype != IB200_F16)) return false;
-    if (in.mode != EW_STAGE_ASYNC_F32X4 && in.mode != EW_STAGE_ASYNC_HALF4 && in.mode != EW_STAGE_BROADCAST) return false;
+    if (in.kind != EW_IN_TENSOR) return false;
+    if (in.dtype != IB200_F32 && in.dtype != IB200_BF16 && in.dtype != IB200_F16 && in.dtype != IB200_BOOL && in.dtype != IB200_U8) return false;
+    if (in.mode != EW_STAGE_ASYNC_F32X4 && in.mode != EW_STAGE_ASYNC_HALF4 && in.mode != EW_STAGE_BYTE4 && in.mode != EW_STAGE_BROADCAST) return false;
   }
   code.n_instr = 0;
   auto emit = [&](uint8_t op, uint8_t src, float imm) {
@@ -355,9 +377,16 @@ bool to_register_code(const EwProgram& p, EwRegCode& code) {
   if (p.out[0].src != EW_ACC) return false;
   for (int ip = 0; ip < p.n_instr; ++ip) {
     const EwInstr& ins = p.instr[ip];
-    if (ins.op == EW_WHERE || ins.dst != EW_NODST || ins.op >= EW_RSUB) return false;
+    if (ins.dst != EW_NODST || ins.op >= EW_RSUB) return false;
     const int a = src_of(ins.a), b = src_of(ins.b);
     if (a < 0 || b < 0) return false;
+    if (ins.op == EW_WHERE) {
+      const int c = src_of(ins.c);
+      if (c < 0) return false;
+      EwRegInstr& r = code.ins[code.n_instr++];
+      r.op = EW_WHERE; r.src = (uint8_t)a; r.pad[0] = (uint8_t)b; r.pad[1] = (uint8_t)c; r.imm = ins.imm;
+      continue;
+    }
     const bool unary = ins.op == EW_MOV || ins.op == EW_RELU || ins.op == EW_EXP || ins.op == EW_RSQRT || ins.op == EW_ABS ||
                        ins.op == EW_FLOOR || ins.op == EW_NOT || ins.op == EW_TO_BOOL || ins.op == EW_TO_INT ||
                        ins.op == EW_ROUND_BF16 || ins.op == EW_ROUND_F16;
@@ -500,9 +529,14 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
     EwRegCode code;
     if (reg_path && fast && to_register_code(p, code)) {
       int bmask = 0;
-      for (int k = 0; k < p.n_inputs; ++k) bmask |= (p.in[k].mode == EW_STAGE_BROADCAST) << k;
+      bool ext = false;
+      for (int k = 0; k < p.n_inputs; ++k) {
+        bmask |= (p.in[k].mode == EW_STAGE_BROADCAST) << k;
+        ext |= p.in[k].dtype == IB200_BOOL || p.in[k].dtype == IB200_U8;
+      }
+      for (int i = 0; i < code.n_instr; ++i) ext |= code.ins[i].op == EW_WHERE;
       void (*rk)(const EwProgram, const EwDivs, const EwRegCode) = nullptr;
-#define IB200_REG(NIN, BM, R) if (p.n_inputs == NIN && bmask == BM && p.rank == R) rk = ew_kernel_reg<NIN, BM, R>;
+#define IB200_REG(NIN, BM, R) if (p.n_inputs == NIN && bmask == BM && p.rank == R) rk = ext ? ew_kernel_reg<NIN, BM, R, true> : ew_kernel_reg<NIN, BM, R, false>;
 #define IB200_REG_R(NIN, BM) IB200_REG(NIN, BM, 1) IB200_REG(NIN, BM, 2)
       IB200_REG_R(0, 0) IB200_REG_R(1, 0) IB200_REG_R(1, 1) IB200_REG_R(2, 0) IB200_REG_R(2, 1) IB200_REG_R(2, 2) IB200_REG_R(2, 3)
       IB200_REG_R(3, 0) IB200_REG_R(3, 1) IB200_REG_R(3, 2) IB200_REG_R(3, 3) IB200_REG_R(3, 4) IB200_REG_R(3, 5) IB200_REG_R(3, 6) IB200_REG_R(3, 7)
@@ -510,7 +544,7 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
 #undef IB200_REG
       if (rk) {
         const int64_t tiles = (p.total + kTile - 1) / kTile;
-        const int64_t cap = (int64_t)kSmCount * 4 * 4;
+        const int64_t cap = (int64_t)kSmCount * (ext ? 4 : 8) * 4;
         rk<<<(int)(tiles < cap ? tiles : cap), kThreads, 0, s>>>(p, divs, code);
         return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "elementwise launch");
       }

@@ -74,6 +74,18 @@ __device__ __forceinline__ void apply(uint8_t op, const float (&a)[N], const flo
       acc[j] = (EXPR);                         \
     }                                          \
     break;
+  // the opcodes of almost every chain first: one compare each instead of a walk down the switch's
+  // comparison tree
+  if (op == EW_ADD) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = a[j] + b[j];
+    return;
+  }
+  if (op == EW_MUL) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = a[j] * b[j];
+    return;
+  }
   switch (op) {
     EW_CASE(EW_MOV, x)
     EW_CASE(EW_ADD, x + y)
