@@ -143,6 +143,17 @@ def workload(name):
         return (g["masked_softmax2d"]["intent"], {"M": m, "N": n},
                 lambda r: {"inp": 3 * r.standard_normal((m, n), dtype=np.float32), "mask": r.random(n) > 0.2},
                 2 * m * n * 4 + n, 0, "masked softmax f32 [4096,4096], column mask (pipeline/tilelang/core.py:1050)")
+    if name == "dag":
+        m, n = 8192, 4096
+        t = lambda sh: {"dtype": "f32", "shape": sh, "layout": "row_major"}  # noqa: E731
+        js = {"name": "ew_dag", "tensors": {"x": t(["M", "N"]), "col": t(["N"]), "row": t(["M", 1]), "y": t(["M", "N"])},
+              "ops": [{"op": "mul", "inputs": ["x", "col"], "output": "a"}, {"op": "add", "inputs": ["a", "row"], "output": "b"},
+                      {"op": "sub", "inputs": ["x", "col"], "output": "c"}, {"op": "mul", "inputs": ["b", "c"], "output": "d"},
+                      {"op": "max", "inputs": ["x", "row"], "output": "e"}, {"op": "add", "inputs": ["d", "e"], "output": "y"}], "outputs": ["y"]}
+        return (js, {"M": m, "N": n},
+                lambda r: {"x": r.standard_normal((m, n), dtype=np.float32), "col": r.standard_normal(n, dtype=np.float32),
+                           "row": r.standard_normal((m, 1), dtype=np.float32)},
+                2 * m * n * 4 + n * 4 + m * 4, 0, "elementwise DAG with reused values (6 ops, two register temporaries), f32 [8192,4096]")
     if name == "rowprog":
         m, n = 8192, 4096
         t = lambda sh: {"dtype": "f32", "shape": sh, "layout": "row_major"}  # noqa: E731
@@ -561,7 +572,7 @@ def main():
                                     "sample": f"{rows_sample} of {rows_full} rows, best of 3, numpy {np.__version__}, host has {os.cpu_count()} cores"}
         if not args.no_ops:
             ops = {}
-            for name in ("layernorm", "groupnorm", "matmul", "chain", "rmsnorm", "layernorm_residual", "masked_softmax", "rowprog", "rope", "dropout",
+            for name in ("layernorm", "groupnorm", "matmul", "chain", "dag", "rmsnorm", "layernorm_residual", "masked_softmax", "rowprog", "rope", "dropout",
                          "reduce_any_large", "reduce_any"):
                 if name == args.workload:
                     continue

@@ -131,7 +131,7 @@ __device__ __forceinline__ void write_outputs(const EwProgram& prog, const float
 // mode) are read once per CTA into registers; the per-tile work is RANK-1 multiply-shift
 // divisions per vector and one 32-bit multiply-add per operand and dimension.
 template <int MAXIN, int RANK, bool VEC, int N>
-__global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs) {
+__global__ void __launch_bounds__(kThreads, N == 8 ? 4 : 2) ew_kernel_fast(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs) {
   extern __shared__ __align__(16) float file[];
   const int t = threadIdx.x;
   constexpr int W = VEC ? 4 : 1, U = N / W;
@@ -229,7 +229,9 @@ __global__ void __launch_bounds__(kThreads) ew_kernel_fast(const __grid_constant
 // operand register set, an immediate or acc itself.  Operand count, which operands are
 // inner-broadcast, and the collapsed rank are template parameters, so staging is branch-free.
 struct EwRegInstr {
-  uint8_t op, src, pad[2];  // src: 0..2 operand, 3 immediate, 4 acc; EW_WHERE: src = condition, pad = the two values
+  uint8_t op, src;     // src: 0..2 operand, 3 immediate, 4 acc, 5..6 temporary; EW_WHERE: the condition
+  uint8_t b, c;        // EW_WHERE: the two values (same codes)
+  uint8_t dst, pad[3]; // 0, or 1..2: also keep the result in that temporary (extended form only)
   float imm;
 };
 struct EwRegCode {
@@ -307,29 +309,36 @@ __global__ void __launch_bounds__(kThreads, EXT ? 4 : 8) ew_kernel_reg(const __g
       }
     }
     float acc[N];
+    float tmp[EXT ? 2 : 1][N];  // values used more than once (extended form)
 #pragma unroll
-    for (int j = 0; j < N; ++j) acc[j] = 0.0f;
+    for (int j = 0; j < N; ++j) acc[j] = tmp[0][j] = tmp[EXT ? 1 : 0][j] = 0.0f;
     for (int ip = 0; ip < code.n_instr; ++ip) {
       const EwRegInstr ins = code.ins[ip];
-      if (EXT && ins.op == EW_WHERE) {  // acc = cond != 0 ? b : c, each an operand, the immediate or acc
+      if (EXT && ins.op == EW_WHERE) {  // acc = cond != 0 ? b : c, each an operand, the immediate, acc or a temporary
         float sel[3][N];
 #pragma unroll
         for (int q = 0; q < 3; ++q) {
-          const uint8_t src = q == 0 ? ins.src : ins.pad[q - 1];
+          const uint8_t src = q == 0 ? ins.src : q == 1 ? ins.b : ins.c;
 #pragma unroll
           for (int j = 0; j < N; ++j)
-            sel[q][j] = src == 0 ? in[0][j] : src == 1 ? in[NIN > 1 ? 1 : 0][j] : src == 2 ? in[NIN > 2 ? 2 : 0][j] : src == 3 ? ins.imm : acc[j];
+            sel[q][j] = src == 0 ? in[0][j] : src == 1 ? in[NIN > 1 ? 1 : 0][j] : src == 2 ? in[NIN > 2 ? 2 : 0][j] : src == 3 ? ins.imm
+                        : src == 4 ? acc[j] : src == 5 ? tmp[0][j] : tmp[1][j];
         }
 #pragma unroll
         for (int j = 0; j < N; ++j) acc[j] = sel[0][j] != 0.0f ? sel[1][j] : sel[2][j];
-        continue;
-      }
+      } else
       switch (ins.src) {
         case 0: apply<N>(ins.op, acc, in[0], acc); break;
         case 1: if (NIN > 1) apply<N>(ins.op, acc, in[NIN > 1 ? 1 : 0], acc); break;
         case 2: if (NIN > 2) apply<N>(ins.op, acc, in[NIN > 2 ? 2 : 0], acc); break;
         case 3: apply_scalar<N>(ins.op, acc, ins.imm); break;
+        case 5: if (EXT) apply<N>(ins.op, acc, tmp[0], acc); break;
+        case 6: if (EXT) apply<N>(ins.op, acc, tmp[1], acc); break;
         default: apply<N>(ins.op, acc, acc, acc);
+      }
+      if (EXT && ins.dst) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) tmp[ins.dst == 1 ? 0 : 1][j] = acc[j];
       }
     }
 #pragma unroll
@@ -344,7 +353,8 @@ __global__ void __launch_bounds__(kThreads, EXT ? 4 : 8) ew_kernel_reg(const __g
 
 // Translate a slot-file program into the register form, if it is a linear chain.
 bool to_register_code(const EwProgram& p, EwRegCode& code) {
-  if (!p.vec || p.n_inputs > 3 || p.n_slots != p.n_inputs || p.n_outputs != 1 || p.rank > 2) return false;
+  // at most two temporaries (slots past the operands): they live in registers in the extended kernel
+  if (!p.vec || p.n_inputs > 3 || p.n_slots > p.n_inputs + 2 || p.n_outputs != 1 || p.rank > 2) return false;
   for (int k = 0; k < p.n_inputs; ++k) {
     const EwInput& in = p.in[k];
     if (in.kind != EW_IN_TENSOR) return false;
@@ -352,11 +362,17 @@ bool to_register_code(const EwProgram& p, EwRegCode& code) {
     if (in.mode != EW_STAGE_ASYNC_F32X4 && in.mode != EW_STAGE_ASYNC_HALF4 && in.mode != EW_STAGE_BYTE4 && in.mode != EW_STAGE_BROADCAST) return false;
   }
   code.n_instr = 0;
-  auto emit = [&](uint8_t op, uint8_t src, float imm) {
+  auto emit = [&](uint8_t op, uint8_t src, float imm, uint8_t dst = 0) -> bool {
+    if (code.n_instr >= kEwMaxInstr) return false;
     EwRegInstr& r = code.ins[code.n_instr++];
-    r.op = op; r.src = src; r.imm = imm; r.pad[0] = r.pad[1] = 0;
+    r = EwRegInstr{};
+    r.op = op; r.src = src; r.imm = imm; r.dst = dst;
+    return true;
   };
-  auto src_of = [&](uint8_t c) -> int { return c == EW_ACC ? 4 : c == EW_IMM ? 3 : (c < p.n_inputs ? c : -1); };
+  auto src_of = [&](uint8_t c) -> int {
+    return c == EW_ACC ? 4 : c == EW_IMM ? 3 : c < p.n_inputs ? c : c < p.n_slots ? 5 + (c - p.n_inputs) : -1;
+  };
+  auto dst_of = [&](uint8_t d) -> int { return d == EW_NODST ? 0 : (d >= p.n_inputs && d < p.n_slots) ? 1 + (d - p.n_inputs) : -1; };
   auto reversed = [](uint8_t op) -> int {
     switch (op) {
       case EW_SUB: return EW_RSUB;
@@ -374,36 +390,41 @@ bool to_register_code(const EwProgram& p, EwRegCode& code) {
     emit(EW_LOADB, p.out[0].src, 0.0f);
     return true;
   }
-  if (p.out[0].src != EW_ACC) return false;
   for (int ip = 0; ip < p.n_instr; ++ip) {
     const EwInstr& ins = p.instr[ip];
-    if (ins.dst != EW_NODST || ins.op >= EW_RSUB) return false;
-    const int a = src_of(ins.a), b = src_of(ins.b);
-    if (a < 0 || b < 0) return false;
+    if (ins.op >= EW_RSUB) return false;
+    const int a = src_of(ins.a), b = src_of(ins.b), dst = dst_of(ins.dst);
+    if (a < 0 || b < 0 || dst < 0) return false;
     if (ins.op == EW_WHERE) {
       const int c = src_of(ins.c);
-      if (c < 0) return false;
+      if (c < 0 || code.n_instr >= kEwMaxInstr) return false;
       EwRegInstr& r = code.ins[code.n_instr++];
-      r.op = EW_WHERE; r.src = (uint8_t)a; r.pad[0] = (uint8_t)b; r.pad[1] = (uint8_t)c; r.imm = ins.imm;
+      r = EwRegInstr{};
+      r.op = EW_WHERE; r.src = (uint8_t)a; r.b = (uint8_t)b; r.c = (uint8_t)c; r.imm = ins.imm; r.dst = (uint8_t)dst;
       continue;
     }
     const bool unary = ins.op == EW_MOV || ins.op == EW_RELU || ins.op == EW_EXP || ins.op == EW_RSQRT || ins.op == EW_ABS ||
                        ins.op == EW_FLOOR || ins.op == EW_NOT || ins.op == EW_TO_BOOL || ins.op == EW_TO_INT ||
                        ins.op == EW_ROUND_BF16 || ins.op == EW_ROUND_F16;
+    bool ok = true;
     if (unary) {
-      if (a != 4) emit(EW_LOADB, (uint8_t)a, ins.imm);
-      emit(ins.op, 4, 0.0f);
+      if (a != 4) ok &= emit(EW_LOADB, (uint8_t)a, ins.imm);
+      ok &= emit(ins.op, 4, 0.0f, (uint8_t)dst);
     } else if (a == 4) {
-      emit(ins.op, (uint8_t)b, ins.imm);
+      ok &= emit(ins.op, (uint8_t)b, ins.imm, (uint8_t)dst);
     } else if (b == 4) {
       const int r = reversed(ins.op);
       if (r < 0) return false;
-      emit((uint8_t)r, (uint8_t)a, ins.imm);
-    } else {  // neither operand is the running value: only legal where nothing is running yet
-      if (ip != 0) return false;
-      emit(EW_LOADB, (uint8_t)a, ins.imm);
-      emit(ins.op, (uint8_t)b, ins.imm);
+      ok &= emit((uint8_t)r, (uint8_t)a, ins.imm, (uint8_t)dst);
+    } else {  // neither operand is the running value: whatever was running is dead or already kept in a temporary
+      ok &= emit(EW_LOADB, (uint8_t)a, ins.imm);
+      ok &= emit(ins.op, (uint8_t)b, ins.imm, (uint8_t)dst);
     }
+    if (!ok) return false;
+  }
+  if (p.out[0].src != EW_ACC) {  // the result sits in an operand or a temporary: bring it into acc
+    const int o = src_of(p.out[0].src);
+    if (o < 0 || !emit(EW_LOADB, (uint8_t)o, 0.0f)) return false;
   }
   return true;
 }
@@ -534,7 +555,7 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
         bmask |= (p.in[k].mode == EW_STAGE_BROADCAST) << k;
         ext |= p.in[k].dtype == IB200_BOOL || p.in[k].dtype == IB200_U8;
       }
-      for (int i = 0; i < code.n_instr; ++i) ext |= code.ins[i].op == EW_WHERE;
+      for (int i = 0; i < code.n_instr; ++i) ext |= code.ins[i].op == EW_WHERE || code.ins[i].dst != 0 || code.ins[i].src >= 5;
       void (*rk)(const EwProgram, const EwDivs, const EwRegCode) = nullptr;
 #define IB200_REG(NIN, BM, R) if (p.n_inputs == NIN && bmask == BM && p.rank == R) rk = ext ? ew_kernel_reg<NIN, BM, R, true> : ew_kernel_reg<NIN, BM, R, false>;
 #define IB200_REG_R(NIN, BM) IB200_REG(NIN, BM, 1) IB200_REG(NIN, BM, 2)
@@ -554,8 +575,10 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
   int per_thread = kPerThread;
   if (fast) {
     const int mi = p.n_inputs <= 2 ? 2 : 4;
-    // 16 elements per thread for large vectorised problems: halves the interpretive overhead per element
-    const bool wide = p.vec && p.total >= (int64_t)kSmCount * kThreads * 16 * 4 && p.n_slots <= 12;
+    // 16 elements per thread (IB200_EW_WIDE=1) halve the decoding per element but leave two CTAs per SM;
+    // measured on a 6-op DAG over [8192,4096]: 148 us against 121 us for 8 elements per thread at four CTAs
+    static const bool allow_wide = std::getenv("IB200_EW_WIDE") && std::getenv("IB200_EW_WIDE")[0] == '1';
+    const bool wide = allow_wide && p.vec && p.total >= (int64_t)kSmCount * kThreads * 16 * 4 && p.n_slots <= 12;
     if (wide) per_thread = 16;
 #define IB200_EW(MI, R)                                                                                   \
   if (mi == MI && p.rank == R)                                                                            \
