@@ -465,6 +465,9 @@ def main():
         }))
         return
 
+    # NCCL announces its version on stdout at the first collective unless told otherwise; stdout is for the JSON line
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     import torch
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
