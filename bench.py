@@ -394,7 +394,7 @@ def bench_sweep(args, rank, world, local):
     if rank == 0:
         summary = merge_records(gathered)
         gpu_s = sum((r.get("t_gpu") or 0.0) for part in gathered for r in part)
-        print(json.dumps({
+        emit(({
             "metric": "verified_cases_per_s", "value": round(summary["ok"] / dt, 3), "unit": "cases/s", "n_gpus": world,
             "steps": len(cases), "warmup": 8, "ms_per_step": round(dt / max(len(cases), 1) * 1e3, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32/bf16", "data": "synthetic",
@@ -409,7 +409,32 @@ def bench_sweep(args, rank, world, local):
 
 # ---------------------------------------------------------------- main -------------------------
 
+_RESULT_FD = None
+
+
+def reserve_stdout():
+    """stdout carries exactly one JSON line.  Libraries (NCCL's version banner, for one) print there too, so
+    everything else written to file descriptor 1 from here on goes to stderr and the line is written to the
+    descriptor saved now."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj) -> None:
+    data = (json.dumps(obj) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    reserve_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -439,7 +464,7 @@ def main():
             return
         threads = os.cpu_count() or 1
         if row_key is None:
-            print(json.dumps({"impl": "reference", "unavailable": f"no row-sharded CPU arm for workload {args.workload}"}))
+            emit(({"impl": "reference", "unavailable": f"no row-sharded CPU arm for workload {args.workload}"}))
             return
         rows_sample = min(rows_full, 512)
         vals = []
@@ -455,7 +480,7 @@ def main():
                 break
         value = float(np.median(vals))
         sample = f"{rows_sample} of {rows_full} rows per step, rows split over {used} threads, median of {len(vals)} steps"
-        print(json.dumps({
+        emit(({
             "impl": "reference", "metric": "hbm_gbs", "value": round(value, 3), "unit": "GB/s", "n_gpus": args.gpus,
             "steps": len(vals), "warmup": min(args.warmup, 3), "ms_per_step": round(float(np.median(step_times)) * 1e3, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -494,7 +519,7 @@ def main():
         time_plan(lowered, sets, 50, 0)
     clocks = sampler.stop()
     if args.profile:
-        print(json.dumps({"profile_run": True, "workload": label, "ms_per_step": ms / args.steps, "kernels": [s["kernel"] for s in lowered.steps]}))
+        emit(({"profile_run": True, "workload": label, "ms_per_step": ms / args.steps, "kernels": [s["kernel"] for s in lowered.steps]}))
         return
 
     # ---- end to end: pinned host buffers, H2D + plan + D2H per step ------------------------
@@ -581,7 +606,7 @@ def main():
                     continue
                 ops[name] = measure_op(name, max(20, min(args.steps, 100)), max(3, min(args.warmup, 10)), peaks)
             line["ops"] = ops
-    print(json.dumps(line))
+    emit((line))
     if world > 1:
         dist.destroy_process_group()
 
