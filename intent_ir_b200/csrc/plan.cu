@@ -2468,6 +2468,38 @@ class Planner {
   // =============================== description ==============================================
   // the row program in readable form, so that the host side (and its tests) can inspect what
   // a fused step does without a GPU
+  static const char* op_name(int op) {
+    static const char* kOps[] = {"mov", "add", "sub", "mul", "div", "max", "min", "relu", "exp", "rsqrt", "abs", "floor", "ne", "lt", "le",
+                                 "gt", "ge", "and", "or", "not", "where", "to_bool", "to_int", "round_bf16", "round_f16", "rsub", "rdiv", "loadb"};
+    return op >= 0 && op < EW_NUM_OPS ? kOps[op] : "?";
+  }
+  static Json describe_ew_program(const Step& s) {
+    auto num = [](double v) { return Json::number(v); };
+    const EwProgram& p = s.ew;
+    Json r = Json::object(), ins = Json::array(), code = Json::array(), outs = Json::array();
+    for (int k = 0; k < p.n_inputs; ++k) {
+      Json j = Json::object(), st = Json::array();
+      j.set("buffer", num(s.ew_in_buf[k])); j.set("offset", num((double)s.ew_in_off[k]));
+      j.set("dtype", Json::string(dtype_name(p.in[k].dtype))); j.set("iota", num(p.in[k].kind == EW_IN_IOTA));
+      for (int d = 0; d < p.rank; ++d) st.push(num((double)p.in[k].stride[d]));
+      j.set("strides", st);
+      ins.push(j);
+    }
+    for (int k = 0; k < p.n_instr; ++k) {
+      const EwInstr& i = p.instr[k];
+      Json j = Json::object();
+      j.set("op", Json::string(op_name(i.op)));
+      j.set("a", num(i.a)); j.set("b", num(i.b)); j.set("c", num(i.c)); j.set("dst", num(i.dst)); j.set("imm", num(i.imm));
+      code.push(j);
+    }
+    for (int k = 0; k < p.n_outputs; ++k) {
+      Json j = Json::object();
+      j.set("buffer", num(s.ew_out_buf[k])); j.set("dtype", Json::string(dtype_name(p.out[k].dtype))); j.set("src", num(p.out[k].src));
+      outs.push(j);
+    }
+    r.set("inputs", ins); r.set("instr", code); r.set("outputs", outs); r.set("n_slots", num(p.n_slots));
+    return r;
+  }
   static Json describe_row_program(const Step& s) {
     static const char* kOps[] = {"mov", "add", "sub", "mul", "div", "max", "min", "relu", "exp", "rsqrt", "abs", "floor", "ne", "lt", "le",
                                  "gt", "ge", "and", "or", "not", "where", "to_bool", "to_int", "round_bf16", "round_f16", "rsub", "rdiv", "loadb"};
@@ -2564,6 +2596,7 @@ class Planner {
       if (s.kind == Step::ELEMENTWISE) { ext = Json::array(); for (int i = 0; i < s.ew.rank; ++i) ext.push(Json::number((double)s.ew.dim[i])); }
       j.set("extents", ext);
       if (s.kind == Step::ROWFUSE) j.set("row_program", describe_row_program(s));
+      if (s.kind == Step::ELEMENTWISE) j.set("program", describe_ew_program(s));
       steps.push(j);
     }
     d.set("steps", steps);
