@@ -44,7 +44,8 @@ int launch_softmax(const void* x, void* y, float* row_max, float* row_sum, int d
                    int64_t cols, cudaStream_t s, int out_dtype = -1);
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
                      int dtype, int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner,
-                     int64_t affine_period, float eps, cudaStream_t s, int32_t* status = nullptr, bool centre = true);
+                     int64_t affine_period, float eps, cudaStream_t s, int32_t* status = nullptr, bool centre = true,
+                     const void* res = nullptr, const void* res_bias = nullptr);
 int32_t* norm_default_status();
 int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_dtype, int out_dtype,
                 int64_t m, int64_t n, int64_t k, int transpose_b, int act, int32_t* status,

@@ -27,6 +27,8 @@
 #include <tuple>
 
 #include "async.cuh"
+#include <type_traits>
+
 #include "common.cuh"
 #include "rowio.cuh"
 
@@ -42,7 +44,30 @@ struct AffineMap {  // widx = (linear / inner) % period, evaluated without 64-bi
   int nowrap;  // rows start on a multiple of `inner` and never run past `period`: no modulo per element
   int small;   // rows*cols < 2^31: the row origin needs no 64-bit division
   int centre;  // 1: subtract the row mean (layernorm / groupnorm); 0: rms-norm, y = x * rsqrt(mean(x^2) + eps)
+  // residual form (f32, rows up to 16384 elements): the normalised value is x + res (+ rbias[col]), summed as
+  // the rows are loaded, in that order, so that the sum never makes a round trip through HBM
+  const void* res;
+  const void* rbias;
 };
+
+// v <- v + res_row (+ bias); padding columns stay 0
+template <typename T, typename TW, int NV, bool VEC>
+__device__ __forceinline__ void add_residual(float (&v)[NV][4], const T* __restrict__ res_row, const TW* __restrict__ bias, int cols, int tid,
+                                             int nthreads) {
+  float t[NV][4];
+  load_row<T, NV, VEC>(res_row, cols, tid, nthreads, 0.0f, t);
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[i][k] += t[i][k];
+  if (bias) {
+    load_row<TW, NV, VEC>(bias, cols, tid, nthreads, 0.0f, t);
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[i][k] += t[i][k];
+  }
+}
 
 template <int NV> __device__ __forceinline__ float local_sum(const float (&v)[NV][4]) {
   float s = 0.0f;
@@ -159,7 +184,7 @@ __device__ __forceinline__ void row_origin(int64_t row, int64_t cols, const Affi
   q = (uint32_t)(qq % map.period.d);
 }
 
-template <typename T, typename TW, int NV, bool VEC, int AFF>
+template <typename T, typename TW, int NV, bool VEC, int AFF, bool RES>
 __global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                                                  T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                  int64_t rows, int cols, float eps, AffineMap map) {
@@ -168,6 +193,7 @@ __global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const 
   for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += stride) {
     float v[NV][4];
     load_row<T, NV, VEC>(x + r * cols, cols, lane, 32, 0.0f, v);
+    if (RES) add_residual<T, TW, NV, VEC>(v, static_cast<const T*>(map.res) + r * cols, static_cast<const TW*>(map.rbias), cols, lane, 32);
     const float mean = map.centre ? warp_reduce<SumOp>(local_sum<NV>(v)) / (float)cols : 0.0f;
     const float var = warp_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, lane, 32)) / (float)cols;
     const float rstd = 1.0f / sqrtf(var + eps);
@@ -182,7 +208,7 @@ __global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const 
   }
 }
 
-template <typename T, typename TW, int THREADS, int NV, bool VEC, int AFF>
+template <typename T, typename TW, int THREADS, int NV, bool VEC, int AFF, bool RES>
 __global__ void __launch_bounds__(THREADS) norm_block(const T* __restrict__ x, const TW* __restrict__ w,
                                                       const TW* __restrict__ b, T* __restrict__ y,
                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -191,6 +217,7 @@ __global__ void __launch_bounds__(THREADS) norm_block(const T* __restrict__ x, c
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     float v[NV][4];
     load_row<T, NV, VEC>(x + r * cols, cols, threadIdx.x, THREADS, 0.0f, v);
+    if (RES) add_residual<T, TW, NV, VEC>(v, static_cast<const T*>(map.res) + r * cols, static_cast<const TW*>(map.rbias), cols, threadIdx.x, THREADS);
     const float mean = map.centre ? block_reduce<SumOp>(local_sum<NV>(v), slots[0]) / (float)cols : 0.0f;
     const float var = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, threadIdx.x, THREADS), slots[1]) / (float)cols;
     const float rstd = 1.0f / sqrtf(var + eps);
@@ -423,6 +450,7 @@ struct Args {
   cudaStream_t s;
   int32_t* status;
   int centre;
+  const void *res, *rbias;
 };
 
 // how many groups of `csize` CTAs of a kernel can be resident at once (cached per kernel)
@@ -486,7 +514,11 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   const T* x = static_cast<const T*>(a.x);
   T* y = static_cast<T*>(a.y);
   const TW *w = static_cast<const TW*>(a.w), *b = static_cast<const TW*>(a.b);
+  constexpr bool kResidualBuilt = std::is_same<T, float>::value && std::is_same<TW, float>::value;
+  if (a.res && (!kResidualBuilt || a.cols > 16384)) return fail(IB200_ERR_UNSUPPORTED, "norm: the residual form covers f32 rows of up to 16384 elements");
   AffineMap map;
+  map.res = a.res;
+  map.rbias = a.rbias;
   map.centre = a.centre;
   map.nowrap = 0;
   map.small = a.rows * a.cols < ((int64_t)1 << 31);
@@ -496,7 +528,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
     map.nowrap = a.cols % a.inner == 0 && a.period % (a.cols / a.inner) == 0;
   }
   const int c = (int)a.cols;
-  if (VEC && a.cols > 4096 && a.cols <= 32768 && (a.cols * sizeof(T)) % 16 == 0) {
+  if (VEC && !a.res && a.cols > 4096 && a.cols <= 32768 && (a.cols * sizeof(T)) % 16 == 0) {
     static const bool enabled = !(std::getenv("IB200_NORM_PIPE") && std::getenv("IB200_NORM_PIPE")[0] == '0');
     int csize = 1;
     while ((int64_t)csize * 4096 < a.cols) csize *= 2;
@@ -509,13 +541,15 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   {                                                                                                               \
     const int64_t blocks = (a.rows + 3) / 4;                                                                      \
     const int grid = (int)(blocks < (int64_t)kSmCount * 32 ? blocks : (int64_t)kSmCount * 32);                    \
-    norm_warp<T, TW, NV, VEC, AFF><<<grid, 128, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map);     \
+    if (!a.res) norm_warp<T, TW, NV, VEC, AFF, false><<<grid, 128, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
+    else if constexpr (kResidualBuilt) norm_warp<T, TW, NV, VEC, AFF, true><<<grid, 128, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
   }
 #define IB200_BLOCK(TH, NV)                                                                                       \
   {                                                                                                               \
     const int64_t cap = (int64_t)kSmCount * (2048 / TH) * 8;                                                      \
     const int grid = (int)(a.rows < cap ? a.rows : cap);                                                          \
-    norm_block<T, TW, TH, NV, VEC, AFF><<<grid, TH, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
+    if (!a.res) norm_block<T, TW, TH, NV, VEC, AFF, false><<<grid, TH, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
+    else if constexpr (kResidualBuilt) norm_block<T, TW, TH, NV, VEC, AFF, true><<<grid, TH, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
   }
   if (a.cols <= 128) IB200_WARP(1)
   else if (a.cols <= 256) IB200_WARP(2)
@@ -608,13 +642,14 @@ int32_t* norm_default_status() {
 
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype,
                      int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps,
-                     cudaStream_t s, int32_t* status, bool centre) {
+                     cudaStream_t s, int32_t* status, bool centre, const void* res, const void* res_bias) {
   if (!status) status = norm_default_status();
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "norm: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
   if (!x || !y) return fail(IB200_ERR_INVALID, "norm: null pointer");
   if ((w || b) && (affine_inner < 1 || affine_period < 1)) return fail(IB200_ERR_INVALID, "norm: affine_inner and affine_period must be >= 1");
-  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status, centre ? 1 : 0};
+  if (res_bias && !res) return fail(IB200_ERR_INVALID, "norm: a residual bias needs a residual");
+  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status, centre ? 1 : 0, res, res_bias};
   const int adt = (w || b) ? affine_dtype : dtype;
   switch (dtype) {
     case IB200_F32:

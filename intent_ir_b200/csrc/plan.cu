@@ -1019,6 +1019,38 @@ class Planner {
     return false;
   }
 
+  // x = a + b, or (a + b) + v with v a vector along the row: a and b dense f32 views of inputs with x's
+  // element count, v an f32 input of L elements.  The row kernels sum these as they load a row.
+  bool residual_sum(int x, int64_t L, int& a_buf, int& b_buf, int& v_buf) const {
+    auto dense_input = [&](int id, int& buf) {
+      View v;
+      if (!input_view(id, v) || !v.contiguous() || numel(v.shape) != numel(nodes_[x].shape)) return false;
+      if (plan_->buffers[v.buffer].dtype != IB200_F32) return false;
+      buf = v.buffer;
+      return true;
+    };
+    auto pair = [&](int id) {
+      id = skip_reshapes(id);
+      const Node& n = nodes_[id];
+      return n.op == "add" && n.in.size() == 2 && dense_input(n.in[0], a_buf) && dense_input(n.in[1], b_buf);
+    };
+    v_buf = -1;
+    if (pair(x)) return true;
+    const Node& n = nodes_[skip_reshapes(x)];
+    if (n.op != "add" || n.in.size() != 2) return false;
+    for (int k = 0; k < 2; ++k) {
+      int vin = -1;
+      int64_t inner = 0, period = 0;
+      if (!pair(n.in[k])) continue;
+      for (auto& o : outputs_) if (by_name_.at(o) == skip_reshapes(n.in[k])) return false;  // the inner sum is itself returned
+      if (!affine_operand(n.in[1 - k], nodes_[x].shape, vin, inner, period) || inner != 1 || period != L) continue;
+      if (nodes_[vin].decl_dtype != IB200_F32) continue;
+      v_buf = nodes_[vin].view.buffer;
+      return true;
+    }
+    return false;
+  }
+
   bool match_norm() {
     for (auto& oname : outputs_) {
       int y = skip_reshapes(by_name_[oname]);
@@ -1141,6 +1173,19 @@ class Planner {
         else if (o == rs) { s.out[2] = buf; covered[other] = 2; }
       }
       if (!all_outputs_in(covered)) continue;
+      int res_a = -1, res_b = -1, res_v = -1;
+      bool x_is_output = false;
+      for (auto& other : outputs_) x_is_output |= by_name_[other] == x;
+      if (!x_is_input && !x_is_output && L <= 16384 && x_dtype == IB200_F32 && wd == IB200_F32 && residual_sum(x, L, res_a, res_b, res_v)) {
+        // the residual sum is formed by the norm kernel itself while it loads the rows
+        s.in[0] = res_a;
+        s.idx_buf = {res_b};
+        if (res_v >= 0) s.idx_buf.push_back(res_v);
+        s.label = "residual+" + s.label;
+        plan_->uses_status = true;
+        plan_->steps.push_back(s);
+        return true;
+      }
       if (!x_is_input) {  // everything checked: now emit the kernel(s) that compute X
         std::function<void(int)> lower_deps = [&](int id) {
           if (nodes_[id].repr != Node::NONE) return;
@@ -2707,7 +2752,8 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
       case Step::NORM:
         rc = launch_norm_rows(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), static_cast<float*>(P(st.out[1])),
                               static_cast<float*>(P(st.out[2])), st.dtype, st.dtype2, st.d[0], st.d[1], st.aff_inner, st.aff_period,
-                              st.eps, s, status, st.act != 0);
+                              st.eps, s, status, st.act != 0, st.idx_buf.size() > 0 ? P(st.idx_buf[0]) : nullptr,
+                              st.idx_buf.size() > 1 ? P(st.idx_buf[1]) : nullptr);
         break;
       case Step::GEMM:
         for (int64_t bi = 0; bi < st.batch && rc == IB200_OK; ++bi)

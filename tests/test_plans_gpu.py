@@ -604,7 +604,9 @@ def test_rms_norm_through_every_norm_kernel_variant(m, n, residual, golden_graph
         ins["residual"] = rng.standard_normal((m, n)).astype(np.float32)
         ins["bias"] = rng.standard_normal(n).astype(np.float32)
     out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
-    assert lowered.steps[-1]["kernel"] == "rmsnorm"
+    assert lowered.steps[-1]["kernel"].endswith("rmsnorm")
+    if residual:  # rows up to 16384 elements are summed inside the norm kernel, longer ones by a kernel in front of it
+        assert (len(lowered.steps) == 1) == (n <= 16384), [s["kernel"] for s in lowered.steps]
     want = execute_intent(intent, ins, {"M": m, "N": n})
     tol = infer_tolerances(intent).to_dict()
     for name in intent.outputs:
