@@ -244,7 +244,7 @@ struct EwRegCode {
 // is held to 32 registers so that eight CTAs (all 64 warps) are resident per SM -- measured on the
 // 4-op broadcast chain: 0.68 of HBM peak at four CTAs per SM, 0.79 at six, 0.83 at eight.
 template <int NIN, int BMASK, int RANK, bool EXT>
-__global__ void __launch_bounds__(kThreads, EXT ? 4 : 8) ew_kernel_reg(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
+__global__ void __launch_bounds__(kThreads, EXT ? 5 : 8) ew_kernel_reg(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
                                                              const __grid_constant__ EwRegCode code) {
   constexpr int N = 8, U = 2;  // 16 values per thread were measured slower (half the resident warps)
   const int t = threadIdx.x;
@@ -565,7 +565,7 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
 #undef IB200_REG
       if (rk) {
         const int64_t tiles = (p.total + kTile - 1) / kTile;
-        const int64_t cap = (int64_t)kSmCount * (ext ? 4 : 8) * 4;
+        const int64_t cap = (int64_t)kSmCount * (ext ? 5 : 8) * 4;
         rk<<<(int)(tiles < cap ? tiles : cap), kThreads, 0, s>>>(p, divs, code);
         return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "elementwise launch");
       }
