@@ -161,7 +161,7 @@ def test_smoke_transpose_row_sum_row_max_any():
     assert got.dtype == np.bool_ and np.array_equal(got, np.any(Z != 0, axis=1))
 
 
-# ---- BASELINE configurations ------------------------------------------------------------------
+# ---- headline configurations at full size ------------------------------------------------------------------
 
 def test_config_reduce_any_16x256(golden_graphs):
     intent = IntentFunction.from_json_dict(golden_graphs["any_kernel_dim"]["intent"])
