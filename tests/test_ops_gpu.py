@@ -67,6 +67,8 @@ def test_reduce_any_non_finite_and_signed_zero_rows(golden_edges):
     ((1, 1), [1]), ((7, 3), [1]), ((5, 17), [1]), ((33, 256), [1]), ((9, 1000), [1]), ((4, 4096), [1]),
     ((3, 5000), [1]), ((2, 70001), [1]), ((64, 33), [0]), ((6, 40, 9), [1]), ((3, 5, 7, 11), [2, 3]),
     ((4, 6, 8), [0, 1]), ((5, 6), [0, 1]), ((2049, 2), [0]),
+    # many short rows: several rows per warp (8 or 16 lanes each)
+    ((5000, 4), [1]), ((4097, 8), [1]), ((6001, 60), [1]), ((4096, 64), [1]), ((7777, 100), [1]), ((5003, 128), [1]), ((4100, 132), [1]),
 ])
 @pytest.mark.parametrize("kind", ["sum", "max", "any"])
 def test_reduce_matches_oracle(shape, dims, kind):
