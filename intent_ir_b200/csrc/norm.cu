@@ -209,9 +209,10 @@ __global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const 
 }
 
 // 256-thread CTAs are held to 51 registers so that five are resident per SM (measured on f32 [8192,4096]:
-// layernorm 0.80 -> 0.86 of HBM peak, rms-norm 0.86 -> 0.90; six CTAs spill and gain nothing)
+// layernorm 0.80 -> 0.86 of HBM peak, rms-norm 0.86 -> 0.90; six CTAs spill and gain nothing); with 8 values
+// per thread (rows of 1025..2048 elements) all eight fit: [32768,2048] 0.78 -> 0.90
 template <typename T, typename TW, int THREADS, int NV, bool VEC, int AFF, bool RES>
-__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 5 : 1) norm_block(const T* __restrict__ x, const TW* __restrict__ w,
+__global__ void __launch_bounds__(THREADS, THREADS == 256 ? (NV <= 2 ? 8 : 5) : 1) norm_block(const T* __restrict__ x, const TW* __restrict__ w,
                                                       const TW* __restrict__ b, T* __restrict__ y,
                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                       int64_t rows, int cols, float eps, AffineMap map) {
