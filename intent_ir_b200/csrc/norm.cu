@@ -184,26 +184,42 @@ __device__ __forceinline__ void row_origin(int64_t row, int64_t cols, const Affi
   q = (uint32_t)(qq % map.period.d);
 }
 
-template <typename T, typename TW, int NV, bool VEC, int AFF, bool RES>
+// all-reduce over aligned groups of LANES lanes (the whole warp takes part in every shuffle)
+template <int LANES> __device__ __forceinline__ float lanes_sum(float v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// LANES lanes per row: 32 for rows of 65..1024 elements, 16 or 8 for shorter ones, so that a warp
+// works on 2 or 4 rows at a time and no lane holds only padding (layernorm [1048576,64] ran at 0.42
+// of HBM peak with a whole warp per row).
+template <typename T, typename TW, int NV, bool VEC, int AFF, bool RES, int LANES>
 __global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                                                  T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                  int64_t rows, int cols, float eps, AffineMap map) {
-  const int lane = threadIdx.x & 31;
-  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
-  for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += stride) {
+  constexpr int kRowsPerWarp = 32 / LANES;
+  const int lane = (threadIdx.x & 31) % LANES, which = (threadIdx.x & 31) / LANES;
+  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5) * kRowsPerWarp;
+  // the loop bound is the same for every lane of a warp: the shuffles need all of them
+  for (int64_t r0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kRowsPerWarp; r0 < rows; r0 += stride) {
+    const bool live = r0 + which < rows;
+    const int64_t r = live ? r0 + which : rows - 1;  // lanes past the last row recompute it and store nothing
     float v[NV][4];
-    load_row<T, NV, VEC>(x + r * cols, cols, lane, 32, 0.0f, v);
-    if (RES) add_residual<T, TW, NV, VEC>(v, static_cast<const T*>(map.res) + r * cols, static_cast<const TW*>(map.rbias), cols, lane, 32);
-    const float mean = map.centre ? warp_reduce<SumOp>(local_sum<NV>(v)) / (float)cols : 0.0f;
-    const float var = warp_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, lane, 32)) / (float)cols;
+    load_row<T, NV, VEC>(x + r * cols, cols, lane, LANES, 0.0f, v);
+    if (RES) add_residual<T, TW, NV, VEC>(v, static_cast<const T*>(map.res) + r * cols, static_cast<const TW*>(map.rbias), cols, lane, LANES);
+    const float mean = map.centre ? lanes_sum<LANES>(local_sum<NV>(v)) / (float)cols : 0.0f;
+    const float var = lanes_sum<LANES>(centre_and_square<NV, VEC>(v, mean, cols, lane, LANES)) / (float)cols;
     const float rstd = 1.0f / sqrtf(var + eps);
     uint32_t lq = 0, lr = 0;
     if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
-    normalise<TW, NV, VEC, AFF>(v, rstd, w, b, cols, 0, lane, 32, map, lq, lr, uniform_affine<TW, AFF>(w, b, cols, 0, map, lq, lr));
-    store_row<T, NV, VEC>(y + r * cols, cols, lane, 32, v);
-    if (lane == 0) {
-      if (mean_out) mean_out[r] = mean;
-      if (rstd_out) rstd_out[r] = rstd;
+    normalise<TW, NV, VEC, AFF>(v, rstd, w, b, cols, 0, lane, LANES, map, lq, lr, uniform_affine<TW, AFF>(w, b, cols, 0, map, lq, lr));
+    if (live) {
+      store_row<T, NV, VEC>(y + r * cols, cols, lane, LANES, v);
+      if (lane == 0) {
+        if (mean_out) mean_out[r] = mean;
+        if (rstd_out) rstd_out[r] = rstd;
+      }
     }
   }
 }
@@ -543,12 +559,13 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
     if (enabled && ((size_t)seg * sizeof(T)) % 16 == 0)
       return csize == 1 ? launch_pipe<T, TW, AFF, false, 4>(a, map, 1, seg) : launch_pipe<T, TW, AFF, true, 4>(a, map, csize, seg);
   }
-#define IB200_WARP(NV)                                                                                            \
+#define IB200_WARP(NV) IB200_WARP_L(NV, 32)
+#define IB200_WARP_L(NV, LANES)                                                                                   \
   {                                                                                                               \
-    const int64_t blocks = (a.rows + 3) / 4;                                                                      \
+    const int64_t blocks = (a.rows + 4 * (32 / LANES) - 1) / (4 * (32 / LANES));                                  \
     const int grid = (int)(blocks < (int64_t)kSmCount * 32 ? blocks : (int64_t)kSmCount * 32);                    \
-    if (!a.res) norm_warp<T, TW, NV, VEC, AFF, false><<<grid, 128, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
-    else if constexpr (kResidualBuilt) norm_warp<T, TW, NV, VEC, AFF, true><<<grid, 128, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
+    if (!a.res) norm_warp<T, TW, NV, VEC, AFF, false, LANES><<<grid, 128, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
+    else if constexpr (kResidualBuilt) norm_warp<T, TW, NV, VEC, AFF, true, LANES><<<grid, 128, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
   }
 #define IB200_BLOCK(TH, NV)                                                                                       \
   {                                                                                                               \
@@ -557,7 +574,9 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
     if (!a.res) norm_block<T, TW, TH, NV, VEC, AFF, false><<<grid, TH, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
     else if constexpr (kResidualBuilt) norm_block<T, TW, TH, NV, VEC, AFF, true><<<grid, TH, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, c, a.eps, map); \
   }
-  if (a.cols <= 128) IB200_WARP(1)
+  if (a.cols <= 32) IB200_WARP_L(1, 8)
+  else if (a.cols <= 64) IB200_WARP_L(1, 16)
+  else if (a.cols <= 128) IB200_WARP(1)
   else if (a.cols <= 256) IB200_WARP(2)
   else if (a.cols <= 512) IB200_WARP(4)
   else if (a.cols <= 1024) IB200_WARP(8)
@@ -600,6 +619,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
     norm_stream<T, TW, AFF><<<grid, 1024, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, a.cols, a.eps, a.inner, a.period, a.centre);
   }
 #undef IB200_WARP
+#undef IB200_WARP_L
 #undef IB200_BLOCK
   return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "norm launch");
 }

@@ -59,21 +59,36 @@ template <int NV> __device__ __forceinline__ void scale(float (&v)[NV][4], float
     for (int k = 0; k < 4; ++k) v[i][k] = v[i][k] * inv;
 }
 
-template <typename T, typename TO, int NV, bool VEC>
+// all-reduce over aligned groups of LANES lanes (the whole warp takes part in every shuffle)
+template <typename Op, int LANES> __device__ __forceinline__ float lanes_reduce(float v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// LANES lanes per row: 32 for rows of 65..1024 elements, 16 or 8 for shorter ones (2 or 4 rows per warp
+// at a time, no lane holding only padding)
+template <typename T, typename TO, int NV, bool VEC, int LANES>
 __global__ void __launch_bounds__(128) softmax_warp(const T* __restrict__ x, TO* __restrict__ y, float* __restrict__ row_max,
                                                     float* __restrict__ row_sum, int64_t rows, int cols) {
-  const int lane = threadIdx.x & 31;
-  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
-  for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += stride) {
+  constexpr int kRowsPerWarp = 32 / LANES;
+  const int lane = (threadIdx.x & 31) % LANES, which = (threadIdx.x & 31) / LANES;
+  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5) * kRowsPerWarp;
+  // the loop bound is the same for every lane of a warp: the shuffles need all of them
+  for (int64_t r0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kRowsPerWarp; r0 < rows; r0 += stride) {
+    const bool live = r0 + which < rows;
+    const int64_t r = live ? r0 + which : rows - 1;  // lanes past the last row recompute it and store nothing
     float v[NV][4];
-    load_row<T, NV, VEC>(x + r * cols, cols, lane, 32, -INFINITY, v);
-    const float m = warp_reduce<MaxOp>(local_max<NV>(v));
-    const float s = warp_reduce<SumOp>(exp_and_sum<NV>(v, m));
+    load_row<T, NV, VEC>(x + r * cols, cols, lane, LANES, -INFINITY, v);
+    const float m = lanes_reduce<MaxOp, LANES>(local_max<NV>(v));
+    const float s = lanes_reduce<SumOp, LANES>(exp_and_sum<NV>(v, m));
     scale<NV>(v, s);
-    store_row<TO, NV, VEC>(y + r * cols, cols, lane, 32, v);
-    if (lane == 0) {
-      if (row_max) row_max[r] = m;
-      if (row_sum) row_sum[r] = s;
+    if (live) {
+      store_row<TO, NV, VEC>(y + r * cols, cols, lane, LANES, v);
+      if (lane == 0) {
+        if (row_max) row_max[r] = m;
+        if (row_sum) row_sum[r] = s;
+      }
     }
   }
 }
@@ -119,11 +134,12 @@ __global__ void __launch_bounds__(1024) softmax_stream(const T* __restrict__ x, 
   }
 }
 
-template <typename T, typename TO, int NV, bool VEC>
+template <typename T, typename TO, int NV, bool VEC, int LANES = 32>
 void launch_warp(const T* x, TO* y, float* mx, float* sm, int64_t rows, int cols, cudaStream_t s) {
-  const int64_t blocks = (rows + 3) / 4;
+  const int64_t per_cta = 4 * (32 / LANES);
+  const int64_t blocks = (rows + per_cta - 1) / per_cta;
   const int grid = (int)(blocks < (int64_t)kSmCount * 32 ? blocks : (int64_t)kSmCount * 32);
-  softmax_warp<T, TO, NV, VEC><<<grid, 128, 0, s>>>(x, y, mx, sm, rows, cols);
+  softmax_warp<T, TO, NV, VEC, LANES><<<grid, 128, 0, s>>>(x, y, mx, sm, rows, cols);
 }
 template <typename T, typename TO, int THREADS, int NV, bool VEC>
 void launch_block(const T* x, TO* y, float* mx, float* sm, int64_t rows, int cols, cudaStream_t s) {
@@ -137,7 +153,9 @@ void launch_block(const T* x, TO* y, float* mx, float* sm, int64_t rows, int col
 template <typename T, typename TO, bool VEC>
 void dispatch(const T* x, TO* y, float* mx, float* sm, int64_t rows, int64_t cols, cudaStream_t s) {
   const int c = (int)cols;
-  if (cols <= 128) launch_warp<T, TO, 1, VEC>(x, y, mx, sm, rows, c, s);
+  if (cols <= 32) launch_warp<T, TO, 1, VEC, 8>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 64) launch_warp<T, TO, 1, VEC, 16>(x, y, mx, sm, rows, c, s);
+  else if (cols <= 128) launch_warp<T, TO, 1, VEC>(x, y, mx, sm, rows, c, s);
   else if (cols <= 256) launch_warp<T, TO, 2, VEC>(x, y, mx, sm, rows, c, s);
   else if (cols <= 512) launch_warp<T, TO, 4, VEC>(x, y, mx, sm, rows, c, s);
   else if (cols <= 1024) launch_warp<T, TO, 8, VEC>(x, y, mx, sm, rows, c, s);

@@ -646,3 +646,20 @@ def test_dropout_with_other_round_counts(rounds):
     ins = {"x": np.random.default_rng(rounds).standard_normal(5000, dtype=np.float32), "p": np.array(0.4, np.float32), "seed": np.array(-3, np.int32)}
     out, _ = _lower_and_run(intent, {"M": 5000}, ins)
     assert np.array_equal(out["y"], execute_intent(intent, ins, {"M": 5000})["y"])
+
+
+@pytest.mark.parametrize("m,n", [(5001, 64), (4099, 32), (1000, 17), (7, 8), (3001, 60), (2, 3), (1025, 33)])
+@pytest.mark.parametrize("key,xname", [("softmax_inner", "input_ptr"), ("layer_norm_persistent", "in_ptr"), ("rms_norm2d", "inp")])
+def test_short_rows_share_a_warp(key, xname, m, n, golden_graphs):
+    """Rows of at most 64 elements run 2 or 4 to a warp; row counts that do not fill the last warp included."""
+    intent = IntentFunction.from_json_dict(golden_graphs[key]["intent"])
+    rng = np.random.default_rng(m * 131 + n)
+    ins = {xname: (1.5 * rng.standard_normal((m, n))).astype(np.float32)}
+    for name in golden_graphs[key]["inputs"]:
+        if name != xname:
+            ins[name] = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    out, _ = _lower_and_run(intent, {"M": m, "N": n}, ins)
+    want = execute_intent(intent, ins, {"M": m, "N": n})
+    tol = infer_tolerances(intent).to_dict()
+    for name in intent.outputs:
+        _agree(out[name], want[name], tol, name)
