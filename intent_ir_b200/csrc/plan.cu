@@ -162,17 +162,21 @@ struct Step {
   std::string label;
   int in[3] = {-1, -1, -1};
   int out[3] = {-1, -1, -1};
-  int64_t d[4] = {0, 0, 0, 0};  // kernel extents
-  int64_t aff_inner = 1, aff_period = 1;
+  // kernel extents.  REDUCE: outer, reduced, inner; SOFTMAX / NORM: rows, cols; GEMM: M, N, K; TRANSPOSE: rows, cols;
+  // GATHER / DROPOUT: elements (DROPOUT d[1]: Philox rounds); ROPE: seq, batch*heads, D; image ops: C, H, W and
+  // d[3] = output channels (correlation) or hw_fl (resize)
+  int64_t d[4] = {0, 0, 0, 0};
+  int64_t aff_inner = 1, aff_period = 1;  // NORM: weight index = (linear / aff_inner) % aff_period
   int reduce_kind = 0;
   float scale = 1.0f, eps = 0.0f;
-  int dtype = IB200_F32, dtype2 = IB200_F32;
-  int transpose_b = 0, act = 0;
+  int dtype = IB200_F32, dtype2 = IB200_F32;  // element types of the main input and of the output (NORM: of w / b; DROPOUT: of p and seed)
+  int transpose_b = 0;
+  int act = 0;  // GEMM: IB200_ACT_*; NORM: 1 when the row mean is subtracted (0: rms-norm)
   int64_t batch = 1, batch_stride[3] = {0, 0, 0};  // batched matmul: elements between consecutive A / B / C matrices
-  std::vector<int> idx_buf;                         // gather: index buffers
+  std::vector<int> idx_buf;  // GATHER: index buffers; NORM: {residual[, residual bias]} summed while the rows are loaded
   Shape g_dim, g_stride;
   double other = 0.0;     // gather: fill value; dropout: p when it is a constant
-  long long seed = 0;     // dropout: the seed when it is a constant
+  long long seed = 0;     // dropout: the seed when it is a constant; correlation: out_shift when it is a constant
   EwProgram ew;
   std::vector<int> ew_in_buf, ew_out_buf;
   std::vector<int64_t> ew_in_off;  // element offsets into the input buffers
