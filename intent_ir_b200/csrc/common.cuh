@@ -40,8 +40,14 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // ---- internal launchers (one per .cu file) ----------------------------------------------
 int launch_reduce(const void* x, void* out, int x_dtype, int out_dtype, int kind, int64_t outer,
                   int64_t reduce, int64_t inner, float scale, cudaStream_t s);
+struct SoftmaxMask {     // softmax(where(mask, x, fill)): the mask is applied while the rows are loaded
+  const uint8_t* mask;   // bool / u8, or null for a plain softmax
+  int64_t row_stride;    // elements between the mask rows of consecutive rows (0: one mask row for all)
+  float fill;
+  int vec;               // filled by the launcher: 4 mask bytes can be read as one word
+};
 int launch_softmax(const void* x, void* y, float* row_max, float* row_sum, int dtype, int64_t rows,
-                   int64_t cols, cudaStream_t s, int out_dtype = -1);
+                   int64_t cols, cudaStream_t s, int out_dtype = -1, const SoftmaxMask* mask = nullptr);
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
                      int dtype, int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner,
                      int64_t affine_period, float eps, cudaStream_t s, int32_t* status = nullptr, bool centre = true,

@@ -167,7 +167,7 @@ struct Step {
   // d[3] = output channels (correlation) or hw_fl (resize)
   int64_t d[4] = {0, 0, 0, 0};
   int64_t aff_inner = 1, aff_period = 1;  // NORM: weight index = (linear / aff_inner) % aff_period
-  int reduce_kind = 0;
+  int reduce_kind = 0;  // REDUCE: IB200_REDUCE_*; SOFTMAX: 1 when in[1] is a mask applied on load (fill = other, mask row stride = aff_inner)
   float scale = 1.0f, eps = 0.0f;
   int dtype = IB200_F32, dtype2 = IB200_F32;  // element types of the main input and of the output (NORM: of w / b; DROPOUT: of p and seed)
   int transpose_b = 0;
@@ -220,6 +220,7 @@ class Planner {
     build();
     if (!match_fused()) lower_general();
     fuse_gemm_epilogues();
+    fuse_softmax_masks();
     fuse_rows();
     finish();
     return std::move(plan_);
@@ -1973,6 +1974,56 @@ class Planner {
     }
   }
 
+  // =============================== masked softmax ===========================================
+  // softmax(where(mask, x, constant)) over f32 rows of up to 16384 elements: the softmax kernel applies the
+  // mask while it loads each row, so the masked scores never exist in HBM (pipeline/tilelang/core.py:1050-1076).
+  void fuse_softmax_masks() {
+    std::vector<Step>& steps = plan_->steps;
+    std::vector<int> reads, writes;
+    for (size_t i = 0; i + 1 < steps.size(); ++i) {
+      const Step& e = steps[i];
+      Step& sm = steps[i + 1];
+      if (e.kind != Step::ELEMENTWISE || sm.kind != Step::SOFTMAX || sm.reduce_kind != 0) continue;
+      const EwProgram& q = e.ew;
+      const int64_t R = sm.d[0], C = sm.d[1];
+      if (q.n_outputs != 1 || q.n_inputs != 2 || q.n_instr != 1 || q.instr[0].op != EW_WHERE || q.out[0].src != EW_ACC) continue;
+      if (e.ew_out_buf[0] != sm.in[0] || plan_->buffers[sm.in[0]].is_arg || sm.dtype != IB200_F32 || sm.dtype2 != IB200_F32) continue;
+      if (q.total != R * C || C > 16384 || C < 1 || sm.out[1] >= 0 || sm.out[2] >= 0) continue;
+      bool used_elsewhere = false;
+      for (size_t k = i + 2; k < steps.size() && !used_elsewhere; ++k) {
+        step_io(steps[k], reads, writes);
+        used_elsewhere = std::find(reads.begin(), reads.end(), sm.in[0]) != reads.end();
+      }
+      if (used_elsewhere) continue;
+      const EwInstr& w = q.instr[0];
+      if (w.a >= q.n_inputs || w.b >= q.n_inputs || w.a == w.b || w.c != EW_IMM) continue;
+      const EwInput &mask = q.in[w.a], &x = q.in[w.b];
+      if (mask.kind != EW_IN_TENSOR || x.kind != EW_IN_TENSOR || e.ew_in_off[w.a] != 0 || e.ew_in_off[w.b] != 0) continue;
+      if (!(mask.dtype == IB200_BOOL || mask.dtype == IB200_U8) || x.dtype != IB200_F32) continue;
+      // strides over [R, C] (rank 2) or over the flat extent (rank 1: everything dense)
+      int64_t mask_row_stride;
+      if (q.rank <= 1) {  // dense operands, rows of one element, or a single row
+        if (q.total == 1) mask_row_stride = 0;
+        else if (x.stride[0] != 1) continue;
+        else if (mask.stride[0] == 1) mask_row_stride = C;
+        else if (mask.stride[0] == 0 && C == 1) mask_row_stride = 0;
+        else continue;
+      } else if (q.rank == 2 && (int64_t)q.dim[0] == R && (int64_t)q.dim[1] == C) {
+        if (x.stride[0] != C || x.stride[1] != 1 || mask.stride[1] != 1 || !(mask.stride[0] == 0 || mask.stride[0] == C)) continue;
+        mask_row_stride = mask.stride[0];
+      } else {
+        continue;
+      }
+      sm.in[0] = e.ew_in_buf[w.b];
+      sm.in[1] = e.ew_in_buf[w.a];
+      sm.reduce_kind = 1;  // SOFTMAX: a mask is applied on load
+      sm.aff_inner = mask_row_stride;
+      sm.other = w.imm;
+      sm.label = "softmax+mask";
+      steps.erase(steps.begin() + i);
+    }
+  }
+
   // =============================== row fusion ===============================================
   // Runs of steps that all work row by row on one [R, C] problem (elementwise chains over
   // [R, C] or over the R per-row results, reductions along the row, softmax) become one
@@ -2749,10 +2800,12 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
       case Step::REDUCE:
         rc = launch_reduce(P(st.in[0]), P(st.out[0]), st.dtype, st.dtype2, st.reduce_kind, st.d[0], st.d[1], st.d[2], st.scale, s);
         break;
-      case Step::SOFTMAX:
+      case Step::SOFTMAX: {
+        const SoftmaxMask mk{static_cast<const uint8_t*>(st.reduce_kind ? P(st.in[1]) : nullptr), st.aff_inner, (float)st.other, 0};
         rc = launch_softmax(P(st.in[0]), P(st.out[0]), static_cast<float*>(P(st.out[1])), static_cast<float*>(P(st.out[2])), st.dtype,
-                            st.d[0], st.d[1], s, st.dtype2);
+                            st.d[0], st.d[1], s, st.dtype2, st.reduce_kind ? &mk : nullptr);
         break;
+      }
       case Step::NORM:
         rc = launch_norm_rows(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), static_cast<float*>(P(st.out[1])),
                               static_cast<float*>(P(st.out[2])), st.dtype, st.dtype2, st.d[0], st.d[1], st.aff_inner, st.aff_period,

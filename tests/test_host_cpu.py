@@ -49,7 +49,7 @@ EXPECTED_KERNELS = {
     "group_norm_kernel": ["groupnorm"], "matmul_bias_relu2d": ["gemm+bias+relu"], "matmul_relu2d": ["gemm+relu"],
     "row_sum": ["reduce_sum"], "row_max": ["reduce_max"], "transpose2d": ["transpose2d"], "gather2d": ["gather"],
     "_attn_fwd": ["gemm", "rowfused(2 steps, 4 phases)", "gemm"],  # scale + mask + softmax in one row program
-    "masked_softmax2d": ["rowfused(2 steps, 4 phases)"], "rms_norm2d": ["rmsnorm"],
+    "masked_softmax2d": ["softmax+mask"], "rms_norm2d": ["rmsnorm"],
     "rms_norm_residual2d": ["residual+rmsnorm"],  # inp + residual + bias summed by the norm kernel as it loads each row
     "layer_norm_residual2d": ["residual+layernorm"],
     "mlp2d": ["gemm+bias+relu", "gemm+bias"], "matmul_transposed_epilogue": ["transpose2d", "gemm+bias+relu"],  # epilogues folded per GEMM

@@ -663,3 +663,72 @@ def test_short_rows_share_a_warp(key, xname, m, n, golden_graphs):
     tol = infer_tolerances(intent).to_dict()
     for name in intent.outputs:
         _agree(out[name], want[name], tol, name)
+
+
+# ---- softmax with a where-mask applied on load --------------------------------------------
+
+def _masked_softmax_graph(full_mask, fill):
+    mshape = ["M", "N"] if full_mask else ["N"]
+    ops = []
+    if not full_mask:
+        ops.append({"op": "broadcast_in_dim", "inputs": ["mask"], "output": "m2", "attrs": {"broadcast_dims": [1], "out_shape": ["M", "N"]}})
+    ops += [{"op": "const", "inputs": [], "output": "neg", "attrs": {"value": fill, "dtype": "f32"}},
+            {"op": "where", "inputs": ["mask" if full_mask else "m2", "x", "neg"], "output": "xm"},
+            {"op": "softmax", "inputs": ["xm"], "output": "y", "attrs": {"axis": -1}}]
+    return {"name": "msm", "tensors": {"x": _t(["M", "N"]), "mask": _t(mshape, "bool"), "m2": _t(["M", "N"], "bool"), "y": _t(["M", "N"])},
+            "ops": ops, "outputs": ["y"]}
+
+
+@pytest.mark.parametrize("m,n", [(1, 1), (5, 1), (1, 9), (5, 7), (16, 64), (4099, 24), (37, 60), (33, 1000), (9, 4099), (3, 16384), (2, 20000)])
+@pytest.mark.parametrize("full_mask", [False, True])
+def test_softmax_applies_the_mask_while_loading(m, n, full_mask):
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+    from intent_ir_b200.runtime import run_lowered
+
+    intent = IntentFunction.from_json_dict(_masked_softmax_graph(full_mask, -1e9))
+    rng = np.random.default_rng(m * 31 + n)
+    x = rng.standard_normal((m, n)).astype(np.float32) * 3
+    mask = rng.random((m, n) if full_mask else (n,)) > 0.4
+    if full_mask and m > 1:
+        mask[1, :] = False  # a row with everything masked: uniform over the fill value
+        mask[m - 1, :] = True
+    low = lower_intent_to_b200_kernel(intent, shape_bindings={"M": m, "N": n})
+    kernels = [s["kernel"] for s in low.steps]
+    assert kernels == (["softmax+mask"] if n <= 16384 else kernels), kernels
+    got = run_lowered(low, {"x": x, "mask": mask})["y"]
+    want = execute_intent(intent, {"x": x, "mask": mask}, shape_bindings={"M": m, "N": n})["y"]
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-7), float(np.abs(got - want).max())
+    assert np.allclose(got.sum(axis=1), 1.0, atol=1e-4)
+    keep = np.broadcast_to(mask, (m, n))
+    live = keep.any(axis=1)
+    assert np.all(got[live][~keep[live]] == 0.0)  # exp(-1e9 - max) is exactly zero
+
+
+def test_masked_softmax_keeps_an_infinite_fill_and_a_consumer_of_the_masked_scores():
+    """-inf as the fill gives NaN rows where nothing is kept, as in numpy; a graph that also
+    returns the masked scores cannot drop them, so the mask stays a step of its own."""
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+    from intent_ir_b200.runtime import run_lowered
+
+    js = _masked_softmax_graph(True, float("-inf"))
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((6, 50)).astype(np.float32)
+    mask = rng.random((6, 50)) > 0.5
+    mask[2, :] = False
+    intent = IntentFunction.from_json_dict(js)
+    low = lower_intent_to_b200_kernel(intent, shape_bindings={"M": 6, "N": 50})
+    got = run_lowered(low, {"x": x, "mask": mask})["y"]
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, {"x": x, "mask": mask}, shape_bindings={"M": 6, "N": 50})["y"]
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-7, equal_nan=True)
+    assert np.isnan(got[2]).all() and np.isfinite(np.delete(got, 2, axis=0)).all()
+
+    js2 = _masked_softmax_graph(True, -1e9)
+    js2["outputs"] = ["y", "xm"]
+    js2["tensors"]["xm"] = _t(["M", "N"])
+    intent2 = IntentFunction.from_json_dict(js2)
+    low2 = lower_intent_to_b200_kernel(intent2, shape_bindings={"M": 6, "N": 50})
+    assert "softmax+mask" not in [s["kernel"] for s in low2.steps]
+    got2 = run_lowered(low2, {"x": x, "mask": mask})
+    want2 = execute_intent(intent2, {"x": x, "mask": mask}, shape_bindings={"M": 6, "N": 50})
+    assert np.array_equal(got2["xm"], want2["xm"]) and np.allclose(got2["y"], want2["y"], rtol=1e-5, atol=1e-7)

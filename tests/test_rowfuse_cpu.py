@@ -41,9 +41,20 @@ def _check(intent, ins, bindings, expect_single=True):
 
 @pytest.mark.parametrize("key", FUSED_GOLDEN)
 def test_golden_graphs_fuse_into_one_row_program(key, golden_graphs, golden_vectors):
-    g = golden_graphs[key]
-    intent = IntentFunction.from_json_dict(g["intent"])
+    """The reference's masked softmax with a per-row shift added before the mask: a softmax does
+    not see a shift of its row, and masked entries underflow to zero either way, so the
+    reference's recorded output still applies; the plain graph goes to the softmax kernel's own
+    mask path and would not exercise a row program."""
+    g = json.loads(json.dumps(golden_graphs[key]))
+    js = g["intent"]
+    js["tensors"]["row"] = _t(["M", 1])
+    js["tensors"]["shifted"] = _t(["M", "N"])
+    where = next(o for o in js["ops"] if o["op"] == "where")
+    js["ops"].insert(js["ops"].index(where), {"op": "add", "inputs": [where["inputs"][1], "row"], "output": "shifted"})
+    where["inputs"][1] = "shifted"
+    intent = IntentFunction.from_json_dict(js)
     ins = {n: golden_vectors[f"{key}/in/{n}"] for n in g["inputs"]}
+    ins["row"] = np.linspace(-2.0, 2.0, g["shapes"]["M"], dtype=np.float32).reshape(-1, 1)
     desc = _check(intent, ins, derive_bindings(g["shapes"]))
     got = run_plan_description(desc, ins)
     for n in g["outputs"]:

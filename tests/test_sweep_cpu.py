@@ -134,4 +134,4 @@ def test_extra_graph_families_are_valid_and_plannable(tmp_path):
         if c.kind in expected_last:
             assert kernels[-1].endswith(expected_last[c.kind]), (c.kind, c.shapes, kernels)
         else:
-            assert kernels[-1] == "softmax" or kernels[-1].startswith("rowfused"), (c.kind, kernels)
+            assert kernels[-1] in ("softmax", "softmax+mask") or kernels[-1].startswith("rowfused"), (c.kind, kernels)
