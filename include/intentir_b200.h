@@ -145,6 +145,14 @@ IB200_API int ib200_softmax(const void* x, void* y, float* row_max, float* row_s
 IB200_API int ib200_softmax_io(const void* x, void* y, float* row_max, float* row_sum, int in_dtype, int out_dtype,
                      int64_t rows, int64_t cols, void* stream);
 
+/* softmax(where(mask, x, fill)) over f32 rows of at most 16384 elements, the mask applied as each row
+ * is loaded (the masked scores are never written): mask holds one byte per element (0 = replace by
+ * `fill`), row r starting at mask + r * mask_row_stride, so 0 shares one mask vector between all rows
+ * and `cols` gives every row its own.  The graph form is where -> softmax,
+ * pipeline/tilelang/core.py:1050-1076; the plan builder folds it into this kernel by itself. */
+IB200_API int ib200_softmax_masked(const void* x, const void* mask, int64_t mask_row_stride, float fill, void* y,
+                         float* row_max, float* row_sum, int64_t rows, int64_t cols, void* stream);
+
 /* Normalisation over contiguous rows of `cols` elements with centred (two-pass) variance:
  *   mean = sum(x)/cols; var = sum((x-mean)^2)/cols; rstd = 1/sqrt(var+eps);
  *   y[r, j] = (x[r, j]-mean)*rstd * w[widx] + b[widx],  widx = ((r*cols + j) / affine_inner) % affine_period

@@ -47,6 +47,7 @@ SIGNATURES = {
     "ib200_reduce_any_f32": (_i, [_vp, _vp, _i64, _i64, _vp]),
     "ib200_softmax": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i64, _vp]),
     "ib200_softmax_io": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _vp]),
+    "ib200_softmax_masked": (_i, [_vp, _vp, _i64, _f, _vp, _vp, _vp, _i64, _i64, _vp]),
     "ib200_norm_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _i64, _f, _vp]),
     "ib200_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _f, _vp]),
     "ib200_groupnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _f, _vp]),

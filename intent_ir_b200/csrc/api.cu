@@ -45,6 +45,13 @@ int ib200_softmax_io(const void* x, void* y, float* row_max, float* row_sum, int
   return launch_softmax(x, y, row_max, row_sum, in_dtype, rows, cols, static_cast<cudaStream_t>(stream), out_dtype);
 }
 
+int ib200_softmax_masked(const void* x, const void* mask, int64_t mask_row_stride, float fill, void* y, float* row_max, float* row_sum,
+                         int64_t rows, int64_t cols, void* stream) {
+  if (!mask) return fail(IB200_ERR_INVALID, "softmax_masked: mask is null");
+  const SoftmaxMask mk{static_cast<const uint8_t*>(mask), mask_row_stride, fill, 0};
+  return launch_softmax(x, y, row_max, row_sum, IB200_F32, rows, cols, static_cast<cudaStream_t>(stream), IB200_F32, &mk);
+}
+
 int ib200_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int affine_dtype,
                     int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps, void* stream) {
   return launch_norm_rows(x, w, b, y, mean, rstd, dtype, affine_dtype, rows, cols, affine_inner, affine_period, eps,

@@ -131,6 +131,29 @@ def softmax(x: torch.Tensor, out: Optional[torch.Tensor] = None, row_max: Option
     return out
 
 
+def softmax_masked(x: torch.Tensor, mask: torch.Tensor, fill: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``softmax(where(mask, x, fill))`` over the last axis of an f32 tensor in one kernel.  ``mask``
+    (bool / uint8) has the shape of ``x`` or of its last axis (one vector shared by all rows)."""
+    _dev(x, "x")
+    _dev(mask, "mask")
+    if x.dtype != torch.float32 or mask.dtype not in (torch.bool, torch.uint8):
+        raise B200RuntimeError("softmax_masked: x must be float32 and mask bool or uint8")
+    cols = x.shape[-1] if x.dim() else 1
+    rows = x.numel() // cols if cols else 0
+    if tuple(mask.shape) == tuple(x.shape):
+        stride = cols
+    elif mask.numel() == cols:
+        stride = 0
+    else:
+        raise B200RuntimeError(f"softmax_masked: mask shape {tuple(mask.shape)} matches neither x {tuple(x.shape)} nor its last axis")
+    if out is None:
+        out = torch.empty_like(x)
+    _dev(out, "out")
+    rc = _lib.load().ib200_softmax_masked(_ptr(x), _ptr(mask), stride, float(fill), _ptr(out), None, None, rows, cols, _stream())
+    _check(rc, "softmax_masked")
+    return out
+
+
 def norm_rows(x, w, b, rows: int, cols: int, affine_inner: int, affine_period: int, eps: float, want_stats: bool = True):
     _dev(x, "x")
     y = torch.empty_like(x)

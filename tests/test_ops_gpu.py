@@ -306,3 +306,32 @@ def test_direct_c_entry_points_through_ctypes():
     assert lib.ib200_check_status(None, stream) == 0  # the library's own status word is clean
     assert lib.ib200_groupnorm(g.data_ptr(), None, None, gy.data_ptr(), None, None, _lib.F32, 2, 6, 16, 4, 1e-5, stream) == _lib.ERR_INVALID
     assert b"multiple" in lib.ib200_last_error()
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (7, 5), (64, 60), (33, 1024), (5, 3, 1000), (6, 4099), (2, 16384)])
+@pytest.mark.parametrize("shared", [False, True])
+def test_softmax_masked_direct_entry(shape, shared):
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(shape[-1] + shared)
+    x = 3 * rng.standard_normal(shape, dtype=np.float32)
+    mask = rng.random(shape[-1:] if shared else shape) > 0.5
+    if not shared and x.ndim == 2 and shape[0] > 1:
+        mask[1] = False
+    got = ops.softmax_masked(_dev(x), torch.from_numpy(mask).cuda(), -1e9).cpu().numpy()
+    xm = np.where(mask, x, np.float32(-1e9))
+    e = np.exp(xm - xm.max(axis=-1, keepdims=True))
+    _agree(got, e / e.sum(axis=-1, keepdims=True), 1e-4, 1e-4)
+    as_bytes = ops.softmax_masked(_dev(x), torch.from_numpy(mask.astype(np.uint8)).cuda(), -1e9).cpu().numpy()
+    assert np.array_equal(as_bytes, got)
+
+
+def test_softmax_masked_rejects_what_it_does_not_cover():
+    from intent_ir_b200 import ops
+    from intent_ir_b200.errors import B200LoweringError, B200RuntimeError
+    x = torch.zeros(2, 20000, device="cuda")
+    with pytest.raises(B200LoweringError):
+        ops.softmax_masked(x, torch.ones(2, 20000, dtype=torch.bool, device="cuda"), 0.0)  # rows above 16384 elements
+    with pytest.raises(B200RuntimeError):
+        ops.softmax_masked(x[:, :8].contiguous(), torch.ones(3, dtype=torch.bool, device="cuda"), 0.0)
+    with pytest.raises(B200RuntimeError):
+        ops.softmax_masked(x[:, :8].contiguous().half(), torch.ones(8, dtype=torch.bool, device="cuda"), 0.0)
