@@ -173,6 +173,7 @@ struct Step {
   int transpose_b = 0;
   int act = 0;  // GEMM: IB200_ACT_*; NORM: 1 when the row mean is subtracted (0: rms-norm)
   int64_t batch = 1, batch_stride[3] = {0, 0, 0};  // batched matmul: elements between consecutive A / B / C matrices
+  int scratch = -1;  // REDUCE: workspace buffer for the split-row kernel (few, long rows), or -1
   std::vector<int> idx_buf;  // GATHER: index buffers; NORM: {residual[, residual bias]} summed while the rows are loaded
   Shape g_dim, g_stride;
   double other = 0.0;     // gather: fill value; dropout: p when it is a constant
@@ -961,6 +962,10 @@ class Planner {
     s.dtype = xd;
     s.dtype2 = plan_->buffers[s.out[0]].dtype;
     if (s.dtype2 != IB200_BOOL) return false;
+    if (reduce_split_factor(s.d[0], s.d[1], s.d[2]) > 1) {
+      s.scratch = new_workspace_buffer(IB200_U8, (int64_t)kReduceScratchBytes, "reduce scratch");
+      s.label += "(split rows)";
+    }
     plan_->steps.push_back(s);
     return true;
   }
@@ -1359,6 +1364,10 @@ class Planner {
         out_written_.erase(n.name);
         s.out[0] = new_workspace_buffer(tmp_dt, numel(n.shape), n.name);
         s.dtype2 = tmp_dt;
+      }
+      if (reduce_split_factor(s.d[0], s.d[1], s.d[2]) > 1) {
+        s.scratch = new_workspace_buffer(IB200_U8, (int64_t)kReduceScratchBytes, "reduce scratch");
+        s.label += "(split rows)";
       }
       plan_->steps.push_back(s);
       set_strided(id, s.out[0]);
@@ -2798,7 +2807,8 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
     auto P = [&](int id) { return buffer_ptr(*plan, id, args, workspace); };
     switch (st.kind) {
       case Step::REDUCE:
-        rc = launch_reduce(P(st.in[0]), P(st.out[0]), st.dtype, st.dtype2, st.reduce_kind, st.d[0], st.d[1], st.d[2], st.scale, s);
+        rc = launch_reduce(P(st.in[0]), P(st.out[0]), st.dtype, st.dtype2, st.reduce_kind, st.d[0], st.d[1], st.d[2], st.scale, s,
+                           st.scratch >= 0 ? P(st.scratch) : nullptr);
         break;
       case Step::SOFTMAX: {
         const SoftmaxMask mk{static_cast<const uint8_t*>(st.reduce_kind ? P(st.in[1]) : nullptr), st.aff_inner, (float)st.other, 0};

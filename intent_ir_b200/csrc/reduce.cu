@@ -6,6 +6,12 @@
 //   inner == 1 (reduction over the trailing axes):
 //     rows_warp  : one warp per row, for rows of up to 2048 elements;
 //     rows_block : one 256-thread CTA per row for longer rows.
+//     rows_split : fewer rows than two per SM and rows of 64 Ki elements or more: every row is cut
+//                  into segments, one CTA each; a CTA leaves its partial in a scratch area and takes a
+//                  ticket from the row's counter, and the CTA that draws the last ticket folds the
+//                  partials in segment order (same result on every run).  Nobody waits for anybody.
+//                  Needs a scratch area from the caller (plans provide it); the launcher zeroes the
+//                  counters with a memset node in front of the kernel, so the area may be shared.
 //   inner  > 1 (reduction over a leading / middle axis):
 //     cols       : a 32x8 CTA covers 32 adjacent inner positions; the 8 thread rows stride
 //                  over the reduced axis and are combined through shared memory.
@@ -117,6 +123,35 @@ __global__ void __launch_bounds__(256) reduce_rows_block(const T* __restrict__ x
   }
 }
 
+constexpr int kSplitCounters = 512;  // counters (one per row) in front of the partials in the scratch area
+constexpr int kSplitPartials = (int)((kReduceScratchBytes - kSplitCounters * sizeof(unsigned)) / sizeof(float));
+constexpr int64_t kSplitAlign = 1024;  // segment length granularity in elements: keeps every segment start 16-byte aligned for all types
+
+template <typename T, typename TO, int KIND, bool VEC>
+__global__ void __launch_bounds__(256) reduce_rows_split(const T* __restrict__ x, TO* __restrict__ out, int64_t n, int split, int64_t seg,
+                                                         float scale, unsigned* __restrict__ counters, float* __restrict__ partials) {
+  using Op = typename KindOp<KIND>::Op;
+  __shared__ float slots[2][8];
+  __shared__ unsigned ticket;
+  const int64_t row = blockIdx.x / split;
+  const int part = blockIdx.x % split;
+  const int64_t lo = (int64_t)part * seg;
+  const int64_t len = n - lo < seg ? n - lo : seg;
+  const float mine = block_reduce<Op>(row_partial<T, KIND, VEC>(x + row * n + lo, len, threadIdx.x, 256), slots[0]);
+  if (threadIdx.x == 0) {
+    __stcg(&partials[blockIdx.x], mine);
+    __threadfence();  // the partial is visible before the ticket is
+    ticket = atomicAdd(&counters[row], 1u);
+  }
+  __syncthreads();
+  if (ticket != (unsigned)split - 1u) return;
+  __threadfence();
+  float acc = Op::identity();
+  for (int k = threadIdx.x; k < split; k += 256) acc = Op::apply(acc, __ldcg(&partials[row * split + k]));
+  acc = block_reduce<Op>(acc, slots[1]);
+  if (threadIdx.x == 0) write_result<TO>(out, row, acc, scale, KIND);
+}
+
 template <typename T, typename TO, int KIND>
 __global__ void __launch_bounds__(256) reduce_cols(const T* __restrict__ x, TO* __restrict__ out, int64_t outer,
                                                    int64_t n, int64_t inner, float scale) {
@@ -144,14 +179,25 @@ __global__ void __launch_bounds__(256) reduce_cols(const T* __restrict__ x, TO* 
 }
 
 template <typename T, typename TO, int KIND>
-int run(const void* xv, void* outv, int64_t outer, int64_t n, int64_t inner, float scale, cudaStream_t s) {
+int run(const void* xv, void* outv, int64_t outer, int64_t n, int64_t inner, float scale, cudaStream_t s, void* scratch) {
   const T* x = static_cast<const T*>(xv);
   TO* out = static_cast<TO*>(outv);
   if (inner == 1) {
     // 4-element vectors need every row start aligned to the vector's byte width: a base
     // pointer aligned to 16 bytes and n % 4 == 0 cover every T used here.
     const bool vec = aligned16(x) && n % 4 == 0;
-    if (vec && n <= 128 && outer >= 4096) {
+    const int want = scratch ? reduce_split_factor(outer, n, inner) : 1;
+    if (want > 1) {
+      int64_t seg = (n + want - 1) / want;
+      seg = (seg + kSplitAlign - 1) / kSplitAlign * kSplitAlign;
+      const int split = (int)((n + seg - 1) / seg);  // no empty segment
+      unsigned* counters = static_cast<unsigned*>(scratch);
+      float* partials = reinterpret_cast<float*>(counters + kSplitCounters);
+      const int grid = (int)(outer * split);
+      IB200_CUDA_OK(cudaMemsetAsync(counters, 0, (size_t)outer * sizeof(unsigned), s));  // the scratch area may hold anything
+      if (vec) reduce_rows_split<T, TO, KIND, true><<<grid, 256, 0, s>>>(x, out, n, split, seg, scale, counters, partials);
+      else reduce_rows_split<T, TO, KIND, false><<<grid, 256, 0, s>>>(x, out, n, split, seg, scale, counters, partials);
+    } else if (vec && n <= 128 && outer >= 4096) {
       const int lanes = n <= 64 ? 8 : 16;
       const int64_t blocks = (outer + 256 / lanes - 1) / (256 / lanes);
       const int grid = (int)(blocks < (int64_t)kSmCount * 32 ? blocks : (int64_t)kSmCount * 32);
@@ -176,27 +222,27 @@ int run(const void* xv, void* outv, int64_t outer, int64_t n, int64_t inner, flo
 }
 
 template <typename T, int KIND> int pick_out(const void* x, void* out, int out_dtype, int64_t outer, int64_t n,
-                                             int64_t inner, float scale, cudaStream_t s) {
+                                             int64_t inner, float scale, cudaStream_t s, void* scratch) {
   if (KIND == IB200_REDUCE_ANY) {
     if (out_dtype != IB200_BOOL && out_dtype != IB200_U8) return fail(IB200_ERR_INVALID, "reduce_any writes one byte per result: out_dtype must be bool");
-    return run<T, uint8_t, KIND>(x, out, outer, n, inner, scale, s);
+    return run<T, uint8_t, KIND>(x, out, outer, n, inner, scale, s, scratch);
   }
   switch (out_dtype) {
-    case IB200_F32: return run<T, float, KIND>(x, out, outer, n, inner, scale, s);
-    case IB200_BF16: return run<T, __nv_bfloat16, KIND>(x, out, outer, n, inner, scale, s);
-    case IB200_F16: return run<T, __half, KIND>(x, out, outer, n, inner, scale, s);
+    case IB200_F32: return run<T, float, KIND>(x, out, outer, n, inner, scale, s, scratch);
+    case IB200_BF16: return run<T, __nv_bfloat16, KIND>(x, out, outer, n, inner, scale, s, scratch);
+    case IB200_F16: return run<T, __half, KIND>(x, out, outer, n, inner, scale, s, scratch);
     default: return fail(IB200_ERR_UNSUPPORTED, "reduce: output dtype must be f32, bf16 or f16");
   }
 }
 
 template <int KIND> int pick_in(const void* x, void* out, int x_dtype, int out_dtype, int64_t outer, int64_t n,
-                                int64_t inner, float scale, cudaStream_t s) {
+                                int64_t inner, float scale, cudaStream_t s, void* scratch) {
   switch (x_dtype) {
-    case IB200_F32: return pick_out<float, KIND>(x, out, out_dtype, outer, n, inner, scale, s);
-    case IB200_BF16: return pick_out<__nv_bfloat16, KIND>(x, out, out_dtype, outer, n, inner, scale, s);
-    case IB200_F16: return pick_out<__half, KIND>(x, out, out_dtype, outer, n, inner, scale, s);
+    case IB200_F32: return pick_out<float, KIND>(x, out, out_dtype, outer, n, inner, scale, s, scratch);
+    case IB200_BF16: return pick_out<__nv_bfloat16, KIND>(x, out, out_dtype, outer, n, inner, scale, s, scratch);
+    case IB200_F16: return pick_out<__half, KIND>(x, out, out_dtype, outer, n, inner, scale, s, scratch);
     case IB200_BOOL: case IB200_U8:
-      if (KIND == IB200_REDUCE_ANY) return pick_out<uint8_t, KIND>(x, out, out_dtype, outer, n, inner, scale, s);
+      if (KIND == IB200_REDUCE_ANY) return pick_out<uint8_t, KIND>(x, out, out_dtype, outer, n, inner, scale, s, scratch);
       return fail(IB200_ERR_UNSUPPORTED, "reduce: sum/max over a bool tensor is not covered");
     default: return fail(IB200_ERR_UNSUPPORTED, "reduce: input dtype must be f32, bf16, f16 or bool");
   }
@@ -204,16 +250,26 @@ template <int KIND> int pick_in(const void* x, void* out, int x_dtype, int out_d
 
 }  // namespace
 
+// Splitting pays when the rows alone cannot fill the GPU (fewer than two per SM) and each is long
+// enough for several segments of at least 16 Ki elements; the aim is about four CTAs per SM.
+int reduce_split_factor(int64_t outer, int64_t reduce, int64_t inner) {
+  if (inner != 1 || outer < 1 || outer >= 2 * kSmCount || outer > kSplitCounters || reduce < 65536) return 1;
+  int64_t split = (4 * (int64_t)kSmCount + outer - 1) / outer;
+  if (split > reduce / 16384) split = reduce / 16384;
+  if (outer * split > kSplitPartials) split = kSplitPartials / outer;
+  return split < 2 ? 1 : (int)split;
+}
+
 int launch_reduce(const void* x, void* out, int x_dtype, int out_dtype, int kind, int64_t outer, int64_t reduce,
-                  int64_t inner, float scale, cudaStream_t s) {
+                  int64_t inner, float scale, cudaStream_t s, void* scratch) {
   if (outer < 0 || reduce < 0 || inner < 0) return fail(IB200_ERR_INVALID, "reduce: negative extent");
   if (outer == 0 || inner == 0) return IB200_OK;  // empty result
   if (!out || (!x && reduce > 0)) return fail(IB200_ERR_INVALID, "reduce: null pointer");
   if (reduce == 0 && kind == IB200_REDUCE_MAX) return fail(IB200_ERR_INVALID, "reduce_max over an empty axis has no identity");
   switch (kind) {
-    case IB200_REDUCE_SUM: return pick_in<IB200_REDUCE_SUM>(x, out, x_dtype, out_dtype, outer, reduce, inner, scale, s);
-    case IB200_REDUCE_MAX: return pick_in<IB200_REDUCE_MAX>(x, out, x_dtype, out_dtype, outer, reduce, inner, scale, s);
-    case IB200_REDUCE_ANY: return pick_in<IB200_REDUCE_ANY>(x, out, x_dtype, out_dtype, outer, reduce, inner, scale, s);
+    case IB200_REDUCE_SUM: return pick_in<IB200_REDUCE_SUM>(x, out, x_dtype, out_dtype, outer, reduce, inner, scale, s, scratch);
+    case IB200_REDUCE_MAX: return pick_in<IB200_REDUCE_MAX>(x, out, x_dtype, out_dtype, outer, reduce, inner, scale, s, scratch);
+    case IB200_REDUCE_ANY: return pick_in<IB200_REDUCE_ANY>(x, out, x_dtype, out_dtype, outer, reduce, inner, scale, s, scratch);
     default: return fail(IB200_ERR_INVALID, "reduce: unknown kind");
   }
 }

@@ -732,3 +732,58 @@ def test_masked_softmax_keeps_an_infinite_fill_and_a_consumer_of_the_masked_scor
     got2 = run_lowered(low2, {"x": x, "mask": mask})
     want2 = execute_intent(intent2, {"x": x, "mask": mask}, shape_bindings={"M": 6, "N": 50})
     assert np.array_equal(got2["xm"], want2["xm"]) and np.allclose(got2["y"], want2["y"], rtol=1e-5, atol=1e-7)
+
+
+# ---- few long rows: the reduction is split over many CTAs ----------------------------------
+
+def _reduce_graph(op, shape_syms, dims, dtype="f32"):
+    out_shape = [s for i, s in enumerate(shape_syms) if i not in dims]
+    return {"name": "r", "tensors": {"x": _t(shape_syms, dtype), "y": _t(out_shape, "bool" if op == "reduce_any" else "f32")},
+            "ops": [{"op": op, "inputs": ["x"], "output": "y", "attrs": {"dims": dims}}], "outputs": ["y"]}
+
+
+@pytest.mark.parametrize("op", ["reduce_sum", "reduce_max", "reduce_any"])
+@pytest.mark.parametrize("m,n", [(1, 65536), (1, 1 << 22), (3, 100003), (7, 262147), (40, 70000), (295, 65537)])
+def test_few_long_rows_are_split_over_the_gpu(op, m, n):
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+    from intent_ir_b200.runtime import run_lowered
+
+    intent = IntentFunction.from_json_dict(_reduce_graph(op, ["M", "N"], [1]))
+    rng = np.random.default_rng(m + n)
+    x = rng.standard_normal((m, n)).astype(np.float32)
+    if op == "reduce_any":
+        x[:] = 0
+        x[0, n - 1] = 2.0  # only the last segment of the first row sees a non-zero
+        if m > 2:
+            x[2, 17] = float("nan")
+    if op == "reduce_max" and m > 1:
+        x[1, n // 2] = float("nan")  # np.max propagates it
+    low = lower_intent_to_b200_kernel(intent, shape_bindings={"M": m, "N": n})
+    assert [s["kernel"] for s in low.steps] == [op + "(split rows)"]
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, {"x": x}, shape_bindings={"M": m, "N": n})["y"]
+    first = run_lowered(low, {"x": x})["y"]
+    again = run_lowered(low, {"x": x})["y"]  # same scratch area a second time; same bits
+    assert np.array_equal(first, again, equal_nan=True)
+    if op == "reduce_sum":
+        assert np.allclose(first, want, rtol=1e-4, atol=1e-2 * np.sqrt(n) * 1e-2), float(np.abs(first - want).max())
+    else:
+        assert np.array_equal(first, want, equal_nan=True)
+
+
+def test_whole_tensor_reductions_and_split_rows_inside_a_graph():
+    """sum over both axes is one row of M*N elements; a split reduction feeding later ops."""
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+    from intent_ir_b200.runtime import run_lowered
+
+    js = {"name": "g", "tensors": {"x": _t(["M", "N"]), "tot": _t([]), "y": _t(["M", "N"])},
+          "ops": [{"op": "reduce_sum", "inputs": ["x"], "output": "tot", "attrs": {"dims": [0, 1]}},
+                  {"op": "sub", "inputs": ["x", "tot"], "output": "y"}], "outputs": ["tot", "y"]}
+    intent = IntentFunction.from_json_dict(js)
+    x = np.random.default_rng(9).random((300, 1000)).astype(np.float32)
+    low = lower_intent_to_b200_kernel(intent, shape_bindings={"M": 300, "N": 1000})
+    assert "reduce_sum(split rows)" in [s["kernel"] for s in low.steps]
+    got = run_lowered(low, {"x": x})
+    want = execute_intent(intent, {"x": x}, shape_bindings={"M": 300, "N": 1000})
+    assert np.allclose(got["tot"], want["tot"], rtol=1e-5)
+    assert np.allclose(got["y"], want["y"], rtol=1e-5, atol=2e-2)
