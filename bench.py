@@ -188,6 +188,15 @@ def workload(name):
         return (js, {"M": m, "N": n},
                 lambda r: {"x": r.standard_normal((m, n), dtype=np.float32), "p": np.array(0.1, np.float32), "seed": np.array(1234, np.int64)},
                 2 * m * n * 4, 0, "dropout f32 [8192,4096], p = 0.1, 10 Philox rounds (verify/interpreter.py:697-742), bit-exact mask")
+    if name in ("reduce_sum_all", "column_sum"):
+        m, n = (8192, 8192) if name == "reduce_sum_all" else (65536, 1024)
+        t = lambda sh: {"dtype": "f32", "shape": sh, "layout": "row_major"}  # noqa: E731
+        whole = name == "reduce_sum_all"
+        js = {"name": name, "tensors": {"x": t(["M", "N"]), "y": t([] if whole else ["N"])},
+              "ops": [{"op": "reduce_sum", "inputs": ["x"], "output": "y", "attrs": {"dims": [0, 1] if whole else [0]}}], "outputs": ["y"]}
+        return (js, {"M": m, "N": n}, lambda r: {"x": r.standard_normal((m, n), dtype=np.float32)}, m * n * 4 + (4 if whole else n * 4), 0,
+                "sum of a whole f32 [8192,8192] tensor: one row, split over the GPU" if whole
+                else "sum over the leading axis of f32 [65536,1024]: the reduced axis split over the GPU")
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -600,7 +609,7 @@ def main():
                                     "sample": f"{rows_sample} of {rows_full} rows, best of 3, numpy {np.__version__}, host has {os.cpu_count()} cores"}
         if not args.no_ops:
             ops = {}
-            for name in ("layernorm", "groupnorm", "matmul", "chain", "dag", "rmsnorm", "layernorm_residual", "masked_softmax", "rowprog", "rope", "dropout",
+            for name in ("layernorm", "groupnorm", "matmul", "chain", "dag", "rmsnorm", "layernorm_residual", "masked_softmax", "rowprog", "rope", "dropout", "reduce_sum_all", "column_sum",
                          "reduce_any_large", "reduce_any"):
                 if name == args.workload:
                     continue

@@ -129,6 +129,17 @@ IB200_API size_t ib200_noalloc_workspace_limit(void);
 IB200_API int ib200_reduce(const void* x, void* out, int x_dtype, int out_dtype, int kind, int64_t outer,
                  int64_t reduce, int64_t inner, float scale, void* stream);
 
+/* The same reduction with scratch memory, which lets shapes with too few independent results to fill
+ * the GPU (a handful of very long rows, a whole-tensor sum, a reduction over the leading axis of a
+ * narrow matrix) be split along the reduced axis: every CTA reduces one segment, and the CTA that
+ * finishes last folds the partial results in segment order, so results do not vary from run to run.
+ * ib200_reduce_scratch_bytes gives the amount for a shape (0: that shape is never split); `scratch`
+ * is 256-byte aligned device memory in any state, not shared with a launch that may run at the
+ * same time.  With too little scratch (or NULL) this is ib200_reduce. */
+IB200_API size_t ib200_reduce_scratch_bytes(int64_t outer, int64_t reduce, int64_t inner);
+IB200_API int ib200_reduce_ws(const void* x, void* out, int x_dtype, int out_dtype, int kind, int64_t outer,
+                    int64_t reduce, int64_t inner, float scale, void* scratch, size_t scratch_bytes, void* stream);
+
 /* The BASELINE any_kernel_dim case: out[m] = any_n(x[m, n] != 0), f32 in, one byte out. */
 IB200_API int ib200_reduce_any_f32(const float* x, uint8_t* out, int64_t rows, int64_t cols, void* stream);
 

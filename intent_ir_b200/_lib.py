@@ -44,6 +44,8 @@ SIGNATURES = {
     "ib200_plan_launch_noalloc": (_i, [_vp, C.POINTER(_vp), _i, _vp]),
     "ib200_noalloc_workspace_limit": (_sz, []),
     "ib200_reduce": (_i, [_vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp]),
+    "ib200_reduce_scratch_bytes": (C.c_size_t, [_i64, _i64, _i64]),
+    "ib200_reduce_ws": (_i, [_vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, C.c_size_t, _vp]),
     "ib200_reduce_any_f32": (_i, [_vp, _vp, _i64, _i64, _vp]),
     "ib200_softmax": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i64, _vp]),
     "ib200_softmax_io": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _vp]),

@@ -32,6 +32,14 @@ int ib200_reduce(const void* x, void* out, int x_dtype, int out_dtype, int kind,
   return launch_reduce(x, out, x_dtype, out_dtype, kind, outer, reduce, inner, scale, static_cast<cudaStream_t>(stream));
 }
 
+size_t ib200_reduce_scratch_bytes(int64_t outer, int64_t reduce, int64_t inner) { return reduce_scratch_bytes(outer, reduce, inner); }
+
+int ib200_reduce_ws(const void* x, void* out, int x_dtype, int out_dtype, int kind, int64_t outer, int64_t reduce, int64_t inner,
+                    float scale, void* scratch, size_t scratch_bytes, void* stream) {
+  if (scratch && (reinterpret_cast<uintptr_t>(scratch) & 255u)) return fail(IB200_ERR_INVALID, "reduce_ws: scratch must be 256-byte aligned");
+  return launch_reduce(x, out, x_dtype, out_dtype, kind, outer, reduce, inner, scale, static_cast<cudaStream_t>(stream), scratch, scratch_bytes);
+}
+
 int ib200_reduce_any_f32(const float* x, uint8_t* out, int64_t rows, int64_t cols, void* stream) {
   return launch_reduce(x, out, IB200_F32, IB200_BOOL, IB200_REDUCE_ANY, rows, cols, 1, 1.0f, static_cast<cudaStream_t>(stream));
 }

@@ -38,12 +38,12 @@ inline int dtype_size(int dt) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- internal launchers (one per .cu file) ----------------------------------------------
-// `scratch` (kReduceScratchBytes of device memory in any state, or null) lets few long rows be split
-// over many CTAs: see reduce_split_factor.
-constexpr size_t kReduceScratchBytes = 8192;
-int reduce_split_factor(int64_t outer, int64_t reduce, int64_t inner);  // 1: the row kernels as they are
+// `scratch` (device memory in any state, or null) lets a reduction with too few independent results to
+// fill the GPU be split along the reduced axis; reduce_scratch_bytes says how much that takes (0: the
+// shape is not split).  With less scratch than that the unsplit kernels run.
+size_t reduce_scratch_bytes(int64_t outer, int64_t reduce, int64_t inner);
 int launch_reduce(const void* x, void* out, int x_dtype, int out_dtype, int kind, int64_t outer,
-                  int64_t reduce, int64_t inner, float scale, cudaStream_t s, void* scratch = nullptr);
+                  int64_t reduce, int64_t inner, float scale, cudaStream_t s, void* scratch = nullptr, size_t scratch_bytes = 0);
 struct SoftmaxMask {     // softmax(where(mask, x, fill)): the mask is applied while the rows are loaded
   const uint8_t* mask;   // bool / u8, or null for a plain softmax
   int64_t row_stride;    // elements between the mask rows of consecutive rows (0: one mask row for all)

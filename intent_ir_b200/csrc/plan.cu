@@ -796,6 +796,14 @@ class Planner {
     return true;
   }
 
+  // reductions whose results alone give too few CTAs are split along the reduced axis; the partial results go through the workspace
+  void add_reduce_scratch(Step& s) {
+    const size_t bytes = reduce_scratch_bytes(s.d[0], s.d[1], s.d[2]);
+    if (bytes == 0) return;
+    s.scratch = new_workspace_buffer(IB200_U8, (int64_t)bytes, "reduce scratch");
+    s.label += s.d[2] == 1 ? "(split rows)" : "(split columns)";
+  }
+
   int new_workspace_buffer(int dtype, int64_t elements, const std::string& name) {
     Buffer b;
     b.dtype = dtype;
@@ -962,10 +970,7 @@ class Planner {
     s.dtype = xd;
     s.dtype2 = plan_->buffers[s.out[0]].dtype;
     if (s.dtype2 != IB200_BOOL) return false;
-    if (reduce_split_factor(s.d[0], s.d[1], s.d[2]) > 1) {
-      s.scratch = new_workspace_buffer(IB200_U8, (int64_t)kReduceScratchBytes, "reduce scratch");
-      s.label += "(split rows)";
-    }
+    add_reduce_scratch(s);
     plan_->steps.push_back(s);
     return true;
   }
@@ -1365,10 +1370,7 @@ class Planner {
         s.out[0] = new_workspace_buffer(tmp_dt, numel(n.shape), n.name);
         s.dtype2 = tmp_dt;
       }
-      if (reduce_split_factor(s.d[0], s.d[1], s.d[2]) > 1) {
-        s.scratch = new_workspace_buffer(IB200_U8, (int64_t)kReduceScratchBytes, "reduce scratch");
-        s.label += "(split rows)";
-      }
+      add_reduce_scratch(s);
       plan_->steps.push_back(s);
       set_strided(id, s.out[0]);
       return;
@@ -2808,7 +2810,7 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
     switch (st.kind) {
       case Step::REDUCE:
         rc = launch_reduce(P(st.in[0]), P(st.out[0]), st.dtype, st.dtype2, st.reduce_kind, st.d[0], st.d[1], st.d[2], st.scale, s,
-                           st.scratch >= 0 ? P(st.scratch) : nullptr);
+                           st.scratch >= 0 ? P(st.scratch) : nullptr, st.scratch >= 0 ? plan->buffers[st.scratch].bytes : 0);
         break;
       case Step::SOFTMAX: {
         const SoftmaxMask mk{static_cast<const uint8_t*>(st.reduce_kind ? P(st.in[1]) : nullptr), st.aff_inner, (float)st.other, 0};

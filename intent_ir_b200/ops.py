@@ -91,8 +91,10 @@ def normalise_axes(dims: Sequence[int], rank: int) -> Tuple[int, ...]:
 
 
 def reduce(x: torch.Tensor, kind: str, dims: Sequence[int], keepdims: bool = False, scale: float = 1.0,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``reduce_sum`` / ``reduce_max`` / ``reduce_any`` over a contiguous run of axes."""
+           out_dtype: Optional[torch.dtype] = None, split: bool = True) -> torch.Tensor:
+    """``reduce_sum`` / ``reduce_max`` / ``reduce_any`` over a contiguous run of axes.  With
+    ``split`` (default) shapes with too few results to fill the GPU get scratch memory and are
+    split along the reduced axis; the result does not vary from run to run either way."""
     _dev(x, "x")
     axes = normalise_axes(dims, x.dim())
     if not axes:
@@ -108,7 +110,14 @@ def reduce(x: torch.Tensor, kind: str, dims: Sequence[int], keepdims: bool = Fal
         out_dtype = torch.bool if kind == "any" else x.dtype
     out_shape = [1 if i in axes else d for i, d in enumerate(shape)] if keepdims else [d for i, d in enumerate(shape) if i not in axes]
     out = torch.empty(out_shape, dtype=out_dtype, device=x.device)
-    rc = _lib.load().ib200_reduce(_ptr(x), _ptr(out), code_of(x), code_of(out), kinds[kind], outer, red, inner, float(scale), _stream())
+    lib = _lib.load()
+    need = int(lib.ib200_reduce_scratch_bytes(outer, red, inner)) if split else 0
+    if need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)  # freed stream-ordered by the caching allocator
+        rc = lib.ib200_reduce_ws(_ptr(x), _ptr(out), code_of(x), code_of(out), kinds[kind], outer, red, inner, float(scale),
+                                 _ptr(scratch), need, _stream())
+    else:
+        rc = lib.ib200_reduce(_ptr(x), _ptr(out), code_of(x), code_of(out), kinds[kind], outer, red, inner, float(scale), _stream())
     _check(rc, f"reduce_{kind}")
     return out
 

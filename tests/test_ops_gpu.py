@@ -335,3 +335,44 @@ def test_softmax_masked_rejects_what_it_does_not_cover():
         ops.softmax_masked(x[:, :8].contiguous(), torch.ones(3, dtype=torch.bool, device="cuda"), 0.0)
     with pytest.raises(B200RuntimeError):
         ops.softmax_masked(x[:, :8].contiguous().half(), torch.ones(8, dtype=torch.bool, device="cuda"), 0.0)
+
+
+@pytest.mark.parametrize("shape,dims", [((2, 200000), [1]), ((1, 70001), [1]), ((50000, 64), [0]), ((3, 7000, 128), [1]), ((9000, 12), [0]),
+                                        ((300, 700), [0, 1])])
+@pytest.mark.parametrize("kind", ["sum", "max", "any"])
+def test_reduce_with_scratch_matches_the_unsplit_kernels(shape, dims, kind):
+    from intent_ir_b200 import _lib, ops
+    x = np.random.default_rng(len(shape) + shape[-1]).standard_normal(shape).astype(np.float32)
+    if kind == "any":
+        x[np.abs(x) < 3.5] = 0
+    xd = _dev(x)
+    lib = _lib.load()
+    outer = int(np.prod(shape[: dims[0]], dtype=np.int64))
+    red = int(np.prod(shape[dims[0]: dims[-1] + 1], dtype=np.int64))
+    inner = int(np.prod(shape[dims[-1] + 1:], dtype=np.int64))
+    assert lib.ib200_reduce_scratch_bytes(outer, red, inner) > 0
+    split = ops.reduce(xd, kind, dims).cpu().numpy()
+    plain = ops.reduce(xd, kind, dims, split=False).cpu().numpy()
+    want = {"sum": np.sum, "max": np.max, "any": lambda a, axis: np.any(a != 0, axis=axis)}[kind](x, axis=tuple(dims))
+    if kind == "sum":
+        _agree(split, want, 1e-3, 1e-4)
+        _agree(plain, want, 1e-3, 1e-4)
+    else:
+        assert np.array_equal(split, want) and np.array_equal(plain, want)
+    assert np.array_equal(split, ops.reduce(xd, kind, dims).cpu().numpy())  # the same bits on every run
+
+
+def test_reduce_ws_falls_back_without_enough_scratch_and_checks_alignment():
+    from intent_ir_b200 import _lib
+    lib = _lib.load()
+    x = torch.ones(1, 1 << 20, device="cuda")
+    out = torch.zeros(1, device="cuda")
+    need = lib.ib200_reduce_scratch_bytes(1, 1 << 20, 1)
+    assert need > 0 and lib.ib200_reduce_scratch_bytes(4096, 4096, 1) == 0
+    small = torch.empty(256, dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert lib.ib200_reduce_ws(x.data_ptr(), out.data_ptr(), _lib.F32, _lib.F32,
+                               _lib.REDUCE_SUM, 1, 1 << 20, 1, 1.0, small.data_ptr(), 256, s) == _lib.OK
+    assert float(out.cpu()) == float(1 << 20)
+    big = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
+    assert lib.ib200_reduce_ws(x.data_ptr(), out.data_ptr(), 0, 0, _lib.REDUCE_SUM, 1, 1 << 20, 1, 1.0, big.data_ptr() + 4, need, s) != _lib.OK

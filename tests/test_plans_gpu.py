@@ -787,3 +787,35 @@ def test_whole_tensor_reductions_and_split_rows_inside_a_graph():
     want = execute_intent(intent, {"x": x}, shape_bindings={"M": 300, "N": 1000})
     assert np.allclose(got["tot"], want["tot"], rtol=1e-5)
     assert np.allclose(got["y"], want["y"], rtol=1e-5, atol=2e-2)
+
+
+@pytest.mark.parametrize("op", ["reduce_sum", "reduce_max", "reduce_any"])
+@pytest.mark.parametrize("shape,dims", [((100000, 64), [0]), ((65536, 1024), [0]), ((5000, 4), [0]), ((333, 8), [0]), ((70000, 132), [0]),
+                                        ((3, 9000, 64), [1]), ((2, 4097, 20), [1]), ((40000, 6), [0]), ((17, 50, 4096), [0, 1])])
+def test_reductions_over_leading_axes_are_split_over_the_gpu(op, shape, dims):
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+    from intent_ir_b200.runtime import run_lowered
+
+    syms = [f"D{i}" for i in range(len(shape))]
+    bind = dict(zip(syms, shape))
+    intent = IntentFunction.from_json_dict(_reduce_graph(op, syms, dims))
+    rng = np.random.default_rng(sum(shape))
+    x = rng.standard_normal(shape).astype(np.float32)
+    if op == "reduce_any":
+        x[:] = 0
+        x[(shape[0] - 1,) + (0,) * (len(shape) - 2) + (shape[-1] - 1,)] = 1.0
+        x[(0,) * (len(shape) - 1) + (1,)] = float("nan")
+    if op == "reduce_max":
+        x[(shape[0] // 2,) + (0,) * (len(shape) - 1)] = float("nan")
+    low = lower_intent_to_b200_kernel(intent, shape_bindings=bind)
+    kernels = [s["kernel"] for s in low.steps]
+    assert kernels == ([op + "(split columns)"] if shape[-1] % 4 == 0 else [op]), kernels
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, {"x": x}, shape_bindings=bind)["y"]
+    first = run_lowered(low, {"x": x})["y"]
+    again = run_lowered(low, {"x": x})["y"]
+    assert first.shape == want.shape and np.array_equal(first, again, equal_nan=True)
+    if op == "reduce_sum":
+        assert np.allclose(first, want, rtol=1e-4, atol=2e-2), float(np.abs(first - want).max())
+    else:
+        assert np.array_equal(first, want, equal_nan=True)
