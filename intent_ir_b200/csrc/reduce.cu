@@ -158,6 +158,8 @@ __global__ void __launch_bounds__(256) reduce_rows_split(const T* __restrict__ x
   if (threadIdx.x == 0) write_result<TO>(out, row, acc, scale, KIND);
 }
 
+constexpr int kColsVecCtasPerSm = 6;  // 40 registers; a split launch is sized to exactly one wave of these
+
 // How a reduction over a leading / middle axis is laid over the GPU (inner % 4 == 0).
 struct ColPlan {
   int lanes;          // L: lanes per row, 4*L columns per CTA
@@ -172,8 +174,8 @@ ColPlan col_plan(int64_t outer, int64_t n, int64_t inner, bool may_split) {
   c.lanes = inner >= 128 ? 32 : inner >= 64 ? 16 : 8;
   const int64_t W = 4 * c.lanes, G = 256 / c.lanes;
   c.col_tiles = (inner + W - 1) / W;
-  const int64_t base = outer * c.col_tiles, target = (int64_t)kSmCount * 8;
-  int64_t split = may_split && base < target ? (target + base - 1) / base : 1;
+  const int64_t base = outer * c.col_tiles, target = (int64_t)kSmCount * kColsVecCtasPerSm;
+  int64_t split = may_split && base < target ? target / base : 1;  // rounded down: never a second, partly filled wave
   if (split > n / (4 * G)) split = n / (4 * G);  // at least four trips over the rows per segment
   if (split < 1) split = 1;
   c.seg = ((n + split - 1) / split + G - 1) / G * G;
@@ -186,7 +188,7 @@ ColPlan col_plan(int64_t outer, int64_t n, int64_t inner, bool may_split) {
 }
 
 template <typename T, typename TO, int KIND, int L>
-__global__ void __launch_bounds__(256) reduce_cols_vec(const T* __restrict__ x, TO* __restrict__ out, int64_t n, int64_t inner, int64_t col_tiles,
+__global__ void __launch_bounds__(256, kColsVecCtasPerSm) reduce_cols_vec(const T* __restrict__ x, TO* __restrict__ out, int64_t n, int64_t inner, int64_t col_tiles,
                                                        int split, int64_t seg, int64_t items, float scale, unsigned* __restrict__ counters,
                                                        float* __restrict__ partials) {
   using Op = typename KindOp<KIND>::Op;
