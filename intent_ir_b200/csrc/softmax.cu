@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(128) softmax_warp(const T* __restrict__ x, TO*
 }
 
 template <typename T, typename TO, int THREADS, int NV, bool VEC, bool MASKED>
-__global__ void __launch_bounds__(THREADS) softmax_block(const T* __restrict__ x, TO* __restrict__ y,
+__global__ void __launch_bounds__(THREADS, (MASKED && THREADS == 256) ? 6 : 1) softmax_block(const T* __restrict__ x, TO* __restrict__ y,
                                                          float* __restrict__ row_max, float* __restrict__ row_sum,
                                                          int64_t rows, int cols, SoftmaxMask mk) {
   __shared__ float slots[2][32];
