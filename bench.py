@@ -47,7 +47,7 @@ L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram bytes per launch from the ncu capture summarised in profiles/ (read + write); None = not captured
 NCU_TRAFFIC = {"softmax": 89600000, "layernorm": 220300000, "groupnorm": 215200000, "matmul": 79500000, "chain": 223500000,
-               "rmsnorm": 217900000, "rowprog": 223600000, "rope": 224200000, "masked_softmax": 89200000, "reduce_sum_all": 273400000,
+               "rmsnorm": 217900000, "rowprog": 223600000, "rope": 224200000, "masked_softmax": 87800000, "reduce_sum_all": 273400000,
                "column_sum": 275900000}
 
 
