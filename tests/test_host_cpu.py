@@ -236,3 +236,35 @@ def test_plan_ids_stay_unique_when_the_plan_cache_evicts(golden_graphs):
     for m in range(1, 560):  # more plans than the cache holds
         ids.add(lower_intent_to_b200_kernel(g, shape_bindings={"M": m, "N": 8}).io_spec["plan_id"])
     assert len(ids) == 559
+
+
+def test_reduce_scratch_sizes_and_plan_labels_agree():
+    """ib200_reduce_scratch_bytes is a host computation: shapes that fill the GPU by themselves need no
+    scratch, few long rows take the fixed row area, narrow leading-axis reductions an area that grows
+    with the number of segments; the plan builder marks exactly the shapes that get scratch."""
+    from intent_ir_b200 import _lib
+    from intent_ir_b200.lowering import plan_json
+
+    lib = _lib.load()
+    need = lambda o, r, i: int(lib.ib200_reduce_scratch_bytes(o, r, i))  # noqa: E731
+    assert need(4096, 4096, 1) == 0 and need(16, 256, 1) == 0 and need(4, 65535, 1) == 0 and need(296, 65536, 1) == 0
+    assert need(1, 1 << 26, 1) == need(295, 65536, 1) == 8192
+    assert need(1, 40000, 6) == 0  # inner extent not a multiple of 4: the scalar tiles, unsplit
+    assert need(1, 1 << 20, 64) > need(1, 1 << 10, 64) > 0
+    assert need(1, 8, 64) == 0 and need(0, 5, 4) == 0 and need(1 << 20, 64, 128) == 0
+
+    def graph(dims):
+        t = lambda sh, dt="f32": {"dtype": dt, "shape": sh, "layout": "row_major"}  # noqa: E731
+        out = [s for k, s in enumerate(["M", "N"]) if k not in dims]
+        return {"name": "r", "tensors": {"x": t(["M", "N"]), "y": t(out)},
+                "ops": [{"op": "reduce_sum", "inputs": ["x"], "output": "y", "attrs": {"dims": dims}}], "outputs": ["y"]}
+
+    for (m, n, dims, o, r, i) in [(1, 1 << 20, [1], 1, 1 << 20, 1), (4096, 4096, [1], 4096, 4096, 1), (1 << 16, 64, [0], 1, 1 << 16, 64),
+                                  (300, 1000, [0, 1], 1, 300000, 1), (40000, 6, [0], 1, 40000, 6)]:
+        d = plan_json(graph(dims), {"M": m, "N": n})
+        label = d["steps"][0]["kernel"]
+        if need(o, r, i):
+            assert label == ("reduce_sum(split rows)" if i == 1 else "reduce_sum(split columns)"), (m, n, label)
+            assert d["workspace_bytes"] >= need(o, r, i)
+        else:
+            assert label == "reduce_sum" and d["workspace_bytes"] == 0, (m, n, label)
