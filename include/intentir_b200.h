@@ -100,22 +100,46 @@ IB200_API int ib200_plan_num_launches(const ib200_plan_t* plan);
 
 /* Enqueue the plan.  `args[i]` is the device pointer of io_spec.arg_names[i].  `workspace`
  * must be 256-byte aligned and at least ib200_plan_workspace_bytes(plan) long (may be NULL
- * when that is 0).  Replaces `mod.launch(...)` (frontends/cuda/runtime.py:723-746). */
+ * when that is 0).  ZERO-FILL THE WORKSPACE ONCE before its first use: plans whose kernels have
+ * bounded device-side waits keep a status word in it that is only ever written when a wait
+ * runs out, so garbage there reads as a failure.  Replaces `mod.launch(...)`
+ * (frontends/cuda/runtime.py:723-746). */
 IB200_API int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, void* workspace,
                       size_t workspace_bytes, void* stream);
+
+/* After the plan's launches: synchronise `stream`, read the plan's status word out of
+ * `workspace` and return IB200_ERR_DEVICE_WAIT if a bounded device-side wait ran out during
+ * the plan (IB200_OK at once for plans without such kernels).  The word is left as found:
+ * clear it (4 bytes at the offset "status_offset" of the plan description) before reusing
+ * the workspace after a failure.  The reference has no counterpart: its kernels have no
+ * device-side waits. */
+IB200_API int ib200_plan_check_status(const ib200_plan_t* plan, const void* workspace, void* stream);
 
 /* Same as ib200_plan_launch, for callers that cannot supply a workspace because they are not
  * allowed to allocate device memory (their memory belongs to another runtime's pool, or
  * their hot loop must never reach cudaMalloc).  The scratch is a fixed array of
- * ib200_noalloc_workspace_limit() bytes (32 MiB) built into the library image and resident
- * on every GPU that loads the library; plans needing more return IB200_ERR_BUFFER and launch
- * nothing.  The array is shared by all calls in the process: calls whose kernels could
- * overlap on the GPU race on it, so keep them ordered.  The first call on a device resolves
- * the array's address and should be made outside any stream capture.  Never allocates.
+ * ib200_noalloc_workspace_limit() bytes (32 MiB) built into the library image; a GPU holds
+ * it from the moment the CUDA runtime loads the library's module there until the process
+ * exits.  Plans needing more return IB200_ERR_BUFFER and launch nothing.  The array is
+ * shared by all calls in the process: calls whose kernels could overlap on the GPU race on
+ * it, so keep them ordered.  The first call on a device resolves the array's address; under
+ * the runtime's lazy module loading (the default) that is also when the runtime backs the
+ * 32 MiB, so make this first call early, while the device still has that much free, and
+ * outside any stream capture.  The library itself never allocates.
  * This entry point has no counterpart in the reference: its runner always allocates through
  * torch (frontends/cuda/runtime.py:961-1008). */
 IB200_API int ib200_plan_launch_noalloc(const ib200_plan_t* plan, void* const* args, int n_args, void* stream);
 IB200_API size_t ib200_noalloc_workspace_limit(void);
+/* ib200_plan_check_status for a plan launched through ib200_plan_launch_noalloc: reads the
+ * status word out of the built-in array on the current device (synchronises `stream`).  Call
+ * it before the next ib200_plan_launch_noalloc, which clears the word.  No counterpart in the
+ * reference. */
+IB200_API int ib200_plan_check_status_noalloc(const ib200_plan_t* plan, void* stream);
+/* Failure injection from the host, for tests of the error path: writes `code` into the plan's
+ * status word inside the built-in array, exactly where a kernel whose bounded wait ran out
+ * would have written it (synchronises `stream`).  No GPU work is disturbed.  No counterpart
+ * in the reference. */
+IB200_API int ib200_noalloc_debug_poke_status(const ib200_plan_t* plan, int32_t code, void* stream);
 
 /* ======================================================================================
  * Direct per-op entry points (the same kernels the plans launch).

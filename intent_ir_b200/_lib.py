@@ -43,6 +43,9 @@ SIGNATURES = {
     "ib200_plan_launch": (_i, [_vp, C.POINTER(_vp), _i, _vp, _sz, _vp]),
     "ib200_plan_launch_noalloc": (_i, [_vp, C.POINTER(_vp), _i, _vp]),
     "ib200_noalloc_workspace_limit": (_sz, []),
+    "ib200_plan_check_status": (_i, [_vp, _vp, _vp]),
+    "ib200_plan_check_status_noalloc": (_i, [_vp, _vp]),
+    "ib200_noalloc_debug_poke_status": (_i, [_vp, C.c_int32, _vp]),
     "ib200_reduce": (_i, [_vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp]),
     "ib200_reduce_scratch_bytes": (C.c_size_t, [_i64, _i64, _i64]),
     "ib200_reduce_ws": (_i, [_vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, C.c_size_t, _vp]),

@@ -9,14 +9,22 @@
 // for their intermediates.
 //
 // What it does instead: the scratch lives in a fixed array in device global memory that is
-// part of this library's image.  Every GPU on which the library gets loaded carries the
-// array (IB200_NOALLOC_WORKSPACE_BYTES, 32 MiB) from load until the process exits, whether or
-// not this entry point is ever called.  Plans that need more are refused with
-// IB200_ERR_BUFFER; nothing is launched in that case.
+// part of this library's image (IB200_NOALLOC_WORKSPACE_BYTES, 32 MiB).  A GPU carries the
+// array from the moment the CUDA runtime loads this translation unit's module on it until the
+// process exits.  When that moment is depends on the runtime's module loading mode: with eager
+// loading it is context creation, whether or not this entry point is ever called; with lazy
+// loading (the default of current CUDA releases, CUDA_MODULE_LOADING=LAZY) it is the first call
+// of this entry point on that device, whose address lookup makes the runtime load the module
+// and back the 32 MiB — measured on a B200: free device memory drops by 32 MiB (plus the
+// module's code) across that first call and stays flat across later ones.  Plans that need
+// more are refused with IB200_ERR_BUFFER; nothing is launched in that case.
 //
 // Rules for callers
-//   * The first call on each device looks up the array's device address (no allocation, but
-//     a runtime query); make that first call outside of any stream capture.
+//   * The first call on each device looks up the array's device address.  This library
+//     allocates nothing for it, but under lazy module loading the runtime materialises the
+//     array at that moment, so it can fail with an out-of-memory status if the device is
+//     already full: make the first call early (a plan that needs no scratch will do), and
+//     outside of any stream capture.
 //   * The array is shared by every call in the process.  Its contents after a call are
 //     whatever that plan left there; the one region a plan expects to start at zero (the
 //     status word of the tensor-core GEMM) is cleared on the stream at the start of each
@@ -66,6 +74,26 @@ int workspace_for_current_device(void** out) {
 extern "C" {
 
 size_t ib200_noalloc_workspace_limit(void) { return IB200_NOALLOC_WORKSPACE_BYTES; }
+
+int ib200_plan_check_status_noalloc(const ib200_plan_t* plan, void* stream) {
+  if (!plan) return ib200::fail(IB200_ERR_INVALID, "plan_check_status_noalloc: null plan");
+  if (ib200::plan_status_offset(plan) < 0) return IB200_OK;
+  void* ws = nullptr;
+  if (int rc = workspace_for_current_device(&ws)) return rc;
+  return ib200_plan_check_status(plan, ws, stream);
+}
+
+int ib200_noalloc_debug_poke_status(const ib200_plan_t* plan, int32_t code, void* stream) {
+  if (!plan) return ib200::fail(IB200_ERR_INVALID, "noalloc_debug_poke_status: null plan");
+  const long status = ib200::plan_status_offset(plan);
+  if (status < 0) return ib200::fail(IB200_ERR_INVALID, "noalloc_debug_poke_status: this plan has no status word");
+  void* ws = nullptr;
+  if (int rc = workspace_for_current_device(&ws)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  IB200_CUDA_OK(cudaMemcpyAsync(static_cast<char*>(ws) + status, &code, sizeof(code), cudaMemcpyHostToDevice, s));
+  IB200_CUDA_OK(cudaStreamSynchronize(s));  // `code` is a stack variable
+  return IB200_OK;
+}
 
 int ib200_plan_launch_noalloc(const ib200_plan_t* plan, void* const* args, int n_args, void* stream) {
   if (!plan) return ib200::fail(IB200_ERR_INVALID, "plan_launch_noalloc: null plan");

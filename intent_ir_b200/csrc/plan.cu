@@ -2794,9 +2794,17 @@ int ib200_plan_num_launches(const ib200_plan_t* plan) {
   return n;
 }
 
+int ib200_plan_check_status(const ib200_plan_t* plan, const void* workspace, void* stream) {
+  if (!plan) return fail(IB200_ERR_INVALID, "plan_check_status: null plan");
+  if (!plan->uses_status) return IB200_OK;  // no kernel of this plan has a bounded wait
+  if (!workspace) return fail(IB200_ERR_INVALID, "plan_check_status: this plan keeps its status word in the workspace; pass it");
+  return ib200_check_status(reinterpret_cast<const int32_t*>(static_cast<const char*>(workspace) + plan->status_offset), stream);
+}
+
 int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, void* workspace, size_t workspace_bytes, void* stream) {
   if (!plan) return fail(IB200_ERR_INVALID, "plan_launch: null plan");
   if (n_args != (int)plan->arg_names.size()) return fail(IB200_ERR_INVALID, "plan_launch: expected " + std::to_string(plan->arg_names.size()) + " arguments");
+  if (n_args > 0 && !args) return fail(IB200_ERR_INVALID, "plan_launch: null argument array");
   if (plan->workspace_bytes > 0 && (!workspace || workspace_bytes < plan->workspace_bytes))
     return fail(IB200_ERR_BUFFER, "plan_launch: workspace of " + std::to_string(plan->workspace_bytes) + " bytes needed");
   if (plan->workspace_bytes > 0 && (reinterpret_cast<uintptr_t>(workspace) & 255u)) return fail(IB200_ERR_INVALID, "plan_launch: workspace must be 256-byte aligned");

@@ -19,12 +19,15 @@ def register(backend: Any) -> None:
 
 
 def get(name: str) -> Any:
+    cause = None
     if name not in _REGISTRY and name in _LAZY:
         try:
             importlib.import_module(_LAZY[name])
-        except Exception:
-            pass  # the KeyError below is the uniform failure
+        except Exception as e:  # the KeyError below is the uniform failure; it carries the reason
+            cause = e
     if name not in _REGISTRY:
+        if cause is not None:
+            raise KeyError(f"backend not registered: {name} (importing {_LAZY[name]} failed: {type(cause).__name__}: {cause})") from cause
         raise KeyError(f"backend not registered: {name}")
     return _REGISTRY[name]
 

@@ -154,18 +154,27 @@ def graph_lowered(lowered: B200LoweredKernel, tensors: Mapping[str, torch.Tensor
 
 
 def check_plan_status(lowered: B200LoweredKernel) -> None:
-    """After a synchronise: raise if a bounded device-side wait expired during the plan."""
+    """Synchronise the current stream and raise if a bounded device-side wait expired during the plan
+    (``ib200_plan_check_status``); the status word is cleared so that the workspace can be used again.
+    Raises as well when the plan's scratch has left the cache since it ran: its status can then no longer
+    be read, and saying nothing would hide a failure."""
     if lowered.status_offset < 0:
         return
+    found = False
     for key, ws in list(_WORKSPACES.items()):
         if key[0] != lowered.io_spec["plan_id"]:
             continue
-        base = _aligned_ptr(ws) - ws.data_ptr() + lowered.status_offset
-        word = ws[base: base + 4].view(torch.int32)
-        code = int(word.item())
-        if code != 0:
-            word.zero_()
-            raise B200RuntimeError(f"B200 kernel gave up on a bounded device-side wait (site {code})")
+        found = True
+        with torch.cuda.device(ws.device):
+            rc = _lib.load().ib200_plan_check_status(lowered.plan.ptr, _aligned_ptr(ws), torch.cuda.current_stream().cuda_stream)
+        if rc != _lib.OK:
+            msg = _lib.last_error()
+            base = _aligned_ptr(ws) - ws.data_ptr() + lowered.status_offset
+            ws[base: base + 4].zero_()
+            raise B200RuntimeError(f"B200 kernel gave up on a bounded device-side wait: {msg} (status {rc})")
+    if not found:
+        raise B200RuntimeError("the status of this plan can no longer be read: its scratch buffer was released "
+                               "(more than 256 other plans ran since); check a plan before running that many others")
 
 
 def _to_device(name: str, arr: np.ndarray, dtype: torch.dtype, device) -> torch.Tensor:
@@ -178,7 +187,11 @@ def _to_device(name: str, arr: np.ndarray, dtype: torch.dtype, device) -> torch.
     return t.contiguous()
 
 
-def run_lowered(lowered: B200LoweredKernel, inputs_np: Mapping[str, np.ndarray], device: str = "cuda") -> Dict[str, np.ndarray]:
+def run_lowered(lowered: B200LoweredKernel, inputs_np: Mapping[str, np.ndarray], device: str = "cuda",
+                out: Optional[Mapping[str, np.ndarray]] = None) -> Dict[str, np.ndarray]:
+    """Host arrays in, host arrays out (inputs and outputs in one dict), synchronous.  A result whose name
+    is in ``out`` with the declared shape (16-bit floats widened to float32) is copied from the device
+    straight into that array, which is then the one returned."""
     _require_cuda()
     specs = lowered.io_spec["tensors"]
     out_set = set(lowered.output_names)
@@ -216,7 +229,13 @@ def run_lowered(lowered: B200LoweredKernel, inputs_np: Mapping[str, np.ndarray],
     for name, t in outs.items():
         if t.dtype in (torch.bfloat16, torch.float16):
             t = t.float()  # numpy has no bfloat16; values are exactly representable in float32
-        result[name] = t.detach().cpu().numpy()
+        dst = out.get(name) if out else None
+        if dst is not None and dst.flags.c_contiguous and dst.flags.writeable and tuple(dst.shape) == tuple(t.shape) \
+                and torch.from_numpy(dst).dtype == t.dtype:
+            torch.from_numpy(dst).copy_(t)
+            result[name] = dst
+        else:
+            result[name] = t.detach().cpu().numpy()
     return result
 
 

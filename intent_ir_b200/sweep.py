@@ -35,7 +35,8 @@ import numpy as np
 
 from .backend import round_to_bf16
 
-__all__ = ["SweepCase", "generate_sweep_cases", "split_rows", "run_sweep", "merge_records", "reference_checker", "KINDS"]
+__all__ = ["SweepCase", "generate_sweep_cases", "split_rows", "run_sweep", "merge_records", "reference_checker", "KINDS",
+           "CheckerPool", "partition_cases", "estimate_cost"]
 
 EDGE_SIZES = (1, 2, 3, 7, 8, 15, 16, 17, 31, 32, 33)
 KINDS = ("reduce_any", "reduce_sum", "reduce_max", "softmax", "layernorm", "groupnorm", "matmul_bias_relu", "chain")
@@ -375,72 +376,410 @@ def reference_checker() -> Tuple[Callable, Callable, type]:
     return dr.run_diff, tol.infer_tolerances, gc.TestCase
 
 
-def _done_ids(path: str) -> set:
-    done = set()
+def _load_shard(path: str) -> Dict[int, Dict[str, Any]]:
+    """Records already in a JSONL shard, by case id (a torn last line is ignored)."""
+    done: Dict[int, Dict[str, Any]] = {}
     if os.path.exists(path):
         with open(path) as f:
             for line in f:
                 try:
-                    done.add(int(json.loads(line)["case_id"]))
+                    rec = json.loads(line)
+                    done[int(rec["case_id"])] = rec
                 except Exception:
                     pass
     return done
 
 
+# CPU milliseconds per million elements for input generation + interpreter + comparison, measured with the
+# numpy checker on one host thread; only the ratios matter (they order and balance the work)
+_COST_MS_PER_MEL = {"reduce_any": 22.0, "reduce_sum": 16.0, "reduce_max": 16.0, "softmax": 52.0, "chain": 85.0, "layernorm": 78.0,
+                    "groupnorm": 46.0, "rmsnorm": 60.0, "layernorm_residual": 95.0, "masked_softmax": 60.0, "rope": 50.0,
+                    "dropout": 120.0, "image": 40.0}
+
+
+def estimate_cost(case: SweepCase) -> float:
+    """Rough host cost of one case in milliseconds (the sweep is bound by the CPU checker)."""
+    s = case.shapes
+    if case.kind == "matmul_bias_relu":
+        m, n, k = s["M"], s["N"], s["K"]
+        return 0.3 + 16.0 * (m * k + k * n) / 1e6 + 30.0 * m * n / 1e6 + m * n * k / 3e7  # BLAS on one thread: ~60 GFLOP/s
+    return 0.3 + _COST_MS_PER_MEL.get(case.kind, 60.0) * case.elements / 1e6
+
+
+def partition_cases(cases: Sequence[SweepCase], world: int, how: str = "mod") -> List[List[int]]:
+    """Positions of ``cases`` per rank.  ``"mod"``: case i -> rank i % world.  ``"lpt"``: longest
+    estimated case first onto the least loaded rank (ties by rank), which every rank computes
+    identically from the case list alone — no communication."""
+    world = max(1, int(world))
+    if how == "mod":
+        return [list(range(r, len(cases), world)) for r in range(world)]
+    if how != "lpt":
+        raise ValueError(f"unknown partition {how!r}")
+    order = sorted(range(len(cases)), key=lambda i: (-estimate_cost(cases[i]), i))
+    load = [0.0] * world
+    parts: List[List[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda q: (load[q], q))
+        parts[r].append(i)
+        load[r] += estimate_cost(cases[i])
+    return parts
+
+
+def _check_case(case: SweepCase, runner_of: Callable, diff_fn: Callable, tolerances_fn: Callable, case_type: type,
+                intent_from_json: Callable, rank: int) -> Dict[str, Any]:
+    """One case through the verifier: ``runner_of(intent, case, timing)`` gives the ``run_ref_fn`` handed
+    to ``diff_fn`` (it may record the device's share of its time as ``timing["device"]``).  Every failure
+    (lowering, device, checker) becomes a failed record."""
+    t0 = time.perf_counter()
+    rec: Dict[str, Any] = {"case_id": case.case_id, "kind": case.kind, "dtype": case.dtype, "shapes": case.shapes, "rank": rank}
+    try:
+        intent = intent_from_json(case.intent)
+        timing: Dict[str, float] = {}
+        backend_fn = runner_of(intent, case, timing)
+
+        def timed(c, _fn=backend_fn, _t=timing):
+            t = time.perf_counter()
+            try:
+                return _fn(c)
+            finally:
+                _t["gpu"] = time.perf_counter() - t
+
+        tol = tolerances_fn(intent).to_dict()
+        diffs, _ = diff_fn(intent, timed, [case_type(shapes=dict(case.shapes), dtypes={}, seed=case.seed)], tolerances=tol)
+        d = diffs[0]
+        rec.update(ok=bool(d.ok), summary=d.summary, max_abs=float(d.max_abs_err) if np.isfinite(d.max_abs_err) else None,
+                   max_rel=float(d.max_rel_err) if np.isfinite(d.max_rel_err) else None, t_gpu=timing.get("device", timing.get("gpu")))
+    except Exception as e:  # lowering, GPU or checker failure: a failed record, not a dead sweep
+        rec.update(ok=False, summary=f"{type(e).__name__}: {e}"[:300], max_abs=None, max_rel=None, t_gpu=None)
+    rec["t_total"] = time.perf_counter() - t0
+    return rec
+
+
+# ---- checker processes ------------------------------------------------------------------------------------
+#
+# The sweep is bound by the host: generating a case's inputs, interpreting the graph with numpy and comparing
+# in float64 cost 10-100 ms per case, the GPU run well under one.  With ``workers`` > 0 a rank therefore keeps
+# its GPU in one process (the one that called run_sweep) and does the host work in ``workers`` child processes:
+# a child generates the inputs into a shared-memory arena, asks the parent to run the plan on them (the parent
+# uploads straight from the arena and downloads the results into it), then interprets and compares while the
+# parent serves the other children.  The verifier is unchanged: each child calls ``diff_fn(intent, run_ref_fn,
+# [case])`` with a ``run_ref_fn`` that happens to do its device work in the parent.
+
+_NP_OUT = {"f32": np.float32, "bf16": np.float32, "f16": np.float32, "f64": np.float64, "i32": np.int32, "i64": np.int64,
+           "i8": np.int8, "i16": np.int16, "u8": np.uint8, "bool": np.bool_, "i1": np.bool_}
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class _Arena:
+    """A shared-memory block owned by one checker process, grown on demand."""
+
+    def __init__(self):
+        self.shm = None
+
+    def ensure(self, nbytes: int):
+        from multiprocessing import shared_memory
+
+        if self.shm is None or self.shm.size < nbytes:
+            self.close()
+            self.shm = shared_memory.SharedMemory(create=True, size=max(_align(nbytes, 1 << 20), 8 << 20))
+        return self.shm
+
+    def close(self):
+        if self.shm is not None:
+            try:
+                self.shm.close()
+                self.shm.unlink()
+            except Exception:
+                pass
+            self.shm = None
+
+
+def _remote_runner(conn, arena: _Arena, intent, case: SweepCase, timing: Optional[Dict[str, float]] = None):
+    """``run_ref_fn`` for one case, run inside a checker process: inputs are generated here, the device
+    work happens in the parent."""
+    from .bindings import derive_bindings
+
+    def run(c):
+        inputs = case_inputs(case)
+        if getattr(c, "inputs", None):
+            inputs.update({k: np.asarray(v) for k, v in c.inputs.items()})
+        inputs = {k: np.ascontiguousarray(v) if np.ndim(v) else np.asarray(v) for k, v in inputs.items()}
+        bind = derive_bindings(dict(c.shapes))
+        layout_in, layout_out, off = [], [], 0
+        for k, v in inputs.items():
+            layout_in.append((k, v.dtype.str, tuple(v.shape), off))
+            off = _align(off + max(v.nbytes, 1))
+        for name in intent.outputs:
+            t = intent.tensors[name]
+            shape = tuple(int(bind[d.value]) if d.kind == "sym" else int(d.value) for d in t.shape)
+            dt = np.dtype(_NP_OUT[t.dtype])
+            layout_out.append((name, dt.str, shape, off))
+            off = _align(off + max(int(np.prod(shape, dtype=np.int64)) * dt.itemsize, 1))
+        shm = arena.ensure(off)
+        for (k, _, shape, o), v in zip(layout_in, inputs.values()):
+            np.ndarray(shape, v.dtype, buffer=shm.buf, offset=o)[...] = v
+        conn.send(("run", case.case_id, case.intent, dict(c.shapes), shm.name, layout_in, layout_out))
+        reply = conn.recv()
+        if reply[0] != "ok":
+            raise RuntimeError(reply[1])
+        if timing is not None:
+            timing["device"] = reply[2]
+        result = dict(inputs)
+        for name, dts, shape, o in layout_out:
+            sent = reply[1].get(name)
+            result[name] = sent if sent is not None else np.ndarray(shape, np.dtype(dts), buffer=shm.buf, offset=o)
+        return result
+
+    return run
+
+
+def _checker_main(conn, checker, intent_from_json, rank: int, cpus: Optional[Sequence[int]]) -> None:
+    """Body of a checker process: cases in, records out, device work delegated to the parent."""
+    if cpus:
+        try:
+            os.sched_setaffinity(0, set(cpus))
+        except Exception:
+            pass
+    diff_fn, tolerances_fn, case_type = checker
+    arena = _Arena()
+    try:
+        conn.send(("ready",))
+        while True:
+            msg = conn.recv()
+            if msg[0] == "stop":
+                break
+            case = msg[1]
+            rec = _check_case(case, lambda intent, cs, timing: _remote_runner(conn, arena, intent, cs, timing), diff_fn, tolerances_fn,
+                              case_type, intent_from_json, rank)
+            conn.send(("done", rec))
+    except (EOFError, KeyboardInterrupt):
+        pass
+    finally:
+        arena.close()
+
+
+class _Served:
+    """Parent-side view of the arenas of the checker processes (attached once per block)."""
+
+    def __init__(self):
+        self.blocks: Dict[str, Any] = {}
+        self.owner: Dict[str, Any] = {}
+
+    def views(self, name: str, layout, owner=None):
+        from multiprocessing import shared_memory
+
+        shm = self.blocks.get(name)
+        if shm is None:
+            shm = shared_memory.SharedMemory(name=name)
+            self.blocks[name] = shm
+            self.owner[name] = owner
+        return {k: np.ndarray(shape, np.dtype(dts), buffer=shm.buf, offset=o) for k, dts, shape, o in layout}
+
+    def drop_owner(self, owner):
+        """The process behind ``owner`` is gone without cleaning up: remove its blocks."""
+        for name in [n for n, o in self.owner.items() if o is owner]:
+            shm = self.blocks.pop(name)
+            del self.owner[name]
+            try:
+                shm.close()
+                shm.unlink()
+            except Exception:
+                pass
+
+    def close(self):
+        for shm in self.blocks.values():
+            try:
+                shm.close()
+            except Exception:
+                pass
+        self.blocks.clear()
+        self.owner.clear()
+
+
+class _Shapes:
+    """The part of a verifier ``TestCase`` a runner reads."""
+
+    def __init__(self, shapes, seed=0):
+        self.shapes, self.seed, self.inputs, self.dtypes = shapes, seed, None, {}
+
+
+def _device_run_b200(intent_json, shapes, ins: Dict[str, np.ndarray], outs: Dict[str, np.ndarray]) -> Dict[str, Any]:
+    """Parent side of one request on the B200 backend: lower (cached), upload from the arena, launch,
+    download into the arena."""
+    from .bindings import derive_bindings
+    from .lowering import lower_intent_to_b200_kernel
+    from .runtime import run_lowered
+
+    lowered = lower_intent_to_b200_kernel(intent_json, shape_bindings=derive_bindings(dict(shapes)))
+    return run_lowered(lowered, ins, out=outs)
+
+
+class CheckerPool:
+    """``workers`` checker processes of one rank and the loop that serves their device requests."""
+
+    def __init__(self, workers: int, checker: Tuple[Callable, Callable, type], intent_from_json: Callable, rank: int = 0,
+                 cpus: Optional[Sequence[int]] = None):
+        import multiprocessing as mp
+
+        ctx = mp.get_context("spawn")  # never fork a process that holds a CUDA context
+        self.rank, self.procs, self.conns = rank, [], []
+        for _ in range(max(1, int(workers))):
+            a, b = ctx.Pipe()
+            p = ctx.Process(target=_checker_main, args=(b, checker, intent_from_json, rank, list(cpus) if cpus else None), daemon=True)
+            p.start()
+            b.close()
+            self.procs.append(p)
+            self.conns.append(a)
+        for c in self.conns:  # imports done, ready for cases
+            if not c.poll(120) or c.recv()[0] != "ready":
+                raise RuntimeError("a checker process did not start")
+        self.served = _Served()
+
+    def run(self, cases: Sequence[SweepCase], device_run: Callable, on_record: Optional[Callable] = None) -> List[Dict[str, Any]]:
+        """Check ``cases`` (handed out in the given order, one in flight per process); returns the records
+        in that order.  ``device_run(intent_json, shapes, ins, outs)`` runs the graph on arrays that live in
+        a child's arena and returns the outputs it could not write in place (or all of them)."""
+        from multiprocessing.connection import wait
+
+        todo = list(range(len(cases)))[::-1]
+        inflight: Dict[Any, int] = {}
+        recs: Dict[int, Dict[str, Any]] = {}
+        live = list(self.conns)
+
+        def feed(c):
+            if todo:
+                i = todo.pop()
+                inflight[c] = i
+                c.send(("case", cases[i]))
+
+        for c in live:
+            feed(c)
+        while inflight:
+            for c in wait(list(inflight)):
+                i = inflight[c]
+                try:
+                    msg = c.recv()
+                except (EOFError, OSError):  # the process died: its case fails, the others carry on
+                    case = cases[i]
+                    recs[i] = {"case_id": case.case_id, "kind": case.kind, "dtype": case.dtype, "shapes": case.shapes, "rank": self.rank,
+                               "ok": False, "summary": "checker process died", "max_abs": None, "max_rel": None, "t_gpu": None, "t_total": None}
+                    if on_record:
+                        on_record(recs[i])
+                    del inflight[c]
+                    live.remove(c)
+                    self.served.drop_owner(c)
+                    if not live and todo:
+                        raise RuntimeError("every checker process died")
+                    continue
+                if msg[0] == "run":
+                    _, _, intent_json, shapes, shm_name, layout_in, layout_out = msg
+                    try:
+                        t = time.perf_counter()
+                        ins = self.served.views(shm_name, layout_in, c)
+                        outs = self.served.views(shm_name, layout_out, c)
+                        extra = device_run(intent_json, shapes, ins, outs) or {}
+                        send = {}
+                        for k, v in extra.items():
+                            if k in outs and v is not outs[k]:
+                                v = np.asarray(v)
+                                if v.shape == outs[k].shape and v.dtype == outs[k].dtype:
+                                    outs[k][...] = v
+                                elif v.size == outs[k].size and v.dtype == outs[k].dtype:
+                                    outs[k][...] = v.reshape(outs[k].shape)
+                                else:
+                                    send[k] = v  # not what the graph declares: the checker should see it as it is
+                        c.send(("ok", send, time.perf_counter() - t))
+                    except Exception as e:
+                        c.send(("err", f"{type(e).__name__}: {e}"[:300]))
+                elif msg[0] == "done":
+                    recs[i] = msg[1]
+                    if on_record:
+                        on_record(msg[1])
+                    del inflight[c]
+                    feed(c)
+        return [recs[i] for i in range(len(cases))]
+
+    def close(self):
+        for c in self.conns:
+            try:
+                c.send(("stop",))
+            except Exception:
+                pass
+        for p in self.procs:
+            p.join(timeout=5)
+            if p.is_alive():
+                p.terminate()
+        self.served.close()
+        for c in self.conns:
+            c.close()
+
+
 def run_sweep(cases: Iterable[SweepCase], *, diff_fn: Callable, tolerances_fn: Callable, case_type: type,
               rank: int = 0, world: int = 1, out_dir: Optional[str] = None, make_runner: Optional[Callable] = None,
-              intent_from_json: Optional[Callable] = None) -> List[Dict[str, Any]]:
-    """Run this rank's share of ``cases`` (case i -> rank i % world, by position) and return
-    its records.  ``make_runner(intent, input_gen)`` defaults to the B200 backend's
-    ``make_run_ref_fn``; ``intent_from_json`` to this package's ``IntentFunction``."""
-    if make_runner is None:
-        from .backend import make_run_ref_fn as make_runner
+              intent_from_json: Optional[Callable] = None, workers: int = 0, partition: str = "mod",
+              pool: Optional[CheckerPool] = None, cpus: Optional[Sequence[int]] = None) -> List[Dict[str, Any]]:
+    """Run this rank's share of ``cases`` and return its records, those found in the rank's shard file
+    from an earlier run included (``"resumed": True``).  ``partition``: see :func:`partition_cases`.
+    ``make_runner(intent, input_gen)`` defaults to the B200 backend's ``make_run_ref_fn``;
+    ``intent_from_json`` to this package's ``IntentFunction``.
+
+    ``workers`` = 0 checks every case in this process, one after the other.  ``workers`` > 0 (or a
+    ready ``pool``) keeps the device in this process and checks in that many child processes, the
+    largest cases first; the checker functions and ``intent_from_json`` must then be importable
+    (module-level) because they travel to the children by name."""
     if intent_from_json is None:
         from .ir import IntentFunction
 
         intent_from_json = IntentFunction.from_json_dict
-    shard = None
-    done: set = set()
+    cases = list(cases)
+    mine = [cases[i] for i in partition_cases(cases, world, partition)[rank]]
+    shard, done = None, {}
     if out_dir:
         os.makedirs(out_dir, exist_ok=True)
         shard = os.path.join(out_dir, f"sweep.rank{rank}.jsonl")
-        done = _done_ids(shard)
-    records: List[Dict[str, Any]] = []
+        done = _load_shard(shard)
     fh = open(shard, "a") if shard else None
+
+    def on_record(rec):
+        if fh:
+            fh.write(json.dumps(rec) + "\n")
+            fh.flush()
+
+    fresh = [c for c in mine if c.case_id not in done]
     try:
-        for pos, case in enumerate(cases):
-            if pos % world != rank or case.case_id in done:
-                continue
-            t0 = time.perf_counter()
-            rec: Dict[str, Any] = {"case_id": case.case_id, "kind": case.kind, "dtype": case.dtype, "shapes": case.shapes, "rank": rank}
+        if workers > 0 or pool is not None:
+            if make_runner is None:
+                device_run = _device_run_b200
+            else:
+                def device_run(intent_json, shapes, ins, outs, _mk=make_runner):
+                    intent = intent_from_json(intent_json)
+                    return {k: v for k, v in _mk(intent, lambda c: ins)(_Shapes(shapes)).items() if k in outs}
+            own = pool is None
+            if own:
+                pool = CheckerPool(workers, (diff_fn, tolerances_fn, case_type), intent_from_json, rank, cpus)
             try:
-                intent = intent_from_json(case.intent)
-                timing: Dict[str, float] = {}
-                backend_fn = make_runner(intent, lambda c, _case=case: case_inputs(_case))
-
-                def timed(c, _fn=backend_fn, _t=timing):
-                    t = time.perf_counter()
-                    try:
-                        return _fn(c)
-                    finally:
-                        _t["gpu"] = time.perf_counter() - t
-
-                tol = tolerances_fn(intent).to_dict()
-                diffs, _ = diff_fn(intent, timed, [case_type(shapes=dict(case.shapes), dtypes={}, seed=case.seed)], tolerances=tol)
-                d = diffs[0]
-                rec.update(ok=bool(d.ok), summary=d.summary, max_abs=float(d.max_abs_err) if np.isfinite(d.max_abs_err) else None,
-                           max_rel=float(d.max_rel_err) if np.isfinite(d.max_rel_err) else None, t_gpu=timing.get("gpu"))
-            except Exception as e:  # lowering, GPU or checker failure: a failed record, not a dead sweep
-                rec.update(ok=False, summary=f"{type(e).__name__}: {e}"[:300], max_abs=None, max_rel=None, t_gpu=None)
-            rec["t_total"] = time.perf_counter() - t0
-            records.append(rec)
-            if fh:
-                fh.write(json.dumps(rec) + "\n")
-                fh.flush()
+                order = sorted(range(len(fresh)), key=lambda i: (-estimate_cost(fresh[i]), i))
+                got = pool.run([fresh[i] for i in order], device_run, on_record)
+                new = {fresh[i].case_id: r for i, r in zip(order, got)}
+            finally:
+                if own:
+                    pool.close()
+        else:
+            if make_runner is None:
+                from .backend import make_run_ref_fn as make_runner
+            new = {}
+            for case in fresh:
+                rec = _check_case(case, lambda intent, cs, timing: make_runner(intent, lambda c, _cs=cs: case_inputs(_cs)), diff_fn,
+                                  tolerances_fn, case_type, intent_from_json, rank)
+                new[case.case_id] = rec
+                on_record(rec)
     finally:
         if fh:
             fh.close()
-    return records
+    return [new[c.case_id] if c.case_id in new else dict(done[c.case_id], resumed=True) for c in mine]
 
 
 def merge_records(per_rank: Sequence[Sequence[Dict[str, Any]]]) -> Dict[str, Any]:

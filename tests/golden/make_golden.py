@@ -9,6 +9,7 @@ It imports the reference's own ``verify.interpreter.execute_intent``,
 ``verify.gen_cases.generate_cases`` and records what THEY return, so that the CPU oracle
 under ``oracle/`` can be checked against the reference on machines that do not have it:
 
+* ``../../intent_ir_b200/config_graphs.json`` — the subset of ``intents.json`` the benchmark runs;
 * ``intents.json``      — IntentIR graphs (``IntentFunction.to_json_dict``) of the reference's
                           deterministic kernel specs and hand-written variants, with the
                           case shapes used;
@@ -232,6 +233,11 @@ def main(ref_root: str) -> None:
 
     with open(os.path.join(HERE, "intents.json"), "w") as f:
         json.dump(graphs, f, indent=1, sort_keys=True)
+    # the benchmark configurations' graphs also ship inside the package (bench.py and the smoke entry read them there)
+    config_keys = ["any_kernel_dim", "softmax_inner", "layer_norm_persistent", "group_norm_kernel", "matmul_bias_relu2d", "add_bias2d",
+                   "rms_norm2d", "layer_norm_residual2d", "masked_softmax2d"]
+    with open(os.path.join(HERE, "..", "..", "intent_ir_b200", "config_graphs.json"), "w") as f:
+        json.dump({k: graphs[k]["intent"] for k in config_keys}, f, indent=0, sort_keys=True)
     with open(os.path.join(HERE, "verdicts.json"), "w") as f:
         json.dump(verdicts, f, indent=1, sort_keys=True)
     np.savez_compressed(os.path.join(HERE, "vectors.npz"), **vectors)

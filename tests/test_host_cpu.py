@@ -268,3 +268,25 @@ def test_reduce_scratch_sizes_and_plan_labels_agree():
             assert d["workspace_bytes"] >= need(o, r, i)
         else:
             assert label == "reduce_sum" and d["workspace_bytes"] == 0, (m, n, label)
+
+
+def test_packaged_config_graphs_are_the_recorded_reference_graphs(golden_graphs):
+    """bench.py and smoke() read their graphs from the package; they must be the graphs recorded from
+    the reference's builders, not a drifting copy."""
+    from intent_ir_b200.config_graphs import config_graph, config_graphs
+
+    packaged = config_graphs()
+    assert set(packaged) >= {"any_kernel_dim", "softmax_inner", "layer_norm_persistent", "group_norm_kernel", "matmul_bias_relu2d"}
+    for key, js in packaged.items():
+        assert js == golden_graphs[key]["intent"], key
+    config_graph("softmax_inner")["name"] = "edited"  # callers get copies
+    assert config_graph("softmax_inner")["name"] != "edited"
+    with pytest.raises(KeyError):
+        config_graph("no_such_graph")
+
+
+def test_registry_keeps_the_reason_a_builtin_backend_failed_to_import(monkeypatch):
+    monkeypatch.setitem(registry._LAZY, "broken", "intent_ir_b200.no_such_module")
+    with pytest.raises(KeyError) as e:
+        registry.get("broken")
+    assert "no_such_module" in str(e.value) and isinstance(e.value.__cause__, ImportError)

@@ -376,3 +376,59 @@ def test_reduce_ws_falls_back_without_enough_scratch_and_checks_alignment():
     assert float(out.cpu()) == float(1 << 20)
     big = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
     assert lib.ib200_reduce_ws(x.data_ptr(), out.data_ptr(), 0, 0, _lib.REDUCE_SUM, 1, 1 << 20, 1, 1.0, big.data_ptr() + 4, need, s) != _lib.OK
+
+
+# ---- the bounded-wait error path, with the failure injected from the host -------------------------------
+# No kernel is made to wait: the status word a kernel would have written is written by a host copy.
+
+def test_device_wait_status_surfaces_as_an_exception_and_clears():
+    from intent_ir_b200 import ops
+    from intent_ir_b200.errors import B200RuntimeError
+
+    a = _dev(np.ones((128, 64), np.float32)).to(torch.bfloat16)
+    b = _dev(np.ones((64, 128), np.float32)).to(torch.bfloat16)
+    ops.gemm_bias_act(a, b, None, "none")
+    ops.check_device_status()  # clean
+    ops.status_word().fill_(4)  # "epilogue waiting for a finished accumulator"
+    with pytest.raises(B200RuntimeError) as e:
+        ops.check_device_status()
+    assert "bounded device wait expired" in str(e.value) and "epilogue" in str(e.value)
+    c = ops.gemm_bias_act(a, b, None, "none")  # the word was cleared: the next launch is judged on its own
+    ops.check_device_status()
+    assert float(c.float().min()) == float(c.float().max()) == 64.0
+    lib = _lib.load()
+    word = torch.full((1,), 2, dtype=torch.int32, device="cuda")
+    assert lib.ib200_check_status(word.data_ptr(), torch.cuda.current_stream().cuda_stream) == _lib.ERR_DEVICE_WAIT
+    assert b"MMA issuer" in lib.ib200_last_error()
+    word.fill_(77)
+    assert lib.ib200_check_status(word.data_ptr(), torch.cuda.current_stream().cuda_stream) == _lib.ERR_DEVICE_WAIT
+    assert b"unknown site" in lib.ib200_last_error()
+
+
+def test_plan_status_word_surfaces_through_check_plan_status(golden_graphs):
+    import json as _json
+
+    from intent_ir_b200 import runtime
+    from intent_ir_b200.errors import B200RuntimeError
+    from intent_ir_b200.lowering import lower_intent_to_b200_kernel
+
+    js = _json.loads(_json.dumps(golden_graphs["matmul_bias_relu2d"]["intent"]))
+    for name in ("A", "B", "bias", "C"):
+        js["tensors"][name]["dtype"] = "bf16"
+    low = lower_intent_to_b200_kernel(js, shape_bindings={"M": 128, "N": 128, "K": 64})
+    assert low.status_offset >= 0
+    ins = {"A": np.ones((128, 64), np.float32), "B": np.ones((64, 128), np.float32), "bias": np.zeros(128, np.float32)}
+    assert float(runtime.run_lowered(low, ins)["C"].max()) == 64.0
+    ws = next(w for k, w in runtime._WORKSPACES.items() if k[0] == low.io_spec["plan_id"])
+    base = runtime._aligned_ptr(ws) - ws.data_ptr() + low.status_offset
+    ws[base: base + 4].view(torch.int32).fill_(1)  # "producer waiting for a free ring stage"
+    with pytest.raises(B200RuntimeError) as e:
+        runtime.check_plan_status(low)
+    assert "ring stage" in str(e.value) and "-5" in str(e.value)
+    assert float(runtime.run_lowered(low, ins)["C"].max()) == 64.0  # cleared: the plan runs and checks clean again
+    # a plan whose scratch left the cache can no longer be checked, and says so
+    for key in [k for k in runtime._WORKSPACES if k[0] == low.io_spec["plan_id"]]:
+        del runtime._WORKSPACES[key]
+    with pytest.raises(B200RuntimeError) as e:
+        runtime.check_plan_status(low)
+    assert "can no longer be read" in str(e.value)

@@ -190,13 +190,13 @@ def test_config_layernorm_8192x4096(golden_graphs):
     b = (0.1 * rng.standard_normal(N)).astype(np.float32)
     out, lowered = _lower_and_run(intent, {"M": M, "N": N}, {"in_ptr": x, "weight_ptr": w, "bias_ptr": b})
     assert [s["kernel"] for s in lowered.steps] == ["layernorm"]
-    # the oracle on a slice of the rows (rows are independent) ...
-    rows = slice(0, 512)
-    want = execute_intent(intent, {"in_ptr": x[rows], "weight_ptr": w, "bias_ptr": b}, {"M": 512, "N": N})
-    tol = {"atol": 1e-3, "rtol": 1e-3}
-    _agree(out["out_ptr"][rows], want["out_ptr"], tol, "y")
-    _agree(out["out_mean_ptr"][rows], want["out_mean_ptr"], tol, "mean")
-    _agree(out["out_rstd_ptr"][rows], want["out_rstd_ptr"], tol, "rstd")
+    # the oracle on the whole tensor, at the verifier's own tolerance for this graph ...
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, {"in_ptr": x, "weight_ptr": w, "bias_ptr": b}, {"M": M, "N": N})
+    tol = infer_tolerances(intent).to_dict()
+    _agree(out["out_ptr"], want["out_ptr"], tol, "y")
+    _agree(out["out_mean_ptr"], want["out_mean_ptr"], tol, "mean")
+    _agree(out["out_rstd_ptr"], want["out_rstd_ptr"], tol, "rstd")
     # ... and size-independent properties on all of them: (y - b)/w has zero mean and unit variance
     z = (out["out_ptr"].astype(np.float64) - b) / w
     assert np.abs(z.mean(axis=1)).max() < 1e-4
@@ -213,12 +213,12 @@ def test_config_groupnorm_32x256x4096(golden_graphs):
     b = rng.standard_normal(256, dtype=np.float32)
     out, lowered = _lower_and_run(intent, shapes, {"X": x, "W": w, "B": b})
     assert [s["kernel"] for s in lowered.steps] == ["groupnorm"]
-    sub = {"N": 2, "C": 256, "HW": 4096, "num_groups": 32}
-    want = execute_intent(intent, {"X": x[:2], "W": w, "B": b}, derive_bindings(sub))
-    tol = {"atol": 1e-3, "rtol": 1e-3}
-    _agree(out["Y"][:2], want["Y"], tol, "Y")
-    _agree(out["Mean"][:2], want["Mean"], tol, "Mean")
-    _agree(out["Rstd"][:2], want["Rstd"], tol, "Rstd")
+    with np.errstate(all="ignore"):  # the oracle on all 32 samples
+        want = execute_intent(intent, {"X": x, "W": w, "B": b}, derive_bindings(shapes))
+    tol = infer_tolerances(intent).to_dict()
+    _agree(out["Y"], want["Y"], tol, "Y")
+    _agree(out["Mean"], want["Mean"], tol, "Mean")
+    _agree(out["Rstd"], want["Rstd"], tol, "Rstd")
     x4 = x.reshape(32, 32, 8 * 4096)
     assert np.allclose(out["Mean"], x4.mean(axis=2, dtype=np.float64), atol=1e-5)
     assert np.allclose(out["Rstd"], 1.0 / np.sqrt(x4.var(axis=2, dtype=np.float64) + 1e-5), rtol=1e-4)
@@ -766,7 +766,7 @@ def test_few_long_rows_are_split_over_the_gpu(op, m, n):
     again = run_lowered(low, {"x": x})["y"]  # same scratch area a second time; same bits
     assert np.array_equal(first, again, equal_nan=True)
     if op == "reduce_sum":
-        assert np.allclose(first, want, rtol=1e-4, atol=1e-2 * np.sqrt(n) * 1e-2), float(np.abs(first - want).max())
+        _agree(first, want, infer_tolerances(intent).to_dict(), "split sum")  # what the verifier grants: 1e-3 + 1e-3 |ref|
     else:
         assert np.array_equal(first, want, equal_nan=True)
 
@@ -816,6 +816,6 @@ def test_reductions_over_leading_axes_are_split_over_the_gpu(op, shape, dims):
     again = run_lowered(low, {"x": x})["y"]
     assert first.shape == want.shape and np.array_equal(first, again, equal_nan=True)
     if op == "reduce_sum":
-        assert np.allclose(first, want, rtol=1e-4, atol=2e-2), float(np.abs(first - want).max())
+        _agree(first, want, infer_tolerances(intent).to_dict(), "split column sum")
     else:
         assert np.array_equal(first, want, equal_nan=True)

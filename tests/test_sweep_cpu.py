@@ -58,7 +58,9 @@ def test_single_rank_sweep_with_resume(tmp_path):
     recs = run_sweep(cases, out_dir=str(tmp_path), make_runner=numpy_runner, **CHECKER)
     assert len(recs) == 24 and all(r["ok"] for r in recs), [r["summary"] for r in recs if not r["ok"]]
     again = run_sweep(cases, out_dir=str(tmp_path), make_runner=numpy_runner, **CHECKER)
-    assert again == []  # every id already recorded in the shard file
+    # every id was already in the shard file: nothing runs again, and the restart still reports every case
+    assert [r["case_id"] for r in again] == [r["case_id"] for r in recs] and all(r["resumed"] and r["ok"] for r in again)
+    assert sum(1 for _ in open(tmp_path / "sweep.rank0.jsonl")) == 24
     s = merge_records([recs])
     assert s["cases"] == s["ok"] == 24 and not s["failed"]
 
@@ -135,3 +137,63 @@ def test_extra_graph_families_are_valid_and_plannable(tmp_path):
             assert kernels[-1].endswith(expected_last[c.kind]), (c.kind, c.shapes, kernels)
         else:
             assert kernels[-1] in ("softmax", "softmax+mask") or kernels[-1].startswith("rowfused"), (c.kind, kernels)
+
+
+# ---- checker processes (the pipelined form) ---------------------------------------------------------------
+
+def _exiting_from_json(js):
+    """An ``intent_from_json`` that takes its whole process down for one graph family: a host-side
+    stand-in for a checker process that dies in the middle of a sweep."""
+    if js.get("name") == "sweep_reduce_max":
+        os._exit(7)
+    return IntentFunction.from_json_dict(js)
+
+
+def test_pool_sweep_matches_the_serial_sweep(tmp_path):
+    cases = generate_sweep_cases(40, base_seed=1000, max_elements=1 << 14)
+    serial = run_sweep(cases, make_runner=numpy_runner, **CHECKER)
+    pooled = run_sweep(cases, make_runner=numpy_runner, workers=2, out_dir=str(tmp_path), **CHECKER)
+    assert [r["case_id"] for r in pooled] == [r["case_id"] for r in serial]  # records come back in case order
+    assert all(r["ok"] for r in pooled), [(r["kind"], r["summary"]) for r in pooled if not r["ok"]]
+    for a, b in zip(serial, pooled):
+        assert (a["ok"], a["max_abs"], a["max_rel"]) == (b["ok"], b["max_abs"], b["max_rel"])
+    assert sum(1 for _ in open(tmp_path / "sweep.rank0.jsonl")) == 40
+
+
+def test_pool_reports_a_wrong_device_result():
+    cases = [c for c in generate_sweep_cases(40, base_seed=1000, max_elements=1 << 12) if c.kind in ("softmax", "reduce_sum")][:6]
+
+    def off_by_a_bit(intent, input_gen):
+        inner = numpy_runner(intent, input_gen)
+
+        def run(case):
+            io = inner(case)
+            for k in intent.outputs:
+                io[k] = io[k] + np.float32(0.25)
+            return io
+
+        return run
+
+    recs = run_sweep(cases, make_runner=off_by_a_bit, workers=2, **CHECKER)
+    assert len(recs) == len(cases) and not any(r["ok"] for r in recs)
+
+
+def test_a_dead_checker_process_fails_its_case_only():
+    cases = generate_sweep_cases(60, base_seed=1000, max_elements=1 << 10)
+    victims = [c for c in cases if c.kind == "reduce_max"][:1]
+    others = [c for c in cases if c.kind != "reduce_max"][:12]
+    recs = run_sweep(others[:6] + victims + others[6:], make_runner=numpy_runner, workers=2, intent_from_json=_exiting_from_json, **CHECKER)
+    assert len(recs) == 13
+    bad = [r for r in recs if not r["ok"]]
+    assert [r["case_id"] for r in bad] == [victims[0].case_id] and bad[0]["summary"] == "checker process died"
+
+
+def test_lpt_partition_is_deterministic_and_balanced():
+    from intent_ir_b200.sweep import estimate_cost, partition_cases
+
+    cases = generate_sweep_cases(512, base_seed=1000, max_elements=1 << 22)
+    parts = partition_cases(cases, 8, "lpt")
+    assert sorted(i for p in parts for i in p) == list(range(512)) and parts == partition_cases(cases, 8, "lpt")
+    loads = [sum(estimate_cost(cases[i]) for i in p) for p in parts]
+    assert max(loads) / min(loads) < 1.02
+    assert partition_cases(cases, 4, "mod")[1][:3] == [1, 5, 9]
