@@ -154,7 +154,10 @@ def workload(name):
         esz = 4 if dt == "f32" else 2
         label = {"matmul": "matmul+bias+ReLU bf16 4096^3, f32 accumulate (configs[3])", "matmul_f16": "matmul+bias+ReLU f16 4096^3",
                  "matmul_f32": "matmul+bias+ReLU f32 4096^3 (tf32 tensor cores)"}[name]
-        return (js, {"M": n, "N": n, "K": n},
+        bind = {"M": n, "N": n, "K": n}
+        if dt == "f32":
+            bind["ALLOW_TF32"] = 1  # the reference's opt-in binding (intentir_to_cuda.py:577-578); without it f32 stays on exact FMA
+        return (js, bind,
                 lambda r: {"A": round_to_bf16(0.02 * r.standard_normal((n, n), dtype=np.float32)),
                            "B": round_to_bf16(0.02 * r.standard_normal((n, n), dtype=np.float32)),
                            "bias": round_to_bf16(0.1 * r.standard_normal(n, dtype=np.float32))},

@@ -67,6 +67,9 @@ extern "C" {
 /* ---- activation codes for ib200_gemm_bias_act ---------------------------------------- */
 #define IB200_ACT_NONE 0
 #define IB200_ACT_RELU 1
+/* ---- flags for ib200_gemm_bias_act_ws ------------------------------------------------- */
+#define IB200_GEMM_ALLOW_TF32 1 /* f32 operands may be multiplied as TF32 on the tensor cores (the reference's
+                                   ALLOW_TF32 binding, intentir_to_cuda.py:577-578); without it f32 stays exact FMA */
 
 IB200_API const char* ib200_last_error(void);
 IB200_API int ib200_version(void);
@@ -208,15 +211,31 @@ IB200_API int ib200_groupnorm(const void* x, const void* w, const void* b, void*
                     void* stream);
 
 /* C[M,N] = act(A[M,K] · B + bias[N]); fp32 accumulation.  B is [K,N] row-major, or [N,K]
- * when transpose_b != 0.  bias may be NULL.  in_dtype (A and B) and out_dtype (C) are
- * IB200_BF16 or IB200_F32; bias has out_dtype.  bf16 inputs whose K and N are multiples of 8 run on
- * the tcgen05 / TMEM tensor-core path; everything else runs on a tiled fp32 FMA kernel.
+ * when transpose_b != 0.  bias may be NULL.  in_dtype (A and B) is IB200_BF16, IB200_F16 or
+ * IB200_F32; out_dtype (C) is in_dtype or IB200_F32; bias has out_dtype.  16-bit inputs whose K
+ * and N are multiples of 8 run on the tcgen05 / TMEM tensor-core path; everything else runs on a
+ * tiled fp32 FMA kernel.
  * `status` is a caller-provided device int32 (zero it once); the tensor-core kernel sets it
  * non-zero if one of its bounded waits runs out (read it with ib200_check_status).  May be
  * NULL for the FMA path only.  Replaces kernels/wmma_matmul.cuh and matmul_fallback.cuh. */
 IB200_API int ib200_gemm_bias_act(const void* a, const void* b, const void* bias, void* c, int in_dtype,
                         int out_dtype, int64_t m, int64_t n, int64_t k, int transpose_b, int act,
                         int32_t* status, void* stream);
+
+/* The same product with options and scratch memory.  `flags`: IB200_GEMM_ALLOW_TF32 sends f32
+ * operands (K, N multiples of 8) to the tensor cores as TF32, which is what the reference's
+ * opt-in wmma kernel does (kernels/wmma_matmul.cuh:124-563); products then carry 10-bit
+ * mantissas, inside the verifier's matmul tolerance for inputs of moderate dynamic range.
+ * `scratch` (256-byte aligned, ib200_gemm_scratch_bytes(...) bytes, contents irrelevant) lets the
+ * tensor-core kernel cut the tiles of a last, mostly empty round of tiles along K and add the
+ * slices up in a fixed order; with scratch == NULL every tile runs whole, as in
+ * ib200_gemm_bias_act.  A TF32 product whose B is [K,N] transposes B into the scratch first
+ * (the tensor-core kernel takes 32-bit operands K-major only) and stays on the FMA kernel
+ * when the scratch is too small for that.  Plans take the scratch from their workspace. */
+IB200_API int ib200_gemm_bias_act_ws(const void* a, const void* b, const void* bias, void* c, int in_dtype,
+                           int out_dtype, int64_t m, int64_t n, int64_t k, int transpose_b, int act, int flags,
+                           void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+IB200_API size_t ib200_gemm_scratch_bytes(int in_dtype, int out_dtype, int64_t m, int64_t n, int64_t k, int transpose_b, int flags);
 
 /* Copy the device status word to the host (this call DOES synchronise `stream`) and map a
  * non-zero word to IB200_ERR_DEVICE_WAIT.  With status == NULL it checks the library's own word,

@@ -17,6 +17,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_BUFFER, ERR_DEVICE_WAIT = 0, -1,
 F32, BF16, F16, I32, I64, BOOL, U8, I8, I16, F64 = range(10)
 REDUCE_SUM, REDUCE_MAX, REDUCE_ANY = 0, 1, 2
 ACT_NONE, ACT_RELU = 0, 1
+GEMM_ALLOW_TF32 = 1
 
 DTYPE_CODE = {"f32": F32, "bf16": BF16, "f16": F16, "i32": I32, "i64": I64, "bool": BOOL, "i1": BOOL,
               "u8": U8, "i8": I8, "i16": I16, "f64": F64}
@@ -57,6 +58,8 @@ SIGNATURES = {
     "ib200_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _f, _vp]),
     "ib200_groupnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _f, _vp]),
     "ib200_gemm_bias_act": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _i, _i, _vp, _vp]),
+    "ib200_gemm_bias_act_ws": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _i, _i, _i, _vp, _sz, _vp, _vp]),
+    "ib200_gemm_scratch_bytes": (_sz, [_i, _i, _i64, _i64, _i64, _i, _i]),
     "ib200_check_status": (_i, [_vp, _vp]),
     "ib200_transpose2d": (_i, [_vp, _vp, _i, _i64, _i64, _vp]),
 }

@@ -84,6 +84,18 @@ int ib200_gemm_bias_act(const void* a, const void* b, const void* bias, void* c,
   return launch_gemm(a, b, bias, c, in_dtype, out_dtype, m, n, k, transpose_b, act, status, static_cast<cudaStream_t>(stream));
 }
 
+int ib200_gemm_bias_act_ws(const void* a, const void* b, const void* bias, void* c, int in_dtype, int out_dtype, int64_t m,
+                           int64_t n, int64_t k, int transpose_b, int act, int flags, void* scratch, size_t scratch_bytes,
+                           int32_t* status, void* stream) {
+  if (scratch && (reinterpret_cast<uintptr_t>(scratch) & 255u)) return fail(IB200_ERR_INVALID, "gemm_bias_act_ws: scratch must be 256-byte aligned");
+  return launch_gemm(a, b, bias, c, in_dtype, out_dtype, m, n, k, transpose_b, act, status, static_cast<cudaStream_t>(stream), flags,
+                     scratch, scratch_bytes);
+}
+
+size_t ib200_gemm_scratch_bytes(int in_dtype, int out_dtype, int64_t m, int64_t n, int64_t k, int transpose_b, int flags) {
+  return gemm_scratch_bytes(in_dtype, out_dtype, m, n, k, flags, transpose_b);
+}
+
 int ib200_check_status(const int32_t* status, void* stream) {
   if (!status) status = norm_default_status();  // the word used by the direct normalisation entry points
   if (!status) return fail(IB200_ERR_CUDA, "check_status: no status word on this device");

@@ -57,9 +57,13 @@ int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float
                      int64_t affine_period, float eps, cudaStream_t s, int32_t* status = nullptr, bool centre = true,
                      const void* res = nullptr, const void* res_bias = nullptr);
 int32_t* norm_default_status();
+// flags: IB200_GEMM_ALLOW_TF32.  With scratch (256-byte aligned, gemm_scratch_bytes says how much) the tiles of a
+// last, mostly empty round of the tensor-core kernel are split along K; without it they run whole.
 int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_dtype, int out_dtype,
                 int64_t m, int64_t n, int64_t k, int transpose_b, int act, int32_t* status,
-                cudaStream_t s);
+                cudaStream_t s, int flags = 0, void* scratch = nullptr, size_t scratch_bytes = 0);
+size_t gemm_scratch_bytes(int in_dtype, int out_dtype, int64_t m, int64_t n, int64_t k, int flags, int transpose_b);
+bool gemm_uses_tensor_cores(int in_dtype, int out_dtype, int64_t n, int64_t k, int flags);
 int launch_transpose2d(const void* x, void* out, int elem_bytes, int64_t rows, int64_t cols,
                        cudaStream_t s);
 struct GatherArgs {

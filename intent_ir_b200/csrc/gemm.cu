@@ -1,21 +1,32 @@
 // C[M,N] = act(A[M,K] · B + bias), fp32 accumulation.
 //
-// Tensor-core path (bf16 operands; K and N multiples of 8): a persistent, warp-specialised
-// sm_100a kernel, one CTA per SM, 128 x BN output tiles (BN = 256, 192 or 128, chosen per
-// problem to waste the fewest SM-waves), K in blocks of 64:
+// Tensor-core path (bf16 or f16 operands, and f32 operands as TF32 when the caller allows it; K and
+// N multiples of 8): a persistent, warp-specialised sm_100a kernel, one CTA per SM, 128 x BN
+// output tiles (BN = 256, 192 or 128, chosen per problem to waste the fewest SM-waves), K in
+// blocks of 128 bytes (64 16-bit or 32 32-bit elements):
 //   warp 0   : TMA producer — cp.async.bulk.tensor (128-byte swizzle) into a 4..6-stage
 //              shared-memory ring, completion on mbarriers;
-//   warp 1   : allocates tensor memory and issues tcgen05.mma (cta_group::1, kind::f16,
-//              M=128 N=BN K=16) from one elected thread; tcgen05.commit releases ring
+//   warp 1   : allocates tensor memory and issues tcgen05.mma (cta_group::1, kind::f16 with
+//              M=128 N=BN K=16, or kind::tf32 with K=8) from one elected thread; tcgen05.commit releases ring
 //              stages back to the producer and publishes finished accumulators;
 //   warps 2-5: epilogue — tcgen05.ld of the fp32 accumulator (one row per thread), + bias,
 //              activation, conversion, 16-byte stores.
 // Two accumulators of up to 256 columns share the 512 TMEM columns, so the epilogue of tile i overlaps
-// the main loop of tile i+1.  A is K-major; B is read as stored: [K,N] row-major is the
+// the main loop of tile i+1.  A is K-major; 16-bit B is read as stored: [K,N] row-major is the
 // MN-major operand form (the descriptor's major bit), [N,K] (transpose_b) is K-major — no
-// transposition pass either way.  Every mbarrier wait is bounded: on expiry the thread
+// transposition pass either way.  A 32-bit (TF32) B is taken K-major only: a [K,N] one is
+// first transposed into scratch (the MN-major form of 32-bit operands wants a shared-memory
+// layout this kernel does not produce).  Every mbarrier wait is bounded: on expiry the thread
 // records where it gave up in *status and the kernel drains and exits, so a wrong
 // descriptor can produce a wrong answer or an error code, never a hung GPU.
+//
+// Tail split: tiles are handed out round by round to the resident CTAs, and a last round that
+// fills less than half of them would leave most SMs idle for a whole tile time (4096^3: 512
+// tiles on 148 SMs = 3.46 rounds).  With scratch memory, every tile of that last round is cut
+// along K into `split` slices, one work unit each; a unit stores its fp32 partial tile to
+// scratch, fences and draws a ticket per 32-row band, and the epilogue warp that draws the
+// last ticket sums the slices in slice order (the same order on every run) and applies bias
+// and activation.  Nobody waits for anybody.
 //
 // Replaces the reference's opt-in TF32 wmma/mma.sync kernel (kernels/wmma_matmul.cuh) and
 // its FMA default (kernels/matmul_fallback.cuh); the bias+activation epilogue that the
@@ -33,16 +44,26 @@ namespace ib200 {
 namespace {
 
 // ============================== tcgen05 path ==========================================
-constexpr int BM = 128, BK = 64, UMMA_K = 16;
-constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int BM = 128;
+constexpr int KROW_BYTES = 128;                    // one K block = one 128-byte swizzled row per tile row
+constexpr int A_STAGE_BYTES = BM * KROW_BYTES;     // 16 KiB
+// operand kinds: element size, elements per K block, K extent of one MMA, instruction-descriptor format code
+enum { KIND_BF16 = 0, KIND_F16 = 1, KIND_TF32 = 2 };
+template <int KIND> struct KindCfg {
+  static constexpr int ESZ = KIND == KIND_TF32 ? 4 : 2;
+  static constexpr int BK = KROW_BYTES / ESZ;       // 64 or 32 elements
+  static constexpr int UMMA_K = 32 / ESZ;           // 16 or 8 elements = 32 bytes of every row per MMA
+  static constexpr uint32_t FMT = KIND == KIND_BF16 ? 1u : KIND == KIND_F16 ? 0u : 2u;
+};
 // The N extent of a tile is a template parameter (256, 192 or 128): the launcher picks the one
 // that minimises waves x time-per-tile for the problem at hand (narrow N, ragged tile counts).
 template <int BN> struct TileCfg {
-  static constexpr int B_STAGE_BYTES = BK * BN * 2;
+  static constexpr int B_STAGE_BYTES = KROW_BYTES * BN;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;      // 48 / 40 / 32 KiB, multiples of 1 KiB
   static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);     // 192 / 200 / 192 KiB of ring
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
+constexpr int kMaxSplit = 4;  // K slices per tail tile, at most
 constexpr int ACC_COLS = 256;  // TMEM columns reserved per accumulator buffer (two buffers = all 512)
 constexpr int GEMM_THREADS = 192;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait, then give up
@@ -106,11 +127,19 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_b
   return d;
 }
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+template <int KIND>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (KIND == KIND_TF32) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  }
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -137,12 +166,63 @@ struct GemmParams {
   const void* bias;
   void* c;
   int32_t* status;
+  // work units: tiles [0, full_tiles) whole, every later tile as `split` K slices (split == 1: no tail split)
+  int full_tiles, split;
+  int* tickets;     // [split tiles][4 row bands], zero before the launch, left zero by it
+  float* partial;   // [split tiles][split][BM][BN] fp32
 };
 
-template <typename TOut, int BN>
+struct Unit {
+  int tile, kb0, kb1, slice;  // slice < 0: a whole tile
+};
+__device__ __forceinline__ Unit decode_unit(int u, const GemmParams& p, int kblocks) {
+  Unit w;
+  if (u < p.full_tiles) {
+    w.tile = u; w.kb0 = 0; w.kb1 = kblocks; w.slice = -1;
+  } else {
+    const int idx = u - p.full_tiles, per = (kblocks + p.split - 1) / p.split;
+    w.tile = p.full_tiles + idx / p.split;
+    w.slice = idx % p.split;
+    w.kb0 = w.slice * per;
+    w.kb1 = w.kb0 + per < kblocks ? w.kb0 + per : kblocks;
+  }
+  return w;
+}
+
+template <typename TOut> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<float>(float a, float) { return __float_as_uint(a); }
+
+// bias, activation, conversion and 16-byte stores for 8 consecutive columns of one row
+template <typename TOut>
+__device__ __forceinline__ void finish8(float (&v)[8], const TOut* bias, int col, int act, TOut* crow) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (bias) v[j] += to_f32<TOut>(bias[col + j]);
+    if (act == IB200_ACT_RELU) v[j] = max_nan(v[j], 0.0f);
+  }
+  if (sizeof(TOut) == 2) {
+    uint4 q;
+    q.x = pack2<TOut>(v[0], v[1]); q.y = pack2<TOut>(v[2], v[3]); q.z = pack2<TOut>(v[4], v[5]); q.w = pack2<TOut>(v[6], v[7]);
+    *reinterpret_cast<uint4*>(crow + col) = q;
+  } else {
+    *reinterpret_cast<float4*>(crow + col) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(crow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+template <typename TOut, int BN, int KIND>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   constexpr int STAGES = TileCfg<BN>::STAGES, STAGE_BYTES = TileCfg<BN>::STAGE_BYTES;
+  constexpr int BK = KindCfg<KIND>::BK, UMMA_K = KindCfg<KIND>::UMMA_K, NBOX = KROW_BYTES / KindCfg<KIND>::ESZ;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -156,6 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
   const int ntiles = tiles_m * tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
+  const int nunits = p.full_tiles + (ntiles - p.full_tiles) * p.split;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
@@ -178,9 +259,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+      for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
+        const Unit w = decode_unit(u, p, kblocks);
+        const int m0 = (w.tile / tiles_n) * BM, n0 = (w.tile % tiles_n) * BN;
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!(ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1))) break;
@@ -189,11 +271,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           mbar_expect_tx(&full[s], STAGE_BYTES);
           tma_load_2d(sa, &map_a, &full[s], kb * BK, m0);
           if (p.b_kmajor) {
-            tma_load_2d(sb, &map_b, &full[s], kb * BK, n0);  // one 64(K) x BN(N rows) box
+            tma_load_2d(sb, &map_b, &full[s], kb * BK, n0);  // one box: BK (K) x BN (N rows)
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)  // BN/64 boxes of 64(N) x 64(K rows)
-              tma_load_2d(sb + j * (BK * 128), &map_b, &full[s], n0 + j * 64, kb * BK);
+            for (int j = 0; j < BN / NBOX; ++j)  // boxes of NBOX (N, 128 bytes) x BK (K rows)
+              tma_load_2d(sb + j * (BK * KROW_BYTES), &map_b, &full[s], n0 + j * NBOX, kb * BK);
           }
         }
       }
@@ -211,17 +293,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.b_kmajor ? 0u : 1u) << 16) | ((uint32_t)(BN >> 3) << 17) |
-                             ((uint32_t)(BM >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (KindCfg<KIND>::FMT << 7) | (KindCfg<KIND>::FMT << 10) | ((p.b_kmajor ? 0u : 1u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint32_t it = 0, t_local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t_local) {
+      for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, ++t_local) {
+        const Unit w = decode_unit(u, p, kblocks);
         const int buf = t_local & 1;
         const uint32_t acc_ph = (t_local >> 1) & 1;
         if (!(ok = mbar_wait(&acc_empty[buf], acc_ph ^ 1, abort_flag, p.status, 2))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!(ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3))) break;
@@ -229,14 +312,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_STAGE_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            // A: K-major, 128-byte swizzled rows; one UMMA_K step = 32 bytes inside the row
-            const uint64_t adesc = umma_desc(sa + k * (UMMA_K * 2), 16, 1024);
-            // B: K-major ([N,K]) like A, or MN-major ([K,N]): 64-column chunks BK*128 bytes
+            // A: K-major, 128-byte swizzled rows; one MMA's K extent = 32 bytes inside the row
+            const uint64_t adesc = umma_desc(sa + k * 32, 16, 1024);
+            // B: K-major ([N,K]) like A, or MN-major ([K,N]): 128-byte column chunks BK*128 bytes
             // apart (leading offset), 8-row K groups 1024 bytes apart (stride offset); one
-            // UMMA_K step = 16 K rows = 2048 bytes
-            const uint64_t bdesc = p.b_kmajor ? umma_desc(sb + k * (UMMA_K * 2), 16, 1024)
-                                              : umma_desc(sb + k * (UMMA_K * 128), BK * 128, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+            // MMA's K extent = UMMA_K rows of 128 bytes
+            const uint64_t bdesc = p.b_kmajor ? umma_desc(sb + k * 32, 16, 1024)
+                                              : umma_desc(sb + k * (UMMA_K * KROW_BYTES), BK * KROW_BYTES, 1024);
+            umma<KIND>(d_tmem, adesc, bdesc, idesc, (kb != w.kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
         }
@@ -248,10 +331,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's
     uint32_t t_local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t_local) {
+    for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, ++t_local) {
+      const Unit w = decode_unit(u, p, kblocks);
       const int buf = t_local & 1;
       const uint32_t acc_ph = (t_local >> 1) & 1;
-      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int m0 = (w.tile / tiles_n) * BM, n0 = (w.tile % tiles_n) * BN;
       ok = mbar_wait(&acc_full[buf], acc_ph, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -259,40 +343,86 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int row = m0 + quarter * 32 + lane;
       TOut* crow = static_cast<TOut*>(p.c) + (size_t)row * p.N;
       const TOut* bias = static_cast<const TOut*>(p.bias);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS;
+      if (w.slice < 0) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS + c * 32, r);
-        const int col0 = n0 + c * 32;
-        if (row < p.M) {
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          const int col0 = n0 + c * 32;
+          if (row < p.M) {
 #pragma unroll
-          for (int g = 0; g < 32; g += 8) {
-            const int col = col0 + g;
-            if (col >= p.N) break;  // N % 8 == 0: a group of 8 columns is all in or all out
-            float v[8];
+            for (int g = 0; g < 32; g += 8) {
+              const int col = col0 + g;
+              if (col >= p.N) break;  // N % 8 == 0: a group of 8 columns is all in or all out
+              float v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              v[j] = __uint_as_float(r[g + j]);
-              if (bias) v[j] += to_f32<TOut>(bias[col + j]);
-              if (p.act == IB200_ACT_RELU) v[j] = max_nan(v[j], 0.0f);
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g + j]);
+              finish8<TOut>(v, bias, col, p.act, crow);
             }
-            if (sizeof(TOut) == 2) {
-              uint4 q;
-              __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
-              __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
-              q.x = *reinterpret_cast<uint32_t*>(&h0); q.y = *reinterpret_cast<uint32_t*>(&h1);
-              q.z = *reinterpret_cast<uint32_t*>(&h2); q.w = *reinterpret_cast<uint32_t*>(&h3);
-              *reinterpret_cast<uint4*>(crow + col) = q;
-            } else {
-              *reinterpret_cast<float4*>(crow + col) = make_float4(v[0], v[1], v[2], v[3]);
-              *reinterpret_cast<float4*>(crow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      } else {
+        // a K slice of a tail tile: park the fp32 partial, then whoever parks last for this 32-row band adds
+        // the slices up in slice order.  Parked layout per (tile, slice): [32-column chunk][4-column group][row][4],
+        // so that the 32 rows of a warp write, and later read, 512 contiguous bytes per instruction.
+        const int st = w.tile - p.full_tiles;
+        const int trow = quarter * 32 + lane;
+        float* mine = p.partial + (size_t)(st * p.split + w.slice) * BM * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            __stcg(reinterpret_cast<float4*>(mine + ((size_t)(c * 8 + g) * BM + trow) * 4),
+                   make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]), __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3])));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);  // the accumulator is free: the next unit's main loop may start
+        __threadfence();
+        __syncwarp();
+        int ticket = 0;
+        if (lane == 0) ticket = atomicAdd(&p.tickets[st * 4 + quarter], 1);
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        if (ticket == p.split - 1) {
+          __threadfence();
+          if (lane == 0) p.tickets[st * 4 + quarter] = 0;  // ready for the next launch
+          const float* base = p.partial + (size_t)(st * p.split) * BM * BN;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col0 = n0 + c * 32;
+            if (col0 >= p.N) break;
+            float4 q[kMaxSplit][8];
+#pragma unroll
+            for (int sl = 0; sl < kMaxSplit; ++sl)  // every load of the chunk in flight before the first add
+              if (sl < p.split) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                  q[sl][g] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)sl * BM * BN + ((size_t)(c * 8 + g) * BM + trow) * 4));
+              }
+            if (row < p.M) {
+#pragma unroll
+              for (int g8 = 0; g8 < 4; ++g8) {
+                const int col = col0 + g8 * 8;
+                if (col >= p.N) break;
+                float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int sl = 0; sl < kMaxSplit; ++sl)
+                  if (sl < p.split) {
+                    const float4 lo = q[sl][2 * g8], hi = q[sl][2 * g8 + 1];
+                    v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w; v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+                  }
+                finish8<TOut>(v, bias, col, p.act, crow);
+              }
             }
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
 
@@ -321,62 +451,116 @@ int get_encoder(EncodeTiledFn* out) {
   return IB200_OK;
 }
 
-// bf16 row-major [rows, cols] tensor, box [box_rows, box_cols], 128-byte swizzle
-int make_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows, int box_cols) {
+// row-major [rows, cols] tensor of 2- or 4-byte elements, box [box_rows, box_cols], 128-byte swizzle
+int make_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, int kind, int64_t rows, int64_t cols, int box_rows, int box_cols) {
+  const int esz = kind == KIND_TF32 ? 4 : 2;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * esz};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  const CUtensorMapDataType dt = kind == KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : kind == KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(IB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
   return IB200_OK;
 }
 
-template <int BN>
+// How the tiles of a problem are handed out: `full` tiles whole, the rest as `split` K slices each.
+struct SplitPlan {
+  int bn, full_tiles, split;
+  int64_t tiles;
+  double cost;  // rounds of the resident CTAs, in units of one 256-wide tile
+  size_t scratch;
+};
+// a slice shorter than this many K blocks costs more in the exchange of partial tiles (a fixed 5-8 us) than the
+// idle SMs it saves: measured on 2560 x 2560 x 1024 (16 blocks, two slices), 27.9 us split against 19.9 us whole
+constexpr int kMinSliceBlocks = 16;
+
+SplitPlan split_plan(int bn, int64_t m, int64_t n, int64_t kblocks, bool allow_split) {
+  static const double penalty[3] = {1.0, 1.18, 1.58};  // time per output column, measured on 4096^3 (256 / 192 / 128 wide)
+  SplitPlan sp{};
+  sp.bn = bn;
+  sp.tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
+  const int64_t rounds = sp.tiles / kSmCount, rest = sp.tiles % kSmCount;
+  sp.full_tiles = (int)sp.tiles;
+  sp.split = 1;
+  double tail = rest ? 1.0 : 0.0;
+  if (allow_split && rest > 0 && sp.tiles < (1 << 20)) {
+    int64_t s = kSmCount / rest;
+    if (s > kMaxSplit) s = kMaxSplit;
+    while (s > 1 && kblocks / s < kMinSliceBlocks) --s;
+    if (s >= 2) {
+      sp.split = (int)s;
+      sp.full_tiles = (int)(rounds * kSmCount);
+      tail = 1.0 / s + 0.08;  // the exchange of partial tiles through L2
+    }
+  }
+  const double w = bn == 256 ? penalty[0] : bn == 192 ? penalty[1] : penalty[2];
+  sp.cost = ((double)rounds + tail) * bn * w;
+  sp.scratch = sp.split > 1 ? 256 + (size_t)rest * 4 * sizeof(int) + 256 + (size_t)rest * sp.split * BM * bn * sizeof(float) : 0;
+  return sp;
+}
+
+SplitPlan choose_plan(int64_t m, int64_t n, int64_t k, int kind, size_t scratch_bytes, bool unlimited) {
+  const int64_t bk = kind == KIND_TF32 ? 32 : 64, kblocks = (k + bk - 1) / bk;
+  SplitPlan best{};
+  const int widths[3] = {256, 192, 128};
+  for (int i = 0; i < 3; ++i) {
+    SplitPlan sp = split_plan(widths[i], m, n, kblocks, true);
+    if (!unlimited && sp.scratch > scratch_bytes) sp = split_plan(widths[i], m, n, kblocks, false);
+    if (i == 0 || sp.cost < best.cost) best = sp;
+  }
+  return best;
+}
+
+template <int BN, int KIND>
 int launch_tile(const void* a, const void* b, const void* bias, void* c, int out_dtype, int64_t m, int64_t n, int64_t k,
-                int transpose_b, int act, int32_t* status, cudaStream_t s) {
+                int transpose_b, int act, int32_t* status, const SplitPlan& sp, void* scratch, cudaStream_t s) {
+  constexpr int BK = KindCfg<KIND>::BK, NBOX = KROW_BYTES / KindCfg<KIND>::ESZ;
   EncodeTiledFn enc;
   if (int rc = get_encoder(&enc)) return rc;
   CUtensorMap map_a, map_b;
-  if (int rc = make_map(enc, &map_a, a, m, k, BM, BK)) return rc;
+  if (int rc = make_map(enc, &map_a, a, KIND, m, k, BM, BK)) return rc;
   if (transpose_b) {
-    if (int rc = make_map(enc, &map_b, b, n, k, BN, BK)) return rc;  // [N,K]: box BN rows x 64 K
+    if (int rc = make_map(enc, &map_b, b, KIND, n, k, BN, BK)) return rc;  // [N,K]: box BN rows x one K block
   } else {
-    if (int rc = make_map(enc, &map_b, b, k, n, BK, 64)) return rc;  // [K,N]: box 64 K rows x 64 N
+    if (int rc = make_map(enc, &map_b, b, KIND, k, n, BK, NBOX)) return rc;  // [K,N]: box BK rows x 128 bytes of N
   }
-  GemmParams p{(int)m, (int)n, (int)k, transpose_b ? 1 : 0, act, bias, c, status};
-  const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-  const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
-  auto kern = out_dtype == IB200_BF16 ? gemm_tcgen05_kernel<__nv_bfloat16, BN> : gemm_tcgen05_kernel<float, BN>;
+  GemmParams p{(int)m, (int)n, (int)k, transpose_b ? 1 : 0, act, bias, c, status, sp.full_tiles, sp.split, nullptr, nullptr};
+  int64_t units = sp.tiles;
+  if (sp.split > 1) {
+    const int64_t rest = sp.tiles - sp.full_tiles;
+    char* base = static_cast<char*>(scratch);
+    p.tickets = reinterpret_cast<int*>(base);
+    p.partial = reinterpret_cast<float*>(base + ((256 + (size_t)rest * 4 * sizeof(int) + 255) & ~(size_t)255));
+    units = sp.full_tiles + rest * sp.split;
+    // whatever used this scratch before (another plan sharing the workspace) may have left anything in the tickets
+    IB200_CUDA_OK(cudaMemsetAsync(p.tickets, 0, (size_t)rest * 4 * sizeof(int), s));
+  }
+  const int grid = (int)(units < kSmCount ? units : kSmCount);
+  void (*kern)(const CUtensorMap, const CUtensorMap, const GemmParams) = nullptr;
+  if (KIND == KIND_BF16) kern = out_dtype == IB200_BF16 ? gemm_tcgen05_kernel<__nv_bfloat16, BN, KIND> : gemm_tcgen05_kernel<float, BN, KIND>;
+  else if (KIND == KIND_F16) kern = out_dtype == IB200_F16 ? gemm_tcgen05_kernel<__half, BN, KIND> : gemm_tcgen05_kernel<float, BN, KIND>;
+  else kern = gemm_tcgen05_kernel<float, BN, KIND>;
   IB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN>::SMEM));
   kern<<<grid, GEMM_THREADS, TileCfg<BN>::SMEM, s>>>(map_a, map_b, p);
   return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "gemm tcgen05 launch");
 }
 
+template <int KIND>
 int run_tcgen05(const void* a, const void* b, const void* bias, void* c, int out_dtype, int64_t m, int64_t n, int64_t k,
-                int transpose_b, int act, int32_t* status, cudaStream_t s) {
-  // tile width: fewest (waves of 148 CTAs) x (time per tile).  Time per output column, measured
-  // on 4096^3: 1.00 / 1.18 / 1.58 for 256 / 192 / 128 — narrower tiles re-read A more often and
+                int transpose_b, int act, int32_t* status, void* scratch, size_t scratch_bytes, cudaStream_t s) {
+  // tile width: fewest (rounds of 148 CTAs) x (time per tile); narrower tiles re-read A more often and
   // the main loop is bound by operand traffic into shared memory, so they only win when they
-  // save whole waves (small or ragged N)
-  const int64_t tiles_m = (m + BM - 1) / BM;
-  int best = 256;
-  double best_cost = 0.0;
-  const int widths[3] = {256, 192, 128};
-  const double penalty[3] = {1.0, 1.18, 1.58};
-  for (int i = 0; i < 3; ++i) {
-    const int64_t tiles = tiles_m * ((n + widths[i] - 1) / widths[i]);
-    const double cost = (double)((tiles + kSmCount - 1) / kSmCount) * widths[i] * penalty[i];
-    if (i == 0 || cost < best_cost) { best = widths[i]; best_cost = cost; }
-  }
-  static const char* force = std::getenv("IB200_GEMM_BN");
-  if (force) best = std::atoi(force);
-  switch (best) {
-    case 192: return launch_tile<192>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
-    case 128: return launch_tile<128>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
-    default: return launch_tile<256>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
+  // save whole rounds (small or ragged N)
+  if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u)) scratch_bytes = 0;
+  const SplitPlan sp = choose_plan(m, n, k, KIND, scratch_bytes, false);
+  switch (sp.bn) {
+    case 192: return launch_tile<192, KIND>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, sp, scratch, s);
+    case 128: return launch_tile<128, KIND>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, sp, scratch, s);
+    default: return launch_tile<256, KIND>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, sp, scratch, s);
   }
 }
 
@@ -449,8 +633,23 @@ int run_fma(const void* a, const void* b, const void* bias, void* c, int64_t m, 
 
 }  // namespace
 
+bool gemm_uses_tensor_cores(int in_dtype, int out_dtype, int64_t n, int64_t k, int flags) {
+  const bool in_ok = in_dtype == IB200_BF16 || in_dtype == IB200_F16 || (in_dtype == IB200_F32 && (flags & IB200_GEMM_ALLOW_TF32));
+  const bool out_ok = out_dtype == IB200_F32 || (in_dtype != IB200_F32 && out_dtype == in_dtype);
+  return in_ok && out_ok && k >= 8 && k % 8 == 0 && n % 8 == 0;
+}
+
+// a [K,N] f32 operand is transposed into the front of the scratch; the K-split area follows
+size_t tf32_transpose_bytes(int64_t n, int64_t k) { return ((size_t)n * k * sizeof(float) + 255) & ~(size_t)255; }
+
+size_t gemm_scratch_bytes(int in_dtype, int out_dtype, int64_t m, int64_t n, int64_t k, int flags, int transpose_b) {
+  if (m <= 0 || n <= 0 || !gemm_uses_tensor_cores(in_dtype, out_dtype, n, k, flags)) return 0;
+  const size_t split = choose_plan(m, n, k, in_dtype == IB200_F32 ? KIND_TF32 : KIND_BF16, 0, true).scratch;
+  return split + (in_dtype == IB200_F32 && !transpose_b ? tf32_transpose_bytes(n, k) : 0);
+}
+
 int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_dtype, int out_dtype, int64_t m, int64_t n,
-                int64_t k, int transpose_b, int act, int32_t* status, cudaStream_t s) {
+                int64_t k, int transpose_b, int act, int32_t* status, cudaStream_t s, int flags, void* scratch, size_t scratch_bytes) {
   if (m < 0 || n < 0 || k < 0) return fail(IB200_ERR_INVALID, "gemm: negative extent");
   if (m == 0 || n == 0) return IB200_OK;
   if (!a || !b || !c) {
@@ -458,17 +657,34 @@ int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_
   }
   if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail(IB200_ERR_UNSUPPORTED, "gemm: extent above 2^31-1");
   if (act != IB200_ACT_NONE && act != IB200_ACT_RELU) return fail(IB200_ERR_INVALID, "gemm: unknown activation");
-  const bool tc = in_dtype == IB200_BF16 && (out_dtype == IB200_BF16 || out_dtype == IB200_F32) && k >= 8 && k % 8 == 0 &&
-                  n % 8 == 0 && aligned16(a) && aligned16(b) && aligned16(c) && (!bias || aligned16(bias));
+  bool tc = gemm_uses_tensor_cores(in_dtype, out_dtype, n, k, flags) && aligned16(a) && aligned16(b) && aligned16(c) &&
+            (!bias || aligned16(bias));
+  if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u)) scratch_bytes = 0;
+  if (tc && in_dtype == IB200_F32 && !transpose_b) {  // TF32 takes B as [N,K]: transpose it into the scratch, or stay on the FMA kernel
+    const size_t need = tf32_transpose_bytes(n, k);
+    if (scratch_bytes < need) {
+      tc = false;
+    } else {
+      if (int rc = launch_transpose2d(b, scratch, 4, k, n, s)) return rc;
+      b = scratch;
+      transpose_b = 1;
+      scratch = static_cast<char*>(scratch) + need;
+      scratch_bytes -= need;
+    }
+  }
   if (tc) {
     if (!status) return fail(IB200_ERR_INVALID, "gemm: the tensor-core path needs a device status word");
-    return run_tcgen05(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
+    if (in_dtype == IB200_BF16) return run_tcgen05<KIND_BF16>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s);
+    if (in_dtype == IB200_F16) return run_tcgen05<KIND_F16>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s);
+    return run_tcgen05<KIND_TF32>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s);
   }
   if (in_dtype == IB200_F32 && out_dtype == IB200_F32) return run_fma<float, float>(a, b, bias, c, m, n, k, transpose_b, act, s);
   if (in_dtype == IB200_BF16 && out_dtype == IB200_BF16) return run_fma<__nv_bfloat16, __nv_bfloat16>(a, b, bias, c, m, n, k, transpose_b, act, s);
   if (in_dtype == IB200_BF16 && out_dtype == IB200_F32) return run_fma<__nv_bfloat16, float>(a, b, bias, c, m, n, k, transpose_b, act, s);
   if (in_dtype == IB200_F32 && out_dtype == IB200_BF16) return run_fma<float, __nv_bfloat16>(a, b, bias, c, m, n, k, transpose_b, act, s);
-  return fail(IB200_ERR_UNSUPPORTED, "gemm: operand dtypes must be f32 or bf16");
+  if (in_dtype == IB200_F16 && out_dtype == IB200_F16) return run_fma<__half, __half>(a, b, bias, c, m, n, k, transpose_b, act, s);
+  if (in_dtype == IB200_F16 && out_dtype == IB200_F32) return run_fma<__half, float>(a, b, bias, c, m, n, k, transpose_b, act, s);
+  return fail(IB200_ERR_UNSUPPORTED, "gemm: operand dtypes must be f32, f16 or bf16");
 }
 
 }  // namespace ib200

@@ -173,7 +173,8 @@ struct Step {
   int transpose_b = 0;
   int act = 0;  // GEMM: IB200_ACT_*; NORM: 1 when the row mean is subtracted (0: rms-norm)
   int64_t batch = 1, batch_stride[3] = {0, 0, 0};  // batched matmul: elements between consecutive A / B / C matrices
-  int scratch = -1;  // REDUCE: workspace buffer for the split-row kernel (few, long rows), or -1
+  int scratch = -1;  // REDUCE: workspace buffer for the split-row kernel (few, long rows), or -1; GEMM: for the K-split tail tiles
+  int flags = 0;     // GEMM: IB200_GEMM_* options
   std::vector<int> idx_buf;  // GATHER: index buffers; NORM: {residual[, residual bias]} summed while the rows are loaded
   Shape g_dim, g_stride;
   double other = 0.0;     // gather: fill value; dropout: p when it is a constant
@@ -1242,10 +1243,10 @@ class Planner {
     const int a = m.in[0], b = m.in[1];
     if (!is_input(a) || !is_input(b)) return false;
     const int in_dt = nodes_[a].decl_dtype;
-    if (in_dt != nodes_[b].decl_dtype || !(in_dt == IB200_F32 || in_dt == IB200_BF16)) return false;
+    if (in_dt != nodes_[b].decl_dtype || !(in_dt == IB200_F32 || in_dt == IB200_BF16 || in_dt == IB200_F16)) return false;
     const int out_buf = out_buffer_[outputs_[0]];
     const int out_dt = plan_->buffers[out_buf].dtype;
-    if (!(out_dt == IB200_F32 || out_dt == IB200_BF16)) return false;
+    if (!(out_dt == IB200_F32 || (out_dt == in_dt && in_dt != IB200_F32))) return false;
     if (numel(nodes_[by_name_[outputs_[0]]].shape) != numel(m.shape)) return false;
     int bias_in = -1;
     if (bias >= 0) {
@@ -1268,9 +1269,27 @@ class Planner {
     s.dtype2 = out_dt;
     s.transpose_b = m.tb;
     s.act = act;
+    finish_gemm(s);
     plan_->uses_status = true;
     plan_->steps.push_back(s);
     return true;
+  }
+
+  // options from the bindings, and the scratch for the K-split tail of the tensor-core kernel
+  void finish_gemm(Step& s) {
+    const auto tf = bind_.find("ALLOW_TF32");
+    if (tf != bind_.end() && tf->second != 0) s.flags |= IB200_GEMM_ALLOW_TF32;
+    if (s.batch != 1) return;
+    const size_t bytes = gemm_scratch_bytes(s.dtype, s.dtype2, s.d[0], s.d[1], s.d[2], s.flags, s.transpose_b);
+    if (bytes) s.scratch = new_workspace_buffer(IB200_U8, (int64_t)bytes, "gemm scratch");
+    s.label += gemm_suffix(s);
+  }
+  static std::string gemm_suffix(const Step& s) {
+    std::string out;
+    const bool tf32 = s.dtype == IB200_F32 && gemm_uses_tensor_cores(s.dtype, s.dtype2, s.d[1], s.d[2], s.flags);
+    if (tf32) out += "(tf32)";
+    if (s.scratch >= 0 && gemm_scratch_bytes(s.dtype, s.dtype2, s.d[0], s.d[1], s.d[2], s.flags, 1) > 0) out += "(split tail)";
+    return out;
   }
 
   // =============================== phase C: general lowering ================================
@@ -1427,7 +1446,7 @@ class Planner {
       materialise_contiguous(a);
       materialise_contiguous(b);
       int adt = plan_->buffers[nodes_[a].view.buffer].dtype, bdt = plan_->buffers[nodes_[b].view.buffer].dtype;
-      if (adt != bdt || !(adt == IB200_F32 || adt == IB200_BF16)) {
+      if (adt != bdt || !(adt == IB200_F32 || adt == IB200_BF16 || adt == IB200_F16)) {
         a = converted_copy(a, IB200_F32);
         b = converted_copy(b, IB200_F32);
         adt = IB200_F32;
@@ -1455,11 +1474,12 @@ class Planner {
       s.transpose_b = tb;
       s.out[0] = result_buffer(id, IB200_F32);
       s.dtype2 = plan_->buffers[s.out[0]].dtype;
-      if (!(s.dtype2 == IB200_F32 || s.dtype2 == IB200_BF16)) {
+      if (!(s.dtype2 == IB200_F32 || (s.dtype2 == adt && adt != IB200_F32))) {
         out_written_.erase(n.name);
         s.out[0] = new_workspace_buffer(IB200_F32, numel(n.shape), n.name);
         s.dtype2 = IB200_F32;
       }
+      finish_gemm(s);
       plan_->uses_status = true;
       plan_->steps.push_back(s);
       set_strided(id, s.out[0]);
@@ -1974,13 +1994,13 @@ class Planner {
       if (q.out[0].src != EW_ACC) continue;
       const int ob = e.ew_out_buf[0];
       const int out_dt = plan_->buffers[ob].dtype;
-      if (!(out_dt == IB200_F32 || out_dt == IB200_BF16)) continue;
+      if (!(out_dt == IB200_F32 || (out_dt == g.dtype && g.dtype != IB200_F32))) continue;
       if (slot_b >= 0 && plan_->buffers[e.ew_in_buf[slot_b]].dtype != out_dt) continue;
       g.in[2] = slot_b >= 0 ? e.ew_in_buf[slot_b] : -1;
       g.act = act;
       g.out[0] = ob;
       g.dtype2 = out_dt;
-      g.label = std::string("gemm") + (slot_b >= 0 ? "+bias" : "") + (act ? "+relu" : "");
+      g.label = std::string("gemm") + (slot_b >= 0 ? "+bias" : "") + (act ? "+relu" : "") + gemm_suffix(g);
       steps.erase(steps.begin() + i + 1);
     }
   }
@@ -2837,7 +2857,8 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
           rc = launch_gemm(static_cast<const char*>(P(st.in[0])) + bi * st.batch_stride[0] * dtype_size(st.dtype),
                            static_cast<const char*>(P(st.in[1])) + bi * st.batch_stride[1] * dtype_size(st.dtype), P(st.in[2]),
                            static_cast<char*>(P(st.out[0])) + bi * st.batch_stride[2] * dtype_size(st.dtype2), st.dtype, st.dtype2,
-                           st.d[0], st.d[1], st.d[2], st.transpose_b, st.act, status, s);
+                           st.d[0], st.d[1], st.d[2], st.transpose_b, st.act, status, s, st.flags,
+                           st.scratch >= 0 ? P(st.scratch) : nullptr, st.scratch >= 0 ? plan->buffers[st.scratch].bytes : 0);
         break;
       case Step::GATHER: {
         GatherArgs ga{};

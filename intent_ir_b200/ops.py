@@ -197,9 +197,16 @@ def groupnorm(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tens
     return y, mean.view(n, groups), rstd.view(n, groups)
 
 
+_gemm_scratch: Dict[int, torch.Tensor] = {}
+
+
 def gemm_bias_act(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
-                  transpose_b: bool = False, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """act(a @ b + bias) with fp32 accumulation; ``b`` is [K,N], or [N,K] with transpose_b."""
+                  transpose_b: bool = False, out_dtype: Optional[torch.dtype] = None, allow_tf32: bool = False,
+                  split_tail: bool = True) -> torch.Tensor:
+    """act(a @ b + bias) with fp32 accumulation; ``b`` is [K,N], or [N,K] with transpose_b.  bf16 / f16 operands
+    (and f32 operands with ``allow_tf32``) whose K and N are multiples of 8 run on the tensor cores.  ``split_tail``
+    gives the kernel scratch memory (kept per device, grown on demand) so that a last, mostly empty round of tiles
+    is split along K."""
     _dev(a, "a"), _dev(b, "b")
     if a.dim() != 2 or b.dim() != 2 or a.dtype != b.dtype:
         raise B200LoweringError("gemm: a and b must be rank-2 tensors of one dtype")
@@ -213,9 +220,19 @@ def gemm_bias_act(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor]
         _dev(bias, "bias")
         if bias.dtype != out_dtype or bias.numel() != n:
             raise B200LoweringError("gemm: bias must have the output dtype and N elements")
-    rc = _lib.load().ib200_gemm_bias_act(
+    lib = _lib.load()
+    flags = _lib.GEMM_ALLOW_TF32 if allow_tf32 else 0
+    need = lib.ib200_gemm_scratch_bytes(code_of(a), code_of(c), m, n, k, int(transpose_b), flags) if split_tail else 0
+    scratch = None
+    if need:
+        dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
+        scratch = _gemm_scratch.get(dev)
+        if scratch is None or scratch.numel() < need + 256:
+            scratch = _gemm_scratch[dev] = torch.empty(need + 256, dtype=torch.uint8, device=a.device)
+    rc = lib.ib200_gemm_bias_act_ws(
         _ptr(a), _ptr(b), _ptr(bias), _ptr(c), code_of(a), code_of(c), m, n, k, int(transpose_b),
-        {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU}[act], status_word().data_ptr(), _stream())
+        {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU}[act], flags, ((scratch.data_ptr() + 255) & ~255) if need else None, need,
+        status_word().data_ptr(), _stream())
     _check(rc, "gemm_bias_act")
     return c
 

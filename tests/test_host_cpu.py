@@ -290,3 +290,33 @@ def test_registry_keeps_the_reason_a_builtin_backend_failed_to_import(monkeypatc
     with pytest.raises(KeyError) as e:
         registry.get("broken")
     assert "no_such_module" in str(e.value) and isinstance(e.value.__cause__, ImportError)
+
+
+def test_gemm_plans_cover_every_float_operand_type(golden_graphs):
+    """bf16 and f16 products always lower to the tensor-core GEMM, f32 products only under the reference's
+    ALLOW_TF32 binding (intentir_to_cuda.py:577-578); a last, mostly empty round of tiles gets scratch for the
+    K split."""
+    from intent_ir_b200.lowering import plan_json
+
+    def graph(dt):
+        js = json.loads(json.dumps(golden_graphs["matmul_bias_relu2d"]["intent"]))
+        for name in ("A", "B", "bias", "C"):
+            js["tensors"][name]["dtype"] = dt
+        return js
+
+    for dt in ("bf16", "f16"):
+        d = plan_json(graph(dt), {"M": 256, "N": 256, "K": 128})
+        assert [s["kernel"] for s in d["steps"]] == ["gemm+bias+relu"] and d["io_spec"]["tensors"]["C"]["dtype"] == dt
+    assert [s["kernel"] for s in plan_json(graph("f32"), {"M": 256, "N": 256, "K": 128})["steps"]] == ["gemm+bias+relu"]
+    assert [s["kernel"] for s in plan_json(graph("f32"), {"M": 256, "N": 256, "K": 128, "ALLOW_TF32": 1})["steps"]] == ["gemm+bias+relu(tf32)"]
+    assert [s["kernel"] for s in plan_json(graph("f32"), {"M": 256, "N": 250, "K": 128, "ALLOW_TF32": 1})["steps"]] == ["gemm+bias+relu"]  # ragged N: FMA
+    big = plan_json(graph("bf16"), {"M": 4096, "N": 4096, "K": 4096})  # 512 tiles on 148 SMs: 68 tail tiles, two slices each
+    assert [s["kernel"] for s in big["steps"]] == ["gemm+bias+relu(split tail)"]
+    lib = _lib.load()
+    need = lib.ib200_gemm_scratch_bytes(_lib.BF16, _lib.BF16, 4096, 4096, 4096, 0, 0)
+    assert need == 256 + 68 * 16 + 256 + 68 * 2 * 128 * 256 * 4 and big["workspace_bytes"] >= need
+    assert lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 0, 0) == 0  # exact FMA path: no tiles to split
+    # TF32 takes B as [N,K]: a [K,N] operand needs room for its transpose on top of the split area
+    tf = _lib.GEMM_ALLOW_TF32
+    assert lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 0, tf) == lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 1, tf) + 4096 * 4096 * 4
+    assert lib.ib200_gemm_scratch_bytes(_lib.BF16, _lib.BF16, 128 * 37, 256 * 4, 4096, 0, 0) == 0  # 148 tiles: a full round

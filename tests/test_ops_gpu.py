@@ -396,6 +396,8 @@ def test_device_wait_status_surfaces_as_an_exception_and_clears():
     c = ops.gemm_bias_act(a, b, None, "none")  # the word was cleared: the next launch is judged on its own
     ops.check_device_status()
     assert float(c.float().min()) == float(c.float().max()) == 64.0
+    from intent_ir_b200 import _lib
+
     lib = _lib.load()
     word = torch.full((1,), 2, dtype=torch.int32, device="cuda")
     assert lib.ib200_check_status(word.data_ptr(), torch.cuda.current_stream().cuda_stream) == _lib.ERR_DEVICE_WAIT
@@ -432,3 +434,80 @@ def test_plan_status_word_surfaces_through_check_plan_status(golden_graphs):
     with pytest.raises(B200RuntimeError) as e:
         runtime.check_plan_status(low)
     assert "can no longer be read" in str(e.value)
+
+
+# ---- tensor cores for every float operand type, and the K-split tail --------------------------------------
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 264, 72), (1, 8, 8), (130, 520, 1000), (512, 1024, 2048)])
+@pytest.mark.parametrize("transpose_b", [False, True])
+def test_gemm_f16_operands_on_tensor_cores(m, n, k, transpose_b):
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(m + n + k + 1)
+    a = (0.5 * rng.standard_normal((m, k))).astype(np.float16).astype(np.float32)
+    b = (0.5 * rng.standard_normal((k, n))).astype(np.float16).astype(np.float32)
+    bias = (0.1 * rng.standard_normal(n)).astype(np.float16).astype(np.float32)
+    want = np.maximum(a.astype(np.float64) @ b.astype(np.float64) + bias, 0)
+    bd = _dev(np.ascontiguousarray(b.T) if transpose_b else b, torch.float16)
+    got = ops.gemm_bias_act(_dev(a, torch.float16), bd, _dev(bias, torch.float16), "relu", transpose_b)
+    ops.check_device_status()
+    assert got.dtype == torch.float16
+    _agree(got.float().cpu().numpy(), want, 2e-2, 2e-2)
+    got32 = ops.gemm_bias_act(_dev(a, torch.float16), bd, None, "none", transpose_b, out_dtype=torch.float32)
+    ops.check_device_status()
+    _agree(got32.cpu().numpy(), a.astype(np.float64) @ b.astype(np.float64), 1e-3, 1e-3)  # f16 products are exact in fp32
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 32), (128, 256, 64), (300, 264, 72), (1, 8, 8), (130, 520, 1000), (512, 1024, 2048)])
+@pytest.mark.parametrize("transpose_b", [False, True])
+def test_gemm_f32_operands_as_tf32(m, n, k, transpose_b):
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(m + n + k + 2)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = (rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k)).astype(np.float32)
+    bias = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    want = np.maximum(a.astype(np.float64) @ b.astype(np.float64) + bias, 0)
+    bd = _dev(np.ascontiguousarray(b.T) if transpose_b else b)
+    got = ops.gemm_bias_act(_dev(a), bd, _dev(bias), "relu", transpose_b, allow_tf32=True)
+    ops.check_device_status()
+    _agree(got.cpu().numpy(), want, 2e-2, 2e-2)  # the verifier's matmul tolerance
+    # TF32 keeps 10 mantissa bits: the result must differ from the exact-FMA kernel's, or the flag did nothing
+    exact = ops.gemm_bias_act(_dev(a), bd, _dev(bias), "relu", transpose_b)
+    _agree(exact.cpu().numpy(), want, 1e-4, 1e-4)
+    if k >= 64:
+        assert not torch.equal(got, exact)
+    # operands exactly representable in TF32 give the exact product
+    a8 = np.round(a * 8) / 8
+    b8 = np.round(b * 64) / 64
+    b8d = _dev(np.ascontiguousarray(b8.T if transpose_b else b8).astype(np.float32))
+    got8 = ops.gemm_bias_act(_dev(a8.astype(np.float32)), b8d, None, "none", transpose_b, allow_tf32=True)
+    _agree(got8.cpu().numpy(), a8.astype(np.float64) @ b8.astype(np.float64), 1e-5, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("m,n,k,transpose_b", [(128 * 20, 256 * 10, 2048, False),  # 200 tiles: one full round + 52 tiles split in two
+                                                (128 * 5, 256 * 6, 4096, True),     # 30 tiles, all split in four
+                                                (640 + 3, 1536 - 8, 2048 + 8, False),  # ragged M, N, K
+                                                (4096, 4096, 2048, False)])         # 512 tiles: three rounds + 68 split in two
+def test_gemm_tail_tiles_split_along_k(dtype, m, n, k, transpose_b):
+    from intent_ir_b200 import _lib, ops
+    rng = np.random.default_rng(m + n + k + 3)
+    a = _bf16_round(rng.standard_normal((m, k)).astype(np.float32) * 0.5)
+    b = _bf16_round((rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32))
+    bias = _bf16_round((0.1 * rng.standard_normal(n)).astype(np.float32))
+    lib = _lib.load()
+    code = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}[dtype]
+    tf32 = dtype == torch.float32
+    assert lib.ib200_gemm_scratch_bytes(code, code, m, n, k, 1, _lib.GEMM_ALLOW_TF32 if tf32 else 0) > 0
+    ad, bd, biasd = _dev(a, dtype), _dev(np.ascontiguousarray(b.T) if transpose_b else b, dtype), _dev(bias, dtype)
+    split = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=True)
+    ops.check_device_status()
+    whole = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=False)
+    ops.check_device_status()
+    again = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=True)  # tickets were left at zero
+    ops.check_device_status()
+    assert torch.equal(split, again)  # slices are added in slice order: the same bits on every run
+    want = np.maximum(a.astype(np.float64) @ b.astype(np.float64) + bias, 0)
+    _agree(split.float().cpu().numpy(), want, 2e-2, 2e-2)
+    _agree(whole.float().cpu().numpy(), want, 2e-2, 2e-2)
+    # bf16 / f16 products are exact and both kernels accumulate in fp32: split and whole agree to accumulation order
+    assert float((split.float() - whole.float()).abs().max()) <= (2e-2 if dtype != torch.float32 else 1e-3)

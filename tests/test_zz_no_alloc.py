@@ -155,33 +155,48 @@ def test_noalloc_status_word_is_readable_and_cleared_by_the_next_launch():
         lib.ib200_plan_destroy(handle)
 
 
-def test_noalloc_first_call_and_device_memory():
-    """What the first call on a device costs in device memory, measured (the header states the outcome): the
-    library allocates nothing, but the CUDA runtime may back the built-in array when it first loads its module."""
-    from intent_ir_b200 import _lib
+_MEMORY_PROBE = r"""
+import ctypes as C, json, sys
+sys.path.insert(0, {root!r})
+import torch
+torch.zeros(1, device="cuda"); torch.cuda.synchronize()
+free = [torch.cuda.mem_get_info()[0]]                      # context up, library not loaded yet
+from intent_ir_b200 import _lib
+from intent_ir_b200.bindings import derive_bindings, normalise_bindings
+lib = _lib.load(); torch.cuda.synchronize()
+free.append(torch.cuda.mem_get_info()[0])                  # after loading the library
+graph = json.load(open({golden!r}))["mlp2d"]["intent"]
+h = C.c_void_p()
+assert lib.ib200_plan_create(json.dumps(graph).encode(), json.dumps(derive_bindings(normalise_bindings({{"M": 96, "N": 64, "K": 72, "H": 80}}))).encode(), C.byref(h)) == 0
+buf = C.create_string_buffer(1 << 18); assert lib.ib200_plan_describe(h, buf, len(buf)) == 0
+d = json.loads(buf.value.decode()); specs = d["io_spec"]["tensors"]
+ts = [torch.zeros([int(x) for x in specs[n]["shape"]], device="cuda") for n in d["io_spec"]["arg_names"]]
+args = (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+torch.cuda.synchronize(); free.append(torch.cuda.mem_get_info()[0])   # the caller's own tensors allocated
+for _ in range(3):
+    assert lib.ib200_plan_launch_noalloc(h, args, len(ts), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize(); free.append(torch.cuda.mem_get_info()[0])
+print(json.dumps(free))
+"""
 
-    lib = _lib.load()
-    with open(GOLDEN) as f:
-        graphs = json.load(f)
-    handle = _plan(lib, _mlp_graph(graphs, "f32"), {"M": 96, "N": 64, "K": 72, "H": 80})
-    try:
-        d = _describe(lib, handle)
-        specs = d["io_spec"]["tensors"]
-        tensors = [torch.zeros([int(x) for x in specs[n]["shape"]], device="cuda") for n in d["io_spec"]["arg_names"]]
-        args = (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
-        stream = torch.cuda.current_stream().cuda_stream
-        torch.cuda.synchronize()
-        free = [torch.cuda.mem_get_info()[0]]
-        for _ in range(3):
-            assert lib.ib200_plan_launch_noalloc(handle, args, len(tensors), stream) == 0
-            torch.cuda.synchronize()
-            free.append(torch.cuda.mem_get_info()[0])
-        drops = [free[i] - free[i + 1] for i in range(3)]
-        print("free device memory consumed by calls 1..3 of ib200_plan_launch_noalloc (bytes):", drops)
-        assert drops[1] == 0 and drops[2] == 0  # nothing is allocated per call
-        assert 0 <= drops[0] <= 96 << 20  # at most the array and its module, once (0 when an earlier test made the first call)
-    finally:
-        lib.ib200_plan_destroy(handle)
+
+def test_noalloc_first_call_and_device_memory():
+    """What the entry point costs in device memory, measured in a fresh process (the header states the outcome):
+    free memory after context creation, after loading the library, after the caller's own allocations, and after
+    each of three calls.  The library allocates nothing; whatever the first call costs is the CUDA runtime
+    materialising the built-in array (and the kernels' code) the first time they are used."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", _MEMORY_PROBE.format(root=root, golden=GOLDEN)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    free = json.loads(r.stdout.strip().splitlines()[-1])
+    steps = ["load library", "caller's tensors", "call 1", "call 2", "call 3"]
+    drops = {k: free[i] - free[i + 1] for i, k in enumerate(steps)}
+    print("free device memory consumed (bytes):", drops)
+    assert drops["call 2"] == 0 and drops["call 3"] == 0  # nothing is allocated per call
+    assert 0 <= drops["call 1"] <= 96 << 20  # at most the 32 MiB array and the kernels' code, once
 
 
 def test_noalloc_refuses_plans_beyond_the_built_in_workspace():
