@@ -242,6 +242,12 @@ def workload(name):
               "ops": [{"op": "reduce_sum", "inputs": ["x"], "output": "y", "attrs": {"dims": [0, 1] if whole else [0]}}], "outputs": ["y"]}
         return (js, {"M": m, "N": n}, lambda r: {"x": r.standard_normal((m, n), dtype=np.float32)}, m * n * 4 + (4 if whole else n * 4), 0,
                 "sum of a whole f32 [8192,8192] tensor" if whole else "sum over the leading axis of f32 [65536,1024]")
+    if name == "copy_long":
+        m, n = 4, 1 << 20
+        js = {"name": "copy", "tensors": {"x": _t(["M", "N"]), "y": _t(["M", "N"])},
+              "ops": [{"op": "identity", "inputs": ["x"], "output": "y"}], "outputs": ["y"]}
+        return (js, {"M": m, "N": n}, lambda r: {"x": r.standard_normal((m, n), dtype=np.float32)}, 2 * m * n * 4, 0,
+                "copy f32 [4,1Mi]: the yardstick for the two long-row workloads")
     if name in ("softmax_long", "layernorm_long"):
         m, n = 4, 1 << 20
         if name == "softmax_long":
@@ -256,7 +262,7 @@ def workload(name):
 
 # the per-op table, least important first: a reader that keeps only the end of the line keeps the BASELINE configurations
 OPS_ORDER = ("reduce_any", "reduce_any_large", "column_sum", "reduce_sum_all", "dropout", "rope", "rowprog", "dag", "chain", "masked_softmax",
-             "layernorm_residual", "rmsnorm", "softmax_long", "layernorm_long", "matmul_f32", "matmul_f16", "layernorm", "groupnorm", "matmul")
+             "layernorm_residual", "rmsnorm", "copy_long", "softmax_long", "layernorm_long", "matmul_f32", "matmul_f16", "layernorm", "groupnorm", "matmul")
 
 
 # ---------------------------------------------------------------- clocks -----------------------
@@ -370,7 +376,7 @@ def measure_op(name, steps, warmup, peaks):
     n = max(steps, MIN_LAUNCHES if nbytes >= (1 << 20) and not flops else 100)
     per = float(np.median(time_plan(lowered, sets, n, warmup, repeats=REPEATS))) / n
     out = {"w": label, "us": round(per * 1e3, 2), "k": "+".join(s["kernel"] for s in lowered.steps)[:60]}
-    if nbytes < (1 << 20):  # launch-latency bound: the same plan replayed from a CUDA graph
+    if per * 1e3 < 40.0 and not flops:  # short enough for the host's launch cost to show: the same plan replayed from a CUDA graph
         import torch
 
         from intent_ir_b200.runtime import graph_lowered
@@ -385,7 +391,7 @@ def measure_op(name, steps, warmup, peaks):
             replay()
         e1.record()
         torch.cuda.synchronize()
-        out["us_graph_replay"] = round(e0.elapsed_time(e1) / n * 1e3, 2)
+        out["us_graph_replay"] = round(e0.elapsed_time(e1) / n * 1e3, 2)  # one buffer set: L2-warm for small tensors
     if flops:
         tf = flops / (per * 1e-3) / 1e12
         out.update({"tflops": round(tf, 1), "frac": round(tf / peaks["bf16_tflops"], 3),

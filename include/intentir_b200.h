@@ -183,6 +183,23 @@ IB200_API int ib200_softmax(const void* x, void* y, float* row_max, float* row_s
 IB200_API int ib200_softmax_io(const void* x, void* y, float* row_max, float* row_sum, int in_dtype, int out_dtype,
                      int64_t rows, int64_t cols, void* stream);
 
+/* Softmax / row normalisation with scratch memory (16-byte aligned, ib200_softmax_scratch_bytes /
+ * ib200_norm_scratch_bytes bytes; 0 means the shape never uses it; contents irrelevant).  Rows
+ * longer than the resident kernels hold (16 Ki elements; 128 Ki for the normalisation's cluster
+ * kernels) that are too few to fill the GPU one CTA per row, or too large for L2, are cut into
+ * segments of 8 Ki .. 64 Ki elements, one CTA each: pass 1 leaves (max, sum) or (mean, squared
+ * deviations) per segment in the scratch, pass 2 folds them in a fixed order and writes the
+ * segment.  Without scratch these shapes run one streaming CTA per row.  Same arithmetic as
+ * ib200_softmax_io / ib200_norm_rows; no counterpart in the reference (its softmax stops at
+ * 1024 columns, kernels/softmax.cuh). */
+IB200_API int ib200_softmax_ws(const void* x, void* y, float* row_max, float* row_sum, int in_dtype, int out_dtype,
+                     int64_t rows, int64_t cols, void* scratch, size_t scratch_bytes, void* stream);
+IB200_API size_t ib200_softmax_scratch_bytes(int dtype, int64_t rows, int64_t cols);
+IB200_API int ib200_norm_rows_ws(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                       int dtype, int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner,
+                       int64_t affine_period, float eps, void* scratch, size_t scratch_bytes, void* stream);
+IB200_API size_t ib200_norm_scratch_bytes(int dtype, int64_t rows, int64_t cols);
+
 /* softmax(where(mask, x, fill)) over f32 rows of at most 16384 elements, the mask applied as each row
  * is loaded (the masked scores are never written): mask holds one byte per element (0 = replace by
  * `fill`), row r starting at mask + r * mask_row_stride, so 0 shares one mask vector between all rows

@@ -57,6 +57,10 @@ SIGNATURES = {
     "ib200_norm_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _i64, _f, _vp]),
     "ib200_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _f, _vp]),
     "ib200_groupnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _f, _vp]),
+    "ib200_softmax_ws": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _vp, _sz, _vp]),
+    "ib200_softmax_scratch_bytes": (_sz, [_i, _i64, _i64]),
+    "ib200_norm_rows_ws": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _i64, _f, _vp, _sz, _vp]),
+    "ib200_norm_scratch_bytes": (_sz, [_i, _i64, _i64]),
     "ib200_gemm_bias_act": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _i, _i, _vp, _vp]),
     "ib200_gemm_bias_act_ws": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _i, _i, _i, _vp, _sz, _vp, _vp]),
     "ib200_gemm_scratch_bytes": (_sz, [_i, _i, _i64, _i64, _i64, _i, _i]),

@@ -60,6 +60,22 @@ int ib200_softmax_masked(const void* x, const void* mask, int64_t mask_row_strid
   return launch_softmax(x, y, row_max, row_sum, IB200_F32, rows, cols, static_cast<cudaStream_t>(stream), IB200_F32, &mk);
 }
 
+int ib200_softmax_ws(const void* x, void* y, float* row_max, float* row_sum, int in_dtype, int out_dtype, int64_t rows, int64_t cols,
+                     void* scratch, size_t scratch_bytes, void* stream) {
+  if (scratch && (reinterpret_cast<uintptr_t>(scratch) & 15u)) return fail(IB200_ERR_INVALID, "softmax_ws: scratch must be 16-byte aligned");
+  return launch_softmax(x, y, row_max, row_sum, in_dtype, rows, cols, static_cast<cudaStream_t>(stream), out_dtype, nullptr, scratch, scratch_bytes);
+}
+size_t ib200_softmax_scratch_bytes(int dtype, int64_t rows, int64_t cols) { return softmax_scratch_bytes(rows, cols, dtype == IB200_F32 ? 4 : 2); }
+
+int ib200_norm_rows_ws(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int affine_dtype,
+                       int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps, void* scratch,
+                       size_t scratch_bytes, void* stream) {
+  if (scratch && (reinterpret_cast<uintptr_t>(scratch) & 15u)) return fail(IB200_ERR_INVALID, "norm_rows_ws: scratch must be 16-byte aligned");
+  return launch_norm_rows(x, w, b, y, mean, rstd, dtype, affine_dtype, rows, cols, affine_inner, affine_period, eps,
+                          static_cast<cudaStream_t>(stream), nullptr, true, nullptr, nullptr, scratch, scratch_bytes);
+}
+size_t ib200_norm_scratch_bytes(int dtype, int64_t rows, int64_t cols) { return norm_scratch_bytes(rows, cols, dtype == IB200_F32 ? 4 : 2); }
+
 int ib200_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int affine_dtype,
                     int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps, void* stream) {
   return launch_norm_rows(x, w, b, y, mean, rstd, dtype, affine_dtype, rows, cols, affine_inner, affine_period, eps,

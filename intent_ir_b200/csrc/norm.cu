@@ -668,13 +668,18 @@ int32_t* norm_default_status() {
 
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype,
                      int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps,
-                     cudaStream_t s, int32_t* status, bool centre, const void* res, const void* res_bias) {
+                     cudaStream_t s, int32_t* status, bool centre, const void* res, const void* res_bias, void* scratch, size_t scratch_bytes) {
   if (!status) status = norm_default_status();
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "norm: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
   if (!x || !y) return fail(IB200_ERR_INVALID, "norm: null pointer");
   if ((w || b) && (affine_inner < 1 || affine_period < 1)) return fail(IB200_ERR_INVALID, "norm: affine_inner and affine_period must be >= 1");
   if (res_bias && !res) return fail(IB200_ERR_INVALID, "norm: a residual bias needs a residual");
+  if (scratch && !res) {  // few, very long rows: segments over the whole GPU (longrow.cu)
+    const int rc = try_norm_segmented(x, w, b, y, mean, rstd, dtype, affine_dtype, rows, cols, affine_inner, affine_period, eps, centre ? 1 : 0,
+                                      scratch, scratch_bytes, s);
+    if (rc != 1) return rc;
+  }
   Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status, centre ? 1 : 0, res, res_bias};
   const int adt = (w || b) ? affine_dtype : dtype;
   switch (dtype) {

@@ -224,6 +224,7 @@ class Planner {
     fuse_gemm_epilogues();
     fuse_softmax_masks();
     fuse_rows();
+    add_long_row_scratch();
     finish();
     return std::move(plan_);
   }
@@ -795,6 +796,19 @@ class Planner {
       else return false;
     }
     return true;
+  }
+
+  // softmax / normalisation over rows too long for the resident kernels and too few (or too large) for one streaming
+  // CTA per row: the rows are cut into segments, whose statistics travel through the workspace
+  void add_long_row_scratch() {
+    for (Step& s : plan_->steps) {
+      size_t bytes = 0;
+      if (s.kind == Step::SOFTMAX && s.reduce_kind == 0) bytes = softmax_scratch_bytes(s.d[0], s.d[1], (int)dtype_size(s.dtype));
+      else if (s.kind == Step::NORM && s.idx_buf.empty()) bytes = norm_scratch_bytes(s.d[0], s.d[1], (int)dtype_size(s.dtype));
+      if (bytes == 0 || s.scratch >= 0) continue;
+      s.scratch = new_workspace_buffer(IB200_U8, (int64_t)bytes, "row segment statistics");
+      s.label += "(segmented)";
+    }
   }
 
   // reductions whose results alone give too few CTAs are split along the reduced axis; the partial results go through the workspace
@@ -2843,14 +2857,16 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
       case Step::SOFTMAX: {
         const SoftmaxMask mk{static_cast<const uint8_t*>(st.reduce_kind ? P(st.in[1]) : nullptr), st.aff_inner, (float)st.other, 0};
         rc = launch_softmax(P(st.in[0]), P(st.out[0]), static_cast<float*>(P(st.out[1])), static_cast<float*>(P(st.out[2])), st.dtype,
-                            st.d[0], st.d[1], s, st.dtype2, st.reduce_kind ? &mk : nullptr);
+                            st.d[0], st.d[1], s, st.dtype2, st.reduce_kind ? &mk : nullptr, st.scratch >= 0 ? P(st.scratch) : nullptr,
+                            st.scratch >= 0 ? plan->buffers[st.scratch].bytes : 0);
         break;
       }
       case Step::NORM:
         rc = launch_norm_rows(P(st.in[0]), P(st.in[1]), P(st.in[2]), P(st.out[0]), static_cast<float*>(P(st.out[1])),
                               static_cast<float*>(P(st.out[2])), st.dtype, st.dtype2, st.d[0], st.d[1], st.aff_inner, st.aff_period,
                               st.eps, s, status, st.act != 0, st.idx_buf.size() > 0 ? P(st.idx_buf[0]) : nullptr,
-                              st.idx_buf.size() > 1 ? P(st.idx_buf[1]) : nullptr);
+                              st.idx_buf.size() > 1 ? P(st.idx_buf[1]) : nullptr, st.scratch >= 0 ? P(st.scratch) : nullptr,
+                              st.scratch >= 0 ? plan->buffers[st.scratch].bytes : 0);
         break;
       case Step::GEMM:
         for (int64_t bi = 0; bi < st.batch && rc == IB200_OK; ++bi)

@@ -8,7 +8,9 @@
 //   cols <= 1024          : one warp per row (no block barrier at all);
 //   cols <= 16384         : one CTA per row, 256..1024 threads, 8..16 elements per thread;
 //   larger rows           : one CTA per row streaming the row three times (the second and
-//                           third pass hit L2).
+//                           third pass hit L2); with scratch memory, rows too few to fill the
+//                           GPU that way (or too large for L2) are cut into segments, one CTA
+//                           each, in two launches (longrow.cu).
 //
 // Non-finite inputs need no special cases: IEEE arithmetic gives what numpy gives — a row
 // holding NaN or +Inf, or only -Inf, becomes all-NaN; -Inf beside finite values gives 0.
@@ -215,12 +217,16 @@ int run(const void* xv, void* yv, float* mx, float* sm, int64_t rows, int64_t co
 }  // namespace
 
 int launch_softmax(const void* x, void* y, float* row_max, float* row_sum, int dtype, int64_t rows, int64_t cols,
-                   cudaStream_t s, int out_dtype, const SoftmaxMask* mask) {
+                   cudaStream_t s, int out_dtype, const SoftmaxMask* mask, void* scratch, size_t scratch_bytes) {
   const SoftmaxMask mk = mask ? *mask : SoftmaxMask{nullptr, 0, 0.0f, 0};
   if (out_dtype < 0) out_dtype = dtype;
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "softmax: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
   if (!x || !y) return fail(IB200_ERR_INVALID, "softmax: null pointer");
+  if (!mk.mask && scratch) {  // few, very long rows: segments over the whole GPU
+    const int rc = try_softmax_segmented(x, y, row_max, row_sum, dtype, out_dtype, rows, cols, scratch, scratch_bytes, s);
+    if (rc != 1) return rc;
+  }
   if (dtype == IB200_F32 && out_dtype == IB200_F32) return run<float, float>(x, y, row_max, row_sum, rows, cols, s, mk);
   if (dtype == IB200_BF16 && out_dtype == IB200_BF16) return run<__nv_bfloat16, __nv_bfloat16>(x, y, row_max, row_sum, rows, cols, s, mk);
   if (dtype == IB200_F16 && out_dtype == IB200_F16) return run<__half, __half>(x, y, row_max, row_sum, rows, cols, s, mk);

@@ -819,3 +819,75 @@ def test_reductions_over_leading_axes_are_split_over_the_gpu(op, shape, dims):
         _agree(first, want, infer_tolerances(intent).to_dict(), "split column sum")
     else:
         assert np.array_equal(first, want, equal_nan=True)
+
+
+# ---- few, very long rows: segments over the whole GPU --------------------------------------------------------
+
+@pytest.mark.parametrize("m,n,dtype", [(4, 1 << 20, "f32"), (1, 20000, "f32"), (3, 100003, "f32"), (2, 65536 + 4, "bf16"), (300, 1 << 17, "f32")])
+def test_softmax_over_few_very_long_rows_is_segmented(m, n, dtype, golden_graphs):
+    from intent_ir_b200.backend import round_to_bf16
+
+    js = json.loads(json.dumps(golden_graphs["softmax_inner"]["intent"]))
+    js["tensors"]["input_ptr"]["dtype"] = dtype  # a 16-bit input with an f32 result, as the sweep declares it
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(m + n)
+    x = 3 * rng.standard_normal((m, n), dtype=np.float32)
+    if dtype == "bf16":
+        x = round_to_bf16(x)
+    x[0, : n // 3] = -np.inf  # whole segments of -inf beside finite ones: exact zeros, no NaN
+    if m > 1:
+        x[1, n - 1] = 40.0  # the row maximum sits in the last segment
+    if m > 2:
+        x[2, 12345] = np.nan  # numpy: the whole row becomes NaN
+    if m > 3:
+        x[3, :] = -np.inf  # numpy: all NaN
+    out, lowered = _lower_and_run(intent, {"M": m, "N": n}, {"input_ptr": x})
+    assert [s["kernel"] for s in lowered.steps] == ["softmax(segmented)"]
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, {"input_ptr": x}, {"M": m, "N": n})["output_ptr"]
+    _agree(out["output_ptr"], want, infer_tolerances(intent).to_dict(), "segmented softmax")
+    assert np.all(out["output_ptr"][0, : n // 3] == 0)
+    again, _ = _lower_and_run(intent, {"M": m, "N": n}, {"input_ptr": x})
+    assert np.array_equal(out["output_ptr"], again["output_ptr"], equal_nan=True)  # a fixed folding order: the same bits every run
+
+
+@pytest.mark.parametrize("m,n", [(4, 1 << 20), (2, 40000), (3, 100003), (1, 131072 + 8)])
+def test_layernorm_over_few_very_long_rows_is_segmented(m, n, golden_graphs):
+    intent = IntentFunction.from_json_dict(golden_graphs["layer_norm_persistent"]["intent"])
+    rng = np.random.default_rng(m * 7 + n)
+    x = (rng.standard_normal((m, n), dtype=np.float32) * np.float32(2.0) + np.float32(5.0)).astype(np.float32)  # a mean far from zero
+    x[0, : n // 2] += np.float32(100.0)  # segment means far apart: the merge of segment moments has to carry it
+    w = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    b = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    ins = {"in_ptr": x, "weight_ptr": w, "bias_ptr": b}
+    out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
+    assert [s["kernel"] for s in lowered.steps] == ["layernorm(segmented)"]
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, ins, {"M": m, "N": n})
+    tol = infer_tolerances(intent).to_dict()
+    for name in ("out_ptr", "out_mean_ptr", "out_rstd_ptr"):
+        _agree(out[name], want[name], tol, name)
+    x64 = x.astype(np.float64)
+    assert np.allclose(out["out_mean_ptr"], x64.mean(axis=1), rtol=1e-6)
+    assert np.allclose(out["out_rstd_ptr"], 1.0 / np.sqrt(x64.var(axis=1) + 1e-5), rtol=1e-5)
+
+
+def test_rmsnorm_and_groupnorm_over_very_long_rows_are_segmented(golden_graphs):
+    rng = np.random.default_rng(5)
+    intent = IntentFunction.from_json_dict(golden_graphs["rms_norm2d"]["intent"])
+    m, n = 2, 300000
+    ins = {"inp": rng.standard_normal((m, n), dtype=np.float32), "weight": rng.uniform(0.5, 1.5, n).astype(np.float32)}
+    out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
+    assert [s["kernel"] for s in lowered.steps] == ["rmsnorm(segmented)"]
+    want = execute_intent(intent, ins, {"M": m, "N": n})
+    for name in intent.outputs:
+        _agree(out[name], want[name], infer_tolerances(intent).to_dict(), name)
+    # one group of 8 channels x 65536 positions: rows of 512 Ki elements with a per-channel affine
+    gn = IntentFunction.from_json_dict(golden_graphs["group_norm_kernel"]["intent"])
+    shapes = {"N": 2, "C": 16, "HW": 65536, "num_groups": 2}
+    ins = {"X": rng.standard_normal((2, 16, 65536), dtype=np.float32), "W": rng.standard_normal(16, dtype=np.float32), "B": rng.standard_normal(16, dtype=np.float32)}
+    out, lowered = _lower_and_run(gn, shapes, ins)
+    assert [s["kernel"] for s in lowered.steps] == ["groupnorm(segmented)"]
+    want = execute_intent(gn, ins, derive_bindings(shapes))
+    for name in gn.outputs:
+        _agree(out[name], want[name], infer_tolerances(gn).to_dict(), name)
