@@ -472,7 +472,7 @@ def sweep_checker(which):
 
 
 def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto", groupnorm_every=0, max_elements=SWEEP_MAX_ELEMENTS):
-    """The verification sweep on `total` seeded cases (base seed 1000), partitioned over the ranks by
+    """The verification sweep on `total` seeded cases (base seed 1000), dealt to the ranks family by family in order of
     estimated cost; each rank keeps its GPU in this process and checks in `threads_per_rank - 1`
     child processes pinned to the rank's own cores.  Wall-clock, max over ranks.  Returns the block on
     rank 0, None elsewhere."""
@@ -499,7 +499,7 @@ def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto
         if dist:
             dist.barrier()
         t0 = time.perf_counter()
-        records = run_sweep(cases, rank=rank, world=world, out_dir=out_dir, partition="lpt", pool=pool, **chk)
+        records = run_sweep(cases, rank=rank, world=world, out_dir=out_dir, partition="deal", pool=pool, **chk)
         torch.cuda.synchronize()
         dt_own = time.perf_counter() - t0
     finally:
@@ -527,7 +527,7 @@ def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto
     gpu_s = sum((r.get("t_gpu") or 0.0) for part in gathered for r in part)
     cps = summary["ok"] / dt
     block = {"cases_per_s": round(cps, 2), "cases": summary["cases"], "ok": summary["ok"], "wall_s": round(dt, 2), "rank_wall_s": rank_s,
-             "scaling": "strong", "partition": "lpt by estimated host cost", "max_elements": max_elements, "base_seed": 1000,
+             "scaling": "strong", "partition": "longest estimated case first, family by family", "max_elements": max_elements, "base_seed": 1000,
              "threads_per_rank": budget, "checker_processes_per_rank": workers, "host_cores": len(cores), "blas_threads": 1,
              "checker": label, "gpu_busy_fraction": round(gpu_s / (dt * world), 4), "failed": summary["failed"][:3],
              "by_kind": {k: f"{v['ok']}/{v['cases']}" for k, v in summary["by_kind"].items()}}

@@ -407,22 +407,38 @@ def estimate_cost(case: SweepCase) -> float:
 
 
 def partition_cases(cases: Sequence[SweepCase], world: int, how: str = "mod") -> List[List[int]]:
-    """Positions of ``cases`` per rank.  ``"mod"``: case i -> rank i % world.  ``"lpt"``: longest
-    estimated case first onto the least loaded rank (ties by rank), which every rank computes
-    identically from the case list alone — no communication."""
+    """Positions of ``cases`` per rank, computed identically by every rank from the case list alone — no
+    communication.  ``"mod"``: case i -> rank i % world.  ``"lpt"``: longest estimated case first onto the
+    least loaded rank.  ``"deal"``: the same longest-first rule applied family by family (ties go to the
+    rank with the smaller total), so that every rank holds an equal share of EACH graph family: within a
+    family the estimate is proportional to the element count and reliable, while the weights between families
+    (which depend on the checker and the host) no longer matter for the balance."""
     world = max(1, int(world))
     if how == "mod":
         return [list(range(r, len(cases), world)) for r in range(world)]
-    if how != "lpt":
-        raise ValueError(f"unknown partition {how!r}")
-    order = sorted(range(len(cases)), key=lambda i: (-estimate_cost(cases[i]), i))
-    load = [0.0] * world
     parts: List[List[int]] = [[] for _ in range(world)]
-    for i in order:
-        r = min(range(world), key=lambda q: (load[q], q))
-        parts[r].append(i)
-        load[r] += estimate_cost(cases[i])
-    return parts
+    if how == "lpt":
+        order = sorted(range(len(cases)), key=lambda i: (-estimate_cost(cases[i]), i))
+        load = [0.0] * world
+        for i in order:
+            r = min(range(world), key=lambda q: (load[q], q))
+            parts[r].append(i)
+            load[r] += estimate_cost(cases[i])
+        return parts
+    if how != "deal":
+        raise ValueError(f"unknown partition {how!r}")
+    by_kind: Dict[str, List[int]] = {}
+    for i, c in enumerate(cases):
+        by_kind.setdefault(c.kind, []).append(i)
+    total = [0.0] * world
+    for kind in sorted(by_kind):
+        mine = [0.0] * world  # this family's load per rank
+        for i in sorted(by_kind[kind], key=lambda j: (-estimate_cost(cases[j]), j)):
+            r = min(range(world), key=lambda q: (mine[q], total[q], q))
+            parts[r].append(i)
+            mine[r] += estimate_cost(cases[i])
+            total[r] += estimate_cost(cases[i])
+    return [sorted(p) for p in parts]
 
 
 def _check_case(case: SweepCase, runner_of: Callable, diff_fn: Callable, tolerances_fn: Callable, case_type: type,

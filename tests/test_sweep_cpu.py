@@ -197,3 +197,11 @@ def test_lpt_partition_is_deterministic_and_balanced():
     loads = [sum(estimate_cost(cases[i]) for i in p) for p in parts]
     assert max(loads) / min(loads) < 1.02
     assert partition_cases(cases, 4, "mod")[1][:3] == [1, 5, 9]
+    # the deal: every rank gets an equal share of every family's load
+    deal = partition_cases(cases, 8, "deal")
+    assert sorted(i for p in deal for i in p) == list(range(512)) and deal == partition_cases(cases, 8, "deal")
+    for kind in {c.kind for c in cases}:  # every family's load is balanced by itself
+        per_rank = [sum(estimate_cost(cases[i]) for i in p if cases[i].kind == kind) for p in deal]
+        assert max(per_rank) / min(per_rank) < 1.25, (kind, per_rank)
+    loads = [sum(estimate_cost(cases[i]) for i in p) for p in deal]
+    assert max(loads) / min(loads) < 1.05
