@@ -87,5 +87,8 @@ struct EwProgram {
 };
 
 int launch_elementwise(const EwProgram& prog, cudaStream_t s);
+// The same program with every value carried as a double: exact for f64 tensors and for integers up to 2^53, which
+// the f32 lanes of the kernels above are not.  `imm` holds the kEwMaxInstr immediates at full precision.
+int launch_elementwise_wide(const EwProgram& prog, const double* imm, cudaStream_t s);
 
 }  // namespace ib200

@@ -175,6 +175,8 @@ struct Step {
   int64_t batch = 1, batch_stride[3] = {0, 0, 0};  // batched matmul: elements between consecutive A / B / C matrices
   int scratch = -1;  // REDUCE: workspace buffer for the split-row kernel (few, long rows), or -1; GEMM: for the K-split tail tiles
   int flags = 0;     // GEMM: IB200_GEMM_* options
+  bool wide = false;  // ELEMENTWISE: values are carried as doubles (f64 tensors, 32/64-bit integers): ew_imm holds the immediates
+  std::vector<double> ew_imm;
   std::vector<int> idx_buf;  // GATHER: index buffers; NORM: {residual[, residual bias]} summed while the rows are loaded
   Shape g_dim, g_stride;
   double other = 0.0;     // gather: fill value; dropout: p when it is a constant
@@ -1370,17 +1372,42 @@ class Planner {
       return;
     }
     if (op == "reduce_sum" || op == "reduce_max" || op == "reduce_any") {
-      const Shape xs = nodes_[n.in[0]].shape;
+      Shape xs = nodes_[n.in[0]].shape;
       if (n.axes.empty()) {  // nothing to reduce (rank-0 input): the value itself
         n.repr = Node::EXPR; n.op = op == "reduce_any" ? "cast" : "identity"; n.cast_to = IB200_BOOL;
         return;
       }
-      for (size_t i = 1; i < n.axes.size(); ++i)
-        if (n.axes[i] != n.axes[i - 1] + 1) {
-          // non-adjacent axes are fine when everything between them has extent 1
-          for (int a = n.axes[i - 1] + 1; a < n.axes[i]; ++a)
-            if (xs[a] != 1) throw Unsupported(op + " over non-adjacent axes of " + shape_str(xs) + " is not covered");
+      // The kernels reduce one run of adjacent axes ([outer, reduced, inner]).  Axes that are not adjacent (gaps of
+      // extent 1 do not count) are reduced run by run, the last run first, so that the indices of the earlier runs stay
+      // valid: np.sum / np.max / np.any over several axes (verify/interpreter.py:478-500) is the same nested reduction.
+      {
+        std::vector<std::pair<int, int>> runs;
+        for (int a : n.axes) {
+          bool joins = !runs.empty();
+          for (int g = joins ? runs.back().second + 1 : a; joins && g < a; ++g) joins = xs[g] == 1;
+          if (joins) runs.back().second = a;
+          else runs.emplace_back(a, a);
         }
+        Shape cur = xs;
+        while (runs.size() > 1) {
+          const std::pair<int, int> run = runs.back();
+          runs.pop_back();
+          Node m;
+          m.op = op;
+          m.in = {nodes_[id].in[0]};
+          m.dclass = op == "reduce_any" ? DC_BOOL : DC_FLOAT;
+          for (int a = run.first; a <= run.second; ++a) m.axes.push_back(a);
+          for (int a = 0; a < (int)cur.size(); ++a)
+            if (a < run.first || a > run.second) m.shape.push_back(cur[a]);
+          const int mid = add(m);
+          lower_node(mid);
+          Node& self = nodes_[id];
+          self.in[0] = mid;
+          self.axes.erase(std::remove_if(self.axes.begin(), self.axes.end(), [&](int a) { return a >= run.first; }), self.axes.end());
+          cur = nodes_[mid].shape;
+        }
+        xs = cur;  // what is left: one run of adjacent axes of the partly reduced tensor
+      }
       materialise_contiguous(n.in[0]);
       const Node& x = nodes_[n.in[0]];
       const int xdt = plan_->buffers[x.view.buffer].dtype;
@@ -1412,7 +1439,41 @@ class Planner {
       if (n.axis != (int)n.shape.size() - 1) {
         bool trailing_units = true;
         for (int a = n.axis + 1; a < (int)n.shape.size(); ++a) trailing_units &= n.shape[a] == 1;
-        if (!trailing_units) throw Unsupported("softmax over a non-trailing axis is not covered");
+        if (!trailing_units) {
+          // softmax along an axis that is not the innermost one (verify/interpreter.py:501-506 takes any axis): the
+          // rows are strided, so it is computed as the interpreter writes it — max over the axis, exp(x - max), sum
+          // over the axis, division — with the reduction kernels' [outer, reduced, inner] form and two elementwise passes
+          const int x = n.in[0], ax = n.axis;
+          const Shape full = n.shape;
+          auto reduce_over_axis = [&](const char* rop, int src) {
+            Node r;
+            r.op = rop;
+            r.in = {src};
+            r.axes = {ax};
+            r.keepdims = true;
+            r.shape = full;
+            r.shape[ax] = 1;
+            r.dclass = DC_FLOAT;
+            const int rid = add(r);
+            lower_node(rid);
+            return rid;
+          };
+          const int mx = reduce_over_axis("reduce_max", x);
+          Node d;
+          d.op = "sub"; d.in = {x, mx}; d.shape = full; d.dclass = DC_FLOAT;
+          const int di = add(d);
+          lower_node(di);
+          Node e;
+          e.op = "exp"; e.in = {di}; e.shape = full; e.dclass = DC_FLOAT;
+          const int ei = add(e);
+          lower_node(ei);
+          const int sm = reduce_over_axis("reduce_sum", ei);  // materialises exp(x - max) once; the division reads it back
+          Node& self = nodes_[id];
+          self.op = "div";
+          self.in = {ei, sm};
+          self.repr = Node::EXPR;
+          return;
+        }
       }
       materialise_contiguous(n.in[0]);
       const Node& x = nodes_[n.in[0]];
@@ -1690,6 +1751,8 @@ class Planner {
     std::vector<int> free_slots;
     int acc_holds = -1;
     bool failed = false;
+    double imm_d[kEwMaxInstr] = {};  // every instruction's immediate at full precision (the wide kernel reads these)
+    double last_imm_d = 0.0;
   };
 
   static uint8_t ew_opcode(const Node& n) {
@@ -1726,10 +1789,11 @@ class Planner {
   uint8_t operand(int id, Gen& g, const Shape& root_shape, float& imm, bool& has_imm, bool force_slot) {
     Node& n = nodes_[id];
     if (n.repr == Node::CONSTANT) {
-      if (has_imm && imm != (float)n.cval) {  // one immediate per instruction: stage this one through ACC/slot
-        return stage_constant((float)n.cval, g, force_slot);
+      if (has_imm && (imm != (float)n.cval || g.last_imm_d != n.cval)) {  // one immediate per instruction: stage this one through ACC/slot
+        return stage_constant(n.cval, g, force_slot);
       }
       imm = (float)n.cval;
+      g.last_imm_d = n.cval;
       has_imm = true;
       return EW_IMM;
     }
@@ -1748,11 +1812,12 @@ class Planner {
     return EW_ACC;
   }
 
-  uint8_t stage_constant(float v, Gen& g, bool force_slot) {
+  uint8_t stage_constant(double v, Gen& g, bool force_slot) {
     if (g.prog.n_instr >= kEwMaxInstr) { g.failed = true; return EW_ACC; }
+    g.imm_d[g.prog.n_instr] = v;
     EwInstr& ins = g.prog.instr[g.prog.n_instr++];
     ins = EwInstr{};
-    ins.op = EW_MOV; ins.a = EW_IMM; ins.b = EW_IMM; ins.c = EW_IMM; ins.imm = v; ins.dst = EW_NODST;
+    ins.op = EW_MOV; ins.a = EW_IMM; ins.b = EW_IMM; ins.c = EW_IMM; ins.imm = (float)v; ins.dst = EW_NODST;
     g.acc_holds = -1;
     if (force_slot) { ins.dst = (uint8_t)alloc_slot(g); return ins.dst; }
     return EW_ACC;
@@ -1834,7 +1899,7 @@ class Planner {
         // park whatever ACC holds if one of our operands lives there
         for (int c : n.in)
           if (g.acc_holds == c && !g.value_slot.count(c)) park_acc(c, g);
-        staged[k] = stage_constant((float)nodes_[n.in[k]].cval, g, true);
+        staged[k] = stage_constant(nodes_[n.in[k]].cval, g, true);
         if (g.failed) return;
       }
     }
@@ -1861,6 +1926,7 @@ class Planner {
       g.value_slot[id] = ins.dst;
     }
     if (g.prog.n_instr >= kEwMaxInstr) { g.failed = true; return; }
+    g.imm_d[g.prog.n_instr] = has_imm ? g.last_imm_d : 0.0;
     g.prog.instr[g.prog.n_instr++] = ins;
     g.acc_holds = id;
   }
@@ -1908,7 +1974,7 @@ class Planner {
         o.src = operand(roots[i], g, root_shape, imm, has_imm, !last);
         if (o.src == EW_ACC && !last) g.failed = true;
       } else if (n.repr == Node::CONSTANT) {
-        o.src = stage_constant((float)n.cval, g, !last);
+        o.src = stage_constant(n.cval, g, !last);
       } else {
         o.src = (uint8_t)g.leaf_slot.at(roots[i]);
       }
@@ -1952,6 +2018,15 @@ class Planner {
     s.ew_in_buf = g.in_buf;
     s.ew_in_off = g.in_off;
     s.ew_out_buf = bufs;
+    // f64 values and 32- / 64-bit integers do not fit the kernels' f32 registers (24 bits of mantissa): such programs run on
+    // the double-valued kernel — exact for f64 and for integers up to 2^53
+    auto needs_wide = [](int dt) { return dt == IB200_F64 || dt == IB200_I32 || dt == IB200_I64; };
+    for (int k = 0; k < p.n_inputs; ++k) s.wide |= p.in[k].kind == EW_IN_TENSOR ? needs_wide(p.in[k].dtype) : p.total >= ((int64_t)1 << 24);
+    for (int o = 0; o < p.n_outputs; ++o) s.wide |= needs_wide(p.out[o].dtype);
+    if (s.wide) {
+      s.ew_imm.assign(g.imm_d, g.imm_d + kEwMaxInstr);
+      s.label += "(f64 lanes)";
+    }
     plan_->steps.push_back(s);
     for (size_t i = 0; i < roots.size(); ++i) {
       set_strided(roots[i], bufs[i]);
@@ -1970,7 +2045,7 @@ class Planner {
     for (size_t i = 0; i + 1 < steps.size(); ++i) {
       Step& g = steps[i];
       const Step& e = steps[i + 1];
-      if (g.kind != Step::GEMM || g.batch != 1 || g.in[2] >= 0 || g.act != IB200_ACT_NONE || e.kind != Step::ELEMENTWISE) continue;
+      if (g.kind != Step::GEMM || g.batch != 1 || g.in[2] >= 0 || g.act != IB200_ACT_NONE || e.kind != Step::ELEMENTWISE || e.wide) continue;
       const int gb = g.out[0];
       if (plan_->buffers[gb].is_arg) continue;
       bool used_elsewhere = false;
@@ -2028,7 +2103,7 @@ class Planner {
     for (size_t i = 0; i + 1 < steps.size(); ++i) {
       const Step& e = steps[i];
       Step& sm = steps[i + 1];
-      if (e.kind != Step::ELEMENTWISE || sm.kind != Step::SOFTMAX || sm.reduce_kind != 0) continue;
+      if (e.kind != Step::ELEMENTWISE || e.wide || sm.kind != Step::SOFTMAX || sm.reduce_kind != 0) continue;
       const EwProgram& q = e.ew;
       const int64_t R = sm.d[0], C = sm.d[1];
       if (q.n_outputs != 1 || q.n_inputs != 2 || q.n_instr != 1 || q.instr[0].op != EW_WHERE || q.out[0].src != EW_ACC) continue;
@@ -2104,7 +2179,7 @@ class Planner {
   static bool row_candidate(const Step& s, int64_t R, int64_t C) {
     int64_t r, c;
     if (row_anchor(s, r, c)) return r == R && c == C;
-    if (s.kind != Step::ELEMENTWISE) return false;
+    if (s.kind != Step::ELEMENTWISE || s.wide) return false;  // row programs carry f32 values
     return s.ew.total == R * C || s.ew.total == R;
   }
 
@@ -2924,7 +2999,7 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
           vec &= aligned16(prog.out[o].ptr);
         }
         prog.vec = vec;
-        rc = launch_elementwise(prog, s);
+        rc = st.wide ? launch_elementwise_wide(prog, st.ew_imm.data(), s) : launch_elementwise(prog, s);
         break;
       }
       case Step::ROWFUSE: {

@@ -320,3 +320,24 @@ def test_gemm_plans_cover_every_float_operand_type(golden_graphs):
     tf = _lib.GEMM_ALLOW_TF32
     assert lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 0, tf) == lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 1, tf) + 4096 * 4096 * 4
     assert lib.ib200_gemm_scratch_bytes(_lib.BF16, _lib.BF16, 128 * 37, 256 * 4, 4096, 0, 0) == 0  # 148 tiles: a full round
+
+
+def test_f64_and_wide_integer_chains_take_the_double_valued_kernel():
+    """The elementwise kernels carry values in f32 lanes, which hold neither f64 nor integers above 2^24:
+    programs that touch f64 / i32 / i64 tensors are marked for the double-valued kernel (and stay out of the
+    f32 row programs)."""
+    from intent_ir_b200.lowering import plan_json
+
+    def t(shape, dt):
+        return {"dtype": dt, "shape": shape, "layout": "row_major"}
+
+    def kernels(dt_in, dt_out, op="add"):
+        js = {"name": "g", "tensors": {"a": t(["M", "N"], dt_in), "b": t(["N"], dt_in), "y": t(["M", "N"], dt_out)},
+              "ops": [{"op": op, "inputs": ["a", "b"], "output": "y"}], "outputs": ["y"]}
+        return [s["kernel"] for s in plan_json(js, {"M": 8, "N": 16})["steps"]]
+
+    assert kernels("f64", "f64") == ["elementwise(1 ops, 2 in, 1 out)(f64 lanes)"]
+    assert kernels("i32", "i32", "mul") == ["elementwise(1 ops, 2 in, 1 out)(f64 lanes)"]
+    assert kernels("i64", "bool", "lt") == ["elementwise(1 ops, 2 in, 1 out)(f64 lanes)"]
+    assert kernels("f32", "f32") == ["elementwise(1 ops, 2 in, 1 out)"]
+    assert kernels("i8", "i8") == ["elementwise(1 ops, 2 in, 1 out)"]  # 8- and 16-bit integers are exact in f32 lanes

@@ -894,3 +894,119 @@ def test_rmsnorm_and_groupnorm_over_very_long_rows_are_segmented(golden_graphs):
     want = execute_intent(gn, ins, derive_bindings(shapes))
     for name in gn.outputs:
         _agree(out[name], want[name], infer_tolerances(gn).to_dict(), name)
+
+
+# ---- f64 tensors and 32- / 64-bit integers: exact, through the double-valued elementwise kernel ------------------
+
+def test_f64_elementwise_graph_matches_numpy_to_the_last_bit():
+    js = {"name": "f64_chain", "tensors": {"a": _t(["M", "N"], "f64"), "b": _t(["N"], "f64"), "y": _t(["M", "N"], "f64"), "z": _t(["M", "N"], "f64")},
+          "ops": [{"op": "add", "inputs": ["a", "b"], "output": "s"},
+                  {"op": "mul", "inputs": ["s"], "output": "y", "attrs": {"mul_factor": 1.0000000001}},
+                  {"op": "sub", "inputs": ["y", "a"], "output": "d"},
+                  {"op": "max", "inputs": ["d", "b"], "output": "z"}], "outputs": ["y", "z"]}
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(8)
+    a = 1.0 + 1e-12 * rng.standard_normal((37, 53))  # differences far below f32 resolution
+    b = 1e-9 * rng.standard_normal(53)
+    b[3] = np.nan
+    out, lowered = _lower_and_run(intent, {"M": 37, "N": 53}, {"a": a, "b": b})
+    assert all(s["kernel"].endswith("(f64 lanes)") for s in lowered.steps)
+    want = execute_intent(intent, {"a": a, "b": b}, {"M": 37, "N": 53})
+    for name in ("y", "z"):
+        assert out[name].dtype == np.float64 and want[name].dtype == np.float64
+        assert np.array_equal(out[name], want[name], equal_nan=True), name
+    assert len(np.unique(out["y"])) > 1000  # the values really differ below f32 resolution
+
+
+@pytest.mark.parametrize("dt,np_dt,big", [("i32", np.int32, 1 << 30), ("i64", np.int64, 1 << 45)])
+def test_integer_elementwise_arithmetic_is_exact_beyond_2_to_24(dt, np_dt, big):
+    js = {"name": "int_chain", "tensors": {"a": _t(["M", "N"], dt), "b": _t(["N"], dt), "s": _t(["M", "N"], dt), "p": _t(["M", "N"], dt),
+                                           "lt": _t(["M", "N"], "bool"), "w": _t(["M", "N"], dt)},
+          "ops": [{"op": "add", "inputs": ["a", "b"], "output": "s"},
+                  {"op": "mul", "inputs": ["b"], "output": "b3", "attrs": {"mul_factor": 3}},
+                  {"op": "sub", "inputs": ["a", "b3"], "output": "p"},
+                  {"op": "lt", "inputs": ["a", "s"], "output": "lt"},
+                  {"op": "where", "inputs": ["lt", "s", "p"], "output": "w"}], "outputs": ["s", "p", "lt", "w"]}
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(9)
+    a = (big + rng.integers(-1000, 1000, size=(19, 40))).astype(np_dt)  # neighbours differ by 1: f32 lanes would merge them
+    b = rng.integers(-5, 6, size=40).astype(np_dt)
+    a[0, :4] = [(1 << 24) + 1, (1 << 24) + 3, -(1 << 24) - 1, 0]
+    out, lowered = _lower_and_run(intent, {"M": 19, "N": 40}, {"a": a, "b": b})
+    assert all(s["kernel"].endswith("(f64 lanes)") for s in lowered.steps)
+    want = execute_intent(intent, {"a": a, "b": b}, {"M": 19, "N": 40})
+    for name in ("s", "p", "lt", "w"):
+        assert np.array_equal(out[name].astype(np.int64), np.asarray(want[name]).astype(np.int64)), name
+    assert out["s"].dtype == np_dt and out["lt"].dtype == np.bool_
+
+
+def test_iota_index_arithmetic_over_a_large_extent_is_exact():
+    """Flattened indices of a [5000, 4000] tensor run to 2*10^7, past the 2^24 an f32 lane counts to."""
+    js = {"name": "flat_index", "tensors": {"y": _t(["M", "N"], "i32")},
+          "ops": [{"op": "iota", "inputs": [], "output": "r", "attrs": {"shape": ["M", "N"], "axis": 0, "dtype": "i32"}},
+                  {"op": "iota", "inputs": [], "output": "c", "attrs": {"shape": ["M", "N"], "axis": 1, "dtype": "i32"}},
+                  {"op": "mul", "inputs": ["r"], "output": "rn", "attrs": {"mul_factor": 4000}},
+                  {"op": "add", "inputs": ["rn", "c"], "output": "y"}], "outputs": ["y"]}
+    intent = IntentFunction.from_json_dict(js)
+    out, lowered = _lower_and_run(intent, {"M": 5000, "N": 4000}, {})
+    assert np.array_equal(out["y"].astype(np.int64).ravel(), np.arange(5000 * 4000, dtype=np.int64))
+
+
+# ---- graph forms the interpreter takes with any axis -----------------------------------------------------------
+
+@pytest.mark.parametrize("shape,axis,dtype", [((4, 100, 64), 1, "f32"), ((40, 64), 0, "f32"), ((3, 7, 5, 33), 2, "f32"), ((2, 1, 300, 17), -2, "bf16"),
+                                              ((1, 2, 3), 0, "f32"), ((16, 2048, 8), 1, "f32")])
+def test_softmax_over_a_non_trailing_axis(shape, axis, dtype):
+    from intent_ir_b200.backend import round_to_bf16
+
+    syms = [f"D{i}" for i in range(len(shape))]
+    js = {"name": "sm_axis", "tensors": {"x": _t(syms, dtype), "y": _t(syms, "f32")},
+          "ops": [{"op": "softmax", "inputs": ["x"], "output": "y", "attrs": {"axis": axis}}], "outputs": ["y"]}
+    intent = IntentFunction.from_json_dict(js)
+    bind = dict(zip(syms, shape))
+    x = 3 * np.random.default_rng(sum(shape)).standard_normal(shape).astype(np.float32)
+    if dtype == "bf16":
+        x = round_to_bf16(x)
+    if x.size > 10:
+        x.reshape(-1)[3] = -np.inf
+    out, lowered = _lower_and_run(intent, bind, {"x": x})
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, {"x": x}, bind)["y"]
+    _agree(out["y"], want, infer_tolerances(intent).to_dict(), "softmax axis")
+    assert np.allclose(out["y"].sum(axis=axis), 1.0, atol=1e-4)
+
+
+@pytest.mark.parametrize("op", ["reduce_sum", "reduce_max", "reduce_any"])
+@pytest.mark.parametrize("shape,dims,keepdims", [((4, 10, 6, 8), [0, 2], False), ((4, 10, 6, 8), [1, 3], True), ((3, 5, 7, 2, 9), [0, 2, 4], False),
+                                                 ((33, 1, 17, 65), [0, 2], False), ((2, 3, 4), [0, 2], True), ((64, 300, 5, 128), [0, 2], False)])
+def test_reductions_over_non_adjacent_axes(op, shape, dims, keepdims):
+    syms = [f"D{i}" for i in range(len(shape))]
+    out_shape = [1 if i in dims else s for i, s in enumerate(syms) if keepdims or i not in dims]
+    js = {"name": "r", "tensors": {"x": _t(syms), "y": _t(out_shape, "bool" if op == "reduce_any" else "f32")},
+          "ops": [{"op": op, "inputs": ["x"], "output": "y", "attrs": {"dims": dims, "keepdims": keepdims}}], "outputs": ["y"]}
+    intent = IntentFunction.from_json_dict(js)
+    bind = dict(zip(syms, shape))
+    rng = np.random.default_rng(sum(shape) + len(dims))
+    x = rng.standard_normal(shape).astype(np.float32)
+    if op == "reduce_any":
+        x = np.where(rng.random(shape) < 0.02, x, np.float32(0))
+    if op == "reduce_max":
+        x.reshape(-1)[5] = np.nan
+    out, lowered = _lower_and_run(intent, bind, {"x": x})
+    assert len(lowered.steps) >= 2 or 1 in shape
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, {"x": x}, bind)["y"]
+    _agree(out["y"], want, infer_tolerances(intent).to_dict(), op)
+
+
+def test_scaled_sum_over_three_separate_axes():
+    js = {"name": "r3", "tensors": {"x": _t(["A", "B", "C", "D", "E"]), "y": _t(["B", "D"])},
+          "ops": [{"op": "reduce_sum", "inputs": ["x"], "output": "y", "attrs": {"dims": [0, 2, 4], "scale": "1.0/(A*C*E)"}}], "outputs": ["y"]}
+    intent = IntentFunction.from_json_dict(js)
+    bind = {"A": 4, "B": 10, "C": 6, "D": 8, "E": 3}
+    x = np.random.default_rng(3).standard_normal((4, 10, 6, 8, 3)).astype(np.float32)
+    out, lowered = _lower_and_run(intent, bind, {"x": x})
+    assert [s["kernel"] for s in lowered.steps] == ["reduce_sum"] * 3
+    want = execute_intent(intent, {"x": x}, bind)["y"]
+    _agree(out["y"], want, infer_tolerances(intent).to_dict(), "mean over three axes")
+    assert np.allclose(out["y"], x.mean(axis=(0, 2, 4)), atol=1e-5)
