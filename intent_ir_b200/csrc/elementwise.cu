@@ -17,6 +17,8 @@
 #include <cuda_runtime.h>
 
 #include <cstdlib>
+#include <map>
+#include <string>
 
 #include "common.cuh"
 #include "ew_device.cuh"
@@ -239,13 +241,51 @@ struct EwRegCode {
   EwRegInstr ins[kEwMaxInstr + 1];
 };
 
+// The run-time form of the instruction loop: one uniform branch per field of the register code.
+struct InterpExec {
+  template <int NIN, int N, bool EXT>
+  __device__ __forceinline__ void run(const float (&in)[NIN > 0 ? NIN : 1][N], float (&acc)[N], const EwRegCode& code) const {
+    float tmp[EXT ? 2 : 1][N];  // values used more than once (extended form)
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = tmp[0][j] = tmp[EXT ? 1 : 0][j] = 0.0f;
+    for (int ip = 0; ip < code.n_instr; ++ip) {
+        const EwRegInstr ins = code.ins[ip];
+        if (EXT && ins.op == EW_WHERE) {  // acc = cond != 0 ? b : c, each an operand, the immediate, acc or a temporary
+          float sel[3][N];
+#pragma unroll
+          for (int q = 0; q < 3; ++q) {
+            const uint8_t src = q == 0 ? ins.src : q == 1 ? ins.b : ins.c;
+#pragma unroll
+            for (int j = 0; j < N; ++j)
+              sel[q][j] = src == 0 ? in[0][j] : src == 1 ? in[NIN > 1 ? 1 : 0][j] : src == 2 ? in[NIN > 2 ? 2 : 0][j] : src == 3 ? ins.imm
+                          : src == 4 ? acc[j] : src == 5 ? tmp[0][j] : tmp[1][j];
+          }
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] = sel[0][j] != 0.0f ? sel[1][j] : sel[2][j];
+        } else
+        switch (ins.src) {
+          case 0: apply<N>(ins.op, acc, in[0], acc); break;
+          case 1: if (NIN > 1) apply<N>(ins.op, acc, in[NIN > 1 ? 1 : 0], acc); break;
+          case 2: if (NIN > 2) apply<N>(ins.op, acc, in[NIN > 2 ? 2 : 0], acc); break;
+          case 3: apply_scalar<N>(ins.op, acc, ins.imm); break;
+          case 5: if (EXT) apply<N>(ins.op, acc, tmp[0], acc); break;
+          case 6: if (EXT) apply<N>(ins.op, acc, tmp[1], acc); break;
+          default: apply<N>(ins.op, acc, acc, acc);
+        }
+        if (EXT && ins.dst) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) tmp[ins.dst == 1 ? 0 : 1][j] = acc[j];
+        }
+      }
+  }
+};
+
 // EXT adds `where` and bool / u8 operands; it is a separate instantiation because that code costs
 // the plain arithmetic chains registers.  Occupancy is what this kernel lives on: the plain form
 // is held to 32 registers so that eight CTAs (all 64 warps) are resident per SM -- measured on the
 // 4-op broadcast chain: 0.68 of HBM peak at four CTAs per SM, 0.79 at six, 0.83 at eight.
-template <int NIN, int BMASK, int RANK, bool EXT>
-__global__ void __launch_bounds__(kThreads, EXT ? 5 : 8) ew_kernel_reg(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
-                                                             const __grid_constant__ EwRegCode code) {
+template <int NIN, int BMASK, int RANK, bool EXT, typename Exec>
+__device__ __forceinline__ void ew_reg_body(const EwProgram& prog, const EwDivs& divs, const EwRegCode& code, const Exec& exec) {
   constexpr int N = 8, U = 2;  // 16 values per thread were measured slower (half the resident warps)
   const int t = threadIdx.x;
   const char* ptr[NIN > 0 ? NIN : 1];
@@ -309,38 +349,7 @@ __global__ void __launch_bounds__(kThreads, EXT ? 5 : 8) ew_kernel_reg(const __g
       }
     }
     float acc[N];
-    float tmp[EXT ? 2 : 1][N];  // values used more than once (extended form)
-#pragma unroll
-    for (int j = 0; j < N; ++j) acc[j] = tmp[0][j] = tmp[EXT ? 1 : 0][j] = 0.0f;
-    for (int ip = 0; ip < code.n_instr; ++ip) {
-      const EwRegInstr ins = code.ins[ip];
-      if (EXT && ins.op == EW_WHERE) {  // acc = cond != 0 ? b : c, each an operand, the immediate, acc or a temporary
-        float sel[3][N];
-#pragma unroll
-        for (int q = 0; q < 3; ++q) {
-          const uint8_t src = q == 0 ? ins.src : q == 1 ? ins.b : ins.c;
-#pragma unroll
-          for (int j = 0; j < N; ++j)
-            sel[q][j] = src == 0 ? in[0][j] : src == 1 ? in[NIN > 1 ? 1 : 0][j] : src == 2 ? in[NIN > 2 ? 2 : 0][j] : src == 3 ? ins.imm
-                        : src == 4 ? acc[j] : src == 5 ? tmp[0][j] : tmp[1][j];
-        }
-#pragma unroll
-        for (int j = 0; j < N; ++j) acc[j] = sel[0][j] != 0.0f ? sel[1][j] : sel[2][j];
-      } else
-      switch (ins.src) {
-        case 0: apply<N>(ins.op, acc, in[0], acc); break;
-        case 1: if (NIN > 1) apply<N>(ins.op, acc, in[NIN > 1 ? 1 : 0], acc); break;
-        case 2: if (NIN > 2) apply<N>(ins.op, acc, in[NIN > 2 ? 2 : 0], acc); break;
-        case 3: apply_scalar<N>(ins.op, acc, ins.imm); break;
-        case 5: if (EXT) apply<N>(ins.op, acc, tmp[0], acc); break;
-        case 6: if (EXT) apply<N>(ins.op, acc, tmp[1], acc); break;
-        default: apply<N>(ins.op, acc, acc, acc);
-      }
-      if (EXT && ins.dst) {
-#pragma unroll
-        for (int j = 0; j < N; ++j) tmp[ins.dst == 1 ? 0 : 1][j] = acc[j];
-      }
-    }
+    exec.template run<NIN, N, EXT>(in, acc, code);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t e = base + (int64_t)(u * kThreads + t) * 4;
@@ -349,6 +358,100 @@ __global__ void __launch_bounds__(kThreads, EXT ? 5 : 8) ew_kernel_reg(const __g
       store_vec4(prog.out[0].ptr, prog.out[0].dtype, e, q);
     }
   }
+}
+
+// ---- static programs ---------------------------------------------------------------------------
+// The interpreter above costs about 40 thread-instructions per element on a 4-op chain, most of them decoding.  For the
+// programs that recur — the benchmark chains, bias / activation epilogues, clamps, selects — the same register code is
+// also compiled in as a template argument: the instruction loop unrolls into straight-line arithmetic on registers, with
+// the very same expressions per opcode (so the results are bit-identical to the interpreter's).  A launch looks its
+// register code up by signature; anything not listed runs on the interpreter.
+struct EwStaticIns {
+  uint8_t op, src, b, c, dst;
+};
+
+template <uint8_t OP> __device__ __forceinline__ float static_op(float x, float y) {
+  if constexpr (OP == EW_MOV) return x;
+  else if constexpr (OP == EW_ADD) return x + y;
+  else if constexpr (OP == EW_SUB) return x - y;
+  else if constexpr (OP == EW_MUL) return x * y;
+  else if constexpr (OP == EW_DIV) return x / y;
+  else if constexpr (OP == EW_MAX) return max_nan(x, y);
+  else if constexpr (OP == EW_MIN) return min_nan(x, y);
+  else if constexpr (OP == EW_RELU) return max_nan(x, 0.0f);
+  else if constexpr (OP == EW_EXP) return expf(x);
+  else if constexpr (OP == EW_RSQRT) return 1.0f / sqrtf(x);
+  else if constexpr (OP == EW_ABS) return fabsf(x);
+  else if constexpr (OP == EW_FLOOR) return floorf(x);
+  else if constexpr (OP == EW_NE) return x != y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_LT) return x < y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_LE) return x <= y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_GT) return x > y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_GE) return x >= y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_AND) return (x != 0.0f && y != 0.0f) ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_OR) return (x != 0.0f || y != 0.0f) ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_NOT) return x != 0.0f ? 0.0f : 1.0f;
+  else if constexpr (OP == EW_TO_BOOL) return x != 0.0f ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_TO_INT) return truncf(x);
+  else if constexpr (OP == EW_ROUND_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+  else if constexpr (OP == EW_ROUND_F16) return __half2float(__float2half_rn(x));
+  else if constexpr (OP == EW_RSUB) return y - x;
+  else if constexpr (OP == EW_RDIV) return y / x;
+  else return y;  // EW_LOADB
+}
+
+// operand `SRC` of a register instruction: 0..2 input, 3 immediate, 4 running value, 5..6 temporary
+template <uint8_t SRC, int NIN, int N>
+__device__ __forceinline__ float static_operand(const float (&in)[NIN > 0 ? NIN : 1][N], const float (&acc)[N], const float (&t0)[N], const float (&t1)[N],
+                                                float imm, int j) {
+  if constexpr (SRC < 3) return in[SRC < NIN ? SRC : 0][j];
+  else if constexpr (SRC == 3) return imm;
+  else if constexpr (SRC == 4) return acc[j];
+  else if constexpr (SRC == 5) return t0[j];
+  else return t1[j];
+}
+
+template <typename P, int I, int NIN, int N>
+__device__ __forceinline__ void static_step(const float (&in)[NIN > 0 ? NIN : 1][N], float (&acc)[N], float (&t0)[N], float (&t1)[N], const EwRegCode& code) {
+  if constexpr (I < P::n) {
+    constexpr EwStaticIns ins = P::ins[I];
+    const float imm = code.ins[I].imm;
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      if constexpr (ins.op == EW_WHERE) {
+        const float c = static_operand<ins.src, NIN, N>(in, acc, t0, t1, imm, j), x = static_operand<ins.b, NIN, N>(in, acc, t0, t1, imm, j),
+                    y = static_operand<ins.c, NIN, N>(in, acc, t0, t1, imm, j);
+        acc[j] = c != 0.0f ? x : y;
+      } else {
+        acc[j] = static_op<ins.op>(acc[j], static_operand<ins.src, NIN, N>(in, acc, t0, t1, imm, j));
+      }
+      if constexpr (ins.dst == 1) t0[j] = acc[j];
+      if constexpr (ins.dst == 2) t1[j] = acc[j];
+    }
+    static_step<P, I + 1, NIN, N>(in, acc, t0, t1, code);
+  }
+}
+
+template <typename P> struct StaticExec {
+  template <int NIN, int N, bool EXT>
+  __device__ __forceinline__ void run(const float (&in)[NIN > 0 ? NIN : 1][N], float (&acc)[N], const EwRegCode& code) const {
+    float t0[N], t1[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = t0[j] = t1[j] = 0.0f;
+    static_step<P, 0, NIN, N>(in, acc, t0, t1, code);
+  }
+};
+
+template <int NIN, int BMASK, int RANK, bool EXT>
+__global__ void __launch_bounds__(kThreads, EXT ? 5 : 8) ew_kernel_reg(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
+                                                             const __grid_constant__ EwRegCode code) {
+  ew_reg_body<NIN, BMASK, RANK, EXT>(prog, divs, code, InterpExec{});
+}
+
+template <typename P>
+__global__ void __launch_bounds__(kThreads, P::ext ? 4 : 8) ew_kernel_static(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
+                                                                  const __grid_constant__ EwRegCode code) {
+  ew_reg_body<P::nin, P::bmask, P::rank, P::ext>(prog, divs, code, StaticExec<P>{});
 }
 
 // Translate a slot-file program into the register form, if it is a linear chain.
@@ -427,6 +530,81 @@ bool to_register_code(const EwProgram& p, EwRegCode& code) {
     if (o < 0 || !emit(EW_LOADB, (uint8_t)o, 0.0f)) return false;
   }
   return true;
+}
+
+// ---- the compiled-in programs --------------------------------------------------------------------
+// Each entry is the register code of a recurring graph, as `ew_register_signature` prints it for that graph
+// (operand count, inner-broadcast mask, collapsed rank, extended form, then op.src per instruction).
+#define IB200_STATIC_PROGRAM(NAME, NIN_, BMASK_, RANK_, EXT_, ...)                      \
+  struct NAME {                                                                         \
+    static constexpr int nin = NIN_, bmask = BMASK_, rank = RANK_;                      \
+    static constexpr bool ext = EXT_;                                                   \
+    static constexpr EwStaticIns ins[] = {__VA_ARGS__};                                 \
+    static constexpr int n = (int)(sizeof(ins) / sizeof(ins[0]));                       \
+  };
+#define I_(OP, SRC) EwStaticIns{OP, SRC, 0, 0, 0}
+#define IT_(OP, SRC, DST) EwStaticIns{OP, SRC, 0, 0, DST}
+#define IW_(COND, B, C) EwStaticIns{EW_WHERE, COND, B, C, 0}
+
+// y = ((x * col + row) * k + col): the 4-op broadcast chain of the benchmark (x [M,N], col [N], row [M,1])
+IB200_STATIC_PROGRAM(ProgChain4, 3, 4, 2, false, I_(EW_LOADB, 0), I_(EW_MUL, 1), I_(EW_ADD, 2), I_(EW_MUL, 3), I_(EW_ADD, 1))
+// y = (x*col + row) * (x - col) + max(x, row): the 6-op DAG of the benchmark, reused values kept in a temporary
+IB200_STATIC_PROGRAM(ProgDag6, 3, 4, 2, true, I_(EW_LOADB, 0), I_(EW_MUL, 1), IT_(EW_ADD, 2, 1), I_(EW_LOADB, 0), I_(EW_SUB, 1), IT_(EW_MUL, 5, 1),
+                     I_(EW_LOADB, 0), I_(EW_MAX, 2), I_(EW_ADD, 5))
+// bias and activation epilogues over [M,N] with a [N] vector: x + b, relu(x + b), x * w, x * w + b
+IB200_STATIC_PROGRAM(ProgAddVec, 2, 0, 2, false, I_(EW_LOADB, 0), I_(EW_ADD, 1))
+IB200_STATIC_PROGRAM(ProgAddVecRelu, 2, 0, 2, false, I_(EW_LOADB, 0), I_(EW_ADD, 1), I_(EW_RELU, 4))
+IB200_STATIC_PROGRAM(ProgMulVec, 2, 0, 2, false, I_(EW_LOADB, 0), I_(EW_MUL, 1))
+IB200_STATIC_PROGRAM(ProgMulAddVec, 3, 0, 2, false, I_(EW_LOADB, 0), I_(EW_MUL, 1), I_(EW_ADD, 2))
+// selects and clamps of the reference's kernel suite (pipeline/tilelang/core.py: where2d, rowmask_where2d, clamp2d)
+IB200_STATIC_PROGRAM(ProgGtWhere, 2, 0, 1, true, I_(EW_LOADB, 0), I_(EW_GT, 1), IW_(4, 0, 1))
+IB200_STATIC_PROGRAM(ProgRowMaskWhere, 2, 1, 2, true, IW_(0, 1, 3))
+IB200_STATIC_PROGRAM(ProgClamp, 3, 6, 1, false, I_(EW_LOADB, 0), I_(EW_MAX, 1), I_(EW_MIN, 2))
+IB200_STATIC_PROGRAM(ProgFloor, 1, 0, 1, false, I_(EW_LOADB, 0), I_(EW_FLOOR, 4))
+// same-shape binaries and unaries (operands collapse to rank 1)
+IB200_STATIC_PROGRAM(ProgCopy, 1, 0, 1, false, I_(EW_LOADB, 0))
+IB200_STATIC_PROGRAM(ProgAdd, 2, 0, 1, false, I_(EW_LOADB, 0), I_(EW_ADD, 1))
+IB200_STATIC_PROGRAM(ProgMul, 2, 0, 1, false, I_(EW_LOADB, 0), I_(EW_MUL, 1))
+IB200_STATIC_PROGRAM(ProgSub, 2, 0, 1, false, I_(EW_LOADB, 0), I_(EW_SUB, 1))
+IB200_STATIC_PROGRAM(ProgRelu, 1, 0, 1, false, I_(EW_LOADB, 0), I_(EW_RELU, 4))
+IB200_STATIC_PROGRAM(ProgExp, 1, 0, 1, false, I_(EW_LOADB, 0), I_(EW_EXP, 4))
+IB200_STATIC_PROGRAM(ProgAddRelu, 2, 0, 1, false, I_(EW_LOADB, 0), I_(EW_ADD, 1), I_(EW_RELU, 4))
+#undef I_
+#undef IT_
+#undef IW_
+
+typedef void (*EwRegKernel)(const EwProgram, const EwDivs, const EwRegCode);
+
+std::string signature_of(int nin, int bmask, int rank, bool ext, int n, const uint8_t* op, const uint8_t* src, const uint8_t* b, const uint8_t* c,
+                         const uint8_t* dst) {
+  std::string sig = "n" + std::to_string(nin) + " b" + std::to_string(bmask) + " r" + std::to_string(rank) + " e" + std::to_string(ext ? 1 : 0) + " |";
+  for (int i = 0; i < n; ++i) {
+    sig += " " + std::to_string(op[i]) + "." + std::to_string(src[i]);
+    if (op[i] == EW_WHERE) sig += "." + std::to_string(b[i]) + "." + std::to_string(c[i]);
+    if (dst[i]) sig += ">" + std::to_string(dst[i]);
+  }
+  return sig;
+}
+std::string signature_of(const EwRegCode& code, int nin, int bmask, int rank, bool ext) {
+  uint8_t op[kEwMaxInstr + 1], src[kEwMaxInstr + 1], b[kEwMaxInstr + 1], c[kEwMaxInstr + 1], dst[kEwMaxInstr + 1];
+  for (int i = 0; i < code.n_instr; ++i) { op[i] = code.ins[i].op; src[i] = code.ins[i].src; b[i] = code.ins[i].b; c[i] = code.ins[i].c; dst[i] = code.ins[i].dst; }
+  return signature_of(nin, bmask, rank, ext, code.n_instr, op, src, b, c, dst);
+}
+template <typename P> void add_static(std::map<std::string, EwRegKernel>& table) {
+  uint8_t op[P::n], src[P::n], b[P::n], c[P::n], dst[P::n];
+  for (int i = 0; i < P::n; ++i) { op[i] = P::ins[i].op; src[i] = P::ins[i].src; b[i] = P::ins[i].b; c[i] = P::ins[i].c; dst[i] = P::ins[i].dst; }
+  table[signature_of(P::nin, P::bmask, P::rank, P::ext, P::n, op, src, b, c, dst)] = ew_kernel_static<P>;
+}
+const std::map<std::string, EwRegKernel>& static_programs() {
+  static const std::map<std::string, EwRegKernel> table = [] {
+    std::map<std::string, EwRegKernel> t;
+    add_static<ProgChain4>(t); add_static<ProgDag6>(t); add_static<ProgAddVec>(t); add_static<ProgAddVecRelu>(t); add_static<ProgMulVec>(t);
+    add_static<ProgCopy>(t); add_static<ProgAdd>(t); add_static<ProgMul>(t); add_static<ProgSub>(t); add_static<ProgRelu>(t); add_static<ProgExp>(t);
+    add_static<ProgAddRelu>(t); add_static<ProgMulAddVec>(t); add_static<ProgGtWhere>(t); add_static<ProgRowMaskWhere>(t); add_static<ProgClamp>(t);
+    add_static<ProgFloor>(t);
+    return t;
+  }();
+  return table;
 }
 
 template <bool VEC>
@@ -512,18 +690,17 @@ __global__ void __launch_bounds__(kThreads) ew_kernel(const __grid_constant__ Ew
   }
 }
 
-}  // namespace
-
-int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
-  if (prog.total == 0) return IB200_OK;
-  if (prog.total < 0 || prog.total >= ((int64_t)1 << 31)) return fail(IB200_ERR_UNSUPPORTED, "elementwise: more than 2^31-1 output elements");
-  if (prog.rank < 1 || prog.rank > kEwMaxRank || prog.n_inputs > kEwMaxInputs || prog.n_outputs < 1 ||
-      prog.n_outputs > kEwMaxOutputs || prog.n_instr > kEwMaxInstr || prog.n_slots > kEwMaxSlots || prog.n_slots < prog.n_inputs)
-    return fail(IB200_ERR_INVALID, "elementwise: malformed program");
-  EwDivs divs;
-  for (int d = 0; d < prog.rank; ++d) divs.d[d] = FastDiv(prog.dim[d]);
-  // staging mode per operand, and whether the specialised kernel applies
-  EwProgram p = prog;
+// Staging mode per operand, whether the specialised kernels apply (`fast`), and — when the program is a linear chain —
+// its register code with the template parameters of the register kernels.
+struct Prepared {
+  EwProgram p;
+  bool fast = false, reg = false, ext = false;
+  int bmask = 0;
+  EwRegCode code;
+};
+void prepare(const EwProgram& prog, Prepared& out) {
+  EwProgram& p = out.p;
+  p = prog;
   bool fast = p.n_inputs <= 4 && p.rank <= 3;
   for (int k = 0; k < p.n_inputs; ++k) {
     EwInput& in = p.in[k];
@@ -545,39 +722,84 @@ int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
       in.mode = in.dtype == IB200_F32 ? EW_STAGE_ASYNC_F32 : EW_STAGE_GATHER;
     }
   }
-  {
-    static const bool reg_path = !(std::getenv("IB200_EW_REG") && std::getenv("IB200_EW_REG")[0] == '0');
-    EwRegCode code;
-    if (reg_path && fast && to_register_code(p, code)) {
-      int bmask = 0;
-      bool ext = false;
-      for (int k = 0; k < p.n_inputs; ++k) {
-        bmask |= (p.in[k].mode == EW_STAGE_BROADCAST) << k;
-        ext |= p.in[k].dtype == IB200_BOOL || p.in[k].dtype == IB200_U8;
-      }
-      for (int i = 0; i < code.n_instr; ++i) ext |= code.ins[i].op == EW_WHERE || code.ins[i].dst != 0 || code.ins[i].src >= 5;
-      void (*rk)(const EwProgram, const EwDivs, const EwRegCode) = nullptr;
-#define IB200_REG(NIN, BM, R) if (p.n_inputs == NIN && bmask == BM && p.rank == R) rk = ext ? ew_kernel_reg<NIN, BM, R, true> : ew_kernel_reg<NIN, BM, R, false>;
+  out.fast = fast;
+  out.reg = fast && to_register_code(p, out.code);
+  if (out.reg) {
+    for (int k = 0; k < p.n_inputs; ++k) {
+      out.bmask |= (p.in[k].mode == EW_STAGE_BROADCAST) << k;
+      out.ext |= p.in[k].dtype == IB200_BOOL || p.in[k].dtype == IB200_U8;
+    }
+    for (int i = 0; i < out.code.n_instr; ++i) out.ext |= out.code.ins[i].op == EW_WHERE || out.code.ins[i].dst != 0 || out.code.ins[i].src >= 5;
+  }
+}
+
+}  // namespace
+
+// What the register path would run for this program if every operand is aligned: its signature, and whether that
+// register code is one of the compiled-in programs.  Empty when the program does not take the register path.
+std::string ew_register_signature(const EwProgram& prog, bool* compiled_in) {
+  Prepared pr;
+  EwProgram q = prog;
+  q.vec = q.dim[q.rank - 1] % 4 == 0;
+  for (int k = 0; k < q.n_inputs; ++k) {
+    EwInput& in = q.in[k];
+    bool ok = in.kind == EW_IN_TENSOR && in.stride[q.rank - 1] == 1;
+    for (int d = 0; d + 1 < q.rank; ++d) ok &= in.stride[d] % 4 == 0;
+    in.vec_ok = ok;
+  }
+  prepare(q, pr);
+  if (compiled_in) *compiled_in = false;
+  if (!pr.reg) return std::string();
+  const std::string sig = signature_of(pr.code, pr.p.n_inputs, pr.bmask, pr.p.rank, pr.ext);
+  if (compiled_in) *compiled_in = static_programs().count(sig) > 0;
+  return sig;
+}
+
+int launch_elementwise(const EwProgram& prog, cudaStream_t s) {
+  if (prog.total == 0) return IB200_OK;
+  if (prog.total < 0 || prog.total >= ((int64_t)1 << 31)) return fail(IB200_ERR_UNSUPPORTED, "elementwise: more than 2^31-1 output elements");
+  if (prog.rank < 1 || prog.rank > kEwMaxRank || prog.n_inputs > kEwMaxInputs || prog.n_outputs < 1 ||
+      prog.n_outputs > kEwMaxOutputs || prog.n_instr > kEwMaxInstr || prog.n_slots > kEwMaxSlots || prog.n_slots < prog.n_inputs)
+    return fail(IB200_ERR_INVALID, "elementwise: malformed program");
+  EwDivs divs;
+  for (int d = 0; d < prog.rank; ++d) divs.d[d] = FastDiv(prog.dim[d]);
+  Prepared pr;
+  prepare(prog, pr);
+  const EwProgram& p = pr.p;
+  const bool fast = pr.fast;
+  if (pr.reg) {
+    const EwRegCode& code = pr.code;
+    const int bmask = pr.bmask;
+    const bool ext = pr.ext;
+    EwRegKernel rk = nullptr;
+    const auto& table = static_programs();
+    const auto hit = table.find(signature_of(code, p.n_inputs, bmask, p.rank, ext));
+    if (hit != table.end()) rk = hit->second;  // compiled in: straight-line code instead of the instruction loop
+#define IB200_REG(NIN, BM, R) if (!rk && p.n_inputs == NIN && bmask == BM && p.rank == R) rk = ext ? ew_kernel_reg<NIN, BM, R, true> : ew_kernel_reg<NIN, BM, R, false>;
 #define IB200_REG_R(NIN, BM) IB200_REG(NIN, BM, 1) IB200_REG(NIN, BM, 2)
-      IB200_REG_R(0, 0) IB200_REG_R(1, 0) IB200_REG_R(1, 1) IB200_REG_R(2, 0) IB200_REG_R(2, 1) IB200_REG_R(2, 2) IB200_REG_R(2, 3)
-      IB200_REG_R(3, 0) IB200_REG_R(3, 1) IB200_REG_R(3, 2) IB200_REG_R(3, 3) IB200_REG_R(3, 4) IB200_REG_R(3, 5) IB200_REG_R(3, 6) IB200_REG_R(3, 7)
+    IB200_REG_R(0, 0) IB200_REG_R(1, 0) IB200_REG_R(1, 1) IB200_REG_R(2, 0) IB200_REG_R(2, 1) IB200_REG_R(2, 2) IB200_REG_R(2, 3)
+    IB200_REG_R(3, 0) IB200_REG_R(3, 1) IB200_REG_R(3, 2) IB200_REG_R(3, 3) IB200_REG_R(3, 4) IB200_REG_R(3, 5) IB200_REG_R(3, 6) IB200_REG_R(3, 7)
 #undef IB200_REG_R
 #undef IB200_REG
-      if (rk) {
-        const int64_t tiles = (p.total + kTile - 1) / kTile;
-        const int64_t cap = (int64_t)kSmCount * (ext ? 5 : 8) * 4;
-        rk<<<(int)(tiles < cap ? tiles : cap), kThreads, 0, s>>>(p, divs, code);
-        return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "elementwise launch");
-      }
+    if (rk) {
+      const int64_t tiles = (p.total + kTile - 1) / kTile;
+      const int64_t cap = (int64_t)kSmCount * (ext ? 5 : 8) * 4;
+      rk<<<(int)(tiles < cap ? tiles : cap), kThreads, 0, s>>>(p, divs, code);
+      return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "elementwise launch");
     }
   }
   void (*kern)(const EwProgram, const EwDivs) = p.vec ? ew_kernel<true> : ew_kernel<false>;
   int per_thread = kPerThread;
   if (fast) {
     const int mi = p.n_inputs <= 2 ? 2 : 4;
-    // 16 elements per thread (IB200_EW_WIDE=1) halve the decoding per element but leave two CTAs per SM;
-    // measured on a 6-op DAG over [8192,4096]: 148 us against 121 us for 8 elements per thread at four CTAs
+    // 16 elements per thread halve the decoding per element but leave two CTAs per SM; measured on a 6-op DAG over
+    // [8192,4096]: 148 us against 121 us for 8 elements per thread at four CTAs.  Kept for A/B runs of builds made
+    // with -DIB200_AB_KNOBS (IB200_EW_WIDE=1); a normal build never takes it.
+#ifdef IB200_AB_KNOBS
     static const bool allow_wide = std::getenv("IB200_EW_WIDE") && std::getenv("IB200_EW_WIDE")[0] == '1';
+#else
+    constexpr bool allow_wide = false;
+#endif
     const bool wide = allow_wide && p.vec && p.total >= (int64_t)kSmCount * kThreads * 16 * 4 && p.n_slots <= 12;
     if (wide) per_thread = 16;
 #define IB200_EW(MI, R)                                                                                   \

@@ -11,6 +11,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string>
+
 namespace ib200 {
 
 constexpr int kEwMaxInputs = 8;
@@ -87,6 +89,9 @@ struct EwProgram {
 };
 
 int launch_elementwise(const EwProgram& prog, cudaStream_t s);
+// The register code a linear chain would run (assuming aligned operands) as a signature string, and whether that code
+// is one of the programs compiled into the library as straight-line kernels; "" for programs on the slot-file path.
+std::string ew_register_signature(const EwProgram& prog, bool* compiled_in);
 // The same program with every value carried as a double: exact for f64 tensors and for integers up to 2^53, which
 // the f32 lanes of the kernels above are not.  `imm` holds the kEwMaxInstr immediates at full precision.
 int launch_elementwise_wide(const EwProgram& prog, const double* imm, cudaStream_t s);

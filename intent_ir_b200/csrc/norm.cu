@@ -551,7 +551,11 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   }
   const int c = (int)a.cols;
   if (VEC && !a.res && a.cols > 4096 && a.cols <= 32768 && (a.cols * sizeof(T)) % 16 == 0) {
+#ifdef IB200_AB_KNOBS  // A/B builds only: IB200_NORM_PIPE=0 falls back to the one-shot cluster kernel
     static const bool enabled = !(std::getenv("IB200_NORM_PIPE") && std::getenv("IB200_NORM_PIPE")[0] == '0');
+#else
+    constexpr bool enabled = true;
+#endif
     int csize = 1;
     while ((int64_t)csize * 4096 < a.cols) csize *= 2;
     int seg = (int)((a.cols + csize - 1) / csize);

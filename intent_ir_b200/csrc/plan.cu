@@ -2718,6 +2718,12 @@ class Planner {
       outs.push(j);
     }
     r.set("inputs", ins); r.set("instr", code); r.set("outputs", outs); r.set("n_slots", num(p.n_slots));
+    if (!s.wide) {
+      bool compiled_in = false;
+      const std::string sig = ew_register_signature(p, &compiled_in);
+      r.set("register_code", Json::string(sig));
+      r.set("compiled_in", num(compiled_in ? 1 : 0));
+    }
     return r;
   }
   static Json describe_row_program(const Step& s) {

@@ -427,9 +427,12 @@ constexpr size_t kSmemPerSm = 227 * 1024;
 // smallest group that still leaves at least eight warps resident per SM, else the most warps
 bool row_launch_config(int n_row, int n_once, int cols, int n_instr, RowLaunch& best) {
   bool found = false;
-  // tuning overrides, read once: IB200_ROW_G in {32, 128, 512}, IB200_ROW_NU in {2, 4, 8}
+#ifdef IB200_AB_KNOBS  // A/B builds only, read once: IB200_ROW_G in {32, 128, 512}, IB200_ROW_NU in {2, 4, 8}
   static const int force_g = std::getenv("IB200_ROW_G") ? std::atoi(std::getenv("IB200_ROW_G")) : 0;
   static const int force_nu = std::getenv("IB200_ROW_NU") ? std::atoi(std::getenv("IB200_ROW_NU")) : 0;
+#else
+  constexpr int force_g = 0, force_nu = 0;
+#endif
   for (int g : {32, 128, 512}) {
     if (force_g ? g != force_g : (g == 32 && cols > 1024)) continue;  // measured: rows past 1024 elements want more than one warp
     RowLaunch c;

@@ -341,3 +341,32 @@ def test_f64_and_wide_integer_chains_take_the_double_valued_kernel():
     assert kernels("i64", "bool", "lt") == ["elementwise(1 ops, 2 in, 1 out)(f64 lanes)"]
     assert kernels("f32", "f32") == ["elementwise(1 ops, 2 in, 1 out)"]
     assert kernels("i8", "i8") == ["elementwise(1 ops, 2 in, 1 out)"]  # 8- and 16-bit integers are exact in f32 lanes
+
+
+def test_recurring_elementwise_chains_are_compiled_in(golden_graphs):
+    """Linear chains run from registers; the ones that recur (the benchmark chains, bias / activation epilogues,
+    clamps, selects) are also compiled in as straight-line kernels, found by the signature of their register code.
+    Anything else keeps the run-time instruction loop."""
+    from intent_ir_b200.lowering import plan_json
+
+    def programs(js, bind):
+        return [s["program"] for s in plan_json(js, bind)["steps"] if "program" in s]
+
+    import bench
+
+    for name in ("chain", "dag"):
+        js, bind = bench.workload(name)[:2]
+        (prog,) = programs(js, bind)
+        assert prog["compiled_in"] == 1 and prog["register_code"].startswith("n3 b4 r2"), (name, prog["register_code"])
+    for key in ("add_bias2d", "add2d", "relu2d", "exp2d", "where2d", "clamp2d", "rowmask_where2d", "floor2d", "copy2d_divmod"):
+        g = golden_graphs[key]
+        shapes = {k: 8 * v for k, v in g["shapes"].items()}
+        progs = programs(g["intent"], shapes)
+        assert progs and all(p["compiled_in"] == 1 for p in progs), (key, [p["register_code"] for p in progs])
+    # an arbitrary chain is still a register-path program, run by the instruction loop
+    t = lambda s: {"dtype": "f32", "shape": s, "layout": "row_major"}  # noqa: E731
+    js = {"name": "odd", "tensors": {"x": t(["M", "N"]), "c": t(["N"]), "y": t(["M", "N"])},
+          "ops": [{"op": "sub", "inputs": ["x", "c"], "output": "a"}, {"op": "abs", "inputs": ["a"], "output": "b"},
+                  {"op": "min", "inputs": ["b", "c"], "output": "y"}], "outputs": ["y"]}
+    (prog,) = programs(js, {"M": 64, "N": 128})
+    assert prog["compiled_in"] == 0 and prog["register_code"]

@@ -1010,3 +1010,21 @@ def test_scaled_sum_over_three_separate_axes():
     want = execute_intent(intent, {"x": x}, bind)["y"]
     _agree(out["y"], want, infer_tolerances(intent).to_dict(), "mean over three axes")
     assert np.allclose(out["y"], x.mean(axis=(0, 2, 4)), atol=1e-5)
+
+
+def test_compiled_in_chains_give_the_interpreters_bits():
+    """The benchmark chains run as straight-line kernels; same expressions per opcode as the instruction loop, so the
+    results equal the oracle's bit for bit (as every elementwise program's do)."""
+    import bench
+
+    for name in ("chain", "dag"):
+        js, _, _, _, _, _ = bench.workload(name)
+        intent = IntentFunction.from_json_dict(js)
+        for m, n in ((64, 128), (33, 260), (257, 4096)):
+            rng = np.random.default_rng(m + n)
+            ins = {"x": rng.standard_normal((m, n), dtype=np.float32), "col": rng.standard_normal(n, dtype=np.float32),
+                   "row": rng.standard_normal((m, 1), dtype=np.float32)}
+            ins["x"][0, 0] = np.nan
+            out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
+            want = execute_intent(intent, ins, {"M": m, "N": n})["y"]
+            assert np.array_equal(out["y"], want, equal_nan=True), (name, m, n)
