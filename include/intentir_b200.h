@@ -68,6 +68,8 @@ extern "C" {
 #define IB200_ACT_NONE 0
 #define IB200_ACT_RELU 1
 /* ---- flags for ib200_gemm_bias_act_ws ------------------------------------------------- */
+#define IB200_GEMM_CTA_PAIRS 2  /* force the tensor-core product onto pairs of CTAs (tcgen05 cta_group::2, 256 x 256 tiles) */
+#define IB200_GEMM_ONE_CTA 4    /* force the one-CTA kernel (128 x 256/192/128 tiles); default: pairs for large products */
 #define IB200_GEMM_ALLOW_TF32 1 /* f32 operands may be multiplied as TF32 on the tensor cores (the reference's
                                    ALLOW_TF32 binding, intentir_to_cuda.py:577-578); without it f32 stays exact FMA */
 
@@ -243,8 +245,10 @@ IB200_API int ib200_gemm_bias_act(const void* a, const void* b, const void* bias
  * operands (K, N multiples of 8) to the tensor cores as TF32, which is what the reference's
  * opt-in wmma kernel does (kernels/wmma_matmul.cuh:124-563); products then carry 10-bit
  * mantissas, inside the verifier's matmul tolerance for inputs of moderate dynamic range.
+ * Large products (M >= 256, tiles for at least half the SM pairs) run on pairs of CTAs sharing
+ * 256 x 256 tiles (tcgen05 cta_group::2); IB200_GEMM_CTA_PAIRS / IB200_GEMM_ONE_CTA force either form.
  * `scratch` (256-byte aligned, ib200_gemm_scratch_bytes(...) bytes, contents irrelevant) lets the
- * tensor-core kernel cut the tiles of a last, mostly empty round of tiles along K and add the
+ * one-CTA kernel cut the tiles of a last, mostly empty round of tiles along K and add the
  * slices up in a fixed order; with scratch == NULL every tile runs whole, as in
  * ib200_gemm_bias_act.  A TF32 product whose B is [K,N] transposes B into the scratch first
  * (the tensor-core kernel takes 32-bit operands K-major only) and stays on the FMA kernel

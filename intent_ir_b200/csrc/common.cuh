@@ -74,6 +74,7 @@ int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_
                 cudaStream_t s, int flags = 0, void* scratch = nullptr, size_t scratch_bytes = 0);
 size_t gemm_scratch_bytes(int in_dtype, int out_dtype, int64_t m, int64_t n, int64_t k, int flags, int transpose_b);
 bool gemm_uses_tensor_cores(int in_dtype, int out_dtype, int64_t n, int64_t k, int flags);
+bool prefers_cta_pairs(int64_t m, int64_t n, int flags);
 int launch_transpose2d(const void* x, void* out, int elem_bytes, int64_t rows, int64_t cols,
                        cudaStream_t s);
 struct GatherArgs {

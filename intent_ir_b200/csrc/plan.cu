@@ -1304,6 +1304,7 @@ class Planner {
     std::string out;
     const bool tf32 = s.dtype == IB200_F32 && gemm_uses_tensor_cores(s.dtype, s.dtype2, s.d[1], s.d[2], s.flags);
     if (tf32) out += "(tf32)";
+    if (gemm_uses_tensor_cores(s.dtype, s.dtype2, s.d[1], s.d[2], s.flags) && prefers_cta_pairs(s.d[0], s.d[1], s.flags)) out += "(cta pairs)";
     if (s.scratch >= 0 && gemm_scratch_bytes(s.dtype, s.dtype2, s.d[0], s.d[1], s.d[2], s.flags, 1) > 0) out += "(split tail)";
     return out;
   }

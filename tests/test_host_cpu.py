@@ -310,15 +310,21 @@ def test_gemm_plans_cover_every_float_operand_type(golden_graphs):
     assert [s["kernel"] for s in plan_json(graph("f32"), {"M": 256, "N": 256, "K": 128})["steps"]] == ["gemm+bias+relu"]
     assert [s["kernel"] for s in plan_json(graph("f32"), {"M": 256, "N": 256, "K": 128, "ALLOW_TF32": 1})["steps"]] == ["gemm+bias+relu(tf32)"]
     assert [s["kernel"] for s in plan_json(graph("f32"), {"M": 256, "N": 250, "K": 128, "ALLOW_TF32": 1})["steps"]] == ["gemm+bias+relu"]  # ragged N: FMA
-    big = plan_json(graph("bf16"), {"M": 4096, "N": 4096, "K": 4096})  # 512 tiles on 148 SMs: 68 tail tiles, two slices each
-    assert [s["kernel"] for s in big["steps"]] == ["gemm+bias+relu(split tail)"]
+    big = plan_json(graph("bf16"), {"M": 4096, "N": 4096, "K": 4096})  # large products: 256 x 256 tiles on pairs of CTAs, no scratch
+    assert [s["kernel"] for s in big["steps"]] == ["gemm+bias+relu(cta pairs)"]
     lib = _lib.load()
-    need = lib.ib200_gemm_scratch_bytes(_lib.BF16, _lib.BF16, 4096, 4096, 4096, 0, 0)
-    assert need == 256 + 68 * 16 + 256 + 68 * 2 * 128 * 256 * 4 and big["workspace_bytes"] >= need
+    assert lib.ib200_gemm_scratch_bytes(_lib.BF16, _lib.BF16, 4096, 4096, 4096, 0, 0) == 0
+    # one row of tiles (M = 128 leaves a pair's second CTA without rows): 40 tiles on 148 SMs, three K slices each
+    flat = plan_json(graph("bf16"), {"M": 128, "N": 10240, "K": 4096})
+    assert [s["kernel"] for s in flat["steps"]] == ["gemm+bias+relu(split tail)"]
+    need = lib.ib200_gemm_scratch_bytes(_lib.BF16, _lib.BF16, 128, 10240, 4096, 0, 0)
+    assert need == 256 + 40 * 16 + 256 + 40 * 3 * 128 * 256 * 4 and flat["workspace_bytes"] >= need
+    # the one-CTA kernel forced onto 4096^3: 512 tiles, 68 tail tiles, two slices each
+    assert lib.ib200_gemm_scratch_bytes(_lib.BF16, _lib.BF16, 4096, 4096, 4096, 0, _lib.GEMM_ONE_CTA) == 256 + 68 * 16 + 256 + 68 * 2 * 128 * 256 * 4
     assert lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 0, 0) == 0  # exact FMA path: no tiles to split
     # TF32 takes B as [N,K]: a [K,N] operand needs room for its transpose on top of the split area
     tf = _lib.GEMM_ALLOW_TF32
-    assert lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 0, tf) == lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 1, tf) + 4096 * 4096 * 4
+    assert lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 0, tf) == lib.ib200_gemm_scratch_bytes(_lib.F32, _lib.F32, 4096, 4096, 4096, 1, tf) + 4096 * 4096 * 4 == 4096 * 4096 * 4
     assert lib.ib200_gemm_scratch_bytes(_lib.BF16, _lib.BF16, 128 * 37, 256 * 4, 4096, 0, 0) == 0  # 148 tiles: a full round
 
 

@@ -497,13 +497,13 @@ def test_gemm_tail_tiles_split_along_k(dtype, m, n, k, transpose_b):
     lib = _lib.load()
     code = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}[dtype]
     tf32 = dtype == torch.float32
-    assert lib.ib200_gemm_scratch_bytes(code, code, m, n, k, 1, _lib.GEMM_ALLOW_TF32 if tf32 else 0) > 0
+    assert lib.ib200_gemm_scratch_bytes(code, code, m, n, k, 1, _lib.GEMM_ONE_CTA | (_lib.GEMM_ALLOW_TF32 if tf32 else 0)) > 0
     ad, bd, biasd = _dev(a, dtype), _dev(np.ascontiguousarray(b.T) if transpose_b else b, dtype), _dev(bias, dtype)
-    split = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=True)
+    split = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=True, cta_pairs=False)
     ops.check_device_status()
-    whole = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=False)
+    whole = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=False, cta_pairs=False)
     ops.check_device_status()
-    again = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=True)  # tickets were left at zero
+    again = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=True, cta_pairs=False)  # tickets were left at zero
     ops.check_device_status()
     assert torch.equal(split, again)  # slices are added in slice order: the same bits on every run
     want = np.maximum(a.astype(np.float64) @ b.astype(np.float64) + bias, 0)
@@ -511,3 +511,27 @@ def test_gemm_tail_tiles_split_along_k(dtype, m, n, k, transpose_b):
     _agree(whole.float().cpu().numpy(), want, 2e-2, 2e-2)
     # bf16 / f16 products are exact and both kernels accumulate in fp32: split and whole agree to accumulation order
     assert float((split.float() - whole.float()).abs().max()) <= (2e-2 if dtype != torch.float32 else 1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("m,n,k,transpose_b", [(256, 256, 64, False), (256, 256, 512, True), (512, 768, 1024, False), (300, 264, 72, False),
+                                                (130, 520, 1000, True), (1, 8, 8, False), (2048, 2048, 2048, False), (4096, 1024, 512, True)])
+def test_gemm_on_cta_pairs(dtype, m, n, k, transpose_b):
+    """tcgen05 cta_group::2: two CTAs share a 256 x 256 tile, each staging half of the operands."""
+    from intent_ir_b200 import ops
+    rng = np.random.default_rng(m + n + k + 4)
+    a = _bf16_round((0.5 * rng.standard_normal((m, k))).astype(np.float32))
+    b = _bf16_round((rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32))
+    bias = _bf16_round((0.1 * rng.standard_normal(n)).astype(np.float32))
+    tf32 = dtype == torch.float32
+    ad, bd, biasd = _dev(a, dtype), _dev(np.ascontiguousarray(b.T) if transpose_b else b, dtype), _dev(bias, dtype)
+    got = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, cta_pairs=True)
+    ops.check_device_status()
+    want = np.maximum(a.astype(np.float64) @ b.astype(np.float64) + bias, 0)
+    _agree(got.float().cpu().numpy(), want, 2e-2, 2e-2)
+    if not tf32 or transpose_b:  # (a [K,N] TF32 operand needs scratch for its transpose, which split_tail=False withholds)
+        lone = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, split_tail=False, cta_pairs=False)
+        ops.check_device_status()
+        # products of bf16-representable values are exact in every operand kind and both kernels accumulate in fp32 in
+        # K order: the pair kernel gives the one-CTA kernel's bits
+        assert torch.equal(got, lone)

@@ -238,7 +238,7 @@ def test_config_matmul_bias_relu_bf16_4096(golden_graphs):
     B = round_to_bf16(0.02 * rng.standard_normal((n, n), dtype=np.float32))
     bias = round_to_bf16(0.1 * rng.standard_normal(n, dtype=np.float32))
     out, lowered = _lower_and_run(intent, {"M": n, "N": n, "K": n}, {"A": A, "B": B, "bias": bias})
-    assert [s["kernel"] for s in lowered.steps] == ["gemm+bias+relu"]
+    assert [s["kernel"] for s in lowered.steps] == ["gemm+bias+relu(cta pairs)"]  # 256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2)
     want = execute_intent(intent, {"A": A, "B": B, "bias": bias})["C"]  # float32-carried bf16 values
     tol = infer_tolerances(intent).to_dict()
     assert tol == {"atol": 2e-2, "rtol": 2e-2}
@@ -256,8 +256,8 @@ def _t0(shape, dtype="f32"):
 @pytest.mark.parametrize("name,js", [
     ("rank-1", {"name": "m", "tensors": {"a": _t0(["M"]), "b": _t0(["M", "N"]), "y": _t0(["N"])},
                 "ops": [{"op": "matmul", "inputs": ["a", "b"], "output": "y"}], "outputs": ["y"]}),
-    ("non-trailing", {"name": "s", "tensors": {"x": _t0(["M", "N"]), "y": _t0(["M", "N"])},
-                      "ops": [{"op": "softmax", "inputs": ["x"], "output": "y", "attrs": {"axis": 0}}], "outputs": ["y"]}),
+    ("gather", {"name": "g", "tensors": {"x": _t0(["M", "N"]), "i": _t0(["M"], "i32"), "y": _t0(["M"])},
+                "ops": [{"op": "gather", "inputs": ["x", "i"], "output": "y"}], "outputs": ["y"]}),  # fewer index tensors than data axes
 ])
 def test_uncovered_graphs_fail_loudly(name, js):
     from intent_ir_b200.errors import B200LoweringError
