@@ -204,20 +204,25 @@ def workload(name):
                 lambda r: {"x": r.standard_normal((m, n), dtype=np.float32), "col": r.standard_normal(n, dtype=np.float32),
                            "row": r.standard_normal((m, 1), dtype=np.float32)},
                 2 * m * n * 4 + n * 4 + m * 4, 0, "elementwise DAG with reused values, 6 ops, f32 [8192,4096]")
-    if name == "rowprog":
+    if name in ("rowprog", "rmsnorm_relu"):
+        # rms-norm with an activation between the normalisation and the weight.  With a ReLU the norm kernel takes it
+        # (an activation hook); with |x| nothing dedicated matches and the graph runs as one fused row program
         m, n = 8192, 4096
-        js = {"name": "rms_relu", "tensors": {"x": _t(["M", "N"]), "w": _t(["N"]), "y": _t(["M", "N"]), "rstd": _t(["M"])},
+        inner = "relu" if name == "rmsnorm_relu" else "abs"
+        js = {"name": "rms_" + inner, "tensors": {"x": _t(["M", "N"]), "w": _t(["N"]), "y": _t(["M", "N"]), "rstd": _t(["M"])},
               "ops": [{"op": "mul", "inputs": ["x", "x"], "output": "sq"},
                       {"op": "reduce_sum", "inputs": ["sq"], "output": "ss", "attrs": {"dims": [1], "keepdims": True, "scale": "1.0/N"}},
                       {"op": "add", "inputs": ["ss"], "output": "ve", "attrs": {"addend": 1e-5}},
                       {"op": "rsqrt", "inputs": ["ve"], "output": "r1"},
                       {"op": "reshape", "inputs": ["r1"], "output": "rstd", "attrs": {"shape": ["M"]}},
                       {"op": "mul", "inputs": ["x", "r1"], "output": "xn"},
-                      {"op": "relu", "inputs": ["xn"], "output": "xr"},
+                      {"op": inner, "inputs": ["xn"], "output": "xr"},
                       {"op": "mul", "inputs": ["xr", "w"], "output": "y"}], "outputs": ["y", "rstd"]}
         return (js, {"M": m, "N": n},
                 lambda r: {"x": r.standard_normal((m, n), dtype=np.float32), "w": r.uniform(0.5, 1.5, n).astype(np.float32)},
-                2 * m * n * 4 + n * 4 + m * 4, 0, "rms-norm with a ReLU inside, f32 [8192,4096] (fused row program)")
+                2 * m * n * 4 + n * 4 + m * 4, 0,
+                "rms-norm with a ReLU inside, f32 [8192,4096] (norm kernel)" if inner == "relu"
+                else "rms-norm with |x| inside, f32 [8192,4096] (fused row program)")
     if name == "rope":
         sq, b, h, d = 8192, 2, 16, 128
         js = {"name": "rope", "tensors": {"x": _t(["S", "B", "H", "D"]), "cos": _t(["S", "D2"]), "sin": _t(["S", "D2"]), "y": _t(["S", "B", "H", "D"])},
@@ -261,7 +266,7 @@ def workload(name):
 
 
 # the per-op table, least important first: a reader that keeps only the end of the line keeps the BASELINE configurations
-OPS_ORDER = ("reduce_any", "reduce_any_large", "column_sum", "reduce_sum_all", "dropout", "rope", "rowprog", "dag", "chain", "masked_softmax",
+OPS_ORDER = ("reduce_any", "reduce_any_large", "column_sum", "reduce_sum_all", "dropout", "rope", "rowprog", "rmsnorm_relu", "dag", "chain", "masked_softmax",
              "layernorm_residual", "rmsnorm", "copy_long", "softmax_long", "layernorm_long", "matmul_f32", "matmul_f16", "layernorm", "groupnorm", "matmul")
 
 

@@ -58,7 +58,8 @@ int launch_softmax(const void* x, void* y, float* row_max, float* row_sum, int d
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
                      int dtype, int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner,
                      int64_t affine_period, float eps, cudaStream_t s, int32_t* status = nullptr, bool centre = true,
-                     const void* res = nullptr, const void* res_bias = nullptr, void* scratch = nullptr, size_t scratch_bytes = 0);
+                     const void* res = nullptr, const void* res_bias = nullptr, void* scratch = nullptr, size_t scratch_bytes = 0,
+                     int act = 0);  // act: a ReLU on the normalised value (1) or on the affine result (2)
 size_t softmax_scratch_bytes(int64_t rows, int64_t cols, int elem_bytes);
 size_t norm_scratch_bytes(int64_t rows, int64_t cols, int elem_bytes);
 int try_softmax_segmented(const void* x, void* y, float* row_max, float* row_sum, int dtype, int out_dtype, int64_t rows, int64_t cols,

@@ -44,6 +44,7 @@ struct AffineMap {  // widx = (linear / inner) % period, evaluated without 64-bi
   int nowrap;  // rows start on a multiple of `inner` and never run past `period`: no modulo per element
   int small;   // rows*cols < 2^31: the row origin needs no 64-bit division
   int centre;  // 1: subtract the row mean (layernorm / groupnorm); 0: rms-norm, y = x * rsqrt(mean(x^2) + eps)
+  int act;     // a ReLU inside the normalisation: 1 on the normalised value before the affine map, 2 on the result after it
   // residual form (f32, rows up to 16384 elements): the normalised value is x + res (+ rbias[col]), summed as
   // the rows are loaded, in that order, so that the sum never makes a round trip through HBM
   const void* res;
@@ -164,8 +165,19 @@ __device__ __forceinline__ void normalise(float (&v)[NV][4], float rstd, const T
           }
       }
     }
+    if (map.act == 0) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) v[i][k] = v[i][k] * rstd * wv[k] + bv[k];
+      for (int k = 0; k < 4; ++k) v[i][k] = v[i][k] * rstd * wv[k] + bv[k];
+    } else {  // graphs with an activation between the statistics and the store (uniform branch: the code is the plan's)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float t = v[i][k] * rstd;
+        if (map.act == 1) t = max_nan(t, 0.0f);
+        t = t * wv[k] + bv[k];
+        if (map.act == 2) t = max_nan(t, 0.0f);
+        v[i][k] = t;
+      }
+    }
   }
 }
 
@@ -433,7 +445,7 @@ __global__ void __launch_bounds__(256) norm_pipe(const T* __restrict__ x, const 
 template <typename T, typename TW, int AFF>
 __global__ void __launch_bounds__(1024) norm_stream(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                                                     T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                                                    int64_t rows, int64_t cols, float eps, int64_t inner, int64_t period, int centre) {
+                                                    int64_t rows, int64_t cols, float eps, int64_t inner, int64_t period, int centre, int act) {
   __shared__ float slots[2][32];
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const T* xr = x + r * cols;
@@ -454,7 +466,11 @@ __global__ void __launch_bounds__(1024) norm_stream(const T* __restrict__ x, con
         if (w) wv = to_f32<TW>(w[idx]);
         if (b) bv = to_f32<TW>(b[idx]);
       }
-      yr[c] = from_f32<T>((to_f32<T>(xr[c]) - mean) * rstd * wv + bv);
+      float t = (to_f32<T>(xr[c]) - mean) * rstd;
+      if (act == 1) t = max_nan(t, 0.0f);
+      t = t * wv + bv;
+      if (act == 2) t = max_nan(t, 0.0f);
+      yr[c] = from_f32<T>(t);
     }
     if (threadIdx.x == 0) {
       if (mean_out) mean_out[r] = mean;
@@ -580,6 +596,7 @@ struct Args {
   int32_t* status;
   int centre;
   const void *res, *rbias;
+  int act;
 };
 
 // whether clusters take the form that hides the exchange of statistics behind the next row's reductions
@@ -658,6 +675,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   map.res = a.res;
   map.rbias = a.rbias;
   map.centre = a.centre;
+  map.act = a.act;
   map.nowrap = 0;
   map.small = a.rows * a.cols < ((int64_t)1 << 31);
   if (AFF == AFF_GENERIC) {
@@ -736,7 +754,7 @@ template <typename T, typename TW, bool VEC, int AFF> int dispatch(const Args& a
   } else {
     if (AFF == AFF_GENERIC && (a.rows * a.cols) / a.inner >= (int64_t)1 << 62) return fail(IB200_ERR_UNSUPPORTED, "norm: extent too large");
     const int grid = (int)(a.rows < (int64_t)kSmCount * 2 ? a.rows : (int64_t)kSmCount * 2);
-    norm_stream<T, TW, AFF><<<grid, 1024, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, a.cols, a.eps, a.inner, a.period, a.centre);
+    norm_stream<T, TW, AFF><<<grid, 1024, 0, a.s>>>(x, w, b, y, a.mean, a.rstd, a.rows, a.cols, a.eps, a.inner, a.period, a.centre, a.act);
   }
 #undef IB200_WARP
 #undef IB200_WARP_L
@@ -788,19 +806,21 @@ int32_t* norm_default_status() {
 
 int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype,
                      int affine_dtype, int64_t rows, int64_t cols, int64_t affine_inner, int64_t affine_period, float eps,
-                     cudaStream_t s, int32_t* status, bool centre, const void* res, const void* res_bias, void* scratch, size_t scratch_bytes) {
+                     cudaStream_t s, int32_t* status, bool centre, const void* res, const void* res_bias, void* scratch, size_t scratch_bytes,
+                     int act) {
   if (!status) status = norm_default_status();
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "norm: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
   if (!x || !y) return fail(IB200_ERR_INVALID, "norm: null pointer");
   if ((w || b) && (affine_inner < 1 || affine_period < 1)) return fail(IB200_ERR_INVALID, "norm: affine_inner and affine_period must be >= 1");
   if (res_bias && !res) return fail(IB200_ERR_INVALID, "norm: a residual bias needs a residual");
-  if (scratch && !res) {  // few, very long rows: segments over the whole GPU (longrow.cu)
+  if (act < 0 || act > 2) return fail(IB200_ERR_INVALID, "norm: unknown activation position");
+  if (scratch && !res && act == 0) {  // few, very long rows: segments over the whole GPU (longrow.cu)
     const int rc = try_norm_segmented(x, w, b, y, mean, rstd, dtype, affine_dtype, rows, cols, affine_inner, affine_period, eps, centre ? 1 : 0,
                                       scratch, scratch_bytes, s);
     if (rc != 1) return rc;
   }
-  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status, centre ? 1 : 0, res, res_bias};
+  Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status, centre ? 1 : 0, res, res_bias, act};
   const int adt = (w || b) ? affine_dtype : dtype;
   switch (dtype) {
     case IB200_F32:

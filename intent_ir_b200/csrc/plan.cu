@@ -806,7 +806,7 @@ class Planner {
     for (Step& s : plan_->steps) {
       size_t bytes = 0;
       if (s.kind == Step::SOFTMAX && s.reduce_kind == 0) bytes = softmax_scratch_bytes(s.d[0], s.d[1], (int)dtype_size(s.dtype));
-      else if (s.kind == Step::NORM && s.idx_buf.empty()) bytes = norm_scratch_bytes(s.d[0], s.d[1], (int)dtype_size(s.dtype));
+      else if (s.kind == Step::NORM && s.idx_buf.empty() && s.flags == 0) bytes = norm_scratch_bytes(s.d[0], s.d[1], (int)dtype_size(s.dtype));
       if (bytes == 0 || s.scratch >= 0) continue;
       s.scratch = new_workspace_buffer(IB200_U8, (int64_t)bytes, "row segment statistics");
       s.label += "(segmented)";
@@ -1108,6 +1108,18 @@ class Planner {
       };
       int d = -1, rs = -1, xh = -1;
       Shape w_full;
+      // a ReLU inside the normalisation rides in the kernel: on the affine result (Y = relu(XH*W + B)) or on the
+      // normalised value (Y = relu(XH)*W + B), as long as the value under it is not itself a graph output
+      int act_pos = 0;
+      auto through_relu = [&](int id, int pos) {
+        id = skip_reshapes(id);
+        if (nodes_[id].op != "relu" || act_pos != 0) return id;
+        for (auto& other : outputs_)
+          if (skip_reshapes(by_name_[other]) == skip_reshapes(nodes_[id].in[0])) return id;
+        act_pos = pos;
+        return skip_reshapes(nodes_[id].in[0]);
+      };
+      y = through_relu(y, 2);
       {
         const Node& n = nodes_[y];
         int scaled = y;
@@ -1123,8 +1135,15 @@ class Planner {
         else if (m.op == "mul") {
           for (int k = 0; k < 2; ++k) {
             View tmp;
-            if (input_view(m.in[k], tmp) && is_xhat(m.in[1 - k], d, rs)) { w = m.in[k]; w_full = m.shape; xh = skip_reshapes(m.in[1 - k]); break; }
+            if (!input_view(m.in[k], tmp)) continue;
+            const int saved = act_pos;
+            const int cand = through_relu(m.in[1 - k], 1);
+            if (is_xhat(cand, d, rs)) { w = m.in[k]; w_full = m.shape; xh = cand; break; }
+            act_pos = saved;
           }
+        } else if (m.op == "relu" && act_pos == 0) {  // Y = relu(XH) [+ B]
+          const int cand = through_relu(scaled, 1);
+          if (cand != scaled && is_xhat(cand, d, rs)) xh = cand;
         }
         if (xh < 0) continue;
       }
@@ -1183,6 +1202,8 @@ class Planner {
       Step s;
       s.kind = Step::NORM;
       s.label = !centred ? "rmsnorm" : (inner == 1 && period == L) || (w < 0 && b < 0) ? "layernorm" : "groupnorm";
+      if (act_pos) s.label += "+relu";
+      s.flags = act_pos;        // NORM steps: where a ReLU sits (1: on the normalised value, 2: on the affine result)
       s.act = centred ? 1 : 0;  // NORM steps: whether the row mean is subtracted
       s.d[0] = total / L;
       s.d[1] = L;
@@ -2948,7 +2969,7 @@ int ib200_plan_launch(const ib200_plan_t* plan, void* const* args, int n_args, v
                               static_cast<float*>(P(st.out[2])), st.dtype, st.dtype2, st.d[0], st.d[1], st.aff_inner, st.aff_period,
                               st.eps, s, status, st.act != 0, st.idx_buf.size() > 0 ? P(st.idx_buf[0]) : nullptr,
                               st.idx_buf.size() > 1 ? P(st.idx_buf[1]) : nullptr, st.scratch >= 0 ? P(st.scratch) : nullptr,
-                              st.scratch >= 0 ? plan->buffers[st.scratch].bytes : 0);
+                              st.scratch >= 0 ? plan->buffers[st.scratch].bytes : 0, st.flags);
         break;
       case Step::GEMM:
         for (int64_t bi = 0; bi < st.batch && rc == IB200_OK; ++bi)

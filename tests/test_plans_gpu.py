@@ -1028,3 +1028,43 @@ def test_compiled_in_chains_give_the_interpreters_bits():
             out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
             want = execute_intent(intent, ins, {"M": m, "N": n})["y"]
             assert np.array_equal(out["y"], want, equal_nan=True), (name, m, n)
+
+
+@pytest.mark.parametrize("m,n", [(7, 64), (33, 1000), (64, 4096), (16, 8192), (40, 20000), (24, 40000), (5, 4099)])
+@pytest.mark.parametrize("where", ["inside", "after"])
+def test_relu_inside_a_normalisation_rides_in_the_norm_kernel(m, n, where, golden_graphs):
+    """rms-norm with relu(x̂)·w and layernorm followed by a ReLU: one norm kernel, checked against the oracle."""
+    rng = np.random.default_rng(m + n)
+    if where == "inside":
+        t = lambda s: {"dtype": "f32", "shape": s, "layout": "row_major"}  # noqa: E731
+        js = {"name": "rms_relu", "tensors": {"x": t(["M", "N"]), "w": t(["N"]), "y": t(["M", "N"]), "rstd": t(["M"])},
+              "ops": [{"op": "mul", "inputs": ["x", "x"], "output": "sq"},
+                      {"op": "reduce_sum", "inputs": ["sq"], "output": "ss", "attrs": {"dims": [1], "keepdims": True, "scale": "1.0/N"}},
+                      {"op": "add", "inputs": ["ss"], "output": "ve", "attrs": {"addend": 1e-5}},
+                      {"op": "rsqrt", "inputs": ["ve"], "output": "r1"},
+                      {"op": "reshape", "inputs": ["r1"], "output": "rstd", "attrs": {"shape": ["M"]}},
+                      {"op": "mul", "inputs": ["x", "r1"], "output": "xn"},
+                      {"op": "relu", "inputs": ["xn"], "output": "xr"},
+                      {"op": "mul", "inputs": ["xr", "w"], "output": "y"}], "outputs": ["y", "rstd"]}
+        ins = {"x": rng.standard_normal((m, n), dtype=np.float32), "w": rng.uniform(-1.5, 1.5, n).astype(np.float32)}
+        label = "rmsnorm+relu"
+    else:
+        js = json.loads(json.dumps(golden_graphs["layer_norm_persistent"]["intent"]))
+        out = js["outputs"][0]
+        for o in js["ops"]:
+            if o["output"] == out:
+                o["output"] = "pre_relu"
+        js["tensors"]["pre_relu"] = dict(js["tensors"][out])
+        js["ops"].append({"op": "relu", "inputs": ["pre_relu"], "output": out})
+        ins = {"in_ptr": rng.standard_normal((m, n), dtype=np.float32), "weight_ptr": rng.uniform(-1.5, 1.5, n).astype(np.float32),
+               "bias_ptr": (0.3 * rng.standard_normal(n)).astype(np.float32)}
+        label = "layernorm+relu"
+    intent = IntentFunction.from_json_dict(js)
+    out_, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
+    assert [s["kernel"] for s in lowered.steps] == [label]
+    want = execute_intent(intent, ins, {"M": m, "N": n})
+    tol = infer_tolerances(intent).to_dict()
+    for name in intent.outputs:
+        _agree(out_[name], want[name], tol, name)
+    main = out_[intent.outputs[0]]
+    assert (main == 0).mean() > 0.2 or where == "inside"  # the ReLU really clipped something

@@ -67,7 +67,8 @@ def _t(shape, dtype="f32"):
 
 
 def _rms(m, n):
-    """rms-norm with a relu between the scaling and the weight, so that the dedicated norm kernel's pattern does not apply"""
+    """rms-norm with |x| between the scaling and the weight, so that no dedicated norm kernel's pattern applies (a ReLU
+    there rides in the norm kernel)"""
     return {"name": "rms", "tensors": {"x": _t(["M", "N"]), "w": _t(["N"]), "y": _t(["M", "N"]), "rstd": _t(["M"])},
             "ops": [{"op": "mul", "inputs": ["x", "x"], "output": "sq"},
                     {"op": "reduce_sum", "inputs": ["sq"], "output": "ss", "attrs": {"dims": [1], "keepdims": True}},
@@ -76,7 +77,7 @@ def _rms(m, n):
                     {"op": "rsqrt", "inputs": ["me"], "output": "r1"},
                     {"op": "reshape", "inputs": ["r1"], "output": "rstd", "attrs": {"shape": ["M"]}},
                     {"op": "mul", "inputs": ["x", "r1"], "output": "xn"},
-                    {"op": "relu", "inputs": ["xn"], "output": "xr"},
+                    {"op": "abs", "inputs": ["xn"], "output": "xr"},
                     {"op": "mul", "inputs": ["xr", "w"], "output": "y"}], "outputs": ["y", "rstd"]}
 
 
