@@ -370,11 +370,14 @@ struct EwStaticIns {
   uint8_t op, src, b, c, dst;
 };
 
+// (the explicitly rounded intrinsics keep the compiler from contracting a multiply and the add of the NEXT micro-op into
+// one FMA, which it would do here, where the chain is straight-line code, and cannot do across the interpreter's
+// branches: every micro-op rounds on its own, as numpy's does)
 template <uint8_t OP> __device__ __forceinline__ float static_op(float x, float y) {
   if constexpr (OP == EW_MOV) return x;
-  else if constexpr (OP == EW_ADD) return x + y;
-  else if constexpr (OP == EW_SUB) return x - y;
-  else if constexpr (OP == EW_MUL) return x * y;
+  else if constexpr (OP == EW_ADD) return __fadd_rn(x, y);
+  else if constexpr (OP == EW_SUB) return __fsub_rn(x, y);
+  else if constexpr (OP == EW_MUL) return __fmul_rn(x, y);
   else if constexpr (OP == EW_DIV) return x / y;
   else if constexpr (OP == EW_MAX) return max_nan(x, y);
   else if constexpr (OP == EW_MIN) return min_nan(x, y);
@@ -395,7 +398,7 @@ template <uint8_t OP> __device__ __forceinline__ float static_op(float x, float 
   else if constexpr (OP == EW_TO_INT) return truncf(x);
   else if constexpr (OP == EW_ROUND_BF16) return __bfloat162float(__float2bfloat16_rn(x));
   else if constexpr (OP == EW_ROUND_F16) return __half2float(__float2half_rn(x));
-  else if constexpr (OP == EW_RSUB) return y - x;
+  else if constexpr (OP == EW_RSUB) return __fsub_rn(y, x);
   else if constexpr (OP == EW_RDIV) return y / x;
   else return y;  // EW_LOADB
 }

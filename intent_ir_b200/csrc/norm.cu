@@ -479,113 +479,6 @@ __global__ void __launch_bounds__(1024) norm_stream(const T* __restrict__ x, con
   }
 }
 
-// The cluster form of norm_pipe with the exchange of statistics taken off the critical path: a CTA sends the statistics
-// of row i and, instead of waiting for its peers' right away, first stages and reduces its segment of row i+1; only then
-// does it collect row i's statistics, normalise and store row i (whose centred values it kept in registers).  The round
-// trip through the peers' shared memory is hidden behind the next row's two block reductions.  Per iteration i:
-//     A(i)  local statistics of row i          C(i)  wait for row i-1's exchange, finish row i-1          B(i)  send row i's
-// Two sets of exchange slots suffice: a CTA sends row i only after C(i), i.e. after every peer has sent row i-1, which each
-// peer does (B(i-1)) after reading the slots of row i-2 (C(i-1)) — the slots row i overwrites.
-template <typename T, typename TW, int AFF, int NV>
-__global__ void __launch_bounds__(256, 4) norm_pipe_overlapped(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
-                                                            T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                                                            int64_t rows, int cols, int seg, int stage_bytes, float eps, AffineMap map,
-                                                            int32_t* status) {
-  constexpr int THREADS = 256;
-  extern __shared__ __align__(128) unsigned char stage_mem[];
-  __shared__ uint64_t bar[2];
-  __shared__ uint64_t xbar[2];
-  __shared__ float slots[2][32];
-  __shared__ float part[2][8][3];
-  __shared__ float merged[2][2];
-  cg::cluster_group cluster = cg::this_cluster();
-  const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
-  const int64_t n_groups = gridDim.x / csize, group = blockIdx.x / csize;
-  const int col0 = rank * seg;
-  const int mine = min(seg, cols - col0) > 0 ? min(seg, cols - col0) : 0;
-  const uint32_t bytes = (uint32_t)mine * sizeof(T);
-  if (threadIdx.x == 0) {
-    mbarrier_init(&bar[0], 1);
-    mbarrier_init(&bar[1], 1);
-    mbarrier_init(&xbar[0], 1);
-    mbarrier_init(&xbar[1], 1);
-    mbarrier_init_fence();
-  }
-  __syncthreads();
-  cluster_arrive();
-  if (threadIdx.x == 0 && bytes && group < rows) {
-    mbarrier_expect_tx(&bar[0], bytes);
-    bulk_load(stage_mem, x + group * cols + col0, bytes, &bar[0]);
-  }
-  float prev[NV][4];       // x - mean_k of the row whose statistics are travelling
-  float prev_mean_k = 0.0f;
-  int64_t prev_r = -1;
-  // collect the peers' statistics of the row in `prev`, normalise and store it
-  auto finish_previous = [&](int it_prev) {
-    const int xs = it_prev & 1;
-    if (threadIdx.x < 32) {
-      if (!mbarrier_wait_bounded(&xbar[xs], (it_prev >> 1) & 1) && status) atomicCAS(status, 0, 6);
-      const bool have = threadIdx.x < csize;
-      const float mk = have ? part[xs][threadIdx.x][0] : 0.0f, qk = have ? part[xs][threadIdx.x][1] : 0.0f, nk = have ? part[xs][threadIdx.x][2] : 0.0f;
-      const float mu = warp_reduce<SumOp>(nk * mk) / (float)cols;
-      const float d = mk - mu;
-      const float total = warp_reduce<SumOp>(qk + nk * d * d);
-      if (threadIdx.x == 0) { merged[xs][0] = mu; merged[xs][1] = total; }
-    }
-    __syncthreads();
-    const float mean = merged[xs][0], rstd = 1.0f / sqrtf(merged[xs][1] / (float)cols + eps);
-    const float shift = prev_mean_k - mean;
-#pragma unroll
-    for (int i = 0; i < NV; ++i)
-#pragma unroll
-      for (int k = 0; k < 4; ++k) prev[i][k] += shift;
-    uint32_t lq = 0, lr = 0;
-    if (AFF == AFF_GENERIC) row_origin(prev_r, cols, map, lq, lr);
-    normalise<TW, NV, true, AFF>(prev, rstd, w, b, mine, col0, threadIdx.x, THREADS, map, lq, lr, uniform_affine<TW, AFF>(w, b, mine, col0, map, lq, lr));
-    store_row<T, NV, true>(y + prev_r * cols + col0, mine, threadIdx.x, THREADS, prev);
-    if (rank == 0 && threadIdx.x == 0) {
-      if (mean_out) mean_out[prev_r] = mean;
-      if (rstd_out) rstd_out[prev_r] = rstd;
-    }
-  };
-  int it = 0;
-  for (int64_t r = group; r < rows; r += n_groups, ++it) {
-    const int st = it & 1;
-    if (threadIdx.x == 0 && bytes && r + n_groups < rows) {  // every thread finished reading stage st^1 one iteration ago
-      mbarrier_expect_tx(&bar[st ^ 1], bytes);
-      bulk_load(stage_mem + (st ^ 1) * stage_bytes, x + (r + n_groups) * cols + col0, bytes, &bar[st ^ 1]);
-    }
-    if (threadIdx.x < 32 && bytes && !mbarrier_wait_bounded(&bar[st], (it >> 1) & 1) && status) atomicCAS(status, 0, 5);
-    __syncthreads();
-    // A(i): this CTA's statistics of row r
-    float v[NV][4];
-    load_row<T, NV, true>(reinterpret_cast<const T*>(stage_mem + st * stage_bytes), mine, threadIdx.x, THREADS, 0.0f, v);
-    const float s = block_reduce<SumOp>(local_sum<NV>(v), slots[0]);
-    const float mean_k = mine > 0 && map.centre ? s / (float)mine : 0.0f;
-    const float q = block_reduce<SumOp>(centre_and_square<NV, true>(v, mean_k, mine, threadIdx.x, THREADS), slots[1]);
-    // C(i): the previous row's exchange has had all of A(i) to complete
-    if (it == 0) cluster_wait();  // every CTA of the cluster runs and has initialised its barriers
-    else finish_previous(it - 1);
-    // B(i): send
-    const int xs = it & 1;
-    if (threadIdx.x == 0) mbarrier_expect_tx(&xbar[xs], (uint32_t)csize * 12u);
-    if (threadIdx.x < csize) {
-      const uint32_t dst = cluster_map(&part[xs][rank][0], threadIdx.x), rbar = cluster_map(&xbar[xs], threadIdx.x);
-      remote_store_signal(dst, mean_k, rbar);
-      remote_store_signal(dst + 4, q, rbar);
-      remote_store_signal(dst + 8, (float)mine, rbar);
-    }
-#pragma unroll
-    for (int i = 0; i < NV; ++i)
-#pragma unroll
-      for (int k = 0; k < 4; ++k) prev[i][k] = v[i][k];
-    prev_mean_k = mean_k;
-    prev_r = r;
-  }
-  if (it == 0) cluster_wait();  // a cluster without rows still has to meet its peers' opening arrive
-  else finish_previous(it - 1);
-}
-
 struct Args {
   const void *x, *w, *b;
   void* y;
@@ -598,12 +491,6 @@ struct Args {
   const void *res, *rbias;
   int act;
 };
-
-// whether clusters take the form that hides the exchange of statistics behind the next row's reductions
-bool overlap_exchange() {
-  static const bool on = std::getenv("IB200_NORM_OVERLAP") && std::getenv("IB200_NORM_OVERLAP")[0] == '1';
-  return on;
-}
 
 // how many groups of `csize` CTAs of a kernel can be resident at once (cached per kernel)
 template <typename K> int resident_groups(K kernel, int csize, int smem) {
@@ -639,10 +526,7 @@ template <typename K> int resident_groups(K kernel, int csize, int smem) {
 }
 
 template <typename T, typename TW, int AFF, bool CLUSTER, int NV> int launch_pipe(const Args& a, const AffineMap& map, int csize, int seg) {
-  void (*kernel)(const T*, const TW*, const TW*, T*, float*, float*, int64_t, int, int, int, float, AffineMap, int32_t*) = norm_pipe<T, TW, AFF, CLUSTER, NV>;
-  if constexpr (CLUSTER) {
-    if (overlap_exchange()) kernel = norm_pipe_overlapped<T, TW, AFF, NV>;
-  }
+  auto kernel = norm_pipe<T, TW, AFF, CLUSTER, NV>;
   const int stage_bytes = (int)(((size_t)seg * sizeof(T) + 127) & ~(size_t)127);
   const int smem = 2 * stage_bytes;
   const int64_t resident = resident_groups(kernel, csize, smem);
