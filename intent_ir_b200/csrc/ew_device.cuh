@@ -21,6 +21,10 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
 }
 
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_committed() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }  // all but the newest group
+
 __device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t off) {
   switch (dtype) {
     case IB200_F32: return static_cast<const float*>(p)[off];
@@ -150,6 +154,41 @@ template <int N> __device__ __forceinline__ void apply_scalar(uint8_t op, float 
     default: break;
   }
 #undef EW_CASE
+}
+
+// One micro-op with its opcode as a template argument, for programs that are compiled in (elementwise.cu,
+// rowfuse.cu): the same expressions per opcode as apply() above.
+// (the explicitly rounded intrinsics keep the compiler from contracting a multiply and the add of the NEXT micro-op into
+// one FMA, which it would do here, where the chain is straight-line code, and cannot do across the interpreter's
+// branches: every micro-op rounds on its own, as numpy's does)
+template <uint8_t OP> __device__ __forceinline__ float static_op(float x, float y) {
+  if constexpr (OP == EW_MOV) return x;
+  else if constexpr (OP == EW_ADD) return __fadd_rn(x, y);
+  else if constexpr (OP == EW_SUB) return __fsub_rn(x, y);
+  else if constexpr (OP == EW_MUL) return __fmul_rn(x, y);
+  else if constexpr (OP == EW_DIV) return x / y;
+  else if constexpr (OP == EW_MAX) return max_nan(x, y);
+  else if constexpr (OP == EW_MIN) return min_nan(x, y);
+  else if constexpr (OP == EW_RELU) return max_nan(x, 0.0f);
+  else if constexpr (OP == EW_EXP) return expf(x);
+  else if constexpr (OP == EW_RSQRT) return 1.0f / sqrtf(x);
+  else if constexpr (OP == EW_ABS) return fabsf(x);
+  else if constexpr (OP == EW_FLOOR) return floorf(x);
+  else if constexpr (OP == EW_NE) return x != y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_LT) return x < y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_LE) return x <= y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_GT) return x > y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_GE) return x >= y ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_AND) return (x != 0.0f && y != 0.0f) ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_OR) return (x != 0.0f || y != 0.0f) ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_NOT) return x != 0.0f ? 0.0f : 1.0f;
+  else if constexpr (OP == EW_TO_BOOL) return x != 0.0f ? 1.0f : 0.0f;
+  else if constexpr (OP == EW_TO_INT) return truncf(x);
+  else if constexpr (OP == EW_ROUND_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+  else if constexpr (OP == EW_ROUND_F16) return __half2float(__float2half_rn(x));
+  else if constexpr (OP == EW_RSUB) return __fsub_rn(y, x);
+  else if constexpr (OP == EW_RDIV) return y / x;
+  else return y;  // EW_LOADB
 }
 
 }  // namespace

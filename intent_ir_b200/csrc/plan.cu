@@ -2759,6 +2759,7 @@ class Planner {
     r.set("n_row_slots", num(p.n_row_slots));
     r.set("n_once_slots", num(p.n_once_slots));
     r.set("n_scalars", num(p.n_scalars));
+    r.set("compiled_in", Json::boolean(row_program_compiled_in(p)));
     Json phases = Json::array();
     for (int ph = 0; ph < p.n_phases; ++ph) {
       const RowPhase& f = p.phase[ph];

@@ -89,4 +89,8 @@ bool row_program_fits(int n_row_slots, int n_once_slots, int cols);
 
 int launch_row_program(const RowProgram& prog, cudaStream_t s);
 
+// whether the program is one of those whose phases are also compiled into the kernel as straight-line code
+// (the same arithmetic, without the decoding); any other program runs decoded
+bool row_program_compiled_in(const RowProgram& prog);
+
 }  // namespace ib200

@@ -1070,3 +1070,56 @@ def test_relu_inside_a_normalisation_rides_in_the_norm_kernel(m, n, where, golde
         _agree(out_[name], want[name], tol, name)
     main = out_[intent.outputs[0]]
     assert (main == 0).mean() > 0.2 or where == "inside"  # the ReLU really clipped something
+
+
+# ---- row programs that are also compiled in (rowfuse.cu): every launch shape against the oracle ----
+
+@pytest.mark.parametrize("key", ["_attn_fwd", "flash_attention2d"])
+@pytest.mark.parametrize("kv", [16, 200, 1024, 1028, 4096, 8200, 250])
+def test_compiled_in_attention_softmax_rows(key, kv, golden_graphs):
+    """The scale + mask + softmax between an attention's two products is one fused row program whose phases are
+    also compiled into the kernel.  Row lengths cover one warp per row (up to 1024), 128 and 512 threads per
+    row, rows that end inside a pass, and a length that is no multiple of 4 (which runs decoded)."""
+    g = golden_graphs[key]
+    intent = IntentFunction.from_json_dict(g["intent"])
+    shapes = dict(g["shapes"], KV_CTX=kv, Q_CTX=24)
+    rng = np.random.default_rng(kv)
+    dims = lambda name: tuple(shapes[d] if isinstance(d, str) else d for d in g["intent"]["tensors"][name]["shape"])  # noqa: E731
+    ins = {n: rng.standard_normal(dims(n), dtype=np.float32) for n in g["inputs"]}
+    ins["sm_scale"] = np.array([0.25], dtype=np.float32)
+    if "attn_mask" in ins:
+        ins["attn_mask"] = np.where(rng.random(dims("attn_mask")) < 0.2, -1e9, 0.0).astype(np.float32)
+    out, lowered = _lower_and_run(intent, shapes, ins)
+    fused = [s for s in lowered.steps if "row_program" in s]
+    assert len(fused) == 1 and fused[0]["row_program"]["compiled_in"] == (kv % 4 == 0), [s["kernel"] for s in lowered.steps]
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, ins, shapes)
+    tol = infer_tolerances(intent).to_dict()
+    for name in g["outputs"]:
+        _agree(out[name], want[name], tol, f"{key}/{name}/kv={kv}")
+
+
+@pytest.mark.parametrize("m,n", [(64, 512), (300, 4096), (16, 8192), (9, 1000), (5, 4100)])
+def test_compiled_in_rms_row_program(m, n):
+    """rms-norm with |x| between the normalisation and the weight: nothing dedicated matches, so it runs as a
+    fused row program, one of those compiled in; rstd is the graph's second output."""
+    t = lambda shape: {"dtype": "f32", "shape": shape, "layout": "row_major"}  # noqa: E731
+    js = {"name": "rms_abs", "tensors": {"x": t(["M", "N"]), "w": t(["N"]), "y": t(["M", "N"]), "rstd": t(["M"])},
+          "ops": [{"op": "mul", "inputs": ["x", "x"], "output": "sq"},
+                  {"op": "reduce_sum", "inputs": ["sq"], "output": "ss", "attrs": {"dims": [1], "keepdims": True, "scale": "1.0/N"}},
+                  {"op": "add", "inputs": ["ss"], "output": "ve", "attrs": {"addend": 1e-5}},
+                  {"op": "rsqrt", "inputs": ["ve"], "output": "r1"},
+                  {"op": "reshape", "inputs": ["r1"], "output": "rstd", "attrs": {"shape": ["M"]}},
+                  {"op": "mul", "inputs": ["x", "r1"], "output": "xn"},
+                  {"op": "abs", "inputs": ["xn"], "output": "xr"},
+                  {"op": "mul", "inputs": ["xr", "w"], "output": "y"}], "outputs": ["y", "rstd"]}
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(n)
+    ins = {"x": rng.standard_normal((m, n), dtype=np.float32), "w": rng.uniform(0.5, 1.5, n).astype(np.float32)}
+    out, lowered = _lower_and_run(intent, {"M": m, "N": n}, ins)
+    fused = [s for s in lowered.steps if "row_program" in s]
+    assert len(lowered.steps) == 1 and fused and fused[0]["row_program"]["compiled_in"]
+    want = execute_intent(intent, ins, {"M": m, "N": n})
+    tol = infer_tolerances(intent).to_dict()
+    for name in ("y", "rstd"):
+        _agree(out[name], want[name], tol, f"rms_abs/{name}/{m}x{n}")
