@@ -63,10 +63,10 @@ int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float
 size_t softmax_scratch_bytes(int64_t rows, int64_t cols, int elem_bytes);
 size_t norm_scratch_bytes(int64_t rows, int64_t cols, int elem_bytes);
 int try_softmax_segmented(const void* x, void* y, float* row_max, float* row_sum, int dtype, int out_dtype, int64_t rows, int64_t cols,
-                          void* scratch, size_t scratch_bytes, cudaStream_t s);  // 1: not taken, use the ordinary kernels
+                          void* scratch, size_t scratch_bytes, cudaStream_t s, int32_t* status = nullptr);  // 1: not taken, use the ordinary kernels
 int try_norm_segmented(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int affine_dtype,
                        int64_t rows, int64_t cols, int64_t inner, int64_t period, float eps, int centre, void* scratch, size_t scratch_bytes,
-                       cudaStream_t s);
+                       cudaStream_t s, int32_t* status = nullptr);
 int32_t* norm_default_status();
 // flags: IB200_GEMM_ALLOW_TF32.  With scratch (256-byte aligned, gemm_scratch_bytes says how much) the tiles of a
 // last, mostly empty round of the tensor-core kernel are split along K; without it they run whole.

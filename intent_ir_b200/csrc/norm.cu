@@ -735,7 +735,7 @@ int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float
   if (act < 0 || act > 2) return fail(IB200_ERR_INVALID, "norm: unknown activation position");
   if (scratch && !res && act == 0) {  // few, very long rows: segments over the whole GPU (longrow.cu)
     const int rc = try_norm_segmented(x, w, b, y, mean, rstd, dtype, affine_dtype, rows, cols, affine_inner, affine_period, eps, centre ? 1 : 0,
-                                      scratch, scratch_bytes, s);
+                                      scratch, scratch_bytes, s, status);
     if (rc != 1) return rc;
   }
   Args a{x, w, b, y, mean, rstd, rows, cols, affine_inner, affine_period, eps, s, status, centre ? 1 : 0, res, res_bias, act};
