@@ -62,11 +62,13 @@ L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # the ncu summary that holds each workload's DRAM counters (dram__bytes_read.sum / dram__bytes_write.sum rows)
 PROFILE_OF = {"softmax": "softmax_block_f32_4096x4096.md", "layernorm": "norm_block_layernorm_f32_8192x4096.md",
-              "groupnorm": "norm_pipe_groupnorm_f32_32x256x4096.md", "matmul": "gemm_tcgen05_bf16_4096x4096x4096.md",
-              "chain": "ew_kernel_reg_chain4_f32_8192x4096.md", "rmsnorm": "norm_block_rmsnorm_f32_8192x4096.md",
-              "rowprog": "row_kernel_rms_relu_f32_8192x4096.md", "rope": "rope_kernel_f32_8192x2x16x128.md",
+              "groupnorm": "norm_pipe_groupnorm_f32_32x256x4096.md", "matmul": "gemm_tcgen05_pair_bf16_4096x4096x4096.md",
+              "chain": "ew_kernel_static_chain4_f32_8192x4096.md", "dag": "ew_kernel_static_dag6_f32_8192x4096.md",
+              "rmsnorm": "norm_block_rmsnorm_f32_8192x4096.md", "rmsnorm_relu": "norm_block_rmsnorm_relu_f32_8192x4096.md",
+              "rowprog": "row_kernel_static_rms_abs_f32_8192x4096.md", "rope": "rope_kernel_f32_8192x2x16x128.md",
               "masked_softmax": "softmax_block_masked_f32_4096x4096.md", "reduce_sum_all": "reduce_rows_split_sum_f32_8192x8192.md",
-              "column_sum": "reduce_cols_vec_sum_f32_65536x1024.md"}
+              "column_sum": "reduce_cols_vec_sum_f32_65536x1024.md", "softmax_long": "softmax_resident_f32_4x1Mi.md",
+              "layernorm_long": "norm_resident_f32_4x1Mi.md"}
 
 
 def host_cores() -> list:
