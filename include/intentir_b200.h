@@ -70,6 +70,7 @@ extern "C" {
 /* ---- flags for ib200_gemm_bias_act_ws ------------------------------------------------- */
 #define IB200_GEMM_CTA_PAIRS 2  /* force the tensor-core product onto pairs of CTAs (tcgen05 cta_group::2, 256 x 256 tiles) */
 #define IB200_GEMM_ONE_CTA 4    /* force the one-CTA kernel (128 x 256/192/128 tiles); default: pairs for large products */
+#define IB200_GEMM_NARROW_TAIL 8 /* CTA pairs: the tiles of a mostly empty last round run as two 256 x 128 units each (default: whole) */
 #define IB200_GEMM_ALLOW_TF32 1 /* f32 operands may be multiplied as TF32 on the tensor cores (the reference's
                                    ALLOW_TF32 binding, intentir_to_cuda.py:577-578); without it f32 stays exact FMA */
 

@@ -20,6 +20,7 @@ ACT_NONE, ACT_RELU = 0, 1
 GEMM_ALLOW_TF32 = 1
 GEMM_CTA_PAIRS = 2
 GEMM_ONE_CTA = 4
+GEMM_NARROW_TAIL = 8
 
 DTYPE_CODE = {"f32": F32, "bf16": BF16, "f16": F16, "i32": I32, "i64": I64, "bool": BOOL, "i1": BOOL,
               "u8": U8, "i8": I8, "i16": I16, "f64": F64}

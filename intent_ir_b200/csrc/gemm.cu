@@ -172,6 +172,8 @@ struct GemmParams {
   int full_tiles, split;
   int* tickets;     // [split tiles][4 row bands], zero before the launch, left zero by it
   float* partial;   // [split tiles][split][BM][BN] fp32
+  // CTA pairs: tiles [0, narrow_from) whole, every later tile as two units of half the width (== tiles: none)
+  int narrow_from;
 };
 
 struct Unit {
@@ -502,6 +504,30 @@ __device__ __forceinline__ void umma_commit_both(uint64_t* bar) {
                ::"r"(smem_u32(bar)), "h"(both) : "memory");
 }
 
+// Work units of the pair kernel.  On request (IB200_GEMM_NARROW_TAIL) the tiles of a last round that would occupy at
+// most half of the pairs run as two units of half the width each (256 x 128), so that twice as many pairs share the
+// round, with no partial sums to exchange.  4096^3: 256 tiles on 74 pairs are 3 full rounds and 34 tiles, i.e. 68
+// narrow units.  Off by default: measured on 4096^3 bf16 it changes nothing (101.3 against 101.0 us, alternating
+// runs) -- at the board's power cap the time of a product follows the energy it takes, not how evenly the SMs finish,
+// and narrow units move more operand bytes per flop.  4096 x 5120 x 2048: 70.8 against 73.4 us.
+struct PairUnit {
+  int m_tile, n0, bn;
+};
+__device__ __forceinline__ PairUnit pair_unit(int u, int narrow_from, int tiles_n, int bn_wide) {
+  PairUnit w;
+  if (u < narrow_from) {
+    w.m_tile = u / tiles_n;
+    w.n0 = (u % tiles_n) * bn_wide;
+    w.bn = bn_wide;
+  } else {
+    const int t = narrow_from + ((u - narrow_from) >> 1);
+    w.m_tile = t / tiles_n;
+    w.bn = bn_wide / 2;
+    w.n0 = (t % tiles_n) * bn_wide + ((u - narrow_from) & 1) * w.bn;
+  }
+  return w;
+}
+
 template <int BN> struct PairCfg {
   static constexpr int B_STAGE_BYTES = KROW_BYTES * (BN / 2);
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;   // 32 KiB at BN = 256
@@ -511,8 +537,9 @@ template <int BN> struct PairCfg {
 
 template <typename TOut, int BN, int KIND>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
-gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
-  constexpr int STAGES = PairCfg<BN>::STAGES, STAGE_BYTES = PairCfg<BN>::STAGE_BYTES, HALF = BN / 2;
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_b_narrow, const GemmParams p) {
+  constexpr int STAGES = PairCfg<BN>::STAGES, STAGE_BYTES = PairCfg<BN>::STAGE_BYTES;
   constexpr int BK = KindCfg<KIND>::BK, UMMA_K = KindCfg<KIND>::UMMA_K, NBOX = KROW_BYTES / KindCfg<KIND>::ESZ;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -528,6 +555,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
   const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM), tiles_n = (p.N + BN - 1) / BN;
   const int ntiles = tiles_m * tiles_n;
+  const int nunits = p.narrow_from + 2 * (ntiles - p.narrow_from);  // tiles from narrow_from on run as two half-width units
   const int kblocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -552,8 +580,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; tile < ntiles && ok; tile += npairs) {
-        const int m0 = (tile / tiles_n) * (2 * BM) + (int)rank * BM, n0 = (tile % tiles_n) * BN + (int)rank * HALF;
+      for (int u = pair; u < nunits && ok; u += npairs) {
+        const PairUnit w = pair_unit(u, p.narrow_from, tiles_n, BN);
+        const int m0 = w.m_tile * (2 * BM) + (int)rank * BM, n0 = w.n0 + (int)rank * (w.bn / 2);
+        const uint32_t stage_tx = 2 * (A_STAGE_BYTES + (w.bn / 2) * KROW_BYTES);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -561,13 +591,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           const uint32_t bar = map_to_cta(&full[s], 0);  // CTA 0's barrier counts the bytes of both CTAs
-          if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(&full[s], stage_tx);
           tma_load_2d_pair(sa, &map_a, bar, kb * BK, m0);
           if (p.b_kmajor) {
-            tma_load_2d_pair(sb, &map_b, bar, kb * BK, n0);  // one box: BK (K) x HALF (N rows)
+            tma_load_2d_pair(sb, w.bn == BN ? &map_b : &map_b_narrow, bar, kb * BK, n0);  // one box: BK (K) x this CTA's N rows
           } else {
-#pragma unroll
-            for (int j = 0; j < HALF / NBOX; ++j)
+            for (int j = 0; j < (w.bn / 2) / NBOX; ++j)
               tma_load_2d_pair(sb + j * (BK * KROW_BYTES), &map_b, bar, n0 + j * NBOX, kb * BK);
           }
         }
@@ -585,11 +614,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       // ------------------------------ MMA issuer (CTA 0) -------------------------------
-      const uint32_t idesc = (1u << 4) | (KindCfg<KIND>::FMT << 7) | (KindCfg<KIND>::FMT << 10) | ((p.b_kmajor ? 0u : 1u) << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      const uint32_t idesc_wide = (1u << 4) | (KindCfg<KIND>::FMT << 7) | (KindCfg<KIND>::FMT << 10) | ((p.b_kmajor ? 0u : 1u) << 16) |
+                                  ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      const uint32_t idesc_narrow = (idesc_wide & ~(0x3Fu << 17)) | ((uint32_t)((BN / 2) >> 3) << 17);
       uint32_t it = 0, t_local = 0;
       bool ok = true;
-      for (int tile = pair; tile < ntiles && ok; tile += npairs, ++t_local) {
+      for (int u = pair; u < nunits && ok; u += npairs, ++t_local) {
+        const uint32_t idesc = u < p.narrow_from ? idesc_wide : idesc_narrow;
         const int buf = t_local & 1;
         const uint32_t acc_ph = (t_local >> 1) & 1;
         if (!(ok = mbar_wait(&acc_empty[buf], acc_ph ^ 1, abort_flag, p.status, 2))) break;
@@ -618,10 +649,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int quarter = warp & 3;
     uint32_t t_local = 0;
     bool ok = true;
-    for (int tile = pair; tile < ntiles && ok; tile += npairs, ++t_local) {
+    for (int u = pair; u < nunits && ok; u += npairs, ++t_local) {
+      const PairUnit w = pair_unit(u, p.narrow_from, tiles_n, BN);
       const int buf = t_local & 1;
       const uint32_t acc_ph = (t_local >> 1) & 1;
-      const int m0 = (tile / tiles_n) * (2 * BM) + (int)rank * BM, n0 = (tile % tiles_n) * BN;
+      const int m0 = w.m_tile * (2 * BM) + (int)rank * BM, n0 = w.n0;
       ok = mbar_wait(&acc_full[buf], acc_ph, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -631,7 +663,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const TOut* bias = static_cast<const TOut*>(p.bias);
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < w.bn / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
         const int col0 = n0 + c * 32;
@@ -782,7 +814,7 @@ int launch_tile(const void* a, const void* b, const void* bias, void* c, int out
 
 template <int KIND>
 int launch_pair(const void* a, const void* b, const void* bias, void* c, int out_dtype, int64_t m, int64_t n, int64_t k, int transpose_b,
-                int act, int32_t* status, cudaStream_t s) {
+                int act, int32_t* status, cudaStream_t s, int flags) {
   constexpr int BN = 256, BK = KindCfg<KIND>::BK, NBOX = KROW_BYTES / KindCfg<KIND>::ESZ;
   EncodeTiledFn enc;
   if (int rc = get_encoder(&enc)) return rc;
@@ -793,25 +825,31 @@ int launch_pair(const void* a, const void* b, const void* bias, void* c, int out
   } else {
     if (int rc = make_map(enc, &map_b, b, KIND, k, n, BK, NBOX)) return rc;
   }
-  GemmParams p{(int)m, (int)n, (int)k, transpose_b ? 1 : 0, act, bias, c, status, 0, 1, nullptr, nullptr};
+  CUtensorMap map_b_narrow = map_b;  // [N,K] operands: the box of a half-width unit (a [K,N] operand is loaded in 128-byte boxes either way)
+  if (transpose_b) {
+    if (int rc = make_map(enc, &map_b_narrow, b, KIND, n, k, BN / 4, BK)) return rc;
+  }
   const int64_t tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
   const int pairs = (int)(tiles < kSmCount / 2 ? tiles : kSmCount / 2);
-  void (*kern)(const CUtensorMap, const CUtensorMap, const GemmParams) = nullptr;
+  const int64_t tail = tiles % pairs;
+  const int narrow_from = (int)((flags & IB200_GEMM_NARROW_TAIL) != 0 && tail > 0 && 2 * tail <= pairs ? tiles - tail : tiles);
+  GemmParams p{(int)m, (int)n, (int)k, transpose_b ? 1 : 0, act, bias, c, status, 0, 1, nullptr, nullptr, narrow_from};
+  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams) = nullptr;
   if (KIND == KIND_BF16) kern = out_dtype == IB200_BF16 ? gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, KIND> : gemm_tcgen05_pair_kernel<float, BN, KIND>;
   else if (KIND == KIND_F16) kern = out_dtype == IB200_F16 ? gemm_tcgen05_pair_kernel<__half, BN, KIND> : gemm_tcgen05_pair_kernel<float, BN, KIND>;
   else kern = gemm_tcgen05_pair_kernel<float, BN, KIND>;
   IB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<BN>::SMEM));
-  kern<<<2 * pairs, GEMM_THREADS, PairCfg<BN>::SMEM, s>>>(map_a, map_b, p);
+  kern<<<2 * pairs, GEMM_THREADS, PairCfg<BN>::SMEM, s>>>(map_a, map_b, map_b_narrow, p);
   return cudaPeekAtLastError() == cudaSuccess ? IB200_OK : cuda_fail(cudaGetLastError(), "gemm tcgen05 (CTA pairs) launch");
 }
 
 template <int KIND>
 int run_tcgen05(const void* a, const void* b, const void* bias, void* c, int out_dtype, int64_t m, int64_t n, int64_t k,
-                int transpose_b, int act, int32_t* status, void* scratch, size_t scratch_bytes, cudaStream_t s, bool pair) {
+                int transpose_b, int act, int32_t* status, void* scratch, size_t scratch_bytes, cudaStream_t s, bool pair, int flags) {
   // tile width: fewest (rounds of 148 CTAs) x (time per tile); narrower tiles re-read A more often and
   // the main loop is bound by operand traffic into shared memory, so they only win when they
   // save whole rounds (small or ragged N)
-  if (pair) return launch_pair<KIND>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s);
+  if (pair) return launch_pair<KIND>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, s, flags);
   if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u)) scratch_bytes = 0;
   const SplitPlan sp = choose_plan(m, n, k, KIND, scratch_bytes, false);
   switch (sp.bn) {
@@ -942,9 +980,9 @@ int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_
   if (tc) {
     if (!status) return fail(IB200_ERR_INVALID, "gemm: the tensor-core path needs a device status word");
     const bool pair = prefers_cta_pairs(m, n, flags);
-    if (in_dtype == IB200_BF16) return run_tcgen05<KIND_BF16>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s, pair);
-    if (in_dtype == IB200_F16) return run_tcgen05<KIND_F16>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s, pair);
-    return run_tcgen05<KIND_TF32>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s, pair);
+    if (in_dtype == IB200_BF16) return run_tcgen05<KIND_BF16>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s, pair, flags);
+    if (in_dtype == IB200_F16) return run_tcgen05<KIND_F16>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s, pair, flags);
+    return run_tcgen05<KIND_TF32>(a, b, bias, c, out_dtype, m, n, k, transpose_b, act, status, scratch, scratch_bytes, s, pair, flags);
   }
   if (in_dtype == IB200_F32 && out_dtype == IB200_F32) return run_fma<float, float>(a, b, bias, c, m, n, k, transpose_b, act, s);
   if (in_dtype == IB200_BF16 && out_dtype == IB200_BF16) return run_fma<__nv_bfloat16, __nv_bfloat16>(a, b, bias, c, m, n, k, transpose_b, act, s);

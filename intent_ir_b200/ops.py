@@ -202,12 +202,12 @@ _gemm_scratch: Dict[int, torch.Tensor] = {}
 
 def gemm_bias_act(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
                   transpose_b: bool = False, out_dtype: Optional[torch.dtype] = None, allow_tf32: bool = False,
-                  split_tail: bool = True, cta_pairs: Optional[bool] = None) -> torch.Tensor:
+                  split_tail: bool = True, cta_pairs: Optional[bool] = None, narrow_tail: bool = False) -> torch.Tensor:
     """act(a @ b + bias) with fp32 accumulation; ``b`` is [K,N], or [N,K] with transpose_b.  bf16 / f16 operands
     (and f32 operands with ``allow_tf32``) whose K and N are multiples of 8 run on the tensor cores.  ``split_tail``
     gives the kernel scratch memory (kept per device, grown on demand) so that a last, mostly empty round of tiles
     is split along K.  ``cta_pairs``: True / False force the two-CTA (cta_group::2) or the one-CTA kernel; None lets the
-    library choose (pairs for large products)."""
+    library choose (pairs for large products).  ``narrow_tail`` runs the pair kernel's last-round tiles as two half-width units each when they fill at most half of the pairs."""
     _dev(a, "a"), _dev(b, "b")
     if a.dim() != 2 or b.dim() != 2 or a.dtype != b.dtype:
         raise B200LoweringError("gemm: a and b must be rank-2 tensors of one dtype")
@@ -223,6 +223,7 @@ def gemm_bias_act(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor]
             raise B200LoweringError("gemm: bias must have the output dtype and N elements")
     lib = _lib.load()
     flags = (_lib.GEMM_ALLOW_TF32 if allow_tf32 else 0) | (_lib.GEMM_CTA_PAIRS if cta_pairs else _lib.GEMM_ONE_CTA if cta_pairs is False else 0)
+    flags |= _lib.GEMM_NARROW_TAIL if narrow_tail else 0
     need = lib.ib200_gemm_scratch_bytes(code_of(a), code_of(c), m, n, k, int(transpose_b), flags) if split_tail else 0
     scratch = None
     if need:

@@ -515,7 +515,8 @@ def test_gemm_tail_tiles_split_along_k(dtype, m, n, k, transpose_b):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("m,n,k,transpose_b", [(256, 256, 64, False), (256, 256, 512, True), (512, 768, 1024, False), (300, 264, 72, False),
-                                                (130, 520, 1000, True), (1, 8, 8, False), (2048, 2048, 2048, False), (4096, 1024, 512, True)])
+                                                (130, 520, 1000, True), (1, 8, 8, False), (2048, 2048, 2048, False), (4096, 1024, 512, True),
+                                                (2560, 2048, 256, False), (2500, 2056, 136, True)])  # (the last two leave a short last round)
 def test_gemm_on_cta_pairs(dtype, m, n, k, transpose_b):
     """tcgen05 cta_group::2: two CTAs share a 256 x 256 tile, each staging half of the operands."""
     from intent_ir_b200 import ops
@@ -535,3 +536,7 @@ def test_gemm_on_cta_pairs(dtype, m, n, k, transpose_b):
         # products of bf16-representable values are exact in every operand kind and both kernels accumulate in fp32 in
         # K order: the pair kernel gives the one-CTA kernel's bits
         assert torch.equal(got, lone)
+    # the last round's tiles as half-width units (taken when they fill at most half of the pairs): the same bits again
+    narrow = ops.gemm_bias_act(ad, bd, biasd, "relu", transpose_b, allow_tf32=tf32, cta_pairs=True, narrow_tail=True)
+    ops.check_device_status()
+    assert torch.equal(got, narrow)
