@@ -122,9 +122,10 @@ int ib200_check_status(const int32_t* status, void* stream) {
   if (host != 0) {
     static const char* where[] = {"", "producer waiting for a free ring stage", "MMA issuer waiting for a drained accumulator",
                                   "MMA issuer waiting for a TMA stage", "epilogue waiting for a finished accumulator",
-                                  "normalisation waiting for a staged row segment"};
+                                  "normalisation waiting for a staged row segment", "normalisation waiting for its cluster's statistics",
+                                  "long-row kernel waiting for the other segments of its row"};
     return fail(IB200_ERR_DEVICE_WAIT, std::string("bounded device wait expired (") +
-                                           (host > 0 && host < 6 ? where[host] : "unknown site") + ")");
+                                           (host > 0 && host < 8 ? where[host] : "unknown site") + ")");
   }
   return IB200_OK;
 }

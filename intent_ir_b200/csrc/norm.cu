@@ -236,6 +236,49 @@ __global__ void __launch_bounds__(128) norm_warp(const T* __restrict__ x, const 
   }
 }
 
+// Mean and sum of squared deviations of a row whose every thread holds exactly NV*4 values, with ONE block barrier:
+// each thread takes the moments of its own values about their own mean (exact two-pass on 4*NV numbers), and equal-sized
+// sets merge without a division -- mean = (ma + mb) / 2, M2 = M2a + M2b + (mb - ma)^2 * n / 2 (Chan, Golub, LeVeque for
+// na = nb = n) -- through a shuffle butterfly inside the warp and another over the warps' results.  Same arithmetic class
+// as the centred two-pass form (no sum of raw squares anywhere), one barrier and ten shuffles fewer per row.
+template <int NV, int THREADS>
+__device__ __forceinline__ void block_moments_full(const float (&v)[NV][4], float (*slots)[2], float& mean, float& m2) {
+  constexpr float kOwn = (float)(NV * 4);
+  float mu = local_sum<NV>(v) * (1.0f / kOwn), q = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float d = v[i][k] - mu;
+      q = fmaf(d, d, q);
+    }
+  float half = kOwn * 0.5f;  // n / 2 of the sets being merged
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float mo = __shfl_xor_sync(0xffffffffu, mu, o), qo = __shfl_xor_sync(0xffffffffu, q, o);
+    const float d = mo - mu;
+    q = (q + qo) + d * d * half;
+    mu = 0.5f * (mu + mo);
+    half *= 2.0f;
+  }
+  constexpr int kWarps = THREADS / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { slots[warp][0] = mu; slots[warp][1] = q; }
+  __syncthreads();
+  mu = slots[lane & (kWarps - 1)][0];
+  q = slots[lane & (kWarps - 1)][1];
+#pragma unroll
+  for (int o = 1; o < kWarps; o <<= 1) {  // lanes 0 .. kWarps-1 hold the warps' results; the other lanes mirror them
+    const float mo = __shfl_xor_sync(0xffffffffu, mu, o), qo = __shfl_xor_sync(0xffffffffu, q, o);
+    const float d = mo - mu;
+    q = (q + qo) + d * d * half;
+    mu = 0.5f * (mu + mo);
+    half *= 2.0f;
+  }
+  mean = mu;
+  m2 = q;
+}
+
 // 256-thread CTAs are held to 51 registers so that five are resident per SM (measured on f32 [8192,4096]:
 // layernorm 0.80 -> 0.86 of HBM peak, rms-norm 0.86 -> 0.90; six CTAs spill and gain nothing); with 8 values
 // per thread (rows of 1025..2048 elements) all eight fit: [32768,2048] 0.78 -> 0.90
@@ -245,15 +288,28 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? (NV <= 2 ? 8 : 5) : 
                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                       int64_t rows, int cols, float eps, AffineMap map) {
   __shared__ float slots[2][32];
+  __shared__ float mslots[2][THREADS / 32][2];
   int parity = 0;
+  const bool full = map.centre && cols == NV * 4 * THREADS;  // every thread holds NV*4 values of the row
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, parity ^= 1) {
     float v[NV][4];
     load_row<T, NV, VEC>(x + r * cols, cols, threadIdx.x, THREADS, 0.0f, v);
     if (RES) add_residual<T, TW, NV, VEC>(v, static_cast<const T*>(map.res) + r * cols, static_cast<const TW*>(map.rbias), cols, threadIdx.x, THREADS);
-    // two reductions per centred row alternate between the two slot arrays; the single reduction of an
-    // uncentred (rms) row alternates by row parity, so that a fast warp never overwrites partials a slow one still reads
-    const float mean = map.centre ? block_reduce<SumOp>(local_sum<NV>(v), slots[0]) / (float)cols : 0.0f;
-    const float var = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, threadIdx.x, THREADS), slots[map.centre ? 1 : parity]) / (float)cols;
+    float mean, var;
+    if (full) {  // one barrier per row (slots alternate by row parity)
+      float m2;
+      block_moments_full<NV, THREADS>(v, mslots[parity], mean, m2);
+      var = m2 / (float)cols;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[i][k] -= mean;
+    } else {
+      // two reductions per centred row alternate between the two slot arrays; the single reduction of an
+      // uncentred (rms) row alternates by row parity, so that a fast warp never overwrites partials a slow one still reads
+      mean = map.centre ? block_reduce<SumOp>(local_sum<NV>(v), slots[0]) / (float)cols : 0.0f;
+      var = block_reduce<SumOp>(centre_and_square<NV, VEC>(v, mean, cols, threadIdx.x, THREADS), slots[map.centre ? 1 : parity]) / (float)cols;
+    }
     const float rstd = 1.0f / sqrtf(var + eps);
     uint32_t lq = 0, lr = 0;
     if (AFF == AFF_GENERIC) row_origin(r, cols, map, lq, lr);
