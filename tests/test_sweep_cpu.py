@@ -205,3 +205,21 @@ def test_lpt_partition_is_deterministic_and_balanced():
         assert max(per_rank) / min(per_rank) < 1.25, (kind, per_rank)
     loads = [sum(estimate_cost(cases[i]) for i in p) for p in deal]
     assert max(loads) / min(loads) < 1.05
+
+
+def test_host_allocator_settings_reach_this_process_and_its_children():
+    """No huge-page advice for numpy's large blocks and glibc's thresholds, set for the calling process and
+    inherited through the environment by the checker processes started afterwards."""
+    import subprocess
+    import sys
+
+    from intent_ir_b200.sweep import host_allocator_settings
+
+    host_allocator_settings()
+    assert os.environ["NUMPY_MADVISE_HUGEPAGE"] == "0" and int(os.environ["MALLOC_MMAP_THRESHOLD_"]) == 32 << 20
+    from numpy._core.multiarray import _set_madvise_hugepage
+
+    assert _set_madvise_hugepage(False) is False  # (returns the previous setting: already off in this process)
+    child = subprocess.run([sys.executable, "-c", "import numpy._core.multiarray as m; print(m._set_madvise_hugepage(False))"],
+                           capture_output=True, text=True, check=True)
+    assert child.stdout.strip() == "False"
