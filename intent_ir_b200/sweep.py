@@ -608,6 +608,12 @@ class _Served:
 
         shm = self.blocks.get(name)
         if shm is None:
+            for stale in [n for n, o in self.owner.items() if owner is not None and o is owner]:  # that process grew its arena: the old block is gone
+                try:
+                    self.blocks.pop(stale).close()
+                except Exception:
+                    pass
+                del self.owner[stale]
             shm = shared_memory.SharedMemory(name=name)
             self.blocks[name] = shm
             self.owner[name] = owner
