@@ -545,11 +545,16 @@ def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto
         return None
     summary = merge_records(gathered)
     gpu_s = sum((r.get("t_gpu") or 0.0) for part in gathered for r in part)
+    host_s = sum((r.get("t_total") or 0.0) for part in gathered for r in part)  # checker-process time, device wait included
+    n_rec = max(1, sum(len(part) for part in gathered))
     cps = summary["ok"] / dt
     block = {"cases_per_s": round(cps, 2), "cases": summary["cases"], "ok": summary["ok"], "wall_s": round(dt, 2), "rank_wall_s": rank_s,
              "scaling": "strong", "partition": "longest estimated case first, family by family", "max_elements": max_elements, "base_seed": 1000,
              "threads_per_rank": budget, "checker_processes_per_rank": workers, "host_cores": len(cores), "blas_threads": 1,
-             "checker": label, "gpu_busy_fraction": round(gpu_s / (dt * world), 4), "failed": summary["failed"][:3],
+             "checker": label, "gpu_busy_fraction": round(gpu_s / (dt * world), 4),
+             # where the time goes: the checker processes' share of the wall clock, and a case's cost on the host and on the GPU
+             "checker_busy_fraction": round(host_s / (dt * world * workers), 3), "host_ms_per_case": round(1e3 * host_s / n_rec, 1),
+             "gpu_ms_per_case": round(1e3 * gpu_s / n_rec, 2), "failed": summary["failed"][:3],
              "by_kind": {k: f"{v['ok']}/{v['cases']}" for k, v in summary["by_kind"].items()}}
     # the one-rank figure of the same case list on the same host, when an N = 1 run left it behind
     note = os.path.join(tempfile.gettempdir(), f"ib200_sweep_n1_{total}_{max_elements}_{budget}.json")
