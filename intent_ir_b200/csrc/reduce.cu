@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(256) reduce_rows_split(const T* __restrict__ x
   if (threadIdx.x == 0) write_result<TO>(out, row, acc, scale, KIND);
 }
 
-constexpr int kColsVecCtasPerSm = 6;  // 40 registers; a split launch is sized to exactly one wave of these
+constexpr int kColsVecCtasPerSm = 4;  // 60 registers (eight rows in flight per thread); a split launch is sized to exactly one wave of these
 
 // How a reduction over a leading / middle axis is laid over the GPU (inner % 4 == 0).
 struct ColPlan {
@@ -209,6 +209,15 @@ __global__ void __launch_bounds__(256, kColsVecCtasPerSm) reduce_cols_vec(const 
     if (c < inner) {
       const T* p = x + o * n * inner + c;
       int64_t r = lo + ty;
+      for (; r + 7 * G < hi; r += 8 * G) {  // eight rows in flight per thread
+        float a[8][4];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) load4<T>(p + (r + u * G) * inner, a[u]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[u & 3][k] = Op::apply(acc[u & 3][k], prep<KIND>(a[u][k]));
+      }
       for (; r + 3 * G < hi; r += 4 * G) {  // four rows in flight per thread
         float a[4][4];
 #pragma unroll
