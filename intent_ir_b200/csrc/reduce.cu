@@ -48,7 +48,15 @@ __device__ __forceinline__ float row_partial(const T* __restrict__ p, int64_t n,
   if (VEC) {
     const int64_t nvec = n >> 2;
     int64_t i = tid;
-    // two 128-bit loads in flight per thread per iteration
+    // four 128-bit loads in flight per thread per iteration while the row lasts, then two, then one
+    for (; i + 3 * (int64_t)nthreads < nvec; i += 4 * (int64_t)nthreads) {
+      float a[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) load4<T>(p + 4 * (i + u * (int64_t)nthreads), a[u]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        acc[k] = Op::apply(Op::apply(Op::apply(acc[k], prep<KIND>(a[0][k])), prep<KIND>(a[1][k])), Op::apply(prep<KIND>(a[2][k]), prep<KIND>(a[3][k])));
+    }
     for (; i + nthreads < nvec; i += 2 * (int64_t)nthreads) {
       float a[4], b[4];
       load4<T>(p + 4 * i, a);
