@@ -67,7 +67,7 @@ PROFILE_OF = {"softmax": "softmax_block_f32_4096x4096.md", "layernorm": "norm_bl
               "rmsnorm": "norm_block_rmsnorm_f32_8192x4096.md", "rmsnorm_relu": "norm_block_rmsnorm_relu_f32_8192x4096.md",
               "rowprog": "row_kernel_static_rms_abs_f32_8192x4096.md", "rope": "rope_kernel_f32_8192x2x16x128.md",
               "masked_softmax": "softmax_block_masked_f32_4096x4096.md", "reduce_sum_all": "reduce_rows_split_sum_f32_8192x8192.md",
-              "column_sum": "reduce_cols_vec_sum_f32_65536x1024.md", "softmax_long": "softmax_resident_f32_4x1Mi.md",
+              "column_sum": "reduce_cols_vec_sum_f32_65536x1024.md", "reduce_any_large": "reduce_rows_block_any_f32_16384x4096.md", "softmax_long": "softmax_resident_f32_4x1Mi.md",
               "layernorm_long": "norm_resident_f32_4x1Mi.md"}
 
 
