@@ -19,6 +19,11 @@
 #include "common.cuh"
 #include "rowio.cuh"
 
+#ifndef SM_LD
+#define SM_LD false
+#define SM_ST false
+#endif
+
 namespace ib200 {
 namespace {
 
@@ -107,13 +112,13 @@ __global__ void __launch_bounds__(128) softmax_warp(const T* __restrict__ x, TO*
     const bool live = r0 + which < rows;
     const int64_t r = live ? r0 + which : rows - 1;  // lanes past the last row recompute it and store nothing
     float v[NV][4];
-    load_row<T, NV, VEC>(x + r * cols, cols, lane, LANES, -INFINITY, v);
+    load_row<T, NV, VEC, SM_LD>(x + r * cols, cols, lane, LANES, -INFINITY, v);
     if (MASKED) apply_mask<NV, VEC>(v, mk.mask + r * mk.row_stride, mk.vec != 0, mk.fill, cols, lane, LANES);
     const float m = lanes_reduce<MaxOp, LANES>(local_max<NV>(v));
     const float s = lanes_reduce<SumOp, LANES>(exp_and_sum<NV>(v, m));
     scale<NV>(v, s);
     if (live) {
-      store_row<TO, NV, VEC>(y + r * cols, cols, lane, LANES, v);
+      store_row<TO, NV, VEC, SM_ST>(y + r * cols, cols, lane, LANES, v);
       if (lane == 0) {
         if (row_max) row_max[r] = m;
         if (row_sum) row_sum[r] = s;
@@ -129,12 +134,12 @@ __global__ void __launch_bounds__(THREADS, (MASKED && THREADS == 256) ? 6 : 1) s
   __shared__ float slots[2][32];
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     float v[NV][4];
-    load_row<T, NV, VEC>(x + r * cols, cols, threadIdx.x, THREADS, -INFINITY, v);
+    load_row<T, NV, VEC, SM_LD>(x + r * cols, cols, threadIdx.x, THREADS, -INFINITY, v);
     if (MASKED) apply_mask<NV, VEC>(v, mk.mask + r * mk.row_stride, mk.vec != 0, mk.fill, cols, threadIdx.x, THREADS);
     const float m = block_reduce<MaxOp>(local_max<NV>(v), slots[0]);
     const float s = block_reduce<SumOp>(exp_and_sum<NV>(v, m), slots[1]);
     scale<NV>(v, s);
-    store_row<TO, NV, VEC>(y + r * cols, cols, threadIdx.x, THREADS, v);
+    store_row<TO, NV, VEC, SM_ST>(y + r * cols, cols, threadIdx.x, THREADS, v);
     if (threadIdx.x == 0) {
       if (row_max) row_max[r] = m;
       if (row_sum) row_sum[r] = s;
