@@ -55,7 +55,7 @@ __device__ __forceinline__ void store_scalar(void* p, int dtype, int64_t off, fl
 
 __device__ __forceinline__ void store_vec4(void* p, int dtype, int64_t off, const float (&v)[4]) {
   switch (dtype) {
-    case IB200_F32: store4<float>(static_cast<float*>(p) + off, v); break;
+    case IB200_F32: __stcs(reinterpret_cast<float4*>(static_cast<float*>(p) + off), make_float4(v[0], v[1], v[2], v[3])); break;  // written once: evict first
     case IB200_BF16: store4<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p) + off, v); break;
     case IB200_F16: store4<__half>(static_cast<__half*>(p) + off, v); break;
     case IB200_BOOL: case IB200_U8: store4<uint8_t>(static_cast<uint8_t*>(p) + off, v); break;
