@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const float* __restrict__ x, 
     float* yr = y + row * 2 * half;
     float lo[V], hi[V], c[V], s[V];
     if (V == 4) {
-      const float4 a = *reinterpret_cast<const float4*>(xr + j), b = *reinterpret_cast<const float4*>(xr + half + j);
+      const float4 a = __ldcs(reinterpret_cast<const float4*>(xr + j)), b = __ldcs(reinterpret_cast<const float4*>(xr + half + j));  // read once: streaming
       const float4 cc = *reinterpret_cast<const float4*>(cs + pos * half + j), ss = *reinterpret_cast<const float4*>(sn + pos * half + j);
       lo[0] = a.x; lo[V > 1 ? 1 : 0] = a.y; lo[V > 2 ? 2 : 0] = a.z; lo[V > 3 ? 3 : 0] = a.w;
       hi[0] = b.x; hi[V > 1 ? 1 : 0] = b.y; hi[V > 2 ? 2 : 0] = b.z; hi[V > 3 ? 3 : 0] = b.w;
@@ -39,8 +39,8 @@ __global__ void __launch_bounds__(256) rope_kernel(const float* __restrict__ x, 
       o2[k] = __fadd_rn(__fmul_rn(lo[k], s[k]), __fmul_rn(hi[k], c[k]));
     }
     if (V == 4) {
-      *reinterpret_cast<float4*>(yr + j) = make_float4(o1[0], o1[V > 1 ? 1 : 0], o1[V > 2 ? 2 : 0], o1[V > 3 ? 3 : 0]);
-      *reinterpret_cast<float4*>(yr + half + j) = make_float4(o2[0], o2[V > 1 ? 1 : 0], o2[V > 2 ? 2 : 0], o2[V > 3 ? 3 : 0]);
+      __stcs(reinterpret_cast<float4*>(yr + j), make_float4(o1[0], o1[V > 1 ? 1 : 0], o1[V > 2 ? 2 : 0], o1[V > 3 ? 3 : 0]));
+      __stcs(reinterpret_cast<float4*>(yr + half + j), make_float4(o2[0], o2[V > 1 ? 1 : 0], o2[V > 2 ? 2 : 0], o2[V > 3 ? 3 : 0]));
     } else {
       yr[j] = o1[0];
       yr[half + j] = o2[0];
