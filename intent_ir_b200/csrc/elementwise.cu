@@ -420,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, EXT ? 5 : 8) ew_kernel_reg(const __g
 }
 
 template <typename P>
-__global__ void __launch_bounds__(kThreads, P::ext ? 4 : 8) ew_kernel_static(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
+__global__ void __launch_bounds__(kThreads, P::ext ? 6 : 8) ew_kernel_static(const __grid_constant__ EwProgram prog, const __grid_constant__ EwDivs divs,
                                                                   const __grid_constant__ EwRegCode code) {
   ew_reg_body<P::nin, P::bmask, P::rank, P::ext>(prog, divs, code, StaticExec<P>{});
 }
