@@ -247,7 +247,8 @@ IB200_API int ib200_gemm_bias_act(const void* a, const void* b, const void* bias
  * opt-in wmma kernel does (kernels/wmma_matmul.cuh:124-563); products then carry 10-bit
  * mantissas, inside the verifier's matmul tolerance for inputs of moderate dynamic range.
  * Large products (M >= 256, tiles for at least half the SM pairs) run on pairs of CTAs sharing
- * 256 x 256 tiles (tcgen05 cta_group::2); IB200_GEMM_CTA_PAIRS / IB200_GEMM_ONE_CTA force either form.
+ * 256 x 256 tiles (tcgen05 cta_group::2); IB200_GEMM_CTA_PAIRS / IB200_GEMM_ONE_CTA force either form, and
+ * IB200_GEMM_NARROW_TAIL lets the pair kernel run the tiles of a short last round as 256 x 128 units.
  * `scratch` (256-byte aligned, ib200_gemm_scratch_bytes(...) bytes, contents irrelevant) lets the
  * one-CTA kernel cut the tiles of a last, mostly empty round of tiles along K and add the
  * slices up in a fixed order; with scratch == NULL every tile runs whole, as in
