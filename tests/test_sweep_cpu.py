@@ -223,3 +223,32 @@ def test_host_allocator_settings_reach_this_process_and_its_children():
     child = subprocess.run([sys.executable, "-c", "import numpy._core.multiarray as m; print(m._set_madvise_hugepage(False))"],
                            capture_output=True, text=True, check=True)
     assert child.stdout.strip() == "False"
+
+
+def test_large_cases_are_checked_block_by_block():
+    """A case of more than half a million elements runs whole on the device and is verified in blocks of rows;
+    a wrong value in one block fails the case and the record names the rows."""
+    from intent_ir_b200.sweep import _row_blocks
+
+    big = [c for c in generate_sweep_cases(400, base_seed=1000, max_elements=1 << 20) if c.kind in ("layernorm", "softmax", "chain", "groupnorm")
+           and c.elements >= 1 << 19][:4]
+    assert big and all(len(_row_blocks(c)) > 1 for c in big)
+    assert not _row_blocks([c for c in generate_sweep_cases(64, base_seed=1000, max_elements=1 << 12)][0])
+    recs = run_sweep(big, make_runner=numpy_runner, **CHECKER)
+    assert all(r["ok"] for r in recs), [(r["kind"], r["summary"]) for r in recs if not r["ok"]]
+
+    def one_bad_row(intent, input_gen):
+        inner = numpy_runner(intent, input_gen)
+
+        def run(case):
+            io = inner(case)
+            k = intent.outputs[0]
+            out = np.array(io[k], copy=True)
+            out[out.shape[0] - 1] += np.float32(0.5)  # the last row (the last batch entry for groupnorm)
+            io[k] = out
+            return io
+
+        return run
+
+    recs = run_sweep(big, make_runner=one_bad_row, **CHECKER)
+    assert not any(r["ok"] for r in recs) and all("rows" in r["summary"] for r in recs), [r["summary"] for r in recs]
