@@ -317,59 +317,103 @@ def _u16(rng, n: int) -> np.ndarray:
     return rng.bit_generator.random_raw((n + 3) // 4).view(np.uint16)[:n]
 
 
-def _normal(rng, shape) -> np.ndarray:
-    """Standard-normal float32 values of the given shape.  Large tensors draw their elements, independently and
-    uniformly, from 65536 normal variates generated for this tensor: the inputs of a sweep case cost the host
-    as much as interpreting the graph when every element goes through the ziggurat (52 ms against 18 ms for
-    4 Mi elements), and a check of a kernel is indifferent to the difference."""
+_CHUNK = 1 << 16  # elements generated at a time: the index and the gathered values stay in the core's cache
+
+
+def _round_bf16_in_place(a: np.ndarray) -> None:
+    """backend.round_to_bf16 on finite float32 values, without a second array."""
+    bits = a.view(np.uint32)
+    bits += np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1))
+    bits &= np.uint32(0xFFFF0000)
+
+
+def _normal(rng, shape, scale=None, bf16: bool = False, out: Optional[np.ndarray] = None) -> np.ndarray:
+    """Standard-normal float32 values of the given shape, times ``scale``, rounded to bf16 on request, written
+    into ``out`` (a C-contiguous float32 array of that shape) when one is given.  Large tensors draw their
+    elements, independently and uniformly, from 65536 normal variates generated for this tensor: the inputs of
+    a sweep case cost the host as much as interpreting the graph when every element goes through the ziggurat
+    (52 ms against 18 ms for 4 Mi elements), and a check of a kernel is indifferent to the difference.  The
+    tensor is produced 64 Ki elements at a time (the same random stream as in one piece), scaled and rounded
+    while the piece is in cache."""
     shape = (shape,) if np.isscalar(shape) else tuple(shape)
     n = int(np.prod(shape, dtype=np.int64))
+    if out is None or out.shape != shape or out.dtype != np.float32 or not out.flags.c_contiguous:
+        out = np.empty(shape, np.float32)
+    flat = out.reshape(-1)
+
+    def finish(piece):
+        if scale is not None:
+            piece *= np.float32(scale)
+        if bf16:
+            _round_bf16_in_place(piece)
+
     if n <= 4 * _POOL:
-        return rng.standard_normal(shape, dtype=np.float32)
-    return rng.standard_normal(_POOL, dtype=np.float32).take(_u16(rng, n)).reshape(shape)
+        if n:
+            rng.standard_normal(out=flat, dtype=np.float32)
+            finish(flat)
+        return out
+    pool = rng.standard_normal(_POOL, dtype=np.float32)
+    for a in range(0, n, _CHUNK):
+        b = min(n, a + _CHUNK)
+        np.take(pool, _u16(rng, b - a), out=flat[a:b])
+        finish(flat[a:b])
+    return out
 
 
-def case_inputs(case: SweepCase) -> Dict[str, np.ndarray]:
+def case_inputs(case: SweepCase, dest: Optional[Callable[[str, tuple], Optional[np.ndarray]]] = None) -> Dict[str, np.ndarray]:
     """Seeded inputs with the value distributions of the benchmark configurations; bf16 tensors
-    are float32 arrays holding bf16-representable values."""
+    are float32 arrays holding bf16-representable values.  ``dest(name, shape)`` may hand out the float32
+    array a large tensor is to be generated into (the checker processes' shared-memory arena)."""
     rng = np.random.default_rng(case.seed)
     s = case.shapes
-    q = round_to_bf16 if case.dtype == "bf16" else (lambda a: a)
+    b16 = case.dtype == "bf16"
+    q = round_to_bf16 if b16 else (lambda a: a)
     k = case.kind
+
+    def normal(name, shape, scale=None, rounded=b16):
+        shape = (shape,) if np.isscalar(shape) else tuple(shape)
+        return _normal(rng, shape, scale, rounded, dest(name, shape) if dest else None)
+
     if k in ("reduce_any",):
         m, n = s["M"], s["N"]
-        x = _normal(rng, (m, n))
-        x[_u16(rng, m * n).reshape(m, n) >= 3277] = 0  # about one element in twenty is non-zero
-        return {"inp": q(x)}
+        x = normal("inp", (m, n), rounded=False)
+        flat = x.reshape(-1)
+        for a in range(0, m * n, _CHUNK):  # about one element in twenty is non-zero
+            piece = flat[a:a + _CHUNK]
+            piece[_u16(rng, piece.size) >= 3277] = 0
+        if b16:
+            _round_bf16_in_place(flat)
+        return {"inp": x}
     if k in ("reduce_sum", "reduce_max"):
-        return {"inp": q(_normal(rng, (s["M"], s["N"])))}
+        return {"inp": normal("inp", (s["M"], s["N"]))}
     if k == "softmax":
-        return {"inp": q(3 * _normal(rng, (s["M"], s["N"])))}
+        return {"inp": normal("inp", (s["M"], s["N"]), 3)}
     if k == "chain":
-        return {"x": q(_normal(rng, (s["M"], s["N"]))), "col": q(_normal(rng, s["N"])), "row": q(_normal(rng, (s["M"], 1)))}
+        return {"x": normal("x", (s["M"], s["N"])), "col": normal("col", s["N"]), "row": normal("row", (s["M"], 1))}
     if k == "layernorm":
-        return {"x": _normal(rng, (s["M"], s["N"])), "w": rng.uniform(0.5, 1.5, s["N"]).astype(np.float32),
+        return {"x": normal("x", (s["M"], s["N"]), rounded=False), "w": rng.uniform(0.5, 1.5, s["N"]).astype(np.float32),
                 "b": (0.1 * rng.standard_normal(s["N"])).astype(np.float32)}
     if k == "groupnorm":
-        return {"X": _normal(rng, (s["N"], s["C"], s["HW"])), "W": _normal(rng, s["C"]), "B": _normal(rng, s["C"])}
+        return {"X": normal("X", (s["N"], s["C"], s["HW"]), rounded=False), "W": normal("W", s["C"], rounded=False),
+                "B": normal("B", s["C"], rounded=False)}
     if k == "matmul_bias_relu":
         sc = np.float32(1.0 / np.sqrt(max(s["K"], 1)))
-        return {"A": q(_normal(rng, (s["M"], s["K"]))), "B": q(sc * _normal(rng, (s["K"], s["N"]))), "bias": q(0.1 * _normal(rng, s["N"]))}
+        return {"A": normal("A", (s["M"], s["K"])), "B": normal("B", (s["K"], s["N"]), sc), "bias": normal("bias", s["N"], 0.1)}
     if k == "rmsnorm":
-        return {"x": _normal(rng, (s["M"], s["N"])), "w": rng.uniform(0.5, 1.5, s["N"]).astype(np.float32)}
+        return {"x": normal("x", (s["M"], s["N"]), rounded=False), "w": rng.uniform(0.5, 1.5, s["N"]).astype(np.float32)}
     if k == "layernorm_residual":
-        return {"x0": _normal(rng, (s["M"], s["N"])), "r": _normal(rng, (s["M"], s["N"])),
+        return {"x0": normal("x0", (s["M"], s["N"]), rounded=False), "r": normal("r", (s["M"], s["N"]), rounded=False),
                 "w": rng.uniform(0.5, 1.5, s["N"]).astype(np.float32), "b": (0.1 * rng.standard_normal(s["N"])).astype(np.float32)}
     if k == "masked_softmax":
         mask = rng.random(s["N"]) > 0.2
         mask[int(rng.integers(0, s["N"]))] = True  # at least one column survives
-        return {"x": 3 * _normal(rng, (s["M"], s["N"])), "mask": mask}
+        return {"x": normal("x", (s["M"], s["N"]), 3, rounded=False), "mask": mask}
     if k == "rope":
         ang = rng.uniform(-np.pi, np.pi, (s["S"], s["D2"]))
-        return {"x": _normal(rng, (s["S"], s["B"], s["H"], s["D"])), "cos": np.cos(ang).astype(np.float32),
+        return {"x": normal("x", (s["S"], s["B"], s["H"], s["D"]), rounded=False), "cos": np.cos(ang).astype(np.float32),
                 "sin": np.sin(ang).astype(np.float32)}
     if k == "dropout":
-        return {"x": _normal(rng, (s["M"], s["N"])), "p": np.array(rng.choice((0.1, 0.25, 0.5)), np.float32),
+        return {"x": normal("x", (s["M"], s["N"]), rounded=False), "p": np.array(rng.choice((0.1, 0.25, 0.5)), np.float32),
                 "seed": np.array(int(rng.integers(-2 ** 40, 2 ** 40)), np.int64)}
     if k == "image":
         i8 = lambda shape: rng.integers(-128, 128, size=shape).astype(np.int8)  # noqa: E731
@@ -567,12 +611,43 @@ class _Arena:
 
     def close(self):
         if self.shm is not None:
-            try:
-                self.shm.close()
-                self.shm.unlink()
-            except Exception:
-                pass
+            for step in (self.shm.close, self.shm.unlink):  # (close refuses while views are alive; the name is removed all the same)
+                try:
+                    step()
+                except Exception:
+                    pass
             self.shm = None
+
+
+def _exchange(conn, shm, case: SweepCase, c, layout_in, layout_out, inputs, timing):
+    """Ask the parent to run the case on the arena's arrays; returns inputs and outputs as the verifier wants them."""
+    conn.send(("run", case.case_id, case.intent, dict(c.shapes), shm.name, layout_in, layout_out))
+    reply = conn.recv()
+    if reply[0] != "ok":
+        raise RuntimeError(reply[1])
+    if timing is not None:
+        timing["device"] = reply[2]
+    result = dict(inputs)
+    for name, dts, shape, o in layout_out:
+        sent = reply[1].get(name)
+        result[name] = sent if sent is not None else np.ndarray(shape, np.dtype(dts), buffer=shm.buf, offset=o)
+    return result
+
+
+def _run_copying(conn, arena: _Arena, intent, case: SweepCase, c, inputs, outs, timing):
+    """The plain form: inputs that live in private memory are copied into an arena sized for exactly this case."""
+    inputs = {k: np.array(v, copy=True) for k, v in inputs.items()}  # (some may be views of the arena that is about to be replaced)
+    layout_in, layout_out, off = [], [], 0
+    for k, v in inputs.items():
+        layout_in.append((k, v.dtype.str, tuple(v.shape), off))
+        off = _align(off + max(v.nbytes, 1))
+    for name, dt, shape in outs:
+        layout_out.append((name, dt.str, shape, off))
+        off = _align(off + max(int(np.prod(shape, dtype=np.int64)) * dt.itemsize, 1))
+    shm = arena.ensure(off)
+    for (k, _, shape, o), v in zip(layout_in, inputs.values()):
+        np.ndarray(shape, v.dtype, buffer=shm.buf, offset=o)[...] = v
+    return _exchange(conn, shm, case, c, layout_in, layout_out, inputs, timing)
 
 
 def _remote_runner(conn, arena: _Arena, intent, case: SweepCase, timing: Optional[Dict[str, float]] = None):
@@ -581,35 +656,53 @@ def _remote_runner(conn, arena: _Arena, intent, case: SweepCase, timing: Optiona
     from .bindings import derive_bindings
 
     def run(c):
-        inputs = case_inputs(case)
-        if getattr(c, "inputs", None):
-            inputs.update({k: np.asarray(v) for k, v in c.inputs.items()})
-        inputs = {k: np.ascontiguousarray(v) if np.ndim(v) else np.asarray(v) for k, v in inputs.items()}
         bind = derive_bindings(dict(c.shapes))
-        layout_in, layout_out, off = [], [], 0
-        for k, v in inputs.items():
-            layout_in.append((k, v.dtype.str, tuple(v.shape), off))
-            off = _align(off + max(v.nbytes, 1))
+        outs = []
+        out_bytes = 0
         for name in intent.outputs:
             t = intent.tensors[name]
             shape = tuple(int(bind[d.value]) if d.kind == "sym" else int(d.value) for d in t.shape)
             dt = np.dtype(_NP_OUT[t.dtype])
+            outs.append((name, dt, shape))
+            out_bytes += _align(max(int(np.prod(shape, dtype=np.int64)) * dt.itemsize, 1))
+        # Large inputs are generated straight into the arena (no copy afterwards), so the arena is sized first: room
+        # for four tensors of the case's largest size beside the outputs covers every graph family of the sweep; an
+        # input that does not fit any more is generated in private memory and copied, as small ones are.
+        shm = arena.ensure(4 * _align(4 * max(int(case.elements), 1)) + out_bytes + (1 << 20))
+        room = shm.size - out_bytes
+        layout_in, placed, off = [], {}, 0
+
+        def dest(name, shape):
+            nonlocal off
+            nbytes = 4 * int(np.prod(shape, dtype=np.int64))
+            if nbytes < (1 << 16) or off + _align(nbytes) > room or name in placed:
+                return None
+            view = np.ndarray(shape, np.float32, buffer=shm.buf, offset=off)
+            placed[name] = off
+            off = _align(off + nbytes)
+            return view
+
+        inputs = case_inputs(case, dest)
+        if getattr(c, "inputs", None):
+            inputs.update({k: np.asarray(v) for k, v in c.inputs.items()})
+        inputs = {k: np.ascontiguousarray(v) if np.ndim(v) else np.asarray(v) for k, v in inputs.items()}
+        for k, v in inputs.items():
+            at = placed.get(k)
+            if at is not None and v.dtype == np.float32 and v.ctypes.data == np.ndarray(v.shape, np.float32, buffer=shm.buf, offset=at).ctypes.data:
+                layout_in.append((k, v.dtype.str, tuple(v.shape), at))  # already in place
+                continue
+            if off + _align(max(v.nbytes, 1)) > room:  # (never seen: the bound above is generous) grow and start over without placement
+                return _run_copying(conn, arena, intent, case, c, inputs, outs, timing)
+            layout_in.append((k, v.dtype.str, tuple(v.shape), off))
+            np.ndarray(v.shape, v.dtype, buffer=shm.buf, offset=off)[...] = v
+            off = _align(off + max(v.nbytes, 1))
+        layout_out = []
+        off = room
+        for name, dt, shape in outs:
             layout_out.append((name, dt.str, shape, off))
             off = _align(off + max(int(np.prod(shape, dtype=np.int64)) * dt.itemsize, 1))
-        shm = arena.ensure(off)
-        for (k, _, shape, o), v in zip(layout_in, inputs.values()):
-            np.ndarray(shape, v.dtype, buffer=shm.buf, offset=o)[...] = v
-        conn.send(("run", case.case_id, case.intent, dict(c.shapes), shm.name, layout_in, layout_out))
-        reply = conn.recv()
-        if reply[0] != "ok":
-            raise RuntimeError(reply[1])
-        if timing is not None:
-            timing["device"] = reply[2]
-        result = dict(inputs)
-        for name, dts, shape, o in layout_out:
-            sent = reply[1].get(name)
-            result[name] = sent if sent is not None else np.ndarray(shape, np.dtype(dts), buffer=shm.buf, offset=o)
-        return result
+        inputs = {k: np.ndarray(shape, np.dtype(dts), buffer=shm.buf, offset=o) for k, dts, shape, o in layout_in}
+        return _exchange(conn, shm, case, c, layout_in, layout_out, inputs, timing)
 
     return run
 
