@@ -665,10 +665,16 @@ def _remote_runner(conn, arena: _Arena, intent, case: SweepCase, timing: Optiona
             dt = np.dtype(_NP_OUT[t.dtype])
             outs.append((name, dt, shape))
             out_bytes += _align(max(int(np.prod(shape, dtype=np.int64)) * dt.itemsize, 1))
-        # Large inputs are generated straight into the arena (no copy afterwards), so the arena is sized first: room
-        # for four tensors of the case's largest size beside the outputs covers every graph family of the sweep; an
-        # input that does not fit any more is generated in private memory and copied, as small ones are.
-        shm = arena.ensure(4 * _align(4 * max(int(case.elements), 1)) + out_bytes + (1 << 20))
+        # Large inputs are generated straight into the arena (no copy afterwards), so the arena is sized first: every
+        # declared tensor that is not an output counts as a possible input (intermediates that a graph declares only
+        # make the bound generous), plus room for the small ones; an input that does not fit after all is generated in
+        # private memory and copied, as small ones are.
+        in_bytes = 1 << 20
+        for name, t in intent.tensors.items():
+            if name not in intent.outputs:
+                numel = int(np.prod([int(bind[d.value]) if d.kind == "sym" else int(d.value) for d in t.shape] or [1], dtype=np.int64))
+                in_bytes += _align(np.dtype(_NP_OUT.get(t.dtype, np.float64)).itemsize * numel)
+        shm = arena.ensure(in_bytes + out_bytes)
         room = shm.size - out_bytes
         layout_in, placed, off = [], {}, 0
 
