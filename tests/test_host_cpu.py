@@ -376,3 +376,27 @@ def test_recurring_elementwise_chains_are_compiled_in(golden_graphs):
                   {"op": "min", "inputs": ["b", "c"], "output": "y"}], "outputs": ["y"]}
     (prog,) = programs(js, {"M": 64, "N": 128})
     assert prog["compiled_in"] == 0 and prog["register_code"]
+
+
+def test_recurring_row_programs_are_compiled_in(golden_graphs):
+    """The softmax between an attention's products (additive-mask and causal forms) and an rms-norm with |x| inside
+    fuse into row programs whose phases the row kernel also holds as compiled-in tables; the plan description
+    says so.  A row length that is no multiple of 4 runs decoded."""
+    for key in ("_attn_fwd", "flash_attention2d", "masked_attention2d"):
+        g = golden_graphs[key]
+        fused = [s for s in plan_json(g["intent"], g["shapes"])["steps"] if "row_program" in s]
+        assert len(fused) == 1 and fused[0]["row_program"]["compiled_in"] is True, key
+        odd = [s for s in plan_json(g["intent"], dict(g["shapes"], KV_CTX=18))["steps"] if "row_program" in s]
+        assert odd and odd[0]["row_program"]["compiled_in"] is False, key
+    t = lambda shape: {"dtype": "f32", "shape": shape, "layout": "row_major"}  # noqa: E731
+    rms = {"name": "rms_abs", "tensors": {"x": t(["M", "N"]), "w": t(["N"]), "y": t(["M", "N"]), "rstd": t(["M"])},
+           "ops": [{"op": "mul", "inputs": ["x", "x"], "output": "sq"},
+                   {"op": "reduce_sum", "inputs": ["sq"], "output": "ss", "attrs": {"dims": [1], "keepdims": True, "scale": "1.0/N"}},
+                   {"op": "add", "inputs": ["ss"], "output": "ve", "attrs": {"addend": 1e-5}},
+                   {"op": "rsqrt", "inputs": ["ve"], "output": "r1"},
+                   {"op": "reshape", "inputs": ["r1"], "output": "rstd", "attrs": {"shape": ["M"]}},
+                   {"op": "mul", "inputs": ["x", "r1"], "output": "xn"},
+                   {"op": "abs", "inputs": ["xn"], "output": "xr"},
+                   {"op": "mul", "inputs": ["xr", "w"], "output": "y"}], "outputs": ["y", "rstd"]}
+    steps = plan_json(rms, {"M": 64, "N": 4096})["steps"]
+    assert len(steps) == 1 and steps[0]["row_program"]["compiled_in"] is True
