@@ -355,7 +355,7 @@ def _normal(rng, shape, scale=None, bf16: bool = False, out: Optional[np.ndarray
     pool = rng.standard_normal(_POOL, dtype=np.float32)
     for a in range(0, n, _CHUNK):
         b = min(n, a + _CHUNK)
-        np.take(pool, _u16(rng, b - a), out=flat[a:b])
+        np.take(pool, _u16(rng, b - a), out=flat[a:b], mode="clip")  # (every index is in range; 'raise' would buffer the output)
         finish(flat[a:b])
     return out
 
