@@ -672,7 +672,10 @@ def _remote_runner(conn, arena: _Arena, intent, case: SweepCase, timing: Optiona
         in_bytes = 1 << 20
         for name, t in intent.tensors.items():
             if name not in intent.outputs:
-                numel = int(np.prod([int(bind[d.value]) if d.kind == "sym" else int(d.value) for d in t.shape] or [1], dtype=np.int64))
+                dims = [bind.get(d.value) if d.kind == "sym" else d.value for d in t.shape]
+                if any(v is None for v in dims):
+                    continue  # (a symbol only the planner derives: not an input)
+                numel = int(np.prod([int(v) for v in dims] or [1], dtype=np.int64))
                 in_bytes += _align(np.dtype(_NP_OUT.get(t.dtype, np.float64)).itemsize * numel)
         shm = arena.ensure(in_bytes + out_bytes)
         room = shm.size - out_bytes
