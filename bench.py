@@ -502,12 +502,15 @@ def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto
 
     cores = host_cores()
     budget = max(1, len(cores) // 8)
-    workers = max(1, budget - 1)
     mine = cores[local * budget:(local + 1) * budget] or cores
     try:
         os.sched_setaffinity(0, set(mine))
     except Exception:
         mine = []
+    # The rank's processes are pinned to its `budget` cores, so the cores bound what the rank can use whatever the
+    # number of processes: as many checker processes as cores, and the GPU-serving parent (busy about a seventh of
+    # the time) shares them.  Without pinning the parent counts as one of the budget.
+    workers = budget if mine else max(1, budget - 1)
     diff_fn, tol_fn, case_type, from_json, label = sweep_checker(checker)
     chk = dict(diff_fn=diff_fn, tolerances_fn=tol_fn, case_type=case_type, intent_from_json=from_json)
     pool = CheckerPool(workers, (diff_fn, tol_fn, case_type), from_json, rank, mine)
@@ -550,7 +553,7 @@ def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto
     cps = summary["ok"] / dt
     block = {"cases_per_s": round(cps, 2), "cases": summary["cases"], "ok": summary["ok"], "wall_s": round(dt, 2), "rank_wall_s": rank_s,
              "scaling": "strong", "partition": "longest estimated case first, family by family", "max_elements": max_elements, "base_seed": 1000,
-             "threads_per_rank": budget, "checker_processes_per_rank": workers, "host_cores": len(cores), "blas_threads": 1,
+             "threads_per_rank": budget, "pinned_to_cores": bool(mine), "checker_processes_per_rank": workers, "host_cores": len(cores), "blas_threads": 1,
              "checker": label, "gpu_busy_fraction": round(gpu_s / (dt * world), 4),
              # where the time goes: the checker processes' share of the wall clock, and a case's cost on the host and on the GPU
              "checker_busy_fraction": round(host_s / (dt * world * workers), 3), "host_ms_per_case": round(1e3 * host_s / n_rec, 1),
