@@ -493,16 +493,16 @@ def sweep_checker(which):
 
 def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto", groupnorm_every=0, max_elements=SWEEP_MAX_ELEMENTS):
     """The verification sweep on `total` seeded cases (base seed 1000), dealt to the ranks family by family in order of
-    estimated cost; each rank keeps its GPU in this process and checks in `threads_per_rank - 1`
-    child processes pinned to the rank's own cores.  Wall-clock, max over ranks.  Returns the block on
+    estimated cost; each rank keeps its GPU in this process and checks in child processes, all pinned to the
+    rank's own `threads_per_rank` logical CPUs.  Wall-clock, max over ranks.  Returns the block on
     rank 0, None elsewhere."""
     import torch
 
-    from intent_ir_b200.sweep import CheckerPool, generate_sweep_cases, merge_records, run_sweep
+    from intent_ir_b200.sweep import CheckerPool, generate_sweep_cases, merge_records, rank_cpu_share, run_sweep
 
     cores = host_cores()
     budget = max(1, len(cores) // 8)
-    mine = cores[local * budget:(local + 1) * budget] or cores
+    mine, smt = rank_cpu_share(cores, local)  # whole cores: the same hardware whether the other ranks run or not
     try:
         os.sched_setaffinity(0, set(mine))
     except Exception:
@@ -553,7 +553,7 @@ def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto
     cps = summary["ok"] / dt
     block = {"cases_per_s": round(cps, 2), "cases": summary["cases"], "ok": summary["ok"], "wall_s": round(dt, 2), "rank_wall_s": rank_s,
              "scaling": "strong", "partition": "longest estimated case first, family by family", "max_elements": max_elements, "base_seed": 1000,
-             "threads_per_rank": budget, "pinned_to_cores": bool(mine), "checker_processes_per_rank": workers, "host_cores": len(cores), "blas_threads": 1,
+             "threads_per_rank": budget, "pinned_to_cores": bool(mine), "checker_processes_per_rank": workers, "host_cores": len(cores), "hw_threads_per_core": smt, "blas_threads": 1,
              "checker": label, "gpu_busy_fraction": round(gpu_s / (dt * world), 4),
              # where the time goes: the checker processes' share of the wall clock, and a case's cost on the host and on the GPU
              "checker_busy_fraction": round(host_s / (dt * world * workers), 3), "host_ms_per_case": round(1e3 * host_s / n_rec, 1),

@@ -835,6 +835,37 @@ def host_allocator_settings() -> None:
         pass
 
 
+def rank_cpu_share(cpus: Sequence[int], local_rank: int, ranks_per_host: int = 8, sysfs: str = "/sys/devices/system/cpu") -> Tuple[List[int], int]:
+    """The logical CPUs of one rank out of `cpus` (the process's affinity), and how many hardware threads share a
+    core there.  Every rank gets ``len(cpus) // ranks_per_host`` of them whatever the number of ranks running.
+
+    Logical CPUs are ordered core by core first (package, core id, cpu number, read from the topology files), so
+    that a share is made of whole cores: Linux numbers the second hardware thread of core k as ``k + cores``, and
+    consecutive CPU numbers would give a rank alone four cores with idle sibling threads but, with all ranks
+    running, two cores' worth of throughput shared with another rank's threads.  Where the topology cannot be read
+    the CPU numbers decide."""
+
+    def where(cpu: int) -> Tuple[int, int, int]:
+        ids = []
+        for name in ("physical_package_id", "core_id"):
+            try:
+                with open(os.path.join(sysfs, f"cpu{cpu}", "topology", name)) as f:
+                    ids.append(int(f.read().strip()))
+            except (OSError, ValueError):
+                ids.append(-1)
+        return (ids[0], ids[1] if ids[1] >= 0 else cpu, cpu)
+
+    placed = sorted((where(c) for c in cpus))
+    ordered = [w[2] for w in placed]
+    per_core: Dict[Tuple[int, int], int] = {}
+    for w in placed:
+        per_core[w[:2]] = per_core.get(w[:2], 0) + 1
+    smt = max(per_core.values()) if per_core else 1
+    share = max(1, len(ordered) // max(1, ranks_per_host))
+    mine = ordered[local_rank * share:(local_rank + 1) * share]
+    return (mine or ordered), smt
+
+
 class CheckerPool:
     """``workers`` checker processes of one rank and the loop that serves their device requests."""
 

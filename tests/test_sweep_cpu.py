@@ -252,3 +252,24 @@ def test_large_cases_are_checked_block_by_block():
 
     recs = run_sweep(big, make_runner=one_bad_row, **CHECKER)
     assert not any(r["ok"] for r in recs) and all("rows" in r["summary"] for r in recs), [r["summary"] for r in recs]
+
+
+def test_a_ranks_cpu_share_is_made_of_whole_cores(tmp_path):
+    """Sixteen logical CPUs on eight two-thread cores, numbered the way Linux does (cpu k and cpu k + 8 share core
+    k): each of eight ranks gets both threads of one core, the same ones whatever else runs; without topology
+    files the CPU numbers decide; a restricted affinity is shared out among eight all the same."""
+    from intent_ir_b200.sweep import rank_cpu_share
+
+    for cpu in range(16):
+        d = tmp_path / f"cpu{cpu}" / "topology"
+        d.mkdir(parents=True)
+        (d / "physical_package_id").write_text("0\n")
+        (d / "core_id").write_text(f"{cpu % 8}\n")
+    shares = [rank_cpu_share(range(16), r, sysfs=str(tmp_path)) for r in range(8)]
+    assert [s[0] for s in shares] == [[k, k + 8] for k in range(8)]
+    assert {s[1] for s in shares} == {2}
+    assert sorted(c for s in shares for c in s[0]) == list(range(16))
+    plain = [rank_cpu_share(range(16), r, sysfs=str(tmp_path / "absent")) for r in range(8)]
+    assert [s[0] for s in plain] == [[2 * k, 2 * k + 1] for k in range(8)] and plain[0][1] == 1
+    assert rank_cpu_share([3, 5, 7], 2, sysfs=str(tmp_path)) == ([7], 1)
+    assert rank_cpu_share([3], 5, sysfs=str(tmp_path))[0] == [3]
