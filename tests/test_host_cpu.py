@@ -400,3 +400,47 @@ def test_recurring_row_programs_are_compiled_in(golden_graphs):
                    {"op": "mul", "inputs": ["xr", "w"], "output": "y"}], "outputs": ["y", "rstd"]}
     steps = plan_json(rms, {"M": 64, "N": 4096})["steps"]
     assert len(steps) == 1 and steps[0]["row_program"]["compiled_in"] is True
+
+
+def test_planner_answers_damaged_graphs_with_a_status_code(golden_graphs):
+    """The stateless C entry takes text from outside the process: whatever is wrong with it — missing or
+    retyped fields, absurd extents, truncated text — the answer is a status code (planned, unsupported or
+    invalid), never a fault.  Seeded structural damage to every recorded reference graph."""
+    import copy
+    import random
+
+    lib = _lib.load()
+    junk = [None, True, -1, 0, 2**31, 2**40, 2**62, -2**40, 1.5, "", "zz", "i64", "softmax", [], {}, [[]], ["a"], [1, 2, 3], {"a": 1}, 1e308, "M"]
+    symbols = "M N K C HW num_groups Z Q_CTX KV_CTX HEAD_DIM q_numhead kv_numhead B H W D S".split()
+
+    def paths(o, p=()):
+        if p:
+            yield p
+        for k in (o if isinstance(o, dict) else range(len(o)) if isinstance(o, list) else ()):
+            yield from paths(o[k], p + (k,))
+
+    def damage(o, rng):
+        o = copy.deepcopy(o)
+        for _ in range(rng.choice([1, 1, 2, 3])):
+            p = rng.choice(list(paths(o)))
+            parent = o
+            for k in p[:-1]:
+                parent = parent[k]
+            if rng.random() < 0.3:
+                del parent[p[-1]]
+            else:
+                parent[p[-1]] = copy.deepcopy(rng.choice(junk))
+        return o
+
+    buf = ctypes.create_string_buffer(1 << 20)
+    seen = set()
+    keys = sorted(golden_graphs)
+    for i in range(600):
+        rng = random.Random(i)
+        text = json.dumps(damage(golden_graphs[keys[i % len(keys)]]["intent"], rng))
+        if i % 20 == 0:
+            text = text[: rng.randrange(len(text))]
+        bind = {s: rng.choice([1, 2, 3, 7, 64, 100, 4096] + ([0, -1, 2**33] if i % 5 == 0 else [])) for s in symbols}
+        seen.add(lib.ib200_plan_json(text.encode(), json.dumps(bind).encode(), buf, len(buf)))
+    assert seen <= {_lib.OK, _lib.ERR_UNSUPPORTED, _lib.ERR_INVALID}, seen
+    assert _lib.ERR_INVALID in seen and _lib.OK in seen
