@@ -89,14 +89,19 @@ def _raise(rc: int, what: str) -> None:
 
 
 def _prepare(intent, shape_bindings) -> Tuple[str, str, Dict[str, Any]]:
+    # A graph whose fields have the wrong type trips over itself somewhere in the parser (a list where a name is
+    # expected, a number where a list is): to the caller that is an invalid graph like any other.
     try:
         fn = as_intent(intent)
-    except IntentIRValidationError as e:
+    except (IntentIRValidationError, TypeError, ValueError, KeyError, AttributeError) as e:
         raise B200LoweringError(f"invalid IntentIR graph: {e}") from e
-    bindings = derive_bindings(normalise_bindings(shape_bindings))
+    try:
+        bindings = derive_bindings(normalise_bindings(shape_bindings))
+    except (TypeError, ValueError, AttributeError) as e:
+        raise B200LoweringError(f"invalid shape bindings: {e}") from e
     try:
         js = resolve_expressions(fn.to_json_dict(), bindings)
-    except ValueError as e:
+    except (TypeError, ValueError, KeyError, AttributeError) as e:
         raise B200LoweringError(str(e)) from e
     # only the numeric bindings travel; tuning knobs are harmless extra symbols
     return json.dumps(js, allow_nan=True), json.dumps(bindings, sort_keys=True), bindings

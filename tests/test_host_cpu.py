@@ -444,3 +444,12 @@ def test_planner_answers_damaged_graphs_with_a_status_code(golden_graphs):
         seen.add(lib.ib200_plan_json(text.encode(), json.dumps(bind).encode(), buf, len(buf)))
     assert seen <= {_lib.OK, _lib.ERR_UNSUPPORTED, _lib.ERR_INVALID}, seen
     assert _lib.ERR_INVALID in seen and _lib.OK in seen
+    # the Python entry in front of it: a plan or B200LoweringError, whatever the parser tripped over
+    for i in range(300):
+        rng = random.Random(10_000 + i)
+        graph = damage(golden_graphs[keys[i % len(keys)]]["intent"], rng)
+        bind = {s: rng.choice([1, 2, 3, 64, 4096] + ([0, -1, "x", None, 1.5] if i % 5 == 0 else [])) for s in symbols}
+        try:
+            plan_json(graph, bind)
+        except B200LoweringError:
+            pass
