@@ -244,16 +244,28 @@ class Planner {
 
   // =============================== phase A: build ==========================================
   int64_t dim_value(const Json& d, const std::string& where) const {
-    if (d.is_num()) return d.as_int();
+    if (d.is_num()) {
+      if (!d.is_int() || d.num < -1 || d.num > (double)kMaxElements) throw Invalid("bad dim in " + where);
+      return d.as_int();
+    }
     if (d.is_str()) {
       auto it = bind_.find(d.s);
-      if (it != bind_.end()) return (int64_t)it->second;
+      if (it != bind_.end()) {
+        if (!(it->second >= 0 && it->second <= (double)kMaxElements) || std::floor(it->second) != it->second)
+          throw Invalid("symbol '" + d.s + "' is bound to something that is not an extent, in " + where);
+        return (int64_t)it->second;
+      }
       char* end = nullptr;
       long long v = std::strtoll(d.s.c_str(), &end, 10);
       if (end && *end == 0 && !d.s.empty()) return v;
       throw Invalid("unbound symbolic dim '" + d.s + "' in " + where);
     }
     throw Invalid("bad dim in " + where);
+  }
+  // an axis, a position or a small count: an integral literal that fits an int
+  static int small_int(const Json& j, const std::string& where) {
+    if (!j.is_int() || std::fabs(j.num) > 2147483647.0) throw Invalid(where + ": expected an integer");
+    return (int)j.as_int();
   }
   Shape shape_of(const Json& arr, const std::string& where) const {
     Shape s;
@@ -262,7 +274,16 @@ class Planner {
     return s;
   }
 
+  // Extents are final when a node is added (reshape has resolved its -1 by then): none negative, and a
+  // product that neither wraps nor exceeds what any device holds.
+  static constexpr int64_t kMaxElements = (int64_t)1 << 40;
   int add(Node n) {
+    int64_t total = 1;
+    for (int64_t d : n.shape) {
+      if (d < 0) throw Invalid("negative extent in the shape of '" + (n.name.empty() ? n.op : n.name) + "': " + shape_str(n.shape));
+      if (__builtin_mul_overflow(total, d, &total) || total > kMaxElements)
+        throw Unsupported("tensor '" + (n.name.empty() ? n.op : n.name) + "' is larger than 2^40 elements: " + shape_str(n.shape));
+    }
     nodes_.push_back(std::move(n));
     int id = (int)nodes_.size() - 1;
     if (!nodes_[id].name.empty()) by_name_[nodes_[id].name] = id;
@@ -303,10 +324,10 @@ class Planner {
     return true;
   }
   bool token_value(const Json& t, int64_t& v) const {
-    if (t.is_num()) { v = t.as_int(); return true; }
+    if (t.is_num()) { if (!t.is_int()) return false; v = t.as_int(); return true; }
     if (t.is_str()) {
       auto it = bind_.find(t.s);
-      if (it != bind_.end()) { v = (int64_t)it->second; return true; }
+      if (it != bind_.end() && std::fabs(it->second) < 9e15) { v = (int64_t)it->second; return true; }
     }
     return false;
   }
@@ -450,7 +471,7 @@ class Planner {
     if (raw->is_arr()) for (auto& j : raw->arr) items.push_back(&j);
     else items.push_back(raw);
     for (auto* j : items) {
-      if (j->is_num()) axes.push_back((int)j->as_int());
+      if (j->is_num()) axes.push_back(small_int(*j, "reduce axes"));
       else if (j->is_str() && !j->s.empty() && std::all_of(j->s.begin(), j->s.end(), ::isdigit)) axes.push_back(std::atoi(j->s.c_str()));
     }
     if (axes.empty()) for (int i = 1; i < rank; ++i) axes.push_back(i);
@@ -527,7 +548,7 @@ class Planner {
         if (!sh) throw Invalid(where + " requires attrs.shape");
         n.shape = shape_of(*sh, where);
         const Json* ax = attrs->find("axis");
-        n.axis = ax && ax->is_num() ? (int)ax->as_int() : 0;
+        n.axis = ax && ax->is_num() ? small_int(*ax, where) : 0;
         if (n.axis < 0 || n.axis >= (int)n.shape.size()) throw Invalid(where + ": iota axis out of range");
         const Json* dt = attrs->find("dtype");
         n.dclass = class_of_dtype(dtype_code(dt && dt->is_str() ? dt->s : "i32"));
@@ -551,7 +572,7 @@ class Planner {
         const Json* bd = attrs->find("broadcast_dims");
         if (!sh || !bd || !bd->is_arr()) throw Invalid(where + " requires out_shape and broadcast_dims");
         n.shape = shape_of(*sh, where);
-        for (auto& j : bd->arr) n.axes.push_back((int)j.as_int());
+        for (auto& j : bd->arr) n.axes.push_back(small_int(j, where));
         for (int a : n.axes) if (a < 0 || a >= (int)n.shape.size()) throw Invalid(where + ": broadcast_dims out of range");
         id = add(n);
       } else if (op == "transpose") {
@@ -560,9 +581,10 @@ class Planner {
         const Json* pj = attrs->find("perm");
         if (!pj || !pj->is_arr() || pj->arr.size() != nodes_[in[0]].shape.size()) throw Invalid(where + " requires attrs.perm of the input's rank");
         for (auto& j : pj->arr) {
-          int a = (int)j.as_int();
+          int a = small_int(j, where);
           if (a < 0) a += (int)pj->arr.size();
           if (a < 0 || a >= (int)pj->arr.size()) throw Invalid(where + ": perm out of range");
+          if (std::find(n.axes.begin(), n.axes.end(), a) != n.axes.end()) throw Invalid(where + ": repeated axis in perm");
           n.axes.push_back(a);
           n.shape.push_back(nodes_[in[0]].shape[a]);
         }
@@ -576,6 +598,7 @@ class Planner {
         const Shape& xs = nodes_[in[0]].shape;
         n.axes = reduce_axes(raw, (int)xs.size());
         const Json* kd = attrs->find("keepdims");
+        if (kd && kd->type != Json::Bool && !kd->is_num() && kd->type != Json::Null) throw Invalid(where + ": keepdims must be a boolean");
         n.keepdims = kd && ((kd->type == Json::Bool && kd->b) || (kd->is_num() && kd->num != 0));
         for (int i = 0; i < (int)xs.size(); ++i) {
           const bool red = std::binary_search(n.axes.begin(), n.axes.end(), i);
@@ -608,7 +631,7 @@ class Planner {
         if (in.size() != 1) throw Invalid(where + " requires 1 input");
         Node n; n.name = out; n.op = op; n.in = in; n.shape = nodes_[in[0]].shape; n.dclass = DC_FLOAT;
         const Json* ax = attrs->find("axis");
-        n.axis = ax && ax->is_num() ? (int)ax->as_int() : -1;
+        n.axis = ax && ax->is_num() ? small_int(*ax, where) : -1;
         if (n.axis < 0) n.axis += (int)n.shape.size();
         if (n.axis < 0 || n.axis >= (int)n.shape.size()) throw Invalid(where + ": axis out of range");
         id = add(n);
@@ -679,7 +702,7 @@ class Planner {
           if (n.shape[0] != src[0]) throw Invalid(where + ": resize channel mismatch");
           if (n.shape[1] != 2 * src[1] || n.shape[2] != 2 * src[2]) throw Invalid(where + ": resize currently expects 2x upsample: src=" + shape_str(src) + " out=" + shape_str(n.shape));
           const Json* fl = attrs->find("hw_fl");
-          n.axis = fl && fl->is_num() ? (int)fl->as_int() : 7;
+          n.axis = fl && fl->is_num() ? small_int(*fl, where) : 7;
         } else {
           if (n.shape != src) throw Invalid(where + ": warp output shape mismatch: src=" + shape_str(src) + " out=" + shape_str(n.shape));
           if (nodes_[in[1]].shape != Shape{src[1], src[2]}) throw Invalid(where + ": warp offset shape mismatch");
@@ -691,7 +714,7 @@ class Planner {
         if (numel(nodes_[in[1]].shape) != 1 || numel(nodes_[in[2]].shape) != 1) throw Invalid(where + ": p and seed must be scalars");
         Node n; n.name = out; n.op = op; n.in = in; n.shape = nodes_[in[0]].shape; n.dclass = DC_FLOAT;
         const Json* nr = attrs->find("n_rounds");
-        n.axis = nr && nr->is_num() && nr->as_int() > 0 ? (int)nr->as_int() : 10;
+        n.axis = nr && nr->is_num() && small_int(*nr, where) > 0 ? small_int(*nr, where) : 10;
         id = add(n);
       } else {
         throw Unsupported("op '" + op + "' is not covered by the B200 kernels (name=" + plan_->kernel_name + ")");
@@ -706,8 +729,14 @@ class Planner {
     const Json* outs = intent_.find("outputs");
     if (outs && outs->is_arr()) for (auto& j : outs->arr) if (j.is_str()) outputs_.push_back(j.s);
     if (outputs_.empty()) outputs_.push_back(ops->arr.back().find("output")->s);
+    for (size_t i = 0; i < outputs_.size(); ++i)
+      for (size_t k = 0; k < i; ++k)
+        if (outputs_[k] == outputs_[i]) throw Invalid("output '" + outputs_[i] + "' is listed twice");
     for (auto& o : outputs_) {
       if (!by_name_.count(o)) throw Invalid("output '" + o + "' is never produced");
+      // an op consumed it before anything produced it, so it entered as an external input: the interpreter would stop
+      // at that op with an undefined value unless the caller supplied the output as an input
+      if (nodes_[by_name_[o]].op == "input") throw Invalid("output '" + o + "' is consumed but no op produces it");
       if (!decl_.count(o)) throw Invalid("outputs entry not found in tensors: " + o);
     }
     // argument list: external inputs in first-use order, then outputs

@@ -101,6 +101,30 @@ def test_planner_rejects_what_it_does_not_cover(golden_graphs):
         plan_json(g["intent"], {"M": 4})
     with pytest.raises(B200LoweringError, match="invalid IntentIR graph"):
         plan_json({"name": "x", "tensors": {}, "ops": []}, {})
+    # extents that are no extents, a consumed output that nothing produces, attributes of the wrong kind
+    add = golden_graphs["add2d"]["intent"]
+    for bad, why in (([-1], "negative extent"), ([1.5, "N"], "invalid dimension type|bad dim"), ([2**31, 2**31], "larger than 2\\^40 elements")):
+        damaged = json.loads(json.dumps(add))
+        for t in damaged["tensors"].values():
+            t["shape"] = bad
+        with pytest.raises(B200LoweringError, match=why):
+            plan_json(damaged, {"M": 4, "N": 8})
+    with pytest.raises(B200LoweringError, match="not an extent"):
+        plan_json(add, {"M": -4, "N": 8})
+    form = json.loads(json.dumps(golden_graphs["softmax_inner__cuda_pipeline_form"]["intent"]))
+    op = next(o for o in form["ops"] if o["output"] == "row_sum_ptr")
+    op["output"] = "elsewhere"
+    form["tensors"]["elsewhere"] = dict(form["tensors"]["row_sum_ptr"])
+    with pytest.raises(B200LoweringError, match="consumed but no op produces it"):
+        plan_json(form, {"M": 4, "N": 8})
+    rows = json.loads(json.dumps(golden_graphs["row_sum"]["intent"]))
+    rows["ops"][0]["attrs"]["keepdims"] = "yes"
+    with pytest.raises(B200LoweringError, match="keepdims must be a boolean"):
+        plan_json(rows, {"M": 4, "N": 8})
+    tr = json.loads(json.dumps(golden_graphs["transpose2d"]["intent"]))
+    tr["ops"][0]["attrs"]["perm"] = [1, 1]
+    with pytest.raises(B200LoweringError, match="repeated axis"):
+        plan_json(tr, {"M": 4, "N": 8})
 
 
 def test_lowered_record_mirrors_the_reference_fields(golden_graphs):
