@@ -506,16 +506,27 @@ def partition_cases(cases: Sequence[SweepCase], world: int, how: str = "mod") ->
 
 # graph families whose result has the row axis at full size: checked in blocks of about this many elements
 _BLOCK_KINDS = ("softmax", "layernorm", "chain", "groupnorm", "rmsnorm", "layernorm_residual", "masked_softmax")
-_BLOCK_ELEMENTS = 1 << 17
+_BLOCK_ELEMENTS = 1 << 16
+_BLOCK_MIN = 2  # cases of fewer than this many blocks are checked whole
+# matmul: a block of rows of A meets all of B again, so its blocks are larger (B is streamed once per block, a tenth of
+# the block's product at 128 rows) and only results of more than a million elements are cut
+_MATMUL_BLOCK_ELEMENTS = 1 << 18
+_MATMUL_MIN_RESULT = 1 << 20
 
 
 def _row_blocks(case: SweepCase) -> List[Tuple[int, int]]:
-    """Row ranges for checking a large case block by block; empty when the case is checked whole (small cases,
-    matmul -- every block would multiply by all of B again -- and reductions, whose results are small)."""
-    if case.kind not in _BLOCK_KINDS or case.elements < 4 * _BLOCK_ELEMENTS:
+    """Row ranges for checking a large case block by block; empty when the case is checked whole (small cases and
+    reductions, whose results are small)."""
+    rows = int(case.shapes.get(_ROW_AXIS.get(case.kind, ""), 0))
+    if case.kind == "matmul_bias_relu":
+        width = int(case.shapes.get("N", 0))
+        if rows * width < _MATMUL_MIN_RESULT:
+            return []
+        step = max(64, _MATMUL_BLOCK_ELEMENTS // max(1, width))
+    elif case.kind in _BLOCK_KINDS and case.elements >= _BLOCK_MIN * _BLOCK_ELEMENTS:
+        step = max(1, _BLOCK_ELEMENTS // max(1, case.elements // max(rows, 1)))
+    else:
         return []
-    rows = int(case.shapes[_ROW_AXIS[case.kind]])
-    step = max(1, _BLOCK_ELEMENTS // max(1, case.elements // max(rows, 1)))
     return [(a, min(rows, a + step)) for a in range(0, rows, step)] if step < rows else []
 
 

@@ -226,13 +226,17 @@ def test_host_allocator_settings_reach_this_process_and_its_children():
 
 
 def test_large_cases_are_checked_block_by_block():
-    """A case of more than half a million elements runs whole on the device and is verified in blocks of rows;
-    a wrong value in one block fails the case and the record names the rows."""
+    """A large case runs whole on the device and is verified in blocks of rows (products with more than a million
+    results included: a block of rows of A against all of B); a wrong value in one block fails the case and the
+    record names the rows."""
     from intent_ir_b200.sweep import _row_blocks
 
-    big = [c for c in generate_sweep_cases(400, base_seed=1000, max_elements=1 << 20) if c.kind in ("layernorm", "softmax", "chain", "groupnorm")
-           and c.elements >= 1 << 19][:4]
-    assert big and all(len(_row_blocks(c)) > 1 for c in big)
+    pool = generate_sweep_cases(400, base_seed=1000, max_elements=1 << 21)
+    big = [c for c in pool if c.kind in ("layernorm", "softmax", "chain", "groupnorm") and c.elements >= 1 << 19][:4]
+    big += [c for c in pool if c.kind == "matmul_bias_relu" and c.shapes["M"] * c.shapes["N"] >= 1 << 20][:1]
+    assert len(big) == 5 and all(len(_row_blocks(c)) > 1 for c in big)
+    assert all(b > a and (b - a >= 64 or c.kind != "matmul_bias_relu") for c in big for a, b in _row_blocks(c)[:-1])
+    assert [blk[0] for blk in _row_blocks(big[-1])][0] == 0 and _row_blocks(big[-1])[-1][1] == big[-1].shapes["M"]
     assert not _row_blocks([c for c in generate_sweep_cases(64, base_seed=1000, max_elements=1 << 12)][0])
     recs = run_sweep(big, make_runner=numpy_runner, **CHECKER)
     assert all(r["ok"] for r in recs), [(r["kind"], r["summary"]) for r in recs if not r["ok"]]
