@@ -515,8 +515,13 @@ def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto
     chk = dict(diff_fn=diff_fn, tolerances_fn=tol_fn, case_type=case_type, intent_from_json=from_json)
     pool = CheckerPool(workers, (diff_fn, tol_fn, case_type), from_json, rank, mine)
     try:
+        # untimed: imports, first plans, and the arenas and heaps of every process at their working size (a few of the
+        # largest kind of case per checker process), so that the timed cases do not start with all ranks' processes
+        # faulting their memory in at once
+        pool.prime(3 * 4 * max_elements)
         warm = generate_sweep_cases(4 * workers, base_seed=10, max_elements=1 << 16)
-        run_sweep(warm, pool=pool, **chk)  # untimed: imports, first plans, first arenas
+        warm += [c for c in generate_sweep_cases(64, base_seed=20, max_elements=max_elements) if 2 * c.elements >= max_elements][:2 * workers]
+        run_sweep(warm, pool=pool, **chk)
         cases = generate_sweep_cases(total, base_seed=1000, max_elements=max_elements, canonical_groupnorm_every=groupnorm_every)
         torch.cuda.synchronize()
         if dist:
@@ -557,7 +562,9 @@ def run_sweep_block(rank, world, local, dist, total, out_dir=None, checker="auto
              "checker": label, "gpu_busy_fraction": round(gpu_s / (dt * world), 4),
              # where the time goes: the checker processes' share of the wall clock, and a case's cost on the host and on the GPU
              "checker_busy_fraction": round(host_s / (dt * world * workers), 3), "host_ms_per_case": round(1e3 * host_s / n_rec, 1),
-             "gpu_ms_per_case": round(1e3 * gpu_s / n_rec, 2), "failed": summary["failed"][:3],
+             "gpu_ms_per_case": round(1e3 * gpu_s / n_rec, 2),
+             "inputs_ms_per_case": round(1e3 * sum((r.get("t_inputs") or 0.0) for part in gathered for r in part) / n_rec, 2),
+             "failed": summary["failed"][:3],
              "by_kind": {k: f"{v['ok']}/{v['cases']}" for k, v in summary["by_kind"].items()}}
     # the one-rank figure of the same case list on the same host, when an N = 1 run left it behind
     note = os.path.join(tempfile.gettempdir(), f"ib200_sweep_n1_{total}_{max_elements}_{budget}.json")

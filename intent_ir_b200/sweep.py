@@ -581,7 +581,8 @@ def _check_case(case: SweepCase, runner_of: Callable, diff_fn: Callable, toleran
                 if not d.ok and ok:
                     ok, summary = False, f"{d.summary} (rows {a}..{b - 1})"
         rec.update(ok=ok, summary=summary, max_abs=float(max_abs) if np.isfinite(max_abs) else None,
-                   max_rel=float(max_rel) if np.isfinite(max_rel) else None, t_gpu=timing.get("device", timing.get("gpu")))
+                   max_rel=float(max_rel) if np.isfinite(max_rel) else None, t_gpu=timing.get("device", timing.get("gpu")),
+                   t_runner=timing.get("gpu"), t_inputs=timing.get("inputs"))
     except Exception as e:  # lowering, GPU or checker failure: a failed record, not a dead sweep
         rec.update(ok=False, summary=f"{type(e).__name__}: {e}"[:300], max_abs=None, max_rel=None, t_gpu=None)
     rec["t_total"] = time.perf_counter() - t0
@@ -667,6 +668,7 @@ def _remote_runner(conn, arena: _Arena, intent, case: SweepCase, timing: Optiona
     from .bindings import derive_bindings
 
     def run(c):
+        t_start = time.perf_counter()
         bind = derive_bindings(dict(c.shapes))
         outs = []
         out_bytes = 0
@@ -722,6 +724,8 @@ def _remote_runner(conn, arena: _Arena, intent, case: SweepCase, timing: Optiona
             layout_out.append((name, dt.str, shape, off))
             off = _align(off + max(int(np.prod(shape, dtype=np.int64)) * dt.itemsize, 1))
         inputs = {k: np.ndarray(shape, np.dtype(dts), buffer=shm.buf, offset=o) for k, dts, shape, o in layout_in}
+        if timing is not None:
+            timing["inputs"] = time.perf_counter() - t_start
         return _exchange(conn, shm, case, c, layout_in, layout_out, inputs, timing)
 
     return run
@@ -742,6 +746,15 @@ def _checker_main(conn, checker, intent_from_json, rank: int, cpus: Optional[Seq
             msg = conn.recv()
             if msg[0] == "stop":
                 break
+            if msg[0] == "prime":  # have the arena at its working size, pages present, before the cases come
+                shm = arena.ensure(int(msg[1]))
+                try:  # (reserve first: touching pages the filesystem cannot back would end the process)
+                    os.posix_fallocate(shm._fd, 0, shm.size)
+                    np.frombuffer(shm.buf, np.uint8)[:] = 0
+                    conn.send(("primed", shm.name, shm.size))
+                except Exception:
+                    conn.send(("not primed",))
+                continue
             case = msg[1]
             rec = _check_case(case, lambda intent, cs, timing: _remote_runner(conn, arena, intent, cs, timing), diff_fn, tolerances_fn,
                               case_type, intent_from_json, rank)
@@ -898,6 +911,23 @@ class CheckerPool:
             if not c.poll(120) or c.recv()[0] != "ready":
                 raise RuntimeError("a checker process did not start")
         self.served = _Served()
+
+    def prime(self, arena_bytes: int) -> None:
+        """Every checker process brings its shared-memory arena to ``arena_bytes`` and touches it, and this process
+        maps and touches it too.  A sweep then starts with its arenas in place instead of every process of every rank
+        faulting tens of thousands of fresh pages in at the same moment (cases that need more still grow theirs)."""
+        for c in self.conns:
+            c.send(("prime", int(arena_bytes)))
+        for c in self.conns:
+            try:
+                if not c.poll(120):
+                    continue
+                msg = c.recv()
+                if msg[0] == "primed":
+                    view = self.served.views(msg[1], [("all", "|u1", (int(msg[2]),), 0)], c)["all"]
+                    int(view[::4096].sum())
+            except (EOFError, OSError):
+                pass  # (run() reports a process that died)
 
     def run(self, cases: Sequence[SweepCase], device_run: Callable, on_record: Optional[Callable] = None) -> List[Dict[str, Any]]:
         """Check ``cases`` (handed out in the given order, one in flight per process); returns the records

@@ -277,3 +277,27 @@ def test_a_ranks_cpu_share_is_made_of_whole_cores(tmp_path):
     assert [s[0] for s in plain] == [[2 * k, 2 * k + 1] for k in range(8)] and plain[0][1] == 1
     assert rank_cpu_share([3, 5, 7], 2, sysfs=str(tmp_path)) == ([7], 1)
     assert rank_cpu_share([3], 5, sysfs=str(tmp_path))[0] == [3]
+
+
+def test_primed_arenas_are_in_place_before_the_cases():
+    """`prime` brings every checker's arena to the asked size (mapped by the serving process too); the cases that
+    follow run in it, a case that needs more still grows its own."""
+    from intent_ir_b200.sweep import CheckerPool, _Shapes
+
+    def DEVICE_STAND_IN(intent_json, shapes, ins, outs):
+        intent = IntentFunction.from_json_dict(intent_json)
+        return {k: v for k, v in numpy_runner(intent, lambda c: ins)(_Shapes(shapes)).items() if k in outs}
+
+    pool = CheckerPool(2, (run_diff, infer_tolerances, TestCase), IntentFunction.from_json_dict)
+    try:
+        pool.prime(3 << 20)
+        primed = dict(pool.served.blocks)
+        assert len(primed) == 2 and all(b.size >= 3 << 20 for b in primed.values())
+        cases = generate_sweep_cases(12, base_seed=1000, max_elements=1 << 16)
+        recs = pool.run(cases, DEVICE_STAND_IN)
+        assert all(r["ok"] for r in recs), [r["summary"] for r in recs if not r["ok"]]
+        assert set(pool.served.blocks) == set(primed)  # nothing grew: the cases ran in the primed arenas
+        big = [c for c in generate_sweep_cases(40, base_seed=1000, max_elements=1 << 21) if c.elements >= 1 << 20][:2]
+        assert all(r["ok"] for r in pool.run(big, DEVICE_STAND_IN))
+    finally:
+        pool.close()
