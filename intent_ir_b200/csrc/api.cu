@@ -56,6 +56,8 @@ int ib200_softmax_io(const void* x, void* y, float* row_max, float* row_sum, int
 int ib200_softmax_masked(const void* x, const void* mask, int64_t mask_row_stride, float fill, void* y, float* row_max, float* row_sum,
                          int64_t rows, int64_t cols, void* stream) {
   if (!mask) return fail(IB200_ERR_INVALID, "softmax_masked: mask is null");
+  if (mask_row_stride < 0 || (mask_row_stride > 0 && rows > 0 && beyond_any_device(rows, mask_row_stride)))
+    return fail(IB200_ERR_INVALID, "softmax_masked: the mask's row stride must be 0 (one vector for all rows) or positive");
   const SoftmaxMask mk{static_cast<const uint8_t*>(mask), mask_row_stride, fill, 0};
   return launch_softmax(x, y, row_max, row_sum, IB200_F32, rows, cols, static_cast<cudaStream_t>(stream), IB200_F32, &mk);
 }
@@ -90,6 +92,7 @@ int ib200_layernorm(const void* x, const void* w, const void* b, void* y, float*
 int ib200_groupnorm(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int dtype, int64_t n,
                     int64_t c, int64_t hw, int64_t groups, float eps, void* stream) {
   if (groups <= 0 || c < 0 || n < 0 || hw < 0) return fail(IB200_ERR_INVALID, "groupnorm: bad extents");
+  if (beyond_any_device(n, c > 0 ? c : 1, hw > 0 ? hw : 1)) return fail(IB200_ERR_INVALID, "groupnorm: more than 2^40 elements");
   if (c % groups != 0) return fail(IB200_ERR_INVALID, "groupnorm: C must be a multiple of the group count");
   return launch_norm_rows(x, w, b, y, mean, rstd, dtype, dtype, n * groups, (c / groups) * hw, hw > 0 ? hw : 1, c > 0 ? c : 1,
                           eps, static_cast<cudaStream_t>(stream));

@@ -36,6 +36,12 @@ inline int dtype_size(int dt) {
   }
 }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// Non-negative extents whose product is more than any device holds (2^40 elements), or wraps: arguments like that are
+// uninitialised or mistaken, and index arithmetic downstream is only checked for sizes that can exist.
+inline bool beyond_any_device(int64_t a, int64_t b = 1, int64_t c = 1) {
+  int64_t n = 0;
+  return __builtin_mul_overflow(a, b, &n) || __builtin_mul_overflow(n, c, &n) || n > ((int64_t)1 << 40);
+}
 
 // ---- internal launchers (one per .cu file) ----------------------------------------------
 // `scratch` (device memory in any state, or null) lets a reduction with too few independent results to

@@ -957,6 +957,8 @@ int launch_gemm(const void* a, const void* b, const void* bias, void* c, int in_
                 int64_t k, int transpose_b, int act, int32_t* status, cudaStream_t s, int flags, void* scratch, size_t scratch_bytes) {
   if (m < 0 || n < 0 || k < 0) return fail(IB200_ERR_INVALID, "gemm: negative extent");
   if (m == 0 || n == 0) return IB200_OK;
+  if (beyond_any_device(m, n) || beyond_any_device(m, k > 0 ? k : 1) || beyond_any_device(k > 0 ? k : 1, n))
+    return fail(IB200_ERR_INVALID, "gemm: more than 2^40 elements in an operand");
   if (!a || !b || !c) {
     if (k > 0 || !c) return fail(IB200_ERR_INVALID, "gemm: null pointer");
   }

@@ -79,6 +79,7 @@ int launch_gather(const void* data, const GatherArgs& a, void* out, int elem_byt
 int launch_transpose2d(const void* x, void* out, int elem_bytes, int64_t rows, int64_t cols, cudaStream_t s) {
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "transpose2d: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
+  if (beyond_any_device(rows, cols)) return fail(IB200_ERR_INVALID, "transpose2d: more than 2^40 elements");
   if (!x || !out) return fail(IB200_ERR_INVALID, "transpose2d: null pointer");
   const int64_t tiles = ((rows + 31) / 32) * ((cols + 31) / 32);
   const int grid = (int)(tiles < (int64_t)kSmCount * 16 ? tiles : (int64_t)kSmCount * 16);

@@ -796,6 +796,7 @@ int launch_norm_rows(const void* x, const void* w, const void* b, void* y, float
   if (!status) status = norm_default_status();
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "norm: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
+  if (beyond_any_device(rows, cols)) return fail(IB200_ERR_INVALID, "norm: more than 2^40 elements");
   if (!x || !y) return fail(IB200_ERR_INVALID, "norm: null pointer");
   if ((w || b) && (affine_inner < 1 || affine_period < 1)) return fail(IB200_ERR_INVALID, "norm: affine_inner and affine_period must be >= 1");
   if (res_bias && !res) return fail(IB200_ERR_INVALID, "norm: a residual bias needs a residual");

@@ -420,6 +420,7 @@ int launch_reduce(const void* x, void* out, int x_dtype, int out_dtype, int kind
                   int64_t inner, float scale, cudaStream_t s, void* scratch, size_t scratch_bytes) {
   if (outer < 0 || reduce < 0 || inner < 0) return fail(IB200_ERR_INVALID, "reduce: negative extent");
   if (outer == 0 || inner == 0) return IB200_OK;  // empty result
+  if (beyond_any_device(outer, reduce > 0 ? reduce : 1, inner)) return fail(IB200_ERR_INVALID, "reduce: more than 2^40 elements");
   if (!out || (!x && reduce > 0)) return fail(IB200_ERR_INVALID, "reduce: null pointer");
   if (reduce == 0 && kind == IB200_REDUCE_MAX) return fail(IB200_ERR_INVALID, "reduce_max over an empty axis has no identity");
   switch (kind) {

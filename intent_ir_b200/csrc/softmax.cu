@@ -227,6 +227,7 @@ int launch_softmax(const void* x, void* y, float* row_max, float* row_sum, int d
   if (out_dtype < 0) out_dtype = dtype;
   if (rows < 0 || cols < 0) return fail(IB200_ERR_INVALID, "softmax: negative extent");
   if (rows == 0 || cols == 0) return IB200_OK;
+  if (beyond_any_device(rows, cols)) return fail(IB200_ERR_INVALID, "softmax: more than 2^40 elements");
   if (!x || !y) return fail(IB200_ERR_INVALID, "softmax: null pointer");
   if (!mk.mask && scratch) {  // few, very long rows: segments over the whole GPU
     const int rc = try_softmax_segmented(x, y, row_max, row_sum, dtype, out_dtype, rows, cols, scratch, scratch_bytes, s);

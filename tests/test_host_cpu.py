@@ -477,3 +477,51 @@ def test_planner_answers_damaged_graphs_with_a_status_code(golden_graphs):
             plan_json(graph, bind)
         except B200LoweringError:
             pass
+
+
+def test_direct_entries_refuse_arguments_that_cannot_be_meant():
+    """Negative extents, extents whose product no device holds (or that wrap), unknown type / kind / activation
+    codes, null operands and a negative mask stride are answered before anything is launched: the codes are
+    INVALID or UNSUPPORTED, never the CUDA error a launch attempt gives on a machine without a device.  Empty
+    tensors are fine and launch nothing."""
+    lib = _lib.load()
+    p = ctypes.c_void_p(0x7F0000000000)  # stands for a device address; nothing on the host dereferences it
+    refused = {_lib.ERR_INVALID, _lib.ERR_UNSUPPORTED}
+
+    def calls(r, c):
+        return [lib.ib200_softmax(p, p, None, None, _lib.F32, r, c, None),
+                lib.ib200_softmax_io(p, p, None, None, _lib.BF16, _lib.F32, r, c, None),
+                lib.ib200_softmax_masked(p, p, 0, -1e9, p, None, None, r, c, None),
+                lib.ib200_layernorm(p, p, p, p, None, None, _lib.F32, r, c, 1e-5, None),
+                lib.ib200_norm_rows(p, p, p, p, None, None, _lib.F32, _lib.F32, r, c, 1, max(c, 1), 1e-5, None),
+                lib.ib200_reduce(p, p, _lib.F32, _lib.F32, _lib.REDUCE_SUM, r, c, 1, 1.0, None),
+                lib.ib200_reduce(p, p, _lib.F32, _lib.F32, _lib.REDUCE_MAX, 1, r, c, 1.0, None),
+                lib.ib200_reduce_any_f32(p, p, r, c, None),
+                lib.ib200_gemm_bias_act(p, p, None, p, _lib.BF16, _lib.BF16, r, c, 8, 0, _lib.ACT_RELU, None, None),
+                lib.ib200_gemm_bias_act(p, p, None, p, _lib.F32, _lib.F32, 8, r, c, 0, _lib.ACT_NONE, None, None),
+                lib.ib200_transpose2d(p, p, 4, r, c, None),
+                lib.ib200_groupnorm(p, p, p, p, None, None, _lib.F32, r, c, 16, 1, 1e-5, None)]
+
+    for r, c in ((-1, 16), (4, -5), (1 << 40, 1 << 40), (1 << 62, 4), (4, 1 << 62), (1 << 21, 1 << 20)):
+        assert set(calls(r, c)) <= refused, (r, c, calls(r, c))
+    for r, c in ((0, 16), (0, 0)):  # (the maximum over an empty axis has no identity: that one call is refused)
+        got = calls(r, c)
+        assert got[6] == (_lib.ERR_INVALID if c else _lib.OK) and set(got[:6] + got[7:]) == {_lib.OK}, (r, c, got)
+    for code in (-1, 99):
+        assert lib.ib200_softmax(p, p, None, None, code, 4, 16, None) in refused
+        assert lib.ib200_layernorm(p, p, p, p, None, None, code, 4, 16, 1e-5, None) in refused
+        assert lib.ib200_reduce(p, p, code, _lib.F32, _lib.REDUCE_SUM, 4, 16, 1, 1.0, None) in refused
+        assert lib.ib200_reduce(p, p, _lib.F32, _lib.F32, code, 4, 16, 1, 1.0, None) in refused
+        assert lib.ib200_gemm_bias_act(p, p, None, p, code, _lib.F32, 8, 8, 8, 0, _lib.ACT_NONE, None, None) in refused
+        assert lib.ib200_gemm_bias_act(p, p, None, p, _lib.F32, _lib.F32, 8, 8, 8, 0, code, None, None) in refused
+        assert lib.ib200_transpose2d(p, p, code, 4, 4, None) in refused
+    assert lib.ib200_softmax(None, p, None, None, _lib.F32, 4, 16, None) == _lib.ERR_INVALID
+    assert lib.ib200_layernorm(p, p, p, None, None, None, _lib.F32, 4, 16, 1e-5, None) == _lib.ERR_INVALID
+    assert lib.ib200_reduce(p, None, _lib.F32, _lib.F32, _lib.REDUCE_SUM, 4, 16, 1, 1.0, None) == _lib.ERR_INVALID
+    assert lib.ib200_gemm_bias_act(None, p, None, p, _lib.F32, _lib.F32, 8, 8, 8, 0, _lib.ACT_NONE, None, None) == _lib.ERR_INVALID
+    assert lib.ib200_groupnorm(p, p, p, p, None, None, _lib.F32, 2, 8, 16, 3, 1e-5, None) == _lib.ERR_INVALID
+    assert lib.ib200_groupnorm(p, p, p, p, None, None, _lib.F32, 2, 8, 16, 0, 1e-5, None) == _lib.ERR_INVALID
+    assert lib.ib200_norm_rows(p, p, p, p, None, None, _lib.F32, _lib.F32, 4, 16, 1, 0, 1e-5, None) == _lib.ERR_INVALID
+    assert lib.ib200_softmax_masked(p, p, -3, -1e9, p, None, None, 4, 16, None) == _lib.ERR_INVALID
+    assert lib.ib200_plan_launch(None, None, 0, None, 0, None) == _lib.ERR_INVALID
+    assert lib.ib200_plan_json(None, None, None, 0) == _lib.ERR_INVALID
