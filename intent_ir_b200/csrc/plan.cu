@@ -2760,7 +2760,8 @@ class Planner {
       const EwInstr& i = p.instr[k];
       Json j = Json::object();
       j.set("op", Json::string(op_name(i.op)));
-      j.set("a", num(i.a)); j.set("b", num(i.b)); j.set("c", num(i.c)); j.set("dst", num(i.dst)); j.set("imm", num(i.imm));
+      j.set("a", num(i.a)); j.set("b", num(i.b)); j.set("c", num(i.c)); j.set("dst", num(i.dst));
+      j.set("imm", num(s.wide && k < (int)s.ew_imm.size() ? s.ew_imm[k] : (double)i.imm));  // what the kernel that runs is given
       code.push(j);
     }
     for (int k = 0; k < p.n_outputs; ++k) {
@@ -2769,6 +2770,7 @@ class Planner {
       outs.push(j);
     }
     r.set("inputs", ins); r.set("instr", code); r.set("outputs", outs); r.set("n_slots", num(p.n_slots));
+    r.set("wide", num(s.wide));
     if (!s.wide) {
       bool compiled_in = false;
       const std::string sig = ew_register_signature(p, &compiled_in);

@@ -52,6 +52,8 @@ def _store(values, dtype):
         return np.trunc(values).astype(_NP[dtype])
     if dtype == "f16":
         return values.astype(np.float16)
+    if dtype == "f64":
+        return values.astype(np.float64)
     return values.astype(np.float32)  # bf16 buffers are modelled as f32 here
 
 
@@ -121,8 +123,47 @@ def _write(buffers, table, buf, start, values, dtype):
     buffers[buf][start:start + len(values)] = _store(values, dtype)
 
 
+def run_elementwise_program(step: dict, buffers: Dict[int, np.ndarray], buffer_table: list) -> None:
+    """Execute one elementwise step (intent_ir_b200/csrc/ew_program.h): every output element reads each operand at
+    ``offset + sum(coordinate * stride)`` over the step's extents (an iota operand's value IS that number), runs the
+    micro-ops with the result of the previous one as the accumulator, and stores slots or the accumulator.  Values
+    are float32, or float64 when the step runs on the double-valued kernel."""
+    prog = step["program"]
+    ext = [int(e) for e in step["extents"]]
+    lane = np.float64 if prog.get("wide") else np.float32
+    total = int(np.prod(ext, dtype=np.int64))
+    coords = np.unravel_index(np.arange(total, dtype=np.int64), ext) if total else [np.zeros(0, np.int64)] * len(ext)
+    slots: Dict[int, np.ndarray] = {}
+    for k, inp in enumerate(prog["inputs"]):
+        idx = np.full(total, int(inp["offset"]), np.int64)
+        for c, st in zip(coords, inp["strides"]):
+            idx += c * int(st)
+        slots[k] = idx.astype(lane) if inp["iota"] else np.asarray(buffers[inp["buffer"]])[idx].astype(lane)
+    acc = np.zeros(total, lane)
+
+    def get(code, imm):
+        if code == ACC: return acc
+        if code == IMM: return np.full(total, imm, lane)
+        return slots[code]
+
+    for ins in prog["instr"]:
+        imm = lane(ins["imm"])
+        if ins["op"] == "where":
+            acc = np.where(get(ins["a"], imm) != 0, get(ins["b"], imm), get(ins["c"], imm)).astype(lane)
+        elif ins["op"] == "round_bf16":
+            bits = get(ins["a"], imm).astype(np.float32).view(np.uint32).astype(np.uint64)
+            bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+            acc = bits.view(np.float32).astype(lane)
+        else:
+            acc = np.asarray(_apply(ins["op"], get(ins["a"], imm), get(ins["b"], imm))).astype(lane)
+        if ins["dst"] != NODST:
+            slots[ins["dst"]] = acc.copy()
+    for out in prog["outputs"]:
+        _write(buffers, buffer_table, out["buffer"], 0, get(out["src"], lane(0)), out["dtype"])
+
+
 def run_plan_description(desc: dict, inputs: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
-    """Run a plan made only of fused row steps; returns the declared outputs by name."""
+    """Run a plan made only of fused row steps and elementwise steps; returns the declared outputs by name."""
     table = desc["buffers"]
     names = desc["io_spec"]["arg_names"]
     buffers: Dict[int, np.ndarray] = {}
@@ -130,9 +171,12 @@ def run_plan_description(desc: dict, inputs: Dict[str, np.ndarray]) -> Dict[str,
         if t["arg"] >= 0 and names[t["arg"]] in inputs:
             buffers[i] = np.ascontiguousarray(inputs[names[t["arg"]]]).reshape(-1)
     for st in desc["steps"]:
-        if "row_program" not in st:
-            raise ValueError(f"emulator covers fused row steps only, not {st['kernel']}")
-        run_row_program(st["row_program"], buffers, table)
+        if "row_program" in st:
+            run_row_program(st["row_program"], buffers, table)
+        elif "program" in st:
+            run_elementwise_program(st, buffers, table)
+        else:
+            raise ValueError(f"emulator covers fused row steps and elementwise steps only, not {st['kernel']}")
     out = {}
     for name in desc["output_names"]:
         i = next(k for k, t in enumerate(table) if t["arg"] >= 0 and names[t["arg"]] == name)
