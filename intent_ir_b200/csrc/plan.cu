@@ -2877,6 +2877,26 @@ class Planner {
       j.set("extents", ext);
       if (s.kind == Step::ROWFUSE) j.set("row_program", describe_row_program(s));
       if (s.kind == Step::ELEMENTWISE) j.set("program", describe_ew_program(s));
+      if (s.kind == Step::REDUCE || s.kind == Step::SOFTMAX || s.kind == Step::NORM || s.kind == Step::GEMM || s.kind == Step::TRANSPOSE) {
+        // what the launcher of this step is given, buffer ids in place of pointers: a CPU restatement of the
+        // kernels' contracts can then run the whole plan
+        auto num = [](double v) { return Json::number(v); };
+        auto ids = [&](const int* v, int n) { Json a = Json::array(); for (int k = 0; k < n; ++k) a.push(num(v[k])); return a; };
+        Json a = Json::object(), res = Json::array(), bs = Json::array();
+        static const char* kKinds[] = {"reduce", "softmax", "norm", "gemm", "elementwise", "transpose"};
+        a.set("kind", Json::string(kKinds[s.kind]));
+        a.set("in", ids(s.in, 3)); a.set("out", ids(s.out, 3));
+        a.set("dtype", Json::string(dtype_name(s.dtype))); a.set("dtype2", Json::string(dtype_name(s.dtype2)));
+        a.set("reduce_kind", num(s.reduce_kind)); a.set("scale", num(s.scale)); a.set("eps", num(s.eps));
+        a.set("aff_inner", num((double)s.aff_inner)); a.set("aff_period", num((double)s.aff_period));
+        a.set("transpose_b", num(s.transpose_b)); a.set("act", num(s.act)); a.set("other", num(s.other));
+        a.set("batch", num((double)s.batch)); a.set("flags", num(s.flags));
+        for (int k = 0; k < 3; ++k) bs.push(num((double)s.batch_stride[k]));
+        a.set("batch_stride", bs);
+        if (s.kind == Step::NORM) for (int id : s.idx_buf) res.push(num(id));
+        a.set("residual", res);
+        j.set("args", a);
+      }
       steps.push(j);
     }
     d.set("steps", steps);

@@ -162,8 +162,93 @@ def run_elementwise_program(step: dict, buffers: Dict[int, np.ndarray], buffer_t
         _write(buffers, buffer_table, out["buffer"], 0, get(out["src"], lane(0)), out["dtype"])
 
 
+def _buffer(buffers, table, i):
+    """Buffer ``i`` as a flat array, created (zeros) when nothing has written it yet."""
+    if i not in buffers:
+        t = table[i]
+        buffers[i] = np.zeros(int(t["bytes"]) // _SIZE[t["dtype"]], _NP[t["dtype"]])
+    return buffers[i]
+
+
+def run_kernel_step(step: dict, buffers: Dict[int, np.ndarray], table: list) -> None:
+    """The contracts of the reduce / softmax / normalisation / product / transpose launchers (include/intentir_b200.h
+    and the step executor of intent_ir_b200/csrc/plan.cu), restated in numpy on the step's buffers."""
+    a, d = step["args"], [int(v) for v in step["extents"]]
+    f = np.float32
+    src = [(_buffer(buffers, table, i) if i >= 0 else None) for i in a["in"]]
+
+    def put(slot, values, dtype):
+        if a["out"][slot] >= 0:
+            _write(buffers, table, a["out"][slot], 0, np.asarray(values).reshape(-1), dtype)
+
+    with np.errstate(all="ignore"):
+        if a["kind"] == "reduce":
+            outer, red, inner = d[0], d[1], d[2]
+            x = src[0][:outer * red * inner].astype(f).reshape(outer, red, inner)
+            k = a["reduce_kind"]
+            r = x.sum(axis=1, dtype=f) * f(a["scale"]) if k == 0 else x.max(axis=1) if k == 1 else (x != 0).any(axis=1).astype(f)
+            put(0, r, a["dtype2"])
+        elif a["kind"] == "softmax":
+            rows, cols = d[0], d[1]
+            x = src[0][:rows * cols].astype(f).reshape(rows, cols)
+            if a["reduce_kind"]:
+                stride = int(a["aff_inner"])
+                m = np.stack([src[1][r * stride:r * stride + cols] for r in range(rows)]) if rows else np.zeros((0, cols))
+                x = np.where(m != 0, x, f(a["other"]))
+            mx = x.max(axis=1, keepdims=True) if cols else np.zeros((rows, 1), f)
+            e = np.exp(x - mx)
+            sm = e.sum(axis=1, keepdims=True, dtype=f)
+            put(0, e / sm, a["dtype2"])
+            put(1, mx, "f32")
+            put(2, sm, "f32")
+        elif a["kind"] == "norm":
+            rows, cols = d[0], d[1]
+            x = src[0][:rows * cols].astype(f).reshape(rows, cols)
+            for j, rid in enumerate(a["residual"]):
+                r = _buffer(buffers, table, rid).astype(f)
+                x = x + (r[:rows * cols].reshape(rows, cols) if j == 0 else r[:cols][None, :])
+            mean = x.mean(axis=1, keepdims=True, dtype=f) if a["act"] else np.zeros((rows, 1), f)
+            xc = x - mean
+            rstd = f(1) / np.sqrt((xc * xc).mean(axis=1, keepdims=True, dtype=f) + f(a["eps"]))
+            lin = np.arange(rows * cols, dtype=np.int64).reshape(rows, cols)
+            idx = (lin // int(a["aff_inner"])) % int(a["aff_period"])
+            t = xc * rstd
+            if a["flags"] == 1:
+                t = np.maximum(t, f(0))
+            if src[1] is not None:
+                t = t * src[1].astype(f)[idx]
+            if src[2] is not None:
+                t = t + src[2].astype(f)[idx]
+            if a["flags"] == 2:
+                t = np.maximum(t, f(0))
+            put(0, t, a["dtype"])
+            put(1, mean, "f32")
+            put(2, rstd, "f32")
+        elif a["kind"] == "gemm":
+            m, n, k = d[0], d[1], d[2]
+            sa, sb, sc = [int(v) for v in a["batch_stride"]]
+            out = _buffer(buffers, table, a["out"][0])
+            for bi in range(int(a["batch"])):
+                A = src[0][bi * sa:bi * sa + m * k].astype(f).reshape(m, k)
+                B = src[1][bi * sb:bi * sb + n * k].astype(f)
+                B = B.reshape(n, k).T if a["transpose_b"] else B.reshape(k, n)
+                c = A @ B
+                if src[2] is not None:
+                    c = c + src[2].astype(f)[:n][None, :]
+                if a["act"] == 1:
+                    c = np.maximum(c, f(0))
+                out[bi * sc:bi * sc + m * n] = _store(c.reshape(-1), a["dtype2"])
+        elif a["kind"] == "transpose":
+            rows, cols = d[0], d[1]
+            out = _buffer(buffers, table, a["out"][0])
+            out[:rows * cols] = src[0][:rows * cols].reshape(rows, cols).T.reshape(-1)
+        else:
+            raise ValueError(f"emulator: step kind {a['kind']}")
+
+
 def run_plan_description(desc: dict, inputs: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
-    """Run a plan made only of fused row steps and elementwise steps; returns the declared outputs by name."""
+    """Run a plan step by step (fused row programs, elementwise programs, and the reduce / softmax / normalisation /
+    product / transpose kernels by their contracts); returns the declared outputs by name."""
     table = desc["buffers"]
     names = desc["io_spec"]["arg_names"]
     buffers: Dict[int, np.ndarray] = {}
@@ -175,8 +260,10 @@ def run_plan_description(desc: dict, inputs: Dict[str, np.ndarray]) -> Dict[str,
             run_row_program(st["row_program"], buffers, table)
         elif "program" in st:
             run_elementwise_program(st, buffers, table)
+        elif "args" in st:
+            run_kernel_step(st, buffers, table)
         else:
-            raise ValueError(f"emulator covers fused row steps and elementwise steps only, not {st['kernel']}")
+            raise ValueError(f"emulator does not cover {st['kernel']}")
     out = {}
     for name in desc["output_names"]:
         i = next(k for k, t in enumerate(table) if t["arg"] >= 0 and names[t["arg"]] == name)
