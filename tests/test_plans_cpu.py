@@ -186,3 +186,29 @@ def test_damaged_graphs_that_still_plan_keep_the_oracles_meaning(golden_graphs):
                 assert np.allclose(g.astype(np.float64), w.astype(np.float64), rtol=1e-4, atol=1e-5, equal_nan=True), (i, keys[i % len(keys)], n)
         agreed += 1
     assert refused > 400 and agreed > 40, (refused, agreed)
+
+
+@pytest.mark.parametrize("what,shapes", [("softmax", {"M": 4, "N": 1 << 18}), ("layernorm", {"M": 3, "N": 200_000}), ("reduce_sum", {"M": 2, "N": 1 << 19}),
+                                         ("reduce_max", {"M": 70_000, "N": 5}), ("matmul_bias_relu", {"M": 300, "N": 40, "K": 2000}),
+                                         ("groupnorm", {"N": 2, "C": 8, "HW": 70_000, "num_groups": 2})])
+def test_plans_of_shapes_that_take_the_split_forms(what, shapes):
+    """Few very long rows (segments over the whole GPU, scratch in the workspace), tall column reductions, a product
+    with a long K: the planner's choices for such shapes change kernels and add scratch buffers, not meaning."""
+    from intent_ir_b200 import sweep
+
+    maker = {"softmax": lambda: sweep.g_softmax("f32"), "layernorm": sweep.g_layernorm, "groupnorm": sweep.g_groupnorm,
+             "reduce_sum": lambda: sweep.g_reduce("reduce_sum", "f32"), "reduce_max": lambda: sweep.g_reduce("reduce_max", "f32"),
+             "matmul_bias_relu": lambda: sweep.g_matmul("f32")}[what]
+    js = maker()
+    bind = derive_bindings(dict(shapes))
+    intent = IntentFunction.from_json_dict(js)
+    rng = np.random.default_rng(7)
+    desc = plan_json(js, bind)
+    spec, outs = desc["io_spec"]["tensors"], desc["output_names"]
+    ins = {n: rng.standard_normal(spec[n]["shape"]).astype(np.float32) for n in desc["io_spec"]["arg_names"] if n not in outs}
+    with np.errstate(all="ignore"):
+        got = run_plan_description(desc, ins)
+        want = execute_intent(intent, ins, shape_bindings=bind)
+    tol = infer_tolerances(intent).to_dict()
+    for n in intent.outputs:
+        _agree(got[n], want[n], tol, (what, n, [s["kernel"] for s in desc["steps"]], desc["workspace_bytes"]))
