@@ -212,3 +212,28 @@ def test_plans_of_shapes_that_take_the_split_forms(what, shapes):
     tol = infer_tolerances(intent).to_dict()
     for n in intent.outputs:
         _agree(got[n], want[n], tol, (what, n, [s["kernel"] for s in desc["steps"]], desc["workspace_bytes"]))
+
+
+@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("finish", ["transcendental", "reduce", "softmax_matmul"])
+def test_fuzzed_graphs_with_tails_plan_to_what_the_oracle_computes(seed, finish):
+    """Random DAGs finished by exp / rsqrt / div, by row, column and any-reductions, or by a softmax and a product with
+    its own transpose: the exact part bit for bit, the rest within the verifier's tolerances."""
+    from tests.test_fuzz_gpu import _inputs, random_elementwise_graph
+
+    rng = np.random.default_rng(1000 + seed)
+    m, n = [(2, 3), (9, 40), (17, 128), (64, 257), (130, 72)][seed % 5]
+    js = random_elementwise_graph(rng, int(rng.integers(1, 9)), finish=finish)
+    intent = IntentFunction.from_json_dict(js)
+    ins = _inputs(rng, m, n)
+    with np.errstate(all="ignore"):
+        want = execute_intent(intent, ins, {"M": m, "N": n})
+    desc, got = _plan_and_emulate(js, {"M": m, "N": n}, ins)
+    tol = infer_tolerances(intent).to_dict()
+    for name in intent.outputs:
+        w, g = np.asarray(want[name]), np.asarray(got[name])
+        assert g.shape == w.shape, (seed, name)
+        if w.dtype == np.bool_ or name in ("Y", "P", "A"):
+            assert np.array_equal(g.astype(w.dtype), w, equal_nan=w.dtype.kind == "f"), (seed, finish, name, [s["kernel"] for s in desc["steps"]])
+        else:
+            _agree(g, w, tol, (seed, finish, name, [s["kernel"] for s in desc["steps"]]))
