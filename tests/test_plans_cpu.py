@@ -237,3 +237,114 @@ def test_fuzzed_graphs_with_tails_plan_to_what_the_oracle_computes(seed, finish)
             assert np.array_equal(g.astype(w.dtype), w, equal_nan=w.dtype.kind == "f"), (seed, finish, name, [s["kernel"] for s in desc["steps"]])
         else:
             _agree(g, w, tol, (seed, finish, name, [s["kernel"] for s in desc["steps"]]))
+
+
+def _random_graph(rng):
+    """A chain of up to six random ops over a tensor of rank 1-4 with literal extents: elementwise ops against tensors
+    of the same shape, broadcast vectors and constants, reductions over any subset of axes, softmax over any axis,
+    permutations, reshapes (merging, splitting, with a -1), broadcasts into a new axis, products with a weight
+    (plain or transposed) and comparisons feeding a `where`."""
+    grid = lambda shape, hi=8: (rng.integers(-hi, hi + 1, size=shape) / 4.0).astype(np.float32)  # noqa: E731
+    shape = [int(rng.choice([1, 2, 3, 4, 5, 7, 8, 16, 33])) for _ in range(int(rng.integers(1, 5)))]
+    tensors, ins, ops = {"x": _t(shape)}, {"x": grid(shape)}, []
+    cur, known = "x", {"x": list(shape)}
+
+    def emit(op, inputs, attrs=None):
+        nonlocal cur
+        out = f"v{len(ops)}"
+        ops.append({"op": op, "inputs": inputs, "output": out, **({"attrs": attrs} if attrs else {})})
+        cur = out
+        known[out] = list(shape)
+
+    for _ in range(int(rng.integers(1, 7))):
+        kind = rng.choice(["unary", "same", "vector", "attr", "reduce", "softmax", "transpose", "reshape", "broadcast", "matmul", "where"])
+        if kind == "unary":
+            emit(str(rng.choice(["relu", "abs", "exp", "floor"])), [cur])
+        elif kind == "same":
+            emit(str(rng.choice(["add", "sub", "mul", "max", "min"])), [cur, str(rng.choice([n for n, s in known.items() if s == shape]))])
+        elif kind == "vector" and shape:
+            name, vs = f"w{len(ops)}", [shape[-1]] if rng.random() < 0.6 else [c if rng.random() < 0.5 else 1 for c in shape]
+            tensors[name], ins[name] = _t(vs), grid(vs)
+            emit(str(rng.choice(["add", "sub", "mul", "max"])), [cur, name] if rng.random() < 0.7 else [name, cur])
+        elif kind == "attr":
+            op, key = [("add", "addend"), ("sub", "subtract"), ("mul", "mul_factor"), ("max", "other"), ("min", "other")][int(rng.integers(0, 5))]
+            emit(op, [cur], {key: float(rng.choice([-1.5, -0.25, 0.5, 2.0]))})
+        elif kind == "reduce" and shape:
+            r = len(shape)
+            dims = sorted(int(d) for d in rng.choice(r, size=int(rng.integers(1, r + 1)), replace=False))
+            keep = bool(rng.random() < 0.5)
+            shown = [d - r for d in dims] if rng.random() < 0.3 else dims
+            shape = [1 if i in dims else s for i, s in enumerate(shape) if keep or i not in dims]
+            emit(str(rng.choice(["reduce_sum", "reduce_max"])), [cur], {"dims": shown, "keepdims": keep})
+        elif kind == "softmax" and shape:
+            emit("softmax", [cur], {"axis": int(rng.integers(-len(shape), len(shape)))})
+        elif kind == "transpose" and len(shape) >= 2:
+            perm = [int(p) for p in rng.permutation(len(shape))]
+            shape = [shape[p] for p in perm]
+            emit("transpose", [cur], {"perm": perm})
+        elif kind == "reshape" and shape:
+            if len(shape) >= 2 and rng.random() < 0.6:
+                i = int(rng.integers(0, len(shape) - 1))
+                new = shape[:i] + [shape[i] * shape[i + 1]] + shape[i + 2:]
+            else:
+                i = int(rng.integers(0, len(shape)))
+                factors = [a for a in (2, 3, 4) if shape[i] % a == 0]
+                if not factors or len(shape) >= 5:
+                    continue
+                a = int(rng.choice(factors))
+                new = shape[:i] + [a, shape[i] // a] + shape[i + 1:]
+            asked = list(new)
+            if rng.random() < 0.3:
+                asked[int(rng.integers(0, len(new)))] = -1
+            shape = new
+            emit("reshape", [cur], {"shape": asked})
+        elif kind == "broadcast" and len(shape) <= 3:
+            pos = int(rng.integers(0, len(shape) + 1))
+            shape = shape[:pos] + [int(rng.choice([2, 3, 5]))] + shape[pos:]
+            emit("broadcast_in_dim", [cur], {"out_shape": list(shape), "broadcast_dims": [i for i in range(len(shape)) if i != pos]})
+        elif kind == "matmul" and len(shape) == 2:
+            name, n2, tb = f"b{len(ops)}", int(rng.choice([1, 3, 8, 17])), bool(rng.random() < 0.4)
+            bs = [n2, shape[1]] if tb else [shape[1], n2]
+            tensors[name], ins[name] = _t(bs), grid(bs, 4)
+            shape = [shape[0], n2]
+            emit("matmul", [cur, name], {"transpose_b": True} if tb else None)
+        elif kind == "where" and shape:
+            value = cur
+            emit("const", [], {"value": 0.25, "dtype": "f32"})
+            const = cur
+            emit(str(rng.choice(["gt", "lt", "ne", "ge"])), [value, const])
+            emit("where", [cur, value, const])
+    if cur == "x":
+        emit("relu", ["x"])
+    tensors[cur] = _t(shape)
+    return {"name": "random_graph", "tensors": tensors, "ops": ops, "outputs": [cur]}, ins
+
+
+@pytest.mark.parametrize("block", range(6))
+def test_random_graphs_plan_to_what_the_oracle_computes(block):
+    """50 seeded random graphs per block: the plan, run step by step, agrees with the oracle within the verifier's
+    tolerances (non-finite results: the same pattern, and the finite part within tolerance)."""
+    ran = 0
+    for seed in range(50 * block, 50 * block + 50):
+        js, ins = _random_graph(np.random.default_rng(seed))
+        intent = IntentFunction.from_json_dict(json.loads(json.dumps(js)))
+        with np.errstate(all="ignore"):
+            want = np.asarray(execute_intent(intent, ins, {})[js["outputs"][0]])
+            if want.dtype == np.float64:  # (constants promote the interpreter's values; the declared type is f32)
+                want = want.astype(np.float32)
+        desc = plan_json(js, {})
+        kernels = [s["kernel"] for s in desc["steps"]]
+        if not all("program" in s or "row_program" in s or "args" in s for s in desc["steps"]):
+            continue
+        with np.errstate(all="ignore"):
+            got = np.asarray(run_plan_description(desc, ins)[js["outputs"][0]])
+        what = (seed, [(o["op"], o.get("attrs")) for o in js["ops"]], js["tensors"]["x"]["shape"], kernels)
+        assert list(got.shape) == list(want.shape), what
+        finite = np.isfinite(want)
+        if finite.all():
+            _agree(got, want.astype(np.float32), infer_tolerances(intent).to_dict(), what)
+        else:
+            assert np.array_equal(np.isnan(want), np.isnan(got)) and np.array_equal(want[np.isinf(want)], got[np.isinf(want)]), what
+            assert np.allclose(got[finite].astype(np.float32), want[finite], rtol=1e-3, atol=1e-3), what
+        ran += 1
+    assert ran >= 40
