@@ -89,8 +89,12 @@ typedef struct ib200_plan ib200_plan_t;
  * The JSON mirrors the reference's lowered-kernel record
  * {kernel_name, cuda_src:"", io_spec{arg_names, tensors{name:{dtype,shape}}, scalars},
  *  launch{grid,block,shared_mem}, output_names, bindings} (intentir_to_cuda.py:2110-2125)
- * plus {"steps":[...], "workspace_bytes":N}.  Returns IB200_ERR_BUFFER when `cap` is too
- * small (the needed size is then reported by ib200_last_error). */
+ * plus {"steps":[...], "buffers":[...], "workspace_bytes":N}.  A step names its kernel and extents and
+ * either its micro-op program ("program" for elementwise steps, "row_program" for fused row steps:
+ * operands with buffer ids, offsets and strides, instructions, stores) or, for the reduce / softmax /
+ * normalisation / product / transpose kernels, "args": the buffer ids and options its launcher is given --
+ * enough for a host to follow, or re-execute, what a launch will do without a device.  Returns
+ * IB200_ERR_BUFFER when `cap` is too small (the needed size is then reported by ib200_last_error). */
 IB200_API int ib200_plan_json(const char* intent_json, const char* bindings_json, char* out, size_t cap);
 
 /* Build a reusable plan object (same lowering as ib200_plan_json). */
