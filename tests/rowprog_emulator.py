@@ -54,7 +54,11 @@ def _store(values, dtype):
         return values.astype(np.float16)
     if dtype == "f64":
         return values.astype(np.float64)
-    return values.astype(np.float32)  # bf16 buffers are modelled as f32 here
+    if dtype == "bf16":  # bf16 buffers are float32 arrays here, holding values rounded to bf16 (nearest even) as a store rounds them
+        bits = np.ascontiguousarray(values, np.float32).view(np.uint32).astype(np.uint64)
+        rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000).astype(np.uint32).view(np.float32)
+        return np.where(np.isnan(values), np.float32(np.nan), rounded)
+    return values.astype(np.float32)
 
 
 def run_row_program(prog: dict, buffers: Dict[int, np.ndarray], buffer_table: list) -> None:
