@@ -1584,9 +1584,10 @@ class Planner {
       s.d[0] = n.shape[n.shape.size() - 2];
       s.d[1] = n.shape.back();
       s.d[2] = as.back();
-      s.batch = numel(n.shape) / std::max<int64_t>(1, s.d[0] * s.d[1]);
-      const int64_t abatch = numel(as) / std::max<int64_t>(1, as.back() * as[as.size() - 2]);
-      const int64_t bbatch = numel(bs) / std::max<int64_t>(1, bs.back() * bs[bs.size() - 2]);
+      // batch counts are the products of the leading extents (not element counts over matrix sizes: K, M or N may be 0)
+      auto leading = [](const Shape& sh) { int64_t n = 1; for (size_t i = 0; i + 2 < sh.size(); ++i) n *= sh[i]; return n; };
+      s.batch = leading(n.shape);
+      const int64_t abatch = leading(as), bbatch = leading(bs);
       if (s.d[0] * s.d[1] == 0) s.batch = 0;
       if ((abatch != s.batch && abatch != 1) || (bbatch != s.batch && bbatch != 1))
         throw Unsupported("matmul: partially broadcast batch axes are not covered (" + shape_str(as) + " x " + shape_str(bs) + ")");

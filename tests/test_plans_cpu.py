@@ -348,3 +348,18 @@ def test_random_graphs_plan_to_what_the_oracle_computes(block):
             assert np.allclose(got[finite].astype(np.float32), want[finite], rtol=1e-3, atol=1e-3), what
         ran += 1
     assert ran >= 40
+
+
+@pytest.mark.parametrize("m,n,k", [(5, 3, 0), (0, 3, 4), (5, 0, 4), (0, 0, 0)])
+def test_products_with_an_empty_axis(m, n, k):
+    """An empty contraction gives the bias (through the ReLU), empty results give nothing; none of them is a batch."""
+    from intent_ir_b200 import sweep
+
+    js = sweep.g_matmul("f32")
+    rng = np.random.default_rng(m + 7 * n + 49 * k)
+    ins = {"A": rng.standard_normal((m, k)).astype(np.float32), "B": rng.standard_normal((k, n)).astype(np.float32),
+           "bias": rng.standard_normal((n,)).astype(np.float32)}
+    desc, got = _plan_and_emulate(js, {"M": m, "N": n, "K": k}, ins)
+    assert [s["kernel"] for s in desc["steps"]] == ["gemm+bias+relu"] and desc["steps"][0]["args"]["batch"] <= 1
+    want = np.maximum(ins["A"] @ ins["B"] + ins["bias"], 0)
+    assert np.array_equal(np.asarray(got["C"]).reshape(m, n), want)
