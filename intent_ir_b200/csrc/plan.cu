@@ -427,7 +427,14 @@ class Planner {
       if (args.size() != 2) throw Invalid(op + " requires 2 inputs (or 1+attrs)");
       align(names[0], args[0], names[1], args[1]);
       n.shape = broadcast(nodes_[args[0]].shape, nodes_[args[1]].shape, op);
-      if (kBinary.count(op)) {
+      if (kBinary.count(op) && nodes_[args[0]].dclass == DC_BOOL && nodes_[args[1]].dclass == DC_BOOL && op != "div") {
+        // numpy's arithmetic on two boolean arrays stays boolean: add and max are "or", mul and min are "and",
+        // and it refuses to subtract them (verify/interpreter.py:17-23 calls np.add / np.multiply / ... as they are)
+        if (op == "add" || op == "max") n.op = "or";
+        else if (op == "mul" || op == "min") n.op = "and";
+        else throw Unsupported(op + " of two boolean tensors (numpy refuses it)");
+        n.dclass = DC_BOOL;
+      } else if (kBinary.count(op)) {
         const int ca = nodes_[args[0]].dclass, cb = nodes_[args[1]].dclass;
         const bool a_const = nodes_[args[0]].op == "const", b_const = nodes_[args[1]].op == "const";
         n.dclass = (ca == DC_FLOAT || cb == DC_FLOAT || op == "div") ? DC_FLOAT : DC_INT;
