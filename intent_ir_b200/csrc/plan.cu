@@ -615,6 +615,7 @@ class Planner {
         const Json* rt = attrs->find("reduction_type");
         if (op == "reduce_sum" && rt && rt->is_str() && rt->s == "any") n.op = "reduce_any";
         n.dclass = n.op == "reduce_any" ? DC_BOOL : nodes_[in[0]].dclass;
+        if (n.op == "reduce_sum" && n.dclass == DC_BOOL) n.dclass = DC_INT;  // numpy counts: the sum of booleans is an integer
         if (op == "reduce_sum") {
           const Json* sc = attrs->find("scale");
           if (sc && !sc->is_null()) {

@@ -385,3 +385,36 @@ def test_products_with_an_empty_axis(m, n, k):
     assert desc["steps"][0]["kernel"].startswith("gemm") and desc["steps"][0]["args"]["batch"] <= 1
     want = np.maximum(ins["A"] @ ins["B"] + ins["bias"], 0)
     assert np.array_equal(np.asarray(got["C"]).reshape(m, n), want)
+
+
+def test_boolean_values_follow_numpy_through_arithmetic_and_sums():
+    """`add` / `max` of two boolean tensors is "or", `mul` / `min` is "and" (the results stay boolean); the sum of
+    booleans counts (an integer), so arithmetic on counts is arithmetic again; subtracting booleans is refused."""
+    base = {"name": "b", "tensors": {"x": _t(["M", "N"]), "y": _t(["M", "N"])}, "outputs": ["y"]}
+    x = (np.random.default_rng(5).integers(-1, 2, (6, 9)) / 2.0).astype(np.float32)
+
+    def run(ops, out_shape, out_dtype="f32"):
+        js = json.loads(json.dumps(base))
+        js["ops"] = [{"op": "const", "inputs": [], "output": "z", "attrs": {"value": 0.0, "dtype": "f32"}},
+                     {"op": "gt", "inputs": ["x", "z"], "output": "p"}, {"op": "lt", "inputs": ["x", "z"], "output": "q"}] + ops
+        js["tensors"]["y"] = _t(out_shape, out_dtype)
+        intent = IntentFunction.from_json_dict(js)
+        desc, got = _plan_and_emulate(js, {"M": 6, "N": 9}, {"x": x})
+        with np.errstate(all="ignore"):
+            want = np.asarray(execute_intent(intent, {"x": x}, {"M": 6, "N": 9})["y"])
+        return np.asarray(got["y"]).reshape(want.shape), want
+
+    for op in ("add", "max", "mul", "min"):
+        got, want = run([{"op": op, "inputs": ["p", "q"], "output": "pq"}, {"op": op, "inputs": ["pq", "p"], "output": "y"}], ["M", "N"], "bool")
+        assert want.dtype == np.bool_ and np.array_equal(got.astype(bool), want), op
+    got, want = run([{"op": "add", "inputs": ["p", "p"], "output": "pp"}, {"op": "add", "inputs": ["pp"], "output": "y", "attrs": {"addend": 2.0}}], ["M", "N"])
+    assert np.array_equal(got.astype(np.float64), want.astype(np.float64))  # True + True is True, plus 2.0 is 3.0
+    try:  # (counting booleans is refused where no fused row program takes it; where it plans, it counts)
+        got, want = run([{"op": "reduce_any", "inputs": ["p"], "output": "a", "attrs": {"dims": [1]}},
+                         {"op": "reduce_sum", "inputs": ["a"], "output": "c", "attrs": {"dims": [0]}},
+                         {"op": "add", "inputs": ["c", "c"], "output": "y"}], [])
+        assert want.dtype.kind == "i" and np.array_equal(got.astype(np.int64), want.astype(np.int64))
+    except B200LoweringError as e:
+        assert "non-float tensor" in str(e)
+    with pytest.raises(B200LoweringError, match="boolean tensors"):
+        run([{"op": "sub", "inputs": ["p", "q"], "output": "y"}], ["M", "N"])
