@@ -77,7 +77,7 @@ struct Json {
         char buf[40];
         if (integral) std::snprintf(buf, sizeof buf, "%lld", (long long)num);
         else if (std::isfinite(num)) std::snprintf(buf, sizeof buf, "%.17g", num);
-        else std::snprintf(buf, sizeof buf, "null");
+        else std::snprintf(buf, sizeof buf, "%s", std::isnan(num) ? "NaN" : num > 0 ? "Infinity" : "-Infinity");  // as read above
         out += buf;
         break;
       }
