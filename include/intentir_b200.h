@@ -93,7 +93,8 @@ typedef struct ib200_plan ib200_plan_t;
  * either its micro-op program ("program" for elementwise steps, "row_program" for fused row steps:
  * operands with buffer ids, offsets and strides, instructions, stores) or, for the reduce / softmax /
  * normalisation / product / transpose kernels, "args": the buffer ids and options its launcher is given --
- * enough for a host to follow, or re-execute, what a launch will do without a device.  Returns
+ * enough for a host to follow, or re-execute, what a launch will do without a device.  Non-finite numbers
+ * are read and written as Python's json module does: NaN, Infinity, -Infinity.  Returns
  * IB200_ERR_BUFFER when `cap` is too small (the needed size is then reported by ib200_last_error). */
 IB200_API int ib200_plan_json(const char* intent_json, const char* bindings_json, char* out, size_t cap);
 
