@@ -2886,13 +2886,14 @@ class Planner {
       j.set("extents", ext);
       if (s.kind == Step::ROWFUSE) j.set("row_program", describe_row_program(s));
       if (s.kind == Step::ELEMENTWISE) j.set("program", describe_ew_program(s));
-      if (s.kind == Step::REDUCE || s.kind == Step::SOFTMAX || s.kind == Step::NORM || s.kind == Step::GEMM || s.kind == Step::TRANSPOSE) {
+      if (s.kind == Step::REDUCE || s.kind == Step::SOFTMAX || s.kind == Step::NORM || s.kind == Step::GEMM || s.kind == Step::TRANSPOSE ||
+          s.kind == Step::GATHER) {
         // what the launcher of this step is given, buffer ids in place of pointers: a CPU restatement of the
         // kernels' contracts can then run the whole plan
         auto num = [](double v) { return Json::number(v); };
         auto ids = [&](const int* v, int n) { Json a = Json::array(); for (int k = 0; k < n; ++k) a.push(num(v[k])); return a; };
         Json a = Json::object(), res = Json::array(), bs = Json::array();
-        static const char* kKinds[] = {"reduce", "softmax", "norm", "gemm", "elementwise", "transpose"};
+        static const char* kKinds[] = {"reduce", "softmax", "norm", "gemm", "elementwise", "transpose", "gather"};
         a.set("kind", Json::string(kKinds[s.kind]));
         a.set("in", ids(s.in, 3)); a.set("out", ids(s.out, 3));
         a.set("dtype", Json::string(dtype_name(s.dtype))); a.set("dtype2", Json::string(dtype_name(s.dtype2)));
@@ -2904,6 +2905,11 @@ class Planner {
         a.set("batch_stride", bs);
         if (s.kind == Step::NORM) for (int id : s.idx_buf) res.push(num(id));
         a.set("residual", res);
+        if (s.kind == Step::GATHER) {  // one index buffer per data axis, with the axis' extent and stride
+          Json idx = Json::array(), dim = Json::array(), stride = Json::array();
+          for (size_t k = 0; k < s.idx_buf.size(); ++k) { idx.push(num(s.idx_buf[k])); dim.push(num((double)s.g_dim[k])); stride.push(num((double)s.g_stride[k])); }
+          a.set("index", idx); a.set("dim", dim); a.set("stride", stride);
+        }
         j.set("args", a);
       }
       steps.push(j);

@@ -242,6 +242,18 @@ def run_kernel_step(step: dict, buffers: Dict[int, np.ndarray], table: list) -> 
                 if a["act"] == 1:
                     c = np.maximum(c, f(0))
                 out[bi * sc:bi * sc + m * n] = _store(c.reshape(-1), a["dtype2"])
+        elif a["kind"] == "gather":  # out[l] = data[idx0[l], idx1[l], ...]; negative indices wrap once, positions outside read `other`
+            n = d[0]
+            off, inside = np.zeros(n, np.int64), np.ones(n, bool)
+            for ib, dim, stride in zip(a["index"], a["dim"], a["stride"]):
+                i = _buffer(buffers, table, ib)[:n].astype(np.int64)
+                i = np.where(i < 0, i + int(dim), i)
+                inside &= (i >= 0) & (i < int(dim))
+                off += i * int(stride)
+            data = src[0]
+            vals = np.where(inside, data[np.where(inside, off, 0)], data.dtype.type(a["other"]))
+            out = _buffer(buffers, table, a["out"][0])
+            out[:n] = vals
         elif a["kind"] == "transpose":
             rows, cols = d[0], d[1]
             out = _buffer(buffers, table, a["out"][0])
