@@ -447,6 +447,7 @@ class Planner {
       if (args.size() != 1) throw Invalid(op + " requires 1 input");
       n.shape = nodes_[args[0]].shape;
       n.dclass = op == "not" ? DC_BOOL : (op == "exp" || op == "rsqrt") ? DC_FLOAT : nodes_[args[0]].dclass;
+      if (op == "relu" && n.dclass == DC_BOOL) n.dclass = DC_INT;  // np.maximum(booleans, 0) is an integer array; abs and floor of booleans stay boolean
       if (op == "cast") {
         const Json* to = attrs ? attrs->find("to") : nullptr;
         if (!to || !to->is_str()) throw Invalid("cast requires attrs.to");
@@ -646,6 +647,8 @@ class Planner {
       } else if (op == "matmul") {
         if (in.size() != 2) throw Invalid(where + " requires 2 inputs (A, B)");
         Node n; n.op = op; n.in = in; n.dclass = DC_FLOAT;
+        if (nodes_[in[0]].dclass == DC_BOOL && nodes_[in[1]].dclass == DC_BOOL)  // np.matmul of booleans is "any(and)", a boolean
+          throw Unsupported(where + ": a product of two boolean tensors is not covered");
         auto flag = [&](const char* k) { const Json* j = attrs->find(k); return j && ((j->type == Json::Bool && j->b) || (j->is_num() && j->num != 0)); };
         n.ta = flag("transpose_a");
         n.tb = flag("transpose_b");
